@@ -1,0 +1,125 @@
+/*
+ * quartz_b200 -- C ABI of the B200 (sm_100a) quantized-weight GEMV/GEMM kernels.
+ *
+ * Part 1 is, symbol for symbol, the extern "C" block the reference's Rust host
+ * binds (src/cuda.rs:6-55 in the reference project; implemented there by
+ * src/cuda_kernels.cu:1025-1293).  A build of the reference links against this
+ * library instead of its own libkernels.a without touching a call site.
+ * Part 2 is additive: entry points the reference does not have.
+ *
+ * Conventions (as in the reference): every pointer is a device pointer unless
+ * the parameter is named `host` or it is the host side of cuda_h2d / cuda_d2h;
+ * dims are int; all work is issued on one stream (the legacy default stream
+ * unless quartz_set_stream changed it); no function returns an error -- failures
+ * are recorded in a sticky status readable with quartz_last_error().  The
+ * library is single-caller: calls must not overlap from several host threads.
+ */
+#ifndef QUARTZ_B200_H
+#define QUARTZ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================= Part 1: the reference's call surface ======================= */
+
+/* src/cuda.rs:7-8, src/cuda_kernels.cu:1046-1079.  y[out_dim] = W[out_dim x in_dim] * x.
+ * ggml_type ids as in src/gguf.rs:172-188, plus 2 (Q4_0), 3 (Q4_1), 18 (IQ3_XXS).
+ * Unknown type: y is zero-filled, a line goes to stderr (reference behaviour) and
+ * the sticky status becomes QZ_ERR_UNSUPPORTED_TYPE. */
+void cuda_gemv(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int in_dim, int out_dim);
+
+/* src/cuda.rs:9-13, src/cuda_kernels.cu:1027-1041: upload the IQ codebooks (host pointers). */
+void cuda_set_iq3s_grid(const uint32_t *host);   /* 512 x u32 */
+void cuda_set_iq2s_grid(const uint64_t *host);   /* 1024 x u64 */
+void cuda_set_iq2xxs_grid(const uint64_t *host); /* 256 x u64 */
+void cuda_set_iq2xs_grid(const uint64_t *host);  /* 512 x u64 */
+void cuda_set_ksigns(const uint8_t *host);       /* 128 bytes */
+
+/* src/cuda.rs:14-19, src/cuda_kernels.cu:1042-1044, 1109-1125 */
+void cuda_mem_info(size_t *free_b, size_t *total_b);
+void *cuda_alloc(size_t bytes);          /* NULL on failure */
+void cuda_drop(void *ptr);
+void cuda_h2d(void *dst, const void *src, size_t bytes);   /* synchronous */
+void cuda_d2h(void *dst, const void *src, size_t bytes);   /* synchronous */
+void cuda_sync(void);
+
+/* src/cuda.rs:20-37, src/cuda_kernels.cu:1129-1186 */
+void cuda_vec_add(float *dst, const float *src, int n);
+void cuda_vec_scale_add(float *dst, const float *src, float scale, int n);
+void cuda_vec_zero(float *dst, int n);
+void cuda_rms_norm(float *out, const float *x, const float *w, int n);
+void cuda_rope_yarn(float *x, int n_heads, int head_dim, int pos, float theta, float yarn_scale, int yarn_orig_ctx,
+                    int neox);
+void cuda_kv_append(float *k_cache, float *v_cache, const float *k, const float *v, int pos, int kv_dim);
+void cuda_attn_score(float *scores, const float *q, const float *k_cache, int seq_len, int head_dim, int kv_dim,
+                     int kv_head_off, float scale);
+void cuda_softmax_sink(float *x, int n, float sink);
+void cuda_attn_values(float *out, const float *scores, const float *v_cache, int seq_len, int head_dim, int kv_dim,
+                      int kv_head_off);
+void cuda_swiglu(float *out, const float *gate, const float *up, int n);
+void cuda_swiglu_oai(float *out, const float *gate, const float *up, int n);
+/* The reference handles types 7, 20, 30 only; here every supported type works. */
+void cuda_embed_lookup(float *out, const uint8_t *data, uint32_t ggml_type, int token, int embed_dim);
+
+/* src/cuda.rs:39-45, src/cuda_kernels.cu:1085-1107: up to four (weights, x, y) GEMVs of one
+ * shape in one call; slots >= n_act are ignored.  One launch for every streaming format
+ * (the reference batches Q5_1 only). */
+void cuda_gemv_moe4(uint32_t ggml_type, const uint8_t *w0, const uint8_t *w1, const uint8_t *w2, const uint8_t *w3,
+                    const float *xi0, const float *xi1, const float *xi2, const float *xi3, float *o0, float *o1,
+                    float *o2, float *o3, int n_act, int in_dim, int out_dim);
+
+/* src/cuda.rs:47-54, src/cuda_kernels.cu:1267-1291 */
+void cuda_attn_score_all(float *scores, const float *q, const float *k_cache, int n_heads, int n_kv_heads,
+                         int seq_len, int head_dim, int kv_dim, int max_seq, float scale);
+void cuda_softmax_sink_all(float *scores, int n_heads, int seq_len, int max_seq, const float *sinks);
+void cuda_attn_values_all(float *out, const float *scores, const float *v_cache, int n_heads, int n_kv_heads,
+                          int seq_len, int head_dim, int kv_dim, int max_seq);
+
+/* ======================= Part 2: additions ======================= */
+
+/* Sticky status (0 = ok; codes below).  The reference reports nothing
+ * (src/cuda_kernels.cu:1109-1125 checks no CUDA call). */
+enum {
+    QZ_OK = 0, QZ_ERR_UNSUPPORTED_TYPE = 1, QZ_ERR_BAD_SHAPE = 2, QZ_ERR_CUDA = 3, QZ_ERR_MISSING_TABLE = 4,
+    QZ_ERR_TOO_LARGE = 5, QZ_ERR_NOT_REPACKED = 6, QZ_ERR_TIMEOUT = 7
+};
+int quartz_last_error(void);
+const char *quartz_error_string(void);
+void quartz_clear_error(void);
+
+/* All later launches and copies go to this cudaStream_t (NULL = legacy default stream,
+ * the reference's behaviour, src/cuda_kernels.cu launches with <<<g,b>>> only). */
+void quartz_set_stream(void *cuda_stream);
+
+/* The IQ3_XXS codebook (256 x u32); the reference has no IQ3_XXS. */
+void cuda_set_iq3xxs_grid(const uint32_t *host);
+
+/* One-time, in-place, size-preserving repack of n_mats consecutive [out_dim x in_dim]
+ * matrices from the raw GGUF block layout (src/gguf.rs:118-123) into the plane layout
+ * the streaming kernels read with aligned 128-bit loads.  To be called once after the
+ * upload (src/cuda.rs:170-172, 202-204 are the places).  The byte range is remembered:
+ * cuda_gemv / cuda_gemv_moe4 / cuda_gemm / cuda_dequant on any pointer inside it (e.g.
+ * an expert slice, src/cuda.rs:250-257) then read the new layout.  Returns 1 if the
+ * bytes were rearranged, 0 if this format/shape is served from the raw layout (nothing
+ * changed; not an error).  Unregistered pointers always mean raw layout. */
+int cuda_repack_weights(uint32_t ggml_type, void *d_data, int in_dim, int out_dim, int n_mats);
+/* Inverse of the above on a registered range (restores the raw bytes); 1 if undone. */
+int cuda_unpack_weights(void *d_data);
+
+/* Dequantize n_rows rows of in_dim weights to f32, bit-identical to the reference's
+ * CPU dequant() (src/dequant.rs:1239-1258), from either layout. */
+void cuda_dequant(uint32_t ggml_type, const uint8_t *d_data, float *d_out, int in_dim, long long n_rows);
+
+/* Batched form: Y[m, out_dim] = X[m, in_dim] * W^T, token-major like the reference's CPU
+ * gemm() (src/dequant.rs:143-200).  The reference has no GPU counterpart. */
+void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,
+               int out_dim);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,39 @@
+"""Build the CUDA library in-tree: saient-quartz_b200/libquartz_b200.so (sm_100a only)."""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libquartz_b200.so")
+
+
+def sources():
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh")))
+
+
+def up_to_date():
+    if not os.path.exists(LIB):
+        return False
+    t = os.path.getmtime(LIB)
+    hdr = os.path.join(HERE, "..", "include", "quartz_b200.h")
+    return all(os.path.getmtime(s) <= t for s in sources() + [hdr])
+
+
+def build(force=False, verbose=False):
+    if not force and up_to_date():
+        return LIB
+    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    arch = os.environ.get("QUARTZ_CUDA_ARCH", "sm_100a")   # same variable as the reference's build.rs:33
+    cc = arch.replace("sm_", "compute_")
+    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", f"arch={cc},code={arch}", "-lineinfo", "-shared",
+           "-Xcompiler", "-fPIC", "-o", LIB] + [s for s in sources() if s.endswith(".cu")]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    subprocess.check_call(cmd)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,355 @@
+// Streaming dequant-GEMV kernels (batch 1): the HBM-bound hot path.
+//
+// Design, in the order the data flows:
+//
+//  * Activations are converted ONCE per GEMV into a 16-bit block-fixed-point form
+//    (quantize_x_kernel): per run of 32 values a scale s = max|x| / 32512 and two
+//    int8 limbs per value, X = 256*h + l, x ~= s*X (relative step 3e-5 of the run
+//    maximum).  Every integer format here is "int code x block scale", so a row
+//    dot-product becomes exact int32 dp4a sums (two per four weights) finished in
+//    f32 with the block scales; "min" terms use the exact f32 sums of x.  This is
+//    what keeps the kernel on the memory roofline: a Q4_K weight has 0.56 bytes,
+//    so at 6.5 TB/s an SM must retire ~44 weights per clock, which leaves under
+//    three issue slots per weight -- nibble->float conversion plus an FMA per
+//    weight does not fit, four weights per dp4a does.
+//  * A thread owns one 64-weight slice of the K dimension for the whole kernel:
+//    its activation limbs live in 32 registers and are reused for every row, so
+//    shared memory and L1 carry no per-row activation traffic at all.
+//  * Weights stream with 128-bit ld.global.nc.L1::no_allocate loads, R rows (so
+//    3R..4R independent 16-byte loads) in flight per thread, from the raw GGUF
+//    layout where blocks are 16-byte multiples (Q4_K, Q5_K) and from the plane
+//    layout (see formats.cuh) otherwise.
+//  * Threads of one row are lanes of the same warp(s); the row sum is a shuffle
+//    butterfly plus, for K > 2048, one shared-memory hop across the row's warps.
+//  * Persistent grid-stride CTAs over row tiles; blockIdx.y selects one of up to
+//    four (weights, activation, output) triples, which is how fused q/k/v and
+//    multi-expert launches are expressed.
+#pragma once
+
+#include "formats.cuh"
+
+namespace qz {
+
+// Block-fixed-point activations.  xl/xh: low/high int8 limbs [K]; xs: f32 scale per
+// 32-run [K/32]; xsum: exact f32 sum of x per 16-run [K/16].
+struct XQ {
+    const int8_t *xl;
+    const int8_t *xh;
+    const float *xs;
+    const float *xsum;
+};
+
+constexpr float XQ_RANGE = 32512.0f;   // 127 * 256: h, l both fit int8
+
+// one thread per 4 values; 8 threads share a 32-run
+__global__ void quantize_x_kernel(const float *__restrict__ x, int8_t *__restrict__ xl, int8_t *__restrict__ xh,
+                                  float *__restrict__ xs, float *__restrict__ xsum, int K)
+{
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    int k = 4 * t;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k < K) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[i] = x[k + i];
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float sum = (v[0] + v[1]) + (v[2] + v[3]);
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    if (k >= K) return;
+    float inv = amax > 0.f ? XQ_RANGE / amax : 0.f;
+    uint32_t wl = 0, wh = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int X = __float2int_rn(v[i] * inv);
+        int l = ((X + 128) & 0xFF) - 128;
+        int h = (X - l) >> 8;
+        wl |= (uint32_t)(l & 0xFF) << (8 * i);
+        wh |= (uint32_t)(h & 0xFF) << (8 * i);
+    }
+    ((uint32_t *)xl)[t] = wl;
+    ((uint32_t *)xh)[t] = wh;
+    if ((t & 7) == 0) xs[t >> 3] = amax / XQ_RANGE;
+    if ((t & 3) == 0) xsum[t >> 2] = sum;
+}
+
+// d = sum over 4 bytes a_i (unsigned) * b_i (signed) + c
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+struct GemvArgs {
+    const uint8_t *W[4];
+    XQ xq[4];
+    float *y[4];
+    int K, N;
+    int U;       // 64-weight units per row
+    int Upad;    // threads per row: U rounded up to a power of two (<32) or a multiple of 32
+    int RP;      // rows per pass = blockDim.x / Upad
+};
+
+// ---- per-format policies ------------------------------------------------------
+// Each policy owns: the thread's activation slice (XRegs), one row's bytes for the
+// slice (WRegs), the loads, and the integer dot product.
+
+struct StreamQ4K {
+    static constexpr uint32_t TYPE = T_Q4_K;
+    static constexpr bool PLANES = false;
+    struct XRegs { uint32_t xl[16], xh[16]; float s0, s1, sum0, sum1; };
+    struct WRegs { uint4 hdr, q0, q1; };
+
+    __device__ static void load_x(XRegs &r, const XQ &q, int u)
+    {
+        const uint4 *pl = (const uint4 *)(q.xl + 64 * u), *ph = (const uint4 *)(q.xh + 64 * u);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint4 a = pl[i], b = ph[i];
+            r.xl[4 * i] = a.x; r.xl[4 * i + 1] = a.y; r.xl[4 * i + 2] = a.z; r.xl[4 * i + 3] = a.w;
+            r.xh[4 * i] = b.x; r.xh[4 * i + 1] = b.y; r.xh[4 * i + 2] = b.z; r.xh[4 * i + 3] = b.w;
+        }
+        r.s0 = q.xs[2 * u];
+        r.s1 = q.xs[2 * u + 1] * 0.0625f;   // high nibbles are used unshifted (x16)
+        r.sum0 = q.xsum[4 * u] + q.xsum[4 * u + 1];
+        r.sum1 = q.xsum[4 * u + 2] + q.xsum[4 * u + 3];
+    }
+    __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
+    {
+        const uint8_t *blk = row + (size_t)(u >> 2) * 144;
+        w.hdr = ld_stream(blk);
+        w.q0 = ld_stream(blk + 16 + 32 * (u & 3));
+        w.q1 = ld_stream(blk + 32 + 32 * (u & 3));
+    }
+    __device__ static float dot(const WRegs &w, const XRegs &x, int u)
+    {
+        const uint32_t q[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
+        int a0h = 0, a0l = 0, a1h = 0, a1l = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            uint32_t lo = q[i] & 0x0F0F0F0Fu, hi = q[i] & 0xF0F0F0F0u;
+            a0h = dp4a_us(lo, x.xh[i], a0h);
+            a0l = dp4a_us(lo, x.xl[i], a0l);
+            a1h = dp4a_us(hi, x.xh[8 + i], a1h);
+            a1l = dp4a_us(hi, x.xl[8 + i], a1l);
+        }
+        // 6-bit scale / min codes of sub-blocks 2p and 2p+1 (src/dequant.rs:1471-1480)
+        const int p = u & 3;
+        const uint32_t s0 = w.hdr.y, s1 = w.hdr.z, s2 = w.hdr.w;
+        uint32_t scw = (p < 2) ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
+        uint32_t mw = (p < 2) ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
+        const int sh = 16 * (p & 1);
+        float sc0 = (float)((scw >> sh) & 0xFF), sc1 = (float)((scw >> (sh + 8)) & 0xFF);
+        float m0 = (float)((mw >> sh) & 0xFF), m1 = (float)((mw >> (sh + 8)) & 0xFF);
+        float2 dm = __half22float2(*(const __half2 *)&w.hdr.x);
+        float t0 = (float)(a0h * 256 + a0l) * x.s0;
+        float t1 = (float)(a1h * 256 + a1l) * x.s1;
+        return dm.x * (sc0 * t0 + sc1 * t1) - dm.y * (m0 * x.sum0 + m1 * x.sum1);
+    }
+};
+
+struct StreamQ6K {
+    static constexpr uint32_t TYPE = T_Q6_K;
+    static constexpr bool PLANES = true;
+    // unit u -> block u/4, half n = (u>>1)&1, 16-lane group g = u&1; run k holds the
+    // weights 128n + 32k + 16g + [0,16) of the block
+    struct XRegs { uint32_t xl[16], xh[16]; float s[4]; int sx[4]; };
+    struct WRegs { uint4 ql0, ql1, qh; uint2 sc; uint32_t d; };
+
+    __device__ static void load_x(XRegs &r, const XQ &q, int u)
+    {
+        const int base = 256 * (u >> 2) + 128 * ((u >> 1) & 1) + 16 * (u & 1);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            uint4 a = *(const uint4 *)(q.xl + base + 32 * k), b = *(const uint4 *)(q.xh + base + 32 * k);
+            r.xl[4 * k] = a.x; r.xl[4 * k + 1] = a.y; r.xl[4 * k + 2] = a.z; r.xl[4 * k + 3] = a.w;
+            r.xh[4 * k] = b.x; r.xh[4 * k + 1] = b.y; r.xh[4 * k + 2] = b.z; r.xh[4 * k + 3] = b.w;
+            r.s[k] = q.xs[(base >> 5) + k];
+            int sl = 0, shh = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                sl = dp4a_ss(0x01010101u, r.xl[4 * k + i], sl);
+                shh = dp4a_ss(0x01010101u, r.xh[4 * k + i], shh);
+            }
+            r.sx[k] = 32 * (256 * shh + sl);   // the -32 offset of every 6-bit code
+        }
+    }
+    __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
+    {
+        const int b = u >> 2, n = (u >> 1) & 1, g = u & 1;
+        const uint8_t *ql = row + (size_t)b * 128 + 64 * n + 16 * g;
+        w.ql0 = ld_stream(ql);
+        w.ql1 = ld_stream(ql + 32);
+        w.qh = ld_stream(row + (size_t)nb * 128 + (size_t)b * 64 + 32 * n + 16 * g);
+        const uint8_t *sc = row + (size_t)nb * 192 + (size_t)b * 16 + 8 * n;
+        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(w.sc.x), "=r"(w.sc.y) : "l"(sc));
+        w.d = ld_stream_u16(row + (size_t)nb * 208 + (size_t)b * 2);
+    }
+    __device__ static float dot(const WRegs &w, const XRegs &x, int u)
+    {
+        const uint32_t a0[4] = {w.ql0.x, w.ql0.y, w.ql0.z, w.ql0.w};
+        const uint32_t a1[4] = {w.ql1.x, w.ql1.y, w.ql1.z, w.ql1.w};
+        const uint32_t hh[4] = {w.qh.x, w.qh.y, w.qh.z, w.qh.w};
+        int dh[4] = {0, 0, 0, 0}, dl[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t h = hh[i];
+            uint32_t q0 = (a0[i] & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
+            uint32_t q1 = (a1[i] & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+            uint32_t q2 = ((a0[i] >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
+            uint32_t q3 = ((a1[i] >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+            dh[0] = dp4a_us(q0, x.xh[i], dh[0]);       dl[0] = dp4a_us(q0, x.xl[i], dl[0]);
+            dh[1] = dp4a_us(q1, x.xh[4 + i], dh[1]);   dl[1] = dp4a_us(q1, x.xl[4 + i], dl[1]);
+            dh[2] = dp4a_us(q2, x.xh[8 + i], dh[2]);   dl[2] = dp4a_us(q2, x.xl[8 + i], dl[2]);
+            dh[3] = dp4a_us(q3, x.xh[12 + i], dh[3]);  dl[3] = dp4a_us(q3, x.xl[12 + i], dl[3]);
+        }
+        // scale bytes g, g+2, g+4, g+6 of the half's eight int8 scales
+        const int g = u & 1;
+        const int sh0 = 8 * g, sh1 = 8 * g + 16;
+        int sc[4];
+        sc[0] = (int)(int8_t)(w.sc.x >> sh0);
+        sc[1] = (int)(int8_t)(w.sc.x >> sh1);
+        sc[2] = (int)(int8_t)(w.sc.y >> sh0);
+        sc[3] = (int)(int8_t)(w.sc.y >> sh1);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; k++) acc = fmaf((float)(sc[k] * (256 * dh[k] + dl[k] - x.sx[k])), x.s[k], acc);
+        return acc * h2f((uint16_t)w.d);
+    }
+};
+
+struct StreamQ8_0 {
+    static constexpr uint32_t TYPE = T_Q8_0;
+    static constexpr bool PLANES = true;
+    // unit u -> blocks 2u and 2u+1
+    struct XRegs { uint32_t xl[16], xh[16]; float s0, s1; };
+    struct WRegs { uint4 q[4]; uint32_t d2; };
+
+    __device__ static void load_x(XRegs &r, const XQ &q, int u)
+    {
+        const uint4 *pl = (const uint4 *)(q.xl + 64 * u), *ph = (const uint4 *)(q.xh + 64 * u);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint4 a = pl[i], b = ph[i];
+            r.xl[4 * i] = a.x; r.xl[4 * i + 1] = a.y; r.xl[4 * i + 2] = a.z; r.xl[4 * i + 3] = a.w;
+            r.xh[4 * i] = b.x; r.xh[4 * i + 1] = b.y; r.xh[4 * i + 2] = b.z; r.xh[4 * i + 3] = b.w;
+        }
+        r.s0 = q.xs[2 * u];
+        r.s1 = q.xs[2 * u + 1];
+    }
+    __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
+    {
+        const uint8_t *qs = row + (size_t)nb * 2 + (size_t)u * 64;
+#pragma unroll
+        for (int i = 0; i < 4; i++) w.q[i] = ld_stream(qs + 16 * i);
+        w.d2 = ld_stream_u32(row + (size_t)u * 4);
+    }
+    __device__ static float dot(const WRegs &w, const XRegs &x, int)
+    {
+        int h0 = 0, l0 = 0, h1 = 0, l1 = 0;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint32_t a[4] = {w.q[i].x, w.q[i].y, w.q[i].z, w.q[i].w};
+            const uint32_t b[4] = {w.q[2 + i].x, w.q[2 + i].y, w.q[2 + i].z, w.q[2 + i].w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                h0 = dp4a_ss(a[j], x.xh[4 * i + j], h0);      l0 = dp4a_ss(a[j], x.xl[4 * i + j], l0);
+                h1 = dp4a_ss(b[j], x.xh[8 + 4 * i + j], h1);  l1 = dp4a_ss(b[j], x.xl[8 + 4 * i + j], l1);
+            }
+        }
+        float2 d = __half22float2(*(const __half2 *)&w.d2);
+        return d.x * ((float)(256 * h0 + l0) * x.s0) + d.y * ((float)(256 * h1 + l1) * x.s1);
+    }
+};
+
+// ---- the kernel ---------------------------------------------------------------
+template <class F, int R>
+__global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
+{
+    __shared__ float part[2][16 * R];   // [parity][row-in-pass * R + i][warp of the row] flattened below
+    __shared__ float part_w[2][16 * R * 16];
+
+    const int m = blockIdx.y;
+    const uint8_t *__restrict__ W = a.W[m];
+    float *__restrict__ y = a.y[m];
+    const FormatInfo fi = format_info(F::TYPE);
+    const int nb = a.K / fi.block_elems;
+    const size_t row_bytes = (size_t)nb * fi.block_bytes;
+
+    const int u = threadIdx.x % a.Upad;
+    const int rl = threadIdx.x / a.Upad;
+    const bool active = u < a.U;
+    const int lane = threadIdx.x & 31;
+    const int wpr = a.Upad >> 5;                 // warps per row (0 when Upad < 32)
+    const int wir = (threadIdx.x >> 5) % (wpr > 0 ? wpr : 1);   // warp index inside the row
+
+    typename F::XRegs xr;
+    if (active) F::load_x(xr, a.xq[m], u);
+
+    const int rows_per_tile = a.RP * R;
+    const int ntiles = (a.N + rows_per_tile - 1) / rows_per_tile;
+    int parity = 0;
+    (void)part;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, parity ^= 1) {
+        const int row0 = tile * rows_per_tile + rl;
+        typename F::WRegs w[R];
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int row = row0 + i * a.RP;
+            if (active && row < a.N) F::load_w(w[i], W + (size_t)row * row_bytes, nb, u);
+        }
+        float acc[R];
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int row = row0 + i * a.RP;
+            acc[i] = (active && row < a.N) ? F::dot(w[i], xr, u) : 0.f;
+        }
+        if (wpr == 0) {
+            // several rows per warp: butterfly inside the row's Upad lanes
+#pragma unroll
+            for (int i = 0; i < R; i++) {
+                float v = acc[i];
+                for (int off = a.Upad >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+                const int row = row0 + i * a.RP;
+                if (u == 0 && row < a.N) y[row] = v;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; i++) acc[i] = warp_sum(acc[i]);
+            if (wpr == 1) {
+                if (lane == 0) {
+#pragma unroll
+                    for (int i = 0; i < R; i++) {
+                        const int row = row0 + i * a.RP;
+                        if (row < a.N) y[row] = acc[i];
+                    }
+                }
+            } else {
+                if (lane == 0) {
+#pragma unroll
+                    for (int i = 0; i < R; i++) part_w[parity][(rl * R + i) * 16 + wir] = acc[i];
+                }
+                __syncthreads();
+                if (threadIdx.x < rows_per_tile) {
+                    const int rl2 = threadIdx.x / R, i2 = threadIdx.x % R;
+                    float v = 0.f;
+                    for (int k = 0; k < wpr; k++) v += part_w[parity][(rl2 * R + i2) * 16 + k];
+                    const int row = tile * rows_per_tile + i2 * a.RP + rl2;
+                    if (row < a.N) y[row] = v;
+                }
+            }
+        }
+    }
+}
+
+}  // namespace qz

@@ -1,0 +1,625 @@
+// quartz_b200: the extern "C" boundary (include/quartz_b200.h) and its host logic.
+// One translation unit on purpose: the IQ codebooks are __device__ globals shared
+// by every kernel, and the library is built without relocatable device code.
+
+#include "../../include/quartz_b200.h"
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "formats.cuh"
+#include "generic.cuh"
+#include "gemv_stream.cuh"
+#include "decode_ops.cuh"
+
+namespace qz {
+
+// ---- process state --------------------------------------------------------------
+static cudaStream_t g_stream = 0;
+static int g_err = QZ_OK;
+static std::string g_err_msg;
+static int g_sm_count = 0;
+
+void set_error(int code, const char *what)
+{
+    if (g_err == QZ_OK) {   // sticky: keep the first failure
+        g_err = code;
+        g_err_msg = what ? what : "";
+    }
+}
+cudaStream_t stream() { return g_stream; }
+int sm_count()
+{
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count <= 0)
+            g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
+// ---- registry of repacked byte ranges ---------------------------------------------
+struct Range {
+    uintptr_t end;
+    uint32_t type;
+    int K;
+    long long rows;
+};
+static std::map<uintptr_t, Range> g_ranges;   // start -> range
+
+static const Range *find_range(const void *p, uintptr_t *start_out = nullptr)
+{
+    if (g_ranges.empty()) return nullptr;
+    uintptr_t a = (uintptr_t)p;
+    auto it = g_ranges.upper_bound(a);
+    if (it == g_ranges.begin()) return nullptr;
+    --it;
+    if (a >= it->second.end) return nullptr;
+    if (start_out) *start_out = it->first;
+    return &it->second;
+}
+
+// ---- activation scratch (block-fixed-point x), owned by the library ------------------
+struct XQScratch {
+    uint8_t *base = nullptr;
+    size_t cap_k = 0;
+    size_t slot_bytes = 0;
+};
+static XQScratch g_xq;
+
+static size_t xq_slot_bytes(size_t K) { return ((2 * K + K / 8 + K / 4 + 64) + 255) & ~(size_t)255; }
+
+static bool ensure_xq(int K)
+{
+    if ((size_t)K <= g_xq.cap_k) return true;
+    if (g_xq.base) {
+        cudaStreamSynchronize(g_stream);
+        cudaFree(g_xq.base);
+        g_xq.base = nullptr;
+        g_xq.cap_k = 0;
+    }
+    size_t cap = (size_t)K < 32768 ? 32768 : (size_t)K;
+    size_t sb = xq_slot_bytes(cap);
+    if (cudaMalloc(&g_xq.base, 4 * sb) != cudaSuccess) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "cudaMalloc of the activation scratch failed");
+        return false;
+    }
+    g_xq.cap_k = cap;
+    g_xq.slot_bytes = sb;
+    return true;
+}
+
+struct XQMut {
+    int8_t *xl, *xh;
+    float *xs, *xsum;
+};
+static XQMut xq_slot(uint8_t *base, size_t slot_bytes, int slot, size_t cap_k)
+{
+    uint8_t *p = base + (size_t)slot * slot_bytes;
+    XQMut q;
+    q.xl = (int8_t *)p;
+    q.xh = (int8_t *)(p + cap_k);
+    q.xs = (float *)(p + 2 * cap_k);
+    q.xsum = (float *)(p + 2 * cap_k + cap_k / 8 + 32);
+    return q;
+}
+
+static void launch_quantize(const float *x, const XQMut &q, int K)
+{
+    int threads = K / 4;
+    int bs = 256, gs = (threads + bs - 1) / bs;
+    quantize_x_kernel<<<gs, bs, 0, g_stream>>>(x, q.xl, q.xh, q.xs, q.xsum, K);
+    QZ_LAUNCH_CHECK();
+}
+
+// ---- one-time init: default sign table ------------------------------------------------
+static bool g_ksigns_set = false;
+static bool g_have_iq2xxs, g_have_iq2xs, g_have_iq2s, g_have_iq3s, g_have_iq3xxs;
+
+static void ensure_ksigns()
+{
+    if (g_ksigns_set) return;
+    // entry i = i with bit 7 set when i has odd parity (even number of minus signs per byte)
+    uint8_t t[128];
+    for (int i = 0; i < 128; i++) t[i] = (uint8_t)(i | ((__builtin_popcount(i) & 1) << 7));
+    QZ_CUDA_CHECK(cudaMemcpyToSymbol(g_ksigns, t, 128));
+    g_ksigns_set = true;
+}
+
+static bool tables_ready(uint32_t t)
+{
+    switch (t) {
+    case T_IQ2_XXS: ensure_ksigns(); return g_have_iq2xxs;
+    case T_IQ2_XS: ensure_ksigns(); return g_have_iq2xs;
+    case T_IQ2_S: return g_have_iq2s;
+    case T_IQ3_S: return g_have_iq3s;
+    case T_IQ3_XXS: ensure_ksigns(); return g_have_iq3xxs;
+    default: return true;
+    }
+}
+
+// ---- dispatch helpers ---------------------------------------------------------------------
+#define QZ_FOR_BLOCK_TYPES(X) \
+    X(T_Q4_0) X(T_Q4_1) X(T_Q5_0) X(T_Q5_1) X(T_Q8_0) X(T_IQ4_NL) X(T_Q2_K) X(T_Q4_K) X(T_Q5_K) X(T_Q6_K) \
+    X(T_IQ2_XXS) X(T_IQ2_XS) X(T_IQ2_S) X(T_IQ3_S) X(T_IQ3_XXS)
+
+static bool is_plain(uint32_t t) { return t == T_F32 || t == T_F16 || t == T_BF16; }
+
+static void launch_generic(uint32_t t, bool planes, const uint8_t *W, const float *x, float *y, int K, int N)
+{
+    dim3 grid((N + 3) / 4), block(128);
+    switch (t) {
+#define X(TT)                                                                             \
+    case TT:                                                                              \
+        if (planes) gemv_generic_kernel<TT, true><<<grid, block, 0, g_stream>>>(W, x, y, K, N);  \
+        else gemv_generic_kernel<TT, false><<<grid, block, 0, g_stream>>>(W, x, y, K, N);        \
+        break;
+        QZ_FOR_BLOCK_TYPES(X)
+#undef X
+    case T_F32: gemv_plain_kernel<T_F32><<<grid, block, 0, g_stream>>>(W, x, y, K, N); break;
+    case T_F16: gemv_plain_kernel<T_F16><<<grid, block, 0, g_stream>>>(W, x, y, K, N); break;
+    case T_BF16: gemv_plain_kernel<T_BF16><<<grid, block, 0, g_stream>>>(W, x, y, K, N); break;
+    default: break;
+    }
+    QZ_LAUNCH_CHECK();
+}
+
+// Which layout the streaming kernel of a format reads: 0 = no streaming kernel,
+// 1 = raw GGUF blocks, 2 = planes.
+static int stream_layout(uint32_t t)
+{
+    switch (t) {
+    case T_Q4_K: return 1;
+    case T_Q6_K: return 2;
+    case T_Q8_0: return 2;
+    default: return 0;
+    }
+}
+
+template <class F>
+static void launch_stream_r(const GemvArgs &a, int n_mats, int T)
+{
+    const int sms = sm_count();
+    // rows per thread: as many as keep at least ~2 tiles per SM
+    int R = 4;
+    while (R > 1 && (long long)(a.N + a.RP * R - 1) / (a.RP * R) * n_mats < 2LL * sms) R >>= 1;
+    const int ntiles = (a.N + a.RP * R - 1) / (a.RP * R);
+    int per_sm = (T <= 256) ? 3 : 1;
+    int gx = ntiles < sms * per_sm ? ntiles : sms * per_sm;
+    if (gx < 1) gx = 1;
+    dim3 grid(gx, n_mats), block(T);
+    if (R == 4) gemv_stream_kernel<F, 4><<<grid, block, 0, g_stream>>>(a);
+    else if (R == 2) gemv_stream_kernel<F, 2><<<grid, block, 0, g_stream>>>(a);
+    else gemv_stream_kernel<F, 1><<<grid, block, 0, g_stream>>>(a);
+    QZ_LAUNCH_CHECK();
+}
+
+// Streaming path for up to four same-shape GEMVs.  Returns false when the shape or the
+// pointers do not qualify (the caller then falls back to the any-shape kernels).
+static bool try_stream(uint32_t t, int n, const uint8_t *const *W, const float *const *x, float *const *y, int K,
+                       int N, const bool *planes)
+{
+    const int want = stream_layout(t);
+    if (!want || K % 64 != 0 || K / 64 > 512) return false;
+    const FormatInfo fi = format_info(t);
+    const size_t row_bytes = (size_t)(K / fi.block_elems) * fi.block_bytes;
+    if (row_bytes % 16 != 0) return false;
+    for (int i = 0; i < n; i++) {
+        if (((uintptr_t)W[i] & 15) || ((uintptr_t)x[i] & 3)) return false;
+        if ((want == 2) != planes[i]) return false;
+    }
+    if (!ensure_xq(K)) return false;
+
+    GemvArgs a;
+    a.K = K;
+    a.N = N;
+    a.U = K / 64;
+    if (a.U < 32) {
+        int p = 1;
+        while (p < a.U) p <<= 1;
+        a.Upad = p;
+    } else {
+        a.Upad = (a.U + 31) & ~31;
+    }
+    a.RP = a.Upad >= 256 ? 1 : 256 / a.Upad;
+    const int T = a.Upad * a.RP;
+
+    // quantize each distinct activation vector once
+    int slot_of[4];
+    int n_slots = 0;
+    for (int i = 0; i < n; i++) {
+        int s = -1;
+        for (int j = 0; j < i; j++)
+            if (x[j] == x[i]) { s = slot_of[j]; break; }
+        if (s < 0) {
+            s = n_slots++;
+            launch_quantize(x[i], xq_slot(g_xq.base, g_xq.slot_bytes, s, g_xq.cap_k), K);
+        }
+        slot_of[i] = s;
+    }
+    for (int i = 0; i < 4; i++) {
+        int j = i < n ? i : 0;
+        XQMut q = xq_slot(g_xq.base, g_xq.slot_bytes, slot_of[j], g_xq.cap_k);
+        a.W[i] = W[j];
+        a.y[i] = y[j];
+        a.xq[i] = XQ{q.xl, q.xh, q.xs, q.xsum};
+    }
+    switch (t) {
+    case T_Q4_K: launch_stream_r<StreamQ4K>(a, n, T); break;
+    case T_Q6_K: launch_stream_r<StreamQ6K>(a, n, T); break;
+    case T_Q8_0: launch_stream_r<StreamQ8_0>(a, n, T); break;
+    default: return false;
+    }
+    return true;
+}
+
+static bool check_shape(uint32_t t, int K, int N, const char *who)
+{
+    const FormatInfo fi = format_info(t);
+    if (fi.block_elems == 0) return false;
+    if (K <= 0 || N < 0 || K % fi.block_elems != 0) {
+        set_error(QZ_ERR_BAD_SHAPE, who);
+        return false;
+    }
+    return true;
+}
+
+static void gemv_n(uint32_t t, int n, const uint8_t *const *W, const float *const *x, float *const *y, int K, int N)
+{
+    const FormatInfo fi = format_info(t);
+    if (fi.block_elems == 0) {
+        // reference behaviour (src/cuda_kernels.cu:1073-1077): zero the output, complain on stderr
+        for (int i = 0; i < n; i++)
+            if (N > 0) QZ_CUDA_CHECK(cudaMemsetAsync(y[i], 0, (size_t)N * sizeof(float), g_stream));
+        fprintf(stderr, "cuda_gemv: unsupported ggml_type %u\n", t);
+        set_error(QZ_ERR_UNSUPPORTED_TYPE, "cuda_gemv: unsupported ggml_type");
+        return;
+    }
+    if (!check_shape(t, K, N, "cuda_gemv: in_dim must be a positive multiple of the block size") || N == 0) return;
+    if (!tables_ready(t)) {
+        for (int i = 0; i < n; i++) QZ_CUDA_CHECK(cudaMemsetAsync(y[i], 0, (size_t)N * sizeof(float), g_stream));
+        set_error(QZ_ERR_MISSING_TABLE, "IQ codebook not uploaded (cuda_set_*_grid)");
+        return;
+    }
+    bool planes[4] = {false, false, false, false};
+    for (int i = 0; i < n; i++) {
+        const Range *r = find_range(W[i]);
+        if (r) {
+            if (r->type != t || r->K != K) {
+                set_error(QZ_ERR_BAD_SHAPE, "cuda_gemv: pointer lies in a repacked range of another type/in_dim");
+                return;
+            }
+            planes[i] = true;
+        }
+    }
+    if (!is_plain(t) && try_stream(t, n, W, x, y, K, N, planes)) return;
+    for (int i = 0; i < n; i++) launch_generic(t, planes[i], W[i], x[i], y[i], K, N);
+}
+
+static void dequant_rows(uint32_t t, const uint8_t *data, float *out, int K, long long rows)
+{
+    const FormatInfo fi = format_info(t);
+    if (fi.block_elems == 0) {
+        set_error(QZ_ERR_UNSUPPORTED_TYPE, "cuda_dequant: unsupported ggml_type");
+        return;
+    }
+    if (!check_shape(t, K, 0, "cuda_dequant: in_dim must be a positive multiple of the block size") || rows <= 0) return;
+    if (!tables_ready(t)) {
+        set_error(QZ_ERR_MISSING_TABLE, "IQ codebook not uploaded (cuda_set_*_grid)");
+        return;
+    }
+    if (is_plain(t)) {
+        long long n = rows * K;
+        dequant_plain_kernel<<<(unsigned)((n + 255) / 256), 256, 0, g_stream>>>(data, out, t, n);
+        QZ_LAUNCH_CHECK();
+        return;
+    }
+    const Range *r = find_range(data);
+    bool planes = false;
+    if (r) {
+        if (r->type != t || r->K != K) {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_dequant: pointer lies in a repacked range of another type/in_dim");
+            return;
+        }
+        planes = true;
+    }
+    long long n_sub = rows * (K / 32);
+    unsigned grid = (unsigned)((n_sub + 127) / 128);
+    switch (t) {
+#define X(TT)                                                                                   \
+    case TT:                                                                                    \
+        if (planes) dequant_kernel<TT, true><<<grid, 128, 0, g_stream>>>(data, out, K, n_sub);  \
+        else dequant_kernel<TT, false><<<grid, 128, 0, g_stream>>>(data, out, K, n_sub);        \
+        break;
+        QZ_FOR_BLOCK_TYPES(X)
+#undef X
+    default: break;
+    }
+    QZ_LAUNCH_CHECK();
+}
+
+}  // namespace qz
+
+using namespace qz;
+
+extern "C" {
+
+// ======================= Part 1 =======================
+
+void cuda_gemv(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int in_dim, int out_dim)
+{
+    gemv_n(ggml_type, 1, &d_data, &d_x, &d_y, in_dim, out_dim);
+}
+
+void cuda_gemv_moe4(uint32_t ggml_type, const uint8_t *w0, const uint8_t *w1, const uint8_t *w2, const uint8_t *w3,
+                    const float *xi0, const float *xi1, const float *xi2, const float *xi3, float *o0, float *o1,
+                    float *o2, float *o3, int n_act, int in_dim, int out_dim)
+{
+    const uint8_t *W[4] = {w0, w1, w2, w3};
+    const float *x[4] = {xi0, xi1, xi2, xi3};
+    float *y[4] = {o0, o1, o2, o3};
+    if (n_act <= 0) return;
+    if (n_act > 4) n_act = 4;
+    gemv_n(ggml_type, n_act, W, x, y, in_dim, out_dim);
+}
+
+void cuda_set_iq3s_grid(const uint32_t *host)
+{
+    QZ_CUDA_CHECK(cudaMemcpyToSymbol(g_iq3s_grid, host, 512 * sizeof(uint32_t)));
+    g_have_iq3s = true;
+}
+void cuda_set_iq2s_grid(const uint64_t *host)
+{
+    QZ_CUDA_CHECK(cudaMemcpyToSymbol(g_iq2s_grid, host, 1024 * sizeof(uint64_t)));
+    g_have_iq2s = true;
+}
+void cuda_set_iq2xxs_grid(const uint64_t *host)
+{
+    QZ_CUDA_CHECK(cudaMemcpyToSymbol(g_iq2xxs_grid, host, 256 * sizeof(uint64_t)));
+    g_have_iq2xxs = true;
+}
+void cuda_set_iq2xs_grid(const uint64_t *host)
+{
+    QZ_CUDA_CHECK(cudaMemcpyToSymbol(g_iq2xs_grid, host, 512 * sizeof(uint64_t)));
+    g_have_iq2xs = true;
+}
+void cuda_set_ksigns(const uint8_t *host)
+{
+    QZ_CUDA_CHECK(cudaMemcpyToSymbol(g_ksigns, host, 128));
+    g_ksigns_set = true;
+}
+void cuda_set_iq3xxs_grid(const uint32_t *host)
+{
+    QZ_CUDA_CHECK(cudaMemcpyToSymbol(g_iq3xxs_grid, host, 256 * sizeof(uint32_t)));
+    g_have_iq3xxs = true;
+}
+
+void cuda_mem_info(size_t *free_b, size_t *total_b) { QZ_CUDA_CHECK(cudaMemGetInfo(free_b, total_b)); }
+
+void *cuda_alloc(size_t bytes)
+{
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        cudaGetLastError();   // the caller checks for NULL (src/cuda.rs:79, 224); not a sticky error
+        return nullptr;
+    }
+    return p;
+}
+
+void cuda_drop(void *p)
+{
+    if (!p) return;
+    // forget repacked ranges that start inside this allocation's base
+    auto it = g_ranges.find((uintptr_t)p);
+    if (it != g_ranges.end()) g_ranges.erase(it);
+    QZ_CUDA_CHECK(cudaFree(p));
+}
+
+void cuda_h2d(void *dst, const void *src, size_t bytes)
+{
+    if (g_stream == 0) {
+        QZ_CUDA_CHECK(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    } else {
+        QZ_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g_stream));
+        QZ_CUDA_CHECK(cudaStreamSynchronize(g_stream));
+    }
+}
+
+void cuda_d2h(void *dst, const void *src, size_t bytes)
+{
+    if (g_stream == 0) {
+        QZ_CUDA_CHECK(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    } else {
+        QZ_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g_stream));
+        QZ_CUDA_CHECK(cudaStreamSynchronize(g_stream));
+    }
+}
+
+void cuda_sync(void) { QZ_CUDA_CHECK(cudaDeviceSynchronize()); }
+
+void cuda_vec_add(float *dst, const float *src, int n)
+{
+    if (n <= 0) return;
+    vec_add_kernel<<<(n + 255) / 256, 256, 0, g_stream>>>(dst, src, n);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_vec_scale_add(float *dst, const float *src, float scale, int n)
+{
+    if (n <= 0) return;
+    vec_scale_add_kernel<<<(n + 255) / 256, 256, 0, g_stream>>>(dst, src, scale, n);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_vec_zero(float *dst, int n)
+{
+    if (n <= 0) return;
+    vec_zero_kernel<<<(n + 255) / 256, 256, 0, g_stream>>>(dst, n);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_rms_norm(float *out, const float *x, const float *w, int n)
+{
+    if (n <= 0) return;
+    int bs = n >= 4096 ? 1024 : (n >= 1024 ? 512 : (n >= 256 ? 128 : 32));
+    rms_norm_kernel<<<1, bs, 0, g_stream>>>(out, x, w, n);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_rope_yarn(float *x, int n_heads, int head_dim, int pos, float theta, float yarn_scale, int yarn_orig_ctx,
+                    int neox)
+{
+    if (n_heads <= 0 || head_dim < 2) return;
+    int half = head_dim / 2;
+    int bs = (half + 31) & ~31;
+    rope_yarn_kernel<<<n_heads, bs, 0, g_stream>>>(x, head_dim, pos, theta, yarn_scale, yarn_orig_ctx, neox);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_kv_append(float *k_cache, float *v_cache, const float *k, const float *v, int pos, int kv_dim)
+{
+    if (kv_dim <= 0) return;
+    kv_append_kernel<<<(kv_dim + 255) / 256, 256, 0, g_stream>>>(k_cache, v_cache, k, v, pos, kv_dim);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_attn_score_all(float *scores, const float *q, const float *k_cache, int n_heads, int n_kv_heads,
+                         int seq_len, int head_dim, int kv_dim, int max_seq, float scale)
+{
+    if (n_heads <= 0 || seq_len <= 0) return;
+    dim3 grid(n_heads, (seq_len + 7) / 8);
+    attn_score_all_kernel<<<grid, 256, 0, g_stream>>>(scores, q, k_cache, n_heads, n_kv_heads, seq_len, head_dim,
+                                                      kv_dim, max_seq, scale);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_softmax_sink_all(float *scores, int n_heads, int seq_len, int max_seq, const float *sinks)
+{
+    if (n_heads <= 0 || seq_len <= 0) return;
+    int bs = seq_len <= 64 ? 64 : 256;
+    softmax_sink_all_kernel<<<n_heads, bs, 0, g_stream>>>(scores, seq_len, max_seq, sinks);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_attn_values_all(float *out, const float *scores, const float *v_cache, int n_heads, int n_kv_heads,
+                          int seq_len, int head_dim, int kv_dim, int max_seq)
+{
+    if (n_heads <= 0 || head_dim <= 0) return;
+    int bs = head_dim >= 128 ? 128 : ((head_dim + 31) & ~31);
+    attn_values_all_kernel<<<n_heads, bs, 0, g_stream>>>(out, scores, v_cache, n_heads, n_kv_heads, seq_len,
+                                                         head_dim, kv_dim, max_seq);
+    QZ_LAUNCH_CHECK();
+}
+// Per-head forms (declared by the reference's FFI, unused by its forward pass): the
+// all-heads kernels with one head and the head's column offset folded into the pointer.
+void cuda_attn_score(float *scores, const float *q, const float *k_cache, int seq_len, int head_dim, int kv_dim,
+                     int kv_head_off, float scale)
+{
+    cuda_attn_score_all(scores, q, k_cache + kv_head_off, 1, 1, seq_len, head_dim, kv_dim, seq_len, scale);
+}
+void cuda_softmax_sink(float *x, int n, float sink)
+{
+    if (n <= 0) return;
+    softmax_sink_kernel<<<1, n <= 64 ? 64 : 256, 0, g_stream>>>(x, n, sink);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_attn_values(float *out, const float *scores, const float *v_cache, int seq_len, int head_dim, int kv_dim,
+                      int kv_head_off)
+{
+    cuda_attn_values_all(out, scores, v_cache + kv_head_off, 1, 1, seq_len, head_dim, kv_dim, seq_len);
+}
+void cuda_swiglu(float *out, const float *gate, const float *up, int n)
+{
+    if (n <= 0) return;
+    swiglu_kernel<<<(n + 255) / 256, 256, 0, g_stream>>>(out, gate, up, n);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_swiglu_oai(float *out, const float *gate, const float *up, int n)
+{
+    if (n <= 0) return;
+    swiglu_oai_kernel<<<(n + 255) / 256, 256, 0, g_stream>>>(out, gate, up, n);
+    QZ_LAUNCH_CHECK();
+}
+void cuda_embed_lookup(float *out, const uint8_t *data, uint32_t ggml_type, int token, int embed_dim)
+{
+    const FormatInfo fi = format_info(ggml_type);
+    if (fi.block_elems == 0 || embed_dim <= 0 || embed_dim % fi.block_elems) {
+        set_error(fi.block_elems ? QZ_ERR_BAD_SHAPE : QZ_ERR_UNSUPPORTED_TYPE, "cuda_embed_lookup");
+        return;
+    }
+    size_t row_bytes = (size_t)(embed_dim / fi.block_elems) * fi.block_bytes;
+    dequant_rows(ggml_type, data + (size_t)token * row_bytes, out, embed_dim, 1);
+}
+
+// ======================= Part 2 =======================
+
+int quartz_last_error(void) { return g_err; }
+const char *quartz_error_string(void) { return g_err_msg.c_str(); }
+void quartz_clear_error(void)
+{
+    g_err = QZ_OK;
+    g_err_msg.clear();
+}
+void quartz_set_stream(void *s) { g_stream = (cudaStream_t)s; }
+
+int cuda_repack_weights(uint32_t ggml_type, void *d_data, int in_dim, int out_dim, int n_mats)
+{
+    const FormatInfo fi = format_info(ggml_type);
+    if (fi.block_elems == 0) {
+        set_error(QZ_ERR_UNSUPPORTED_TYPE, "cuda_repack_weights: unsupported ggml_type");
+        return 0;
+    }
+    if (!check_shape(ggml_type, in_dim, out_dim, "cuda_repack_weights: bad shape") || n_mats <= 0) return 0;
+    if (stream_layout(ggml_type) != 2) return 0;            // served from the raw layout
+    const int nb = in_dim / fi.block_elems;
+    if (nb % 8 != 0 || ((uintptr_t)d_data & 15)) return 0;  // planes would not be 16-byte aligned
+    const size_t row_bytes = (size_t)nb * fi.block_bytes;
+    if (row_bytes > 200 * 1024) return 0;                   // a row must fit the staging shared memory
+    if (find_range(d_data)) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_repack_weights: range already repacked");
+        return 0;
+    }
+    const long long rows = (long long)out_dim * n_mats;
+    if (rows == 0) return 0;
+    static bool attr_set = false;
+    if (!attr_set) {
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(repack_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           200 * 1024));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(repack_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           200 * 1024));
+        attr_set = true;
+    }
+    unsigned grid = (unsigned)(rows < 65535 ? rows : 65535);
+    repack_rows_kernel<true><<<grid, 256, row_bytes, g_stream>>>((uint8_t *)d_data, fi, nb, rows);
+    QZ_LAUNCH_CHECK();
+    uintptr_t a = (uintptr_t)d_data;
+    g_ranges[a] = Range{a + (size_t)rows * row_bytes, ggml_type, in_dim, rows};
+    return 1;
+}
+
+int cuda_unpack_weights(void *d_data)
+{
+    auto it = g_ranges.find((uintptr_t)d_data);
+    if (it == g_ranges.end()) return 0;
+    const Range r = it->second;
+    const FormatInfo fi = format_info(r.type);
+    const int nb = r.K / fi.block_elems;
+    const size_t row_bytes = (size_t)nb * fi.block_bytes;
+    unsigned grid = (unsigned)(r.rows < 65535 ? r.rows : 65535);
+    repack_rows_kernel<false><<<grid, 256, row_bytes, g_stream>>>((uint8_t *)d_data, fi, nb, r.rows);
+    QZ_LAUNCH_CHECK();
+    g_ranges.erase(it);
+    return 1;
+}
+
+void cuda_dequant(uint32_t ggml_type, const uint8_t *d_data, float *d_out, int in_dim, long long n_rows)
+{
+    dequant_rows(ggml_type, d_data, d_out, in_dim, n_rows);
+}
+
+void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,
+               int out_dim)
+{
+    // first form: token by token (what the reference's GPU prefill does, src/main.rs:1410-1416)
+    for (int t = 0; t < m; t++)
+        cuda_gemv(ggml_type, d_data, d_x + (size_t)t * in_dim, d_y + (size_t)t * out_dim, in_dim, out_dim);
+}
+
+}  // extern "C"
