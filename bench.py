@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--small", action="store_true", help="profiling case: lm_head cut to 16032 rows (a few hundred MB on the device)")
+    ap.add_argument("--small", action="store_true", help="profiling case: lm_head cut to 40080 rows (134 MB, still larger than L2; ~0.3 GB on the device)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -53,7 +53,7 @@ def sweep(small=False):
     from saient_quartz_b200 import synth
     shapes = list(synth.LLAMA3_8B_GEMV_SWEEP)
     if small:
-        shapes = [(l, t, k, (16032 if n == 128256 else n)) for (l, t, k, n) in shapes]
+        shapes = [(l, t, k, (40080 if n == 128256 else n)) for (l, t, k, n) in shapes]
     return shapes
 
 
