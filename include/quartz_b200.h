@@ -95,6 +95,11 @@ void quartz_clear_error(void);
  * the reference's behaviour, src/cuda_kernels.cu launches with <<<g,b>>> only). */
 void quartz_set_stream(void *cuda_stream);
 
+/* Which streaming GEMV serves the formats that have one: 0 = TMA-staged shared-memory ring
+ * (default), 1 = register-streaming 128-bit loads.  For A/B measurements; results are
+ * bit-identical.  The environment variable QUARTZ_GEMV_IMPL=ldg selects 1 at start-up. */
+void quartz_set_gemv_impl(int impl);
+
 /* The IQ3_XXS codebook (256 x u32); the reference has no IQ3_XXS. */
 void cuda_set_iq3xxs_grid(const uint32_t *host);
 

@@ -59,6 +59,7 @@ _SIGS = {
     "quartz_error_string": (C.c_char_p, []),
     "quartz_clear_error": (None, []),
     "quartz_set_stream": (None, [C.c_void_p]),
+    "quartz_set_gemv_impl": (None, [C.c_int]),
     "cuda_set_iq3xxs_grid": (None, [C.c_void_p]),
     "cuda_repack_weights": (C.c_int, [C.c_uint32, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_unpack_weights": (C.c_int, [C.c_void_p]),

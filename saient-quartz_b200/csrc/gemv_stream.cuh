@@ -90,6 +90,18 @@ __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
     return d;
 }
 
+struct LdGlobal {
+    __device__ static uint4 v4(const uint8_t *p) { return ld_stream(p); }
+    __device__ static uint2 v2(const uint8_t *p)
+    {
+        uint2 v;
+        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+        return v;
+    }
+    __device__ static uint32_t u32(const uint8_t *p) { return ld_stream_u32(p); }
+    __device__ static uint32_t u16(const uint8_t *p) { return ld_stream_u16(p); }
+};
+
 struct GemvArgs {
     const uint8_t *W[4];
     XQ xq[4];
@@ -124,12 +136,13 @@ struct StreamQ4K {
         r.sum0 = q.xsum[4 * u] + q.xsum[4 * u + 1];
         r.sum1 = q.xsum[4 * u + 2] + q.xsum[4 * u + 3];
     }
+    template <class LD>
     __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
     {
         const uint8_t *blk = row + (size_t)(u >> 2) * 144;
-        w.hdr = ld_stream(blk);
-        w.q0 = ld_stream(blk + 16 + 32 * (u & 3));
-        w.q1 = ld_stream(blk + 32 + 32 * (u & 3));
+        w.hdr = LD::v4(blk);
+        w.q0 = LD::v4(blk + 16 + 32 * (u & 3));
+        w.q1 = LD::v4(blk + 32 + 32 * (u & 3));
     }
     __device__ static float dot(const WRegs &w, const XRegs &x, int u)
     {
@@ -184,16 +197,16 @@ struct StreamQ6K {
             r.sx[k] = 32 * (256 * shh + sl);   // the -32 offset of every 6-bit code
         }
     }
+    template <class LD>
     __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
     {
         const int b = u >> 2, n = (u >> 1) & 1, g = u & 1;
         const uint8_t *ql = row + (size_t)b * 128 + 64 * n + 16 * g;
-        w.ql0 = ld_stream(ql);
-        w.ql1 = ld_stream(ql + 32);
-        w.qh = ld_stream(row + (size_t)nb * 128 + (size_t)b * 64 + 32 * n + 16 * g);
-        const uint8_t *sc = row + (size_t)nb * 192 + (size_t)b * 16 + 8 * n;
-        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(w.sc.x), "=r"(w.sc.y) : "l"(sc));
-        w.d = ld_stream_u16(row + (size_t)nb * 208 + (size_t)b * 2);
+        w.ql0 = LD::v4(ql);
+        w.ql1 = LD::v4(ql + 32);
+        w.qh = LD::v4(row + (size_t)nb * 128 + (size_t)b * 64 + 32 * n + 16 * g);
+        w.sc = LD::v2(row + (size_t)nb * 192 + (size_t)b * 16 + 8 * n);
+        w.d = LD::u16(row + (size_t)nb * 208 + (size_t)b * 2);
     }
     __device__ static float dot(const WRegs &w, const XRegs &x, int u)
     {
@@ -247,12 +260,13 @@ struct StreamQ8_0 {
         r.s0 = q.xs[2 * u];
         r.s1 = q.xs[2 * u + 1];
     }
+    template <class LD>
     __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
     {
         const uint8_t *qs = row + (size_t)nb * 2 + (size_t)u * 64;
 #pragma unroll
-        for (int i = 0; i < 4; i++) w.q[i] = ld_stream(qs + 16 * i);
-        w.d2 = ld_stream_u32(row + (size_t)u * 4);
+        for (int i = 0; i < 4; i++) w.q[i] = LD::v4(qs + 16 * i);
+        w.d2 = LD::u32(row + (size_t)u * 4);
     }
     __device__ static float dot(const WRegs &w, const XRegs &x, int)
     {
@@ -276,8 +290,7 @@ struct StreamQ8_0 {
 template <class F, int R>
 __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
 {
-    __shared__ float part[2][16 * R];   // [parity][row-in-pass * R + i][warp of the row] flattened below
-    __shared__ float part_w[2][16 * R * 16];
+    __shared__ float part_w[2][4 * R * 16];   // [parity][(row-in-pass * R + i) * 16 + warp of the row]
 
     const int m = blockIdx.y;
     const uint8_t *__restrict__ W = a.W[m];
@@ -299,14 +312,13 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
     const int rows_per_tile = a.RP * R;
     const int ntiles = (a.N + rows_per_tile - 1) / rows_per_tile;
     int parity = 0;
-    (void)part;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, parity ^= 1) {
         const int row0 = tile * rows_per_tile + rl;
         typename F::WRegs w[R];
 #pragma unroll
         for (int i = 0; i < R; i++) {
             const int row = row0 + i * a.RP;
-            if (active && row < a.N) F::load_w(w[i], W + (size_t)row * row_bytes, nb, u);
+            if (active && row < a.N) F::template load_w<LdGlobal>(w[i], W + (size_t)row * row_bytes, nb, u);
         }
         float acc[R];
 #pragma unroll

@@ -1,0 +1,232 @@
+// TMA-staged streaming GEMV: the production batch-1 kernel.
+//
+// One persistent CTA per SM.  A producer lane walks this CTA's row tiles and moves
+// each tile (RT consecutive rows = one contiguous, 16-byte aligned byte range in
+// either weight layout) from HBM into a shared-memory ring with one bulk async copy
+// (cp.async.bulk ... mbarrier::complete_tx::bytes), as many stages ahead as the ring
+// is deep (~200 KB per SM in flight).  Memory traffic therefore never waits on
+// arithmetic, and a matrix of a few tens of MB has all of its bytes requested within
+// the first microsecond.  Sixteen consumer warps unpack from shared memory with the
+// same per-format integer dot products as gemv_stream.cuh (activation slice in
+// registers, dp4a on two int8 limbs), reduce each row with shuffles and a
+// row-group named barrier, and hand the stage back through an "empty" mbarrier.
+//
+// Every wait is bounded: a thread that polls an mbarrier for longer than ~1 s of SM
+// clocks records QZ_ERR_TIMEOUT in a device status word and leaves; a timeout on a
+// "full" barrier is seen by all consumers of the CTA at the same stage, so none is
+// left behind at a named barrier, and the producer drains its own outstanding
+// copies (bounded) before it exits.
+#pragma once
+
+#include "gemv_stream.cuh"
+
+namespace qz {
+
+constexpr int TMA_MAX_STAGES = 16;
+constexpr int TMA_CONSUMERS = 512;
+constexpr long long TMA_WAIT_CYCLES = 2000000000LL;   // ~1 s at 1.9 GHz
+
+struct TmaArgs {
+    const uint8_t *W[4];
+    XQ xq[4];
+    float *y[4];
+    int K, N;
+    int U, Upad, RP, R;      // units per row, threads per row, rows per pass, passes per stage
+    int n_mats;
+    int stage_bytes;         // RP * R * row_bytes, a multiple of 16
+    int n_stages;
+    int *status;             // device status word (0 = ok)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > TMA_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_1d(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+struct LdShared {
+    __device__ static uint4 v4(const uint8_t *p) { return *(const uint4 *)p; }
+    __device__ static uint2 v2(const uint8_t *p) { return *(const uint2 *)p; }
+    __device__ static uint32_t u32(const uint8_t *p) { return *(const uint32_t *)p; }
+    __device__ static uint32_t u16(const uint8_t *p) { return *(const uint16_t *)p; }
+};
+
+template <class F>
+__global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const TmaArgs a)
+{
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ uint64_t full_bar[TMA_MAX_STAGES], empty_bar[TMA_MAX_STAGES];
+    __shared__ float part[2][64];
+
+    const int m = blockIdx.x % a.n_mats;
+    const int cta = blockIdx.x / a.n_mats, n_cta = gridDim.x / a.n_mats;
+    const FormatInfo fi = format_info(F::TYPE);
+    const int nb = a.K / fi.block_elems;
+    const size_t row_bytes = (size_t)nb * fi.block_bytes;
+    const int rows_per_tile = a.RP * a.R;
+    const int ntiles = (a.N + rows_per_tile - 1) / rows_per_tile;
+    const int n_consumers = a.Upad * a.RP;
+    const int n_cons_warps = (n_consumers + 31) >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.n_stages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], n_cons_warps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (threadIdx.x >= TMA_CONSUMERS) {
+        // ---------------- producer ----------------
+        if (threadIdx.x != TMA_CONSUMERS) return;
+        const uint8_t *W = a.W[m];
+        int it = 0;
+        bool ok = true;
+        for (int tile = cta; tile < ntiles && ok; tile += n_cta, it++) {
+            const int s = it % a.n_stages;
+            const uint32_t round = it / a.n_stages;
+            if (round > 0) ok = mbar_wait(&empty_bar[s], (round - 1) & 1);
+            if (!ok) break;
+            const int row0 = tile * rows_per_tile;
+            const int rows = min(rows_per_tile, a.N - row0);
+            const uint32_t bytes = (uint32_t)(rows * row_bytes);
+            mbar_arrive_expect_tx(&full_bar[s], bytes);
+            tma_load_1d(ring + (size_t)s * a.stage_bytes, W + (size_t)row0 * row_bytes, bytes, &full_bar[s]);
+        }
+        if (!ok) {
+            atomicExch(a.status, QZ_ERR_TIMEOUT);
+            // drain: copies already issued must land before this CTA's shared memory goes away
+            for (int k = 0; k < a.n_stages && k < it; k++) {
+                const int j = it - 1 - k;
+                mbar_wait(&full_bar[j % a.n_stages], (j / a.n_stages) & 1);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    if ((int)threadIdx.x >= n_consumers) return;
+    const int u = threadIdx.x % a.Upad;
+    const int rl = threadIdx.x / a.Upad;
+    const bool active = u < a.U;
+    const int lane = threadIdx.x & 31;
+    const int wpr = a.Upad >> 5;
+    const int wir = wpr > 0 ? (threadIdx.x >> 5) % wpr : 0;
+    float *__restrict__ y = a.y[m];
+
+    typename F::XRegs xr;
+    if (active) F::load_x(xr, a.xq[m], u);
+
+    int it = 0;
+    for (int tile = cta; tile < ntiles; tile += n_cta, it++) {
+        const int s = it % a.n_stages;
+        const uint32_t round = it / a.n_stages;
+        if (!mbar_wait(&full_bar[s], round & 1)) {
+            atomicExch(a.status, QZ_ERR_TIMEOUT);
+            return;
+        }
+        const uint8_t *stage = ring + (size_t)s * a.stage_bytes;
+        const int row0 = tile * rows_per_tile;
+        float acc[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            acc[i] = 0.f;
+            if (i < a.R) {
+                const int rs = i * a.RP + rl;
+                if (active && row0 + rs < a.N) {
+                    typename F::WRegs w;
+                    F::template load_w<LdShared>(w, stage + (size_t)rs * row_bytes, nb, u);
+                    acc[i] = F::dot(w, xr, u);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);   // this warp no longer reads the stage
+
+        if (wpr == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (i < a.R) {
+                    float v = acc[i];
+                    for (int off = a.Upad >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+                    const int row = row0 + i * a.RP + rl;
+                    if (u == 0 && row < a.N) y[row] = v;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (i < a.R) acc[i] = warp_sum(acc[i]);
+            if (wpr == 1) {
+                if (lane == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int row = row0 + i * a.RP + rl;
+                        if (i < a.R && row < a.N) y[row] = acc[i];
+                    }
+                }
+            } else {
+                // the row's warps meet at their own named barrier; its first warp finishes the sum
+                float *p = part[it & 1] + rl * wpr * 4;
+                if (lane == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        if (i < a.R) p[i * wpr + wir] = acc[i];
+                }
+                named_bar_sync(1 + rl, wpr * 32);
+                if (wir == 0 && lane < a.R) {
+                    float v = 0.f;
+                    for (int k = 0; k < wpr; k++) v += p[lane * wpr + k];
+                    const int row = row0 + lane * a.RP + rl;
+                    if (row < a.N) y[row] = v;
+                }
+            }
+        }
+    }
+}
+
+}  // namespace qz

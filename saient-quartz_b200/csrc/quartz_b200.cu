@@ -4,6 +4,8 @@
 
 #include "../../include/quartz_b200.h"
 
+#include <stdlib.h>
+
 #include <map>
 #include <mutex>
 #include <string>
@@ -13,6 +15,7 @@
 #include "formats.cuh"
 #include "generic.cuh"
 #include "gemv_stream.cuh"
+#include "gemv_tma.cuh"
 #include "decode_ops.cuh"
 
 namespace qz {
@@ -181,6 +184,82 @@ static int stream_layout(uint32_t t)
     }
 }
 
+// ---- device status word written by kernels whose bounded waits gave up ------------------
+static int *g_status = nullptr;
+static int *status_word()
+{
+    if (!g_status) {
+        if (cudaMalloc(&g_status, sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            g_status = nullptr;
+            set_error(QZ_ERR_CUDA, "cudaMalloc of the status word failed");
+            return nullptr;
+        }
+        cudaMemset(g_status, 0, sizeof(int));
+    }
+    return g_status;
+}
+static void poll_status()
+{
+    if (!g_status) return;
+    int h = 0;
+    if (cudaMemcpy(&h, g_status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && h != 0) {
+        set_error(h, "a device-side bounded wait gave up");
+        cudaMemset(g_status, 0, sizeof(int));
+    }
+}
+
+static int g_use_tma = -1;
+static bool use_tma()
+{
+    if (g_use_tma < 0) {
+        const char *e = getenv("QUARTZ_GEMV_IMPL");   // "ldg" selects the register-streaming kernel
+        g_use_tma = (e && std::string(e) == "ldg") ? 0 : 1;
+    }
+    return g_use_tma == 1;
+}
+
+template <class F>
+static bool launch_tma(const GemvArgs &g, int n_mats)
+{
+    const FormatInfo fi = format_info(F::TYPE);
+    const size_t row_bytes = (size_t)(g.K / fi.block_elems) * fi.block_bytes;
+    TmaArgs a;
+    for (int i = 0; i < 4; i++) { a.W[i] = g.W[i]; a.xq[i] = g.xq[i]; a.y[i] = g.y[i]; }
+    a.K = g.K; a.N = g.N; a.U = g.U; a.Upad = g.Upad; a.n_mats = n_mats;
+    a.RP = g.Upad >= TMA_CONSUMERS ? 1 : TMA_CONSUMERS / g.Upad;
+    const int sms = sm_count();
+    const int ctas_per_mat = sms / n_mats > 0 ? sms / n_mats : 1;
+    // passes per stage: aim at ~24 KB stages, but keep at least ~2 tiles per CTA when N allows
+    int R = (int)(24 * 1024 / ((size_t)a.RP * row_bytes));
+    if (R > 4) R = 4;
+    if (R < 1) R = 1;
+    while (R > 1 && (g.N + a.RP * R - 1) / (a.RP * R) < 2 * ctas_per_mat) R--;
+    a.R = R;
+    a.stage_bytes = (int)((size_t)a.RP * R * row_bytes);
+    const int ring_budget = 200 * 1024;
+    if (a.stage_bytes * 2 > ring_budget) return false;
+    const int ntiles = (g.N + a.RP * R - 1) / (a.RP * R);
+    const int n_cta = ntiles < ctas_per_mat ? ntiles : ctas_per_mat;
+    int stages = ring_budget / a.stage_bytes;
+    if (stages > TMA_MAX_STAGES) stages = TMA_MAX_STAGES;
+    const int need = (ntiles + n_cta - 1) / n_cta;
+    if (stages > need) stages = need;
+    if (stages < 1) stages = 1;
+    a.n_stages = stages;
+    a.status = status_word();
+    if (!a.status) return false;
+    static bool attr_set = false;
+    if (!attr_set) {
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           ring_budget));
+        attr_set = true;
+    }
+    gemv_tma_kernel<F><<<n_cta * n_mats, TMA_CONSUMERS + 32, (size_t)stages * a.stage_bytes, g_stream>>>(a);
+    QZ_LAUNCH_CHECK();
+    return true;
+}
+
 template <class F>
 static void launch_stream_r(const GemvArgs &a, int n_mats, int T)
 {
@@ -248,6 +327,16 @@ static bool try_stream(uint32_t t, int n, const uint8_t *const *W, const float *
         a.W[i] = W[j];
         a.y[i] = y[j];
         a.xq[i] = XQ{q.xl, q.xh, q.xs, q.xsum};
+    }
+    if (use_tma()) {
+        bool done = false;
+        switch (t) {
+        case T_Q4_K: done = launch_tma<StreamQ4K>(a, n); break;
+        case T_Q6_K: done = launch_tma<StreamQ6K>(a, n); break;
+        case T_Q8_0: done = launch_tma<StreamQ8_0>(a, n); break;
+        default: break;
+        }
+        if (done) return true;
     }
     switch (t) {
     case T_Q4_K: launch_stream_r<StreamQ4K>(a, n, T); break;
@@ -440,7 +529,11 @@ void cuda_d2h(void *dst, const void *src, size_t bytes)
     }
 }
 
-void cuda_sync(void) { QZ_CUDA_CHECK(cudaDeviceSynchronize()); }
+void cuda_sync(void)
+{
+    QZ_CUDA_CHECK(cudaDeviceSynchronize());
+    poll_status();
+}
 
 void cuda_vec_add(float *dst, const float *src, int n)
 {
@@ -550,7 +643,11 @@ void cuda_embed_lookup(float *out, const uint8_t *data, uint32_t ggml_type, int 
 
 // ======================= Part 2 =======================
 
-int quartz_last_error(void) { return g_err; }
+int quartz_last_error(void)
+{
+    poll_status();
+    return g_err;
+}
 const char *quartz_error_string(void) { return g_err_msg.c_str(); }
 void quartz_clear_error(void)
 {
@@ -558,6 +655,7 @@ void quartz_clear_error(void)
     g_err_msg.clear();
 }
 void quartz_set_stream(void *s) { g_stream = (cudaStream_t)s; }
+void quartz_set_gemv_impl(int impl) { g_use_tma = impl == 1 ? 0 : 1; }
 
 int cuda_repack_weights(uint32_t ggml_type, void *d_data, int in_dim, int out_dim, int n_mats)
 {

@@ -147,6 +147,25 @@ def test_lm_head_full_size(gpu, oracle_mod):
 
 
 @pytest.mark.parametrize("t", STREAM_TYPES)
+def test_both_streaming_kernels_agree_bitwise(gpu, oracle_mod, t):
+    """The TMA-staged ring and the register-streaming kernel do the same arithmetic in the same order."""
+    from saient_quartz_b200 import synth
+    L = gpu.lib()
+    try:
+        for (K, N) in [(4096, 1030), (14336, 257), (1024, 64), (8192, 100), (28672, 33)]:
+            w = synth.make_weights(t, K, N, tensor_id=55)
+            x = synth.make_x(K, tensor_id=56)
+            L.quartz_set_gemv_impl(0)
+            y_tma = gpu.verify_gemv_cuda(x, w, t, K, N, repack=True)
+            L.quartz_set_gemv_impl(1)
+            y_ldg = gpu.verify_gemv_cuda(x, w, t, K, N, repack=True)
+            assert np.array_equal(y_tma, y_ldg), (t, K, N)
+            _check_gemv(oracle_mod, y_tma, x, w, t, K, N)
+    finally:
+        L.quartz_set_gemv_impl(0)
+
+
+@pytest.mark.parametrize("t", STREAM_TYPES)
 def test_gemv_linearity_and_zero(gpu, t):
     """Size-independent properties: W*0 = 0 exactly; W*(2x) = 2*(W*x) exactly (power-of-two scaling
     commutes with the block-fixed-point activation format and with every f32 rounding)."""
