@@ -113,38 +113,66 @@ struct GemvArgs {
 };
 
 // ---- per-format policies ------------------------------------------------------
-// Each policy owns: the thread's activation slice (XRegs), one row's bytes for the
-// slice (WRegs), the loads, and the integer dot product.
+// Each policy owns: the thread's activation slice (XRegs), the thread's byte offsets
+// inside a row (Off: they depend on the unit only, never on the row), one row's bytes
+// for the slice (WRegs), the loads, and the integer dot product.
+
+__device__ __forceinline__ void load_x64(uint32_t *xl, uint32_t *xh, const XQ &q, int at)
+{
+    const uint4 *pl = (const uint4 *)(q.xl + at), *ph = (const uint4 *)(q.xh + at);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint4 a = pl[i], b = ph[i];
+        xl[4 * i] = a.x; xl[4 * i + 1] = a.y; xl[4 * i + 2] = a.z; xl[4 * i + 3] = a.w;
+        xh[4 * i] = b.x; xh[4 * i + 1] = b.y; xh[4 * i + 2] = b.z; xh[4 * i + 3] = b.w;
+    }
+}
+
+// byte b of v, sign-extended to 32 bits, by one PRMT (selector nibble b|8 replicates the sign)
+__device__ __forceinline__ uint32_t sext_selector(int b) { return (uint32_t)(b | ((b | 8) << 4) | ((b | 8) << 8) | ((b | 8) << 12)); }
+__device__ __forceinline__ int sext_byte(uint32_t v, uint32_t selector)
+{
+    int d;   // the __byte_perm intrinsic ignores the sign-replication bit of the selector; raw PRMT honours it
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v), "r"(0u), "r"(selector));
+    return d;
+}
 
 struct StreamQ4K {
     static constexpr uint32_t TYPE = T_Q4_K;
     static constexpr bool PLANES = false;
     struct XRegs { uint32_t xl[16], xh[16]; float s0, s1, sum0, sum1; };
+    struct Off { int hdr, qs; int hi_pair; uint32_t sel_sc, sel_m; };
     struct WRegs { uint4 hdr, q0, q1; };
 
     __device__ static void load_x(XRegs &r, const XQ &q, int u)
     {
-        const uint4 *pl = (const uint4 *)(q.xl + 64 * u), *ph = (const uint4 *)(q.xh + 64 * u);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint4 a = pl[i], b = ph[i];
-            r.xl[4 * i] = a.x; r.xl[4 * i + 1] = a.y; r.xl[4 * i + 2] = a.z; r.xl[4 * i + 3] = a.w;
-            r.xh[4 * i] = b.x; r.xh[4 * i + 1] = b.y; r.xh[4 * i + 2] = b.z; r.xh[4 * i + 3] = b.w;
-        }
+        load_x64(r.xl, r.xh, q, 64 * u);
         r.s0 = q.xs[2 * u];
         r.s1 = q.xs[2 * u + 1] * 0.0625f;   // high nibbles are used unshifted (x16)
         r.sum0 = q.xsum[4 * u] + q.xsum[4 * u + 1];
         r.sum1 = q.xsum[4 * u + 2] + q.xsum[4 * u + 3];
     }
-    template <class LD>
-    __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
+    __device__ static Off make_off(int nb, int u)
     {
-        const uint8_t *blk = row + (size_t)(u >> 2) * 144;
-        w.hdr = LD::v4(blk);
-        w.q0 = LD::v4(blk + 16 + 32 * (u & 3));
-        w.q1 = LD::v4(blk + 32 + 32 * (u & 3));
+        Off o;
+        const int p = u & 3;
+        o.hdr = (u >> 2) * 144;
+        o.qs = o.hdr + 16 + 32 * p;
+        o.hi_pair = p >> 1;   // sub-blocks 4..7 take their 6-bit codes from the packed upper part
+        // bytes (2p & 3) and (2p & 3) + 1 of the 4-byte code word, zero-extended into bytes 0 and 2
+        const int b = 2 * (p & 1);
+        o.sel_sc = (uint32_t)(b | (4 << 4) | ((b + 1) << 8) | (4 << 12));
+        o.sel_m = o.sel_sc;
+        return o;
     }
-    __device__ static float dot(const WRegs &w, const XRegs &x, int u)
+    template <class LD>
+    __device__ static void load_w(WRegs &w, const uint8_t *row, const Off &o)
+    {
+        w.hdr = LD::v4(row + o.hdr);
+        w.q0 = LD::v4(row + o.qs);
+        w.q1 = LD::v4(row + o.qs + 16);
+    }
+    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &o)
     {
         const uint32_t q[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
         int a0h = 0, a0l = 0, a1h = 0, a1l = 0;
@@ -157,16 +185,15 @@ struct StreamQ4K {
             a1l = dp4a_us(hi, x.xl[8 + i], a1l);
         }
         // 6-bit scale / min codes of sub-blocks 2p and 2p+1 (src/dequant.rs:1471-1480)
-        const int p = u & 3;
         const uint32_t s0 = w.hdr.y, s1 = w.hdr.z, s2 = w.hdr.w;
-        uint32_t scw = (p < 2) ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
-        uint32_t mw = (p < 2) ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
-        const int sh = 16 * (p & 1);
-        float sc0 = (float)((scw >> sh) & 0xFF), sc1 = (float)((scw >> (sh + 8)) & 0xFF);
-        float m0 = (float)((mw >> sh) & 0xFF), m1 = (float)((mw >> (sh + 8)) & 0xFF);
-        float2 dm = __half22float2(*(const __half2 *)&w.hdr.x);
-        float t0 = (float)(a0h * 256 + a0l) * x.s0;
-        float t1 = (float)(a1h * 256 + a1l) * x.s1;
+        const uint32_t scw = o.hi_pair ? ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u)) : (s0 & 0x3F3F3F3Fu);
+        const uint32_t mw = o.hi_pair ? (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u)) : (s1 & 0x3F3F3F3Fu);
+        const uint32_t sc2 = __byte_perm(scw, 0, o.sel_sc), m2 = __byte_perm(mw, 0, o.sel_m);   // two codes in 16-bit lanes
+        const float sc0 = (float)(sc2 & 0xFFFF), sc1 = (float)(sc2 >> 16);
+        const float m0 = (float)(m2 & 0xFFFF), m1 = (float)(m2 >> 16);
+        const float2 dm = __half22float2(*(const __half2 *)&w.hdr.x);
+        const float t0 = (float)(a0h * 256 + a0l) * x.s0;
+        const float t1 = (float)(a1h * 256 + a1l) * x.s1;
         return dm.x * (sc0 * t0 + sc1 * t1) - dm.y * (m0 * x.sum0 + m1 * x.sum1);
     }
 };
@@ -176,7 +203,8 @@ struct StreamQ6K {
     static constexpr bool PLANES = true;
     // unit u -> block u/4, half n = (u>>1)&1, 16-lane group g = u&1; run k holds the
     // weights 128n + 32k + 16g + [0,16) of the block
-    struct XRegs { uint32_t xl[16], xh[16]; float s[4]; int sx[4]; };
+    struct XRegs { uint32_t xl[16], xh[16]; float s[4]; int nsx[4]; };
+    struct Off { int ql, qh, sc, d; uint32_t sel0, sel1; };
     struct WRegs { uint4 ql0, ql1, qh; uint2 sc; uint32_t d; };
 
     __device__ static void load_x(XRegs &r, const XQ &q, int u)
@@ -194,26 +222,37 @@ struct StreamQ6K {
                 sl = dp4a_ss(0x01010101u, r.xl[4 * k + i], sl);
                 shh = dp4a_ss(0x01010101u, r.xh[4 * k + i], shh);
             }
-            r.sx[k] = 32 * (256 * shh + sl);   // the -32 offset of every 6-bit code
+            r.nsx[k] = -32 * (256 * shh + sl);   // the -32 offset of every 6-bit code, pre-summed
         }
     }
-    template <class LD>
-    __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
+    __device__ static Off make_off(int nb, int u)
     {
         const int b = u >> 2, n = (u >> 1) & 1, g = u & 1;
-        const uint8_t *ql = row + (size_t)b * 128 + 64 * n + 16 * g;
-        w.ql0 = LD::v4(ql);
-        w.ql1 = LD::v4(ql + 32);
-        w.qh = LD::v4(row + (size_t)nb * 128 + (size_t)b * 64 + 32 * n + 16 * g);
-        w.sc = LD::v2(row + (size_t)nb * 192 + (size_t)b * 16 + 8 * n);
-        w.d = LD::u16(row + (size_t)nb * 208 + (size_t)b * 2);
+        Off o;
+        o.ql = b * 128 + 64 * n + 16 * g;
+        o.qh = nb * 128 + b * 64 + 32 * n + 16 * g;
+        o.sc = nb * 192 + b * 16 + 8 * n;
+        o.d = nb * 208 + b * 2;
+        o.sel0 = sext_selector(g);       // scale bytes g and g+2 of each 4-byte word
+        o.sel1 = sext_selector(g + 2);
+        return o;
     }
-    __device__ static float dot(const WRegs &w, const XRegs &x, int u)
+    template <class LD>
+    __device__ static void load_w(WRegs &w, const uint8_t *row, const Off &o)
+    {
+        w.ql0 = LD::v4(row + o.ql);
+        w.ql1 = LD::v4(row + o.ql + 32);
+        w.qh = LD::v4(row + o.qh);
+        w.sc = LD::v2(row + o.sc);
+        w.d = LD::u16(row + o.d);
+    }
+    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &o)
     {
         const uint32_t a0[4] = {w.ql0.x, w.ql0.y, w.ql0.z, w.ql0.w};
         const uint32_t a1[4] = {w.ql1.x, w.ql1.y, w.ql1.z, w.ql1.w};
         const uint32_t hh[4] = {w.qh.x, w.qh.y, w.qh.z, w.qh.w};
-        int dh[4] = {0, 0, 0, 0}, dl[4] = {0, 0, 0, 0};
+        int dh[4] = {0, 0, 0, 0};
+        int dl[4] = {x.nsx[0], x.nsx[1], x.nsx[2], x.nsx[3]};
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const uint32_t h = hh[i];
@@ -227,16 +266,11 @@ struct StreamQ6K {
             dh[3] = dp4a_us(q3, x.xh[12 + i], dh[3]);  dl[3] = dp4a_us(q3, x.xl[12 + i], dl[3]);
         }
         // scale bytes g, g+2, g+4, g+6 of the half's eight int8 scales
-        const int g = u & 1;
-        const int sh0 = 8 * g, sh1 = 8 * g + 16;
-        int sc[4];
-        sc[0] = (int)(int8_t)(w.sc.x >> sh0);
-        sc[1] = (int)(int8_t)(w.sc.x >> sh1);
-        sc[2] = (int)(int8_t)(w.sc.y >> sh0);
-        sc[3] = (int)(int8_t)(w.sc.y >> sh1);
+        const int sc[4] = {sext_byte(w.sc.x, o.sel0), sext_byte(w.sc.x, o.sel1), sext_byte(w.sc.y, o.sel0),
+                           sext_byte(w.sc.y, o.sel1)};
         float acc = 0.f;
 #pragma unroll
-        for (int k = 0; k < 4; k++) acc = fmaf((float)(sc[k] * (256 * dh[k] + dl[k] - x.sx[k])), x.s[k], acc);
+        for (int k = 0; k < 4; k++) acc = fmaf((float)(sc[k] * (256 * dh[k] + dl[k])), x.s[k], acc);
         return acc * h2f((uint16_t)w.d);
     }
 };
@@ -246,29 +280,24 @@ struct StreamQ8_0 {
     static constexpr bool PLANES = true;
     // unit u -> blocks 2u and 2u+1
     struct XRegs { uint32_t xl[16], xh[16]; float s0, s1; };
+    struct Off { int qs, d; };
     struct WRegs { uint4 q[4]; uint32_t d2; };
 
     __device__ static void load_x(XRegs &r, const XQ &q, int u)
     {
-        const uint4 *pl = (const uint4 *)(q.xl + 64 * u), *ph = (const uint4 *)(q.xh + 64 * u);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint4 a = pl[i], b = ph[i];
-            r.xl[4 * i] = a.x; r.xl[4 * i + 1] = a.y; r.xl[4 * i + 2] = a.z; r.xl[4 * i + 3] = a.w;
-            r.xh[4 * i] = b.x; r.xh[4 * i + 1] = b.y; r.xh[4 * i + 2] = b.z; r.xh[4 * i + 3] = b.w;
-        }
+        load_x64(r.xl, r.xh, q, 64 * u);
         r.s0 = q.xs[2 * u];
         r.s1 = q.xs[2 * u + 1];
     }
+    __device__ static Off make_off(int nb, int u) { return Off{nb * 2 + u * 64, u * 4}; }
     template <class LD>
-    __device__ static void load_w(WRegs &w, const uint8_t *row, int nb, int u)
+    __device__ static void load_w(WRegs &w, const uint8_t *row, const Off &o)
     {
-        const uint8_t *qs = row + (size_t)nb * 2 + (size_t)u * 64;
 #pragma unroll
-        for (int i = 0; i < 4; i++) w.q[i] = LD::v4(qs + 16 * i);
-        w.d2 = LD::u32(row + (size_t)u * 4);
+        for (int i = 0; i < 4; i++) w.q[i] = LD::v4(row + o.qs + 16 * i);
+        w.d2 = LD::u32(row + o.d);
     }
-    __device__ static float dot(const WRegs &w, const XRegs &x, int)
+    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &)
     {
         int h0 = 0, l0 = 0, h1 = 0, l1 = 0;
 #pragma unroll
@@ -285,6 +314,22 @@ struct StreamQ8_0 {
         return d.x * ((float)(256 * h0 + l0) * x.s0) + d.y * ((float)(256 * h1 + l1) * x.s1);
     }
 };
+
+// Sum four per-lane values over the warp with 6 shuffles: afterwards every lane holds
+// the warp total of value number (lane >> 3) (all 8 lanes of an octet hold the same).
+__device__ __forceinline__ float warp_sum4(float a0, float a1, float a2, float a3, int lane)
+{
+    const bool up16 = lane & 16, up8 = lane & 8;
+    float k0 = up16 ? a2 : a0, k1 = up16 ? a3 : a1;
+    k0 += __shfl_xor_sync(0xFFFFFFFFu, up16 ? a0 : a2, 16);
+    k1 += __shfl_xor_sync(0xFFFFFFFFu, up16 ? a1 : a3, 16);
+    float k = up8 ? k1 : k0;
+    k += __shfl_xor_sync(0xFFFFFFFFu, up8 ? k0 : k1, 8);
+    k += __shfl_xor_sync(0xFFFFFFFFu, k, 4);
+    k += __shfl_xor_sync(0xFFFFFFFFu, k, 2);
+    k += __shfl_xor_sync(0xFFFFFFFFu, k, 1);
+    return k;
+}
 
 // ---- the kernel ---------------------------------------------------------------
 template <class F, int R>
@@ -308,6 +353,7 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
 
     typename F::XRegs xr;
     if (active) F::load_x(xr, a.xq[m], u);
+    const typename F::Off off = F::make_off(nb, u);
 
     const int rows_per_tile = a.RP * R;
     const int ntiles = (a.N + rows_per_tile - 1) / rows_per_tile;
@@ -318,13 +364,13 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
 #pragma unroll
         for (int i = 0; i < R; i++) {
             const int row = row0 + i * a.RP;
-            if (active && row < a.N) F::template load_w<LdGlobal>(w[i], W + (size_t)row * row_bytes, nb, u);
+            if (active && row < a.N) F::template load_w<LdGlobal>(w[i], W + (size_t)row * row_bytes, off);
         }
         float acc[R];
 #pragma unroll
         for (int i = 0; i < R; i++) {
             const int row = row0 + i * a.RP;
-            acc[i] = (active && row < a.N) ? F::dot(w[i], xr, u) : 0.f;
+            acc[i] = (active && row < a.N) ? F::dot(w[i], xr, off) : 0.f;
         }
         if (wpr == 0) {
             // several rows per warp: butterfly inside the row's Upad lanes

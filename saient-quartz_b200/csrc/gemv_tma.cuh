@@ -31,9 +31,9 @@ struct TmaArgs {
     XQ xq[4];
     float *y[4];
     int K, N;
-    int U, Upad, RP, R;      // units per row, threads per row, rows per pass, passes per stage
+    int U, Upad, RP;         // units per row, threads per row, rows per stage
     int n_mats;
-    int stage_bytes;         // RP * R * row_bytes, a multiple of 16
+    int stage_bytes;         // RP * row_bytes, a multiple of 16
     int n_stages;
     int *status;             // device status word (0 = ok)
 };
@@ -93,7 +93,10 @@ struct LdShared {
     __device__ static uint32_t u16(const uint8_t *p) { return *(const uint16_t *)p; }
 };
 
-template <class F>
+// MODE 0: fewer than 32 threads per row (K < 2048); 1: one warp per row; 2: several warps per row.
+// A stage holds RP consecutive rows (one per thread-row); partial sums are carried over
+// GROUP = 4 stages and reduced together (6 shuffles for 4 rows instead of 20).
+template <class F, int MODE>
 __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const TmaArgs a)
 {
     extern __shared__ __align__(128) uint8_t ring[];
@@ -104,16 +107,14 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     const int cta = blockIdx.x / a.n_mats, n_cta = gridDim.x / a.n_mats;
     const FormatInfo fi = format_info(F::TYPE);
     const int nb = a.K / fi.block_elems;
-    const size_t row_bytes = (size_t)nb * fi.block_bytes;
-    const int rows_per_tile = a.RP * a.R;
-    const int ntiles = (a.N + rows_per_tile - 1) / rows_per_tile;
+    const int row_bytes = nb * fi.block_bytes;
+    const int ntiles = (a.N + a.RP - 1) / a.RP;
     const int n_consumers = a.Upad * a.RP;
-    const int n_cons_warps = (n_consumers + 31) >> 5;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.n_stages; s++) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], n_cons_warps);
+            mbar_init(&empty_bar[s], (n_consumers + 31) >> 5);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -124,18 +125,18 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
         // ---------------- producer ----------------
         if (threadIdx.x != TMA_CONSUMERS) return;
         const uint8_t *W = a.W[m];
-        int it = 0;
+        int it = 0, s = 0;
+        uint32_t round = 0;
         bool ok = true;
-        for (int tile = cta; tile < ntiles && ok; tile += n_cta, it++) {
-            const int s = it % a.n_stages;
-            const uint32_t round = it / a.n_stages;
+        for (int tile = cta; tile < ntiles; tile += n_cta, it++) {
             if (round > 0) ok = mbar_wait(&empty_bar[s], (round - 1) & 1);
             if (!ok) break;
-            const int row0 = tile * rows_per_tile;
-            const int rows = min(rows_per_tile, a.N - row0);
-            const uint32_t bytes = (uint32_t)(rows * row_bytes);
+            const int row0 = tile * a.RP;
+            const int rows = min(a.RP, a.N - row0);
+            const uint32_t bytes = (uint32_t)rows * (uint32_t)row_bytes;
             mbar_arrive_expect_tx(&full_bar[s], bytes);
             tma_load_1d(ring + (size_t)s * a.stage_bytes, W + (size_t)row0 * row_bytes, bytes, &full_bar[s]);
+            if (++s == a.n_stages) { s = 0; round++; }
         }
         if (!ok) {
             atomicExch(a.status, QZ_ERR_TIMEOUT);
@@ -155,74 +156,66 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     const bool active = u < a.U;
     const int lane = threadIdx.x & 31;
     const int wpr = a.Upad >> 5;
-    const int wir = wpr > 0 ? (threadIdx.x >> 5) % wpr : 0;
+    const int wir = MODE == 2 ? (threadIdx.x >> 5) % wpr : 0;
     float *__restrict__ y = a.y[m];
 
     typename F::XRegs xr;
     if (active) F::load_x(xr, a.xq[m], u);
+    const typename F::Off off = F::make_off(nb, u);
+    const int my_row_off = rl * row_bytes;
 
-    int it = 0;
-    for (int tile = cta; tile < ntiles; tile += n_cta, it++) {
-        const int s = it % a.n_stages;
-        const uint32_t round = it / a.n_stages;
-        if (!mbar_wait(&full_bar[s], round & 1)) {
-            atomicExch(a.status, QZ_ERR_TIMEOUT);
-            return;
-        }
-        const uint8_t *stage = ring + (size_t)s * a.stage_bytes;
-        const int row0 = tile * rows_per_tile;
+    int s = 0;
+    uint32_t parity = 0;
+    int grp = 0;
+    for (int tile0 = cta; tile0 < ntiles; tile0 += 4 * n_cta, grp++) {
         float acc[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            acc[i] = 0.f;
-            if (i < a.R) {
-                const int rs = i * a.RP + rl;
-                if (active && row0 + rs < a.N) {
-                    typename F::WRegs w;
-                    F::template load_w<LdShared>(w, stage + (size_t)rs * row_bytes, nb, u);
-                    acc[i] = F::dot(w, xr, u);
+        for (int j = 0; j < 4; j++) {
+            acc[j] = 0.f;
+            const int tile = tile0 + j * n_cta;
+            if (tile < ntiles) {
+                if (!mbar_wait(&full_bar[s], parity)) {
+                    atomicExch(a.status, QZ_ERR_TIMEOUT);
+                    return;
                 }
+                if (active && tile * a.RP + rl < a.N) {
+                    typename F::WRegs w;
+                    F::template load_w<LdShared>(w, ring + (size_t)s * a.stage_bytes + my_row_off, off);
+                    acc[j] = F::dot(w, xr, off);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[s]);   // this warp no longer reads the stage
+                if (++s == a.n_stages) { s = 0; parity ^= 1; }
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);   // this warp no longer reads the stage
-
-        if (wpr == 0) {
+        // ---- reduce the group's (up to) four rows ----
+        if (MODE == 0) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                if (i < a.R) {
-                    float v = acc[i];
-                    for (int off = a.Upad >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
-                    const int row = row0 + i * a.RP + rl;
-                    if (u == 0 && row < a.N) y[row] = v;
-                }
+            for (int j = 0; j < 4; j++) {
+                float v = acc[j];
+                for (int o = a.Upad >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+                const int tile = tile0 + j * n_cta;
+                const int row = tile * a.RP + rl;
+                if (u == 0 && tile < ntiles && row < a.N) y[row] = v;
             }
         } else {
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                if (i < a.R) acc[i] = warp_sum(acc[i]);
-            if (wpr == 1) {
-                if (lane == 0) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int row = row0 + i * a.RP + rl;
-                        if (i < a.R && row < a.N) y[row] = acc[i];
-                    }
-                }
+            const float v = warp_sum4(acc[0], acc[1], acc[2], acc[3], lane);
+            const int j = lane >> 3;   // which of the four rows this lane's total belongs to
+            if (MODE == 1) {
+                const int tile = tile0 + j * n_cta;
+                const int row = tile * a.RP + rl;
+                if ((lane & 7) == 0 && tile < ntiles && row < a.N) y[row] = v;
             } else {
-                // the row's warps meet at their own named barrier; its first warp finishes the sum
-                float *p = part[it & 1] + rl * wpr * 4;
-                if (lane == 0) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++)
-                        if (i < a.R) p[i * wpr + wir] = acc[i];
-                }
+                // the row's warps meet at their own named barrier; its first warp finishes the sums
+                float *p = part[grp & 1] + rl * wpr * 4;
+                if ((lane & 7) == 0) p[j * wpr + wir] = v;
                 named_bar_sync(1 + rl, wpr * 32);
-                if (wir == 0 && lane < a.R) {
-                    float v = 0.f;
-                    for (int k = 0; k < wpr; k++) v += p[lane * wpr + k];
-                    const int row = row0 + lane * a.RP + rl;
-                    if (row < a.N) y[row] = v;
+                if (wir == 0 && lane < 4) {
+                    float t = 0.f;
+                    for (int k = 0; k < wpr; k++) t += p[lane * wpr + k];
+                    const int tile = tile0 + lane * n_cta;
+                    const int row = tile * a.RP + rl;
+                    if (tile < ntiles && row < a.N) y[row] = t;
                 }
             }
         }

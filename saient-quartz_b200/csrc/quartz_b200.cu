@@ -230,16 +230,10 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     a.RP = g.Upad >= TMA_CONSUMERS ? 1 : TMA_CONSUMERS / g.Upad;
     const int sms = sm_count();
     const int ctas_per_mat = sms / n_mats > 0 ? sms / n_mats : 1;
-    // passes per stage: aim at ~24 KB stages, but keep at least ~2 tiles per CTA when N allows
-    int R = (int)(24 * 1024 / ((size_t)a.RP * row_bytes));
-    if (R > 4) R = 4;
-    if (R < 1) R = 1;
-    while (R > 1 && (g.N + a.RP * R - 1) / (a.RP * R) < 2 * ctas_per_mat) R--;
-    a.R = R;
-    a.stage_bytes = (int)((size_t)a.RP * R * row_bytes);
+    a.stage_bytes = (int)((size_t)a.RP * row_bytes);
     const int ring_budget = 200 * 1024;
     if (a.stage_bytes * 2 > ring_budget) return false;
-    const int ntiles = (g.N + a.RP * R - 1) / (a.RP * R);
+    const int ntiles = (g.N + a.RP - 1) / a.RP;
     const int n_cta = ntiles < ctas_per_mat ? ntiles : ctas_per_mat;
     int stages = ring_budget / a.stage_bytes;
     if (stages > TMA_MAX_STAGES) stages = TMA_MAX_STAGES;
@@ -251,11 +245,16 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     if (!a.status) return false;
     static bool attr_set = false;
     if (!attr_set) {
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           ring_budget));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget));
         attr_set = true;
     }
-    gemv_tma_kernel<F><<<n_cta * n_mats, TMA_CONSUMERS + 32, (size_t)stages * a.stage_bytes, g_stream>>>(a);
+    const dim3 grid(n_cta * n_mats), block(TMA_CONSUMERS + 32);
+    const size_t smem = (size_t)stages * a.stage_bytes;
+    if (g.Upad < 32) gemv_tma_kernel<F, 0><<<grid, block, smem, g_stream>>>(a);
+    else if (g.Upad == 32) gemv_tma_kernel<F, 1><<<grid, block, smem, g_stream>>>(a);
+    else gemv_tma_kernel<F, 2><<<grid, block, smem, g_stream>>>(a);
     QZ_LAUNCH_CHECK();
     return true;
 }

@@ -147,8 +147,9 @@ def test_lm_head_full_size(gpu, oracle_mod):
 
 
 @pytest.mark.parametrize("t", STREAM_TYPES)
-def test_both_streaming_kernels_agree_bitwise(gpu, oracle_mod, t):
-    """The TMA-staged ring and the register-streaming kernel do the same arithmetic in the same order."""
+def test_both_streaming_kernels_agree(gpu, oracle_mod, t):
+    """The TMA-staged ring and the register-streaming kernel share the per-unit integer arithmetic;
+    only the order of the final f32 row sums differs."""
     from saient_quartz_b200 import synth
     L = gpu.lib()
     try:
@@ -159,8 +160,10 @@ def test_both_streaming_kernels_agree_bitwise(gpu, oracle_mod, t):
             y_tma = gpu.verify_gemv_cuda(x, w, t, K, N, repack=True)
             L.quartz_set_gemv_impl(1)
             y_ldg = gpu.verify_gemv_cuda(x, w, t, K, N, repack=True)
-            assert np.array_equal(y_tma, y_ldg), (t, K, N)
             _check_gemv(oracle_mod, y_tma, x, w, t, K, N)
+            _check_gemv(oracle_mod, y_ldg, x, w, t, K, N)
+            tol = oracle_mod.tolerance(w, t, K, N, x)
+            assert np.all(np.abs(y_tma - y_ldg) <= 1e-2 * tol), (t, K, N)
     finally:
         L.quartz_set_gemv_impl(0)
 
