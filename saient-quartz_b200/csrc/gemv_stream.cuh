@@ -165,8 +165,8 @@ struct StreamQ4K {
         o.sel_m = o.sel_sc;
         return o;
     }
-    template <class LD>
-    __device__ static void load_w(WRegs &w, const uint8_t *row, const Off &o)
+    template <class LD, class P>
+    __device__ static void load_w(WRegs &w, P row, const Off &o)
     {
         w.hdr = LD::v4(row + o.hdr);
         w.q0 = LD::v4(row + o.qs);
@@ -237,8 +237,8 @@ struct StreamQ6K {
         o.sel1 = sext_selector(g + 2);
         return o;
     }
-    template <class LD>
-    __device__ static void load_w(WRegs &w, const uint8_t *row, const Off &o)
+    template <class LD, class P>
+    __device__ static void load_w(WRegs &w, P row, const Off &o)
     {
         w.ql0 = LD::v4(row + o.ql);
         w.ql1 = LD::v4(row + o.ql + 32);
@@ -290,8 +290,8 @@ struct StreamQ8_0 {
         r.s1 = q.xs[2 * u + 1];
     }
     __device__ static Off make_off(int nb, int u) { return Off{nb * 2 + u * 64, u * 4}; }
-    template <class LD>
-    __device__ static void load_w(WRegs &w, const uint8_t *row, const Off &o)
+    template <class LD, class P>
+    __device__ static void load_w(WRegs &w, P row, const Off &o)
     {
 #pragma unroll
         for (int i = 0; i < 4; i++) w.q[i] = LD::v4(row + o.qs + 16 * i);

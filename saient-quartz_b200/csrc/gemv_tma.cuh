@@ -86,12 +86,61 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads)
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-struct LdShared {
-    __device__ static uint4 v4(const uint8_t *p) { return *(const uint4 *)p; }
-    __device__ static uint2 v2(const uint8_t *p) { return *(const uint2 *)p; }
-    __device__ static uint32_t u32(const uint8_t *p) { return *(const uint32_t *)p; }
-    __device__ static uint32_t u16(const uint8_t *p) { return *(const uint16_t *)p; }
+// loads through 32-bit shared-window addresses (no generic-address arithmetic in the hot loop)
+struct LdSharedAddr {
+    __device__ static uint4 v4(uint32_t a)
+    {
+        uint4 v;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+        return v;
+    }
+    __device__ static uint2 v2(uint32_t a)
+    {
+        uint2 v;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+        return v;
+    }
+    __device__ static uint32_t u32(uint32_t a)
+    {
+        uint32_t v;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+        return v;
+    }
+    __device__ static uint32_t u16(uint32_t a)
+    {
+        uint16_t v;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+        return v;
+    }
 };
+
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity)
+{
+    const long long t0 = clock64();
+    while (!mbar_try_wait_addr(bar, parity)) {
+        if (clock64() - t0 > TMA_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try_wait_addr(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity);
+}
+__device__ __forceinline__ void mbar_arrive_addr(uint32_t bar)
+{
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
 
 // MODE 0: fewer than 32 threads per row (K < 2048); 1: one warp per row; 2: several warps per row.
 // A stage holds RP consecutive rows (one per thread-row); partial sums are carried over
@@ -159,63 +208,67 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     const int wir = MODE == 2 ? (threadIdx.x >> 5) % wpr : 0;
     float *__restrict__ y = a.y[m];
 
+    // Padding lanes (u >= U) run on unit 0's bytes and are masked out of the sums; rows past
+    // N in the last tile are computed from stale shared memory and simply never stored.
     typename F::XRegs xr;
-    if (active) F::load_x(xr, a.xq[m], u);
-    const typename F::Off off = F::make_off(nb, u);
-    const int my_row_off = rl * row_bytes;
+    F::load_x(xr, a.xq[m], active ? u : 0);
+    const typename F::Off off = F::make_off(nb, active ? u : 0);
 
+    const int my_tiles = (ntiles - cta + n_cta - 1) / n_cta;
+    const int n_stages = a.n_stages;
+    const uint32_t stage_bytes = (uint32_t)a.stage_bytes;
+    const uint32_t row_base = smem_u32(ring) + (uint32_t)(rl * row_bytes);   // my row inside stage 0
+    const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+    uint32_t sp = row_base, bar_off = 0, parity = 0;
     int s = 0;
-    uint32_t parity = 0;
-    int grp = 0;
-    for (int tile0 = cta; tile0 < ntiles; tile0 += 4 * n_cta, grp++) {
+    for (int t0 = 0; t0 < my_tiles; t0 += 4) {
         float acc[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             acc[j] = 0.f;
-            const int tile = tile0 + j * n_cta;
-            if (tile < ntiles) {
-                if (!mbar_wait(&full_bar[s], parity)) {
+            if (t0 + j < my_tiles) {
+                if (!mbar_wait_addr(full0 + bar_off, parity)) {
                     atomicExch(a.status, QZ_ERR_TIMEOUT);
                     return;
                 }
-                if (active && tile * a.RP + rl < a.N) {
-                    typename F::WRegs w;
-                    F::template load_w<LdShared>(w, ring + (size_t)s * a.stage_bytes + my_row_off, off);
-                    acc[j] = F::dot(w, xr, off);
-                }
+                typename F::WRegs w;
+                F::template load_w<LdSharedAddr>(w, sp, off);
+                acc[j] = F::dot(w, xr, off);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&empty_bar[s]);   // this warp no longer reads the stage
-                if (++s == a.n_stages) { s = 0; parity ^= 1; }
+                if (lane == 0) mbar_arrive_addr(empty0 + bar_off);   // this warp no longer reads the stage
+                sp += stage_bytes;
+                bar_off += 8;
+                if (++s == n_stages) { s = 0; sp = row_base; bar_off = 0; parity ^= 1; }
             }
         }
         // ---- reduce the group's (up to) four rows ----
+        // row of group member j: tile (cta + (t0 + j) * n_cta), thread-row rl
+        const int row_j0 = (cta + t0 * n_cta) * a.RP + rl, row_step = n_cta * a.RP;
         if (MODE == 0) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                float v = acc[j];
+                float v = active ? acc[j] : 0.f;
                 for (int o = a.Upad >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-                const int tile = tile0 + j * n_cta;
-                const int row = tile * a.RP + rl;
-                if (u == 0 && tile < ntiles && row < a.N) y[row] = v;
+                const int row = row_j0 + j * row_step;
+                if (u == 0 && t0 + j < my_tiles && row < a.N) y[row] = v;
             }
         } else {
-            const float v = warp_sum4(acc[0], acc[1], acc[2], acc[3], lane);
+            const float v = warp_sum4(active ? acc[0] : 0.f, active ? acc[1] : 0.f, active ? acc[2] : 0.f,
+                                      active ? acc[3] : 0.f, lane);
             const int j = lane >> 3;   // which of the four rows this lane's total belongs to
             if (MODE == 1) {
-                const int tile = tile0 + j * n_cta;
-                const int row = tile * a.RP + rl;
-                if ((lane & 7) == 0 && tile < ntiles && row < a.N) y[row] = v;
+                const int row = row_j0 + j * row_step;
+                if ((lane & 7) == 0 && t0 + j < my_tiles && row < a.N) y[row] = v;
             } else {
                 // the row's warps meet at their own named barrier; its first warp finishes the sums
-                float *p = part[grp & 1] + rl * wpr * 4;
+                float *p = part[(t0 >> 2) & 1] + rl * wpr * 4;
                 if ((lane & 7) == 0) p[j * wpr + wir] = v;
                 named_bar_sync(1 + rl, wpr * 32);
                 if (wir == 0 && lane < 4) {
                     float t = 0.f;
                     for (int k = 0; k < wpr; k++) t += p[lane * wpr + k];
-                    const int tile = tile0 + lane * n_cta;
-                    const int row = tile * a.RP + rl;
-                    if (tile < ntiles && row < a.N) y[row] = t;
+                    const int row = row_j0 + lane * row_step;
+                    if (t0 + lane < my_tiles && row < a.N) y[row] = t;
                 }
             }
         }
