@@ -119,6 +119,21 @@ int cuda_unpack_weights(void *d_data);
  * CPU dequant() (src/dequant.rs:1239-1258), from either layout. */
 void cuda_dequant(uint32_t ggml_type, const uint8_t *d_data, float *d_out, int in_dim, long long n_rows);
 
+/* No counterpart in the reference.  cuda_gemv for callers that must not allocate device memory
+ * when they call it -- code running inside a stream capture, hosts with a fixed memory plan, or
+ * processes whose allocator owns the whole device.  Same arguments, same results as cuda_gemv,
+ * but the converted-activation scratch is a 78,080-byte array built into the library (resident
+ * on every GPU that loads it) instead of a buffer obtained with cudaMalloc at first use; the
+ * call makes no cudaMalloc/cudaFree and uses no allocating library routine.
+ *   - limit: in_dim <= 32768; larger sizes set QZ_ERR_TOO_LARGE and leave d_y untouched.
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call before starting any stream capture on that device.
+ *   - all calls share the one array: two calls whose kernels can overlap on the GPU (different
+ *     streams) race on it; calls on one stream are safe.  Nothing in it needs clearing between
+ *     calls -- each call rewrites what it reads. */
+void cuda_gemv_noalloc(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int in_dim,
+                       int out_dim);
+
 /* Batched form: Y[m, out_dim] = X[m, in_dim] * W^T, token-major like the reference's CPU
  * gemm() (src/dequant.rs:143-200).  The reference has no GPU counterpart. */
 void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,

@@ -64,6 +64,7 @@ _SIGS = {
     "cuda_repack_weights": (C.c_int, [C.c_uint32, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_unpack_weights": (C.c_int, [C.c_void_p]),
     "cuda_dequant": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong]),
+    "cuda_gemv_noalloc": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "cuda_gemm": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
 }
 

@@ -431,6 +431,127 @@ static void dequant_rows(uint32_t t, const uint8_t *data, float *out, int K, lon
     QZ_LAUNCH_CHECK();
 }
 
+// ---- allocation-free GEMV: scratch that lives in the library image -------------------------
+// Some hosts may not call cudaMalloc at the moment they need a GEMV: a thread that is in the
+// middle of a CUDA stream capture, a real-time or sandboxed caller whose memory is fixed up
+// front, or a process that has handed the whole device pool to another allocator.  For them
+// the converted activation vector (the only scratch the streaming GEMV needs) lives in this
+// file-scope device array instead of a lazily cudaMalloc'ed buffer.  One slot: in_dim <=
+// QZ_NOALLOC_MAX_K.  Every GPU that loads the library carries these 78,080 bytes until exit.
+constexpr int QZ_NOALLOC_MAX_K = 32768;
+constexpr size_t QZ_NOALLOC_BYTES = 2 * (size_t)QZ_NOALLOC_MAX_K + QZ_NOALLOC_MAX_K / 8 + QZ_NOALLOC_MAX_K / 4 + 256;
+static __device__ __align__(256) unsigned char qz_noalloc_scratch[QZ_NOALLOC_BYTES];
+
+// In host code `qz_noalloc_scratch` is only a handle for the runtime, not a device address;
+// the address a kernel can use comes from cudaGetSymbolAddress, per device.
+static unsigned char *g_noalloc_ptr[64];
+
+static unsigned char *noalloc_scratch_ptr()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "cuda_gemv_noalloc: cudaGetDevice failed");
+        return nullptr;
+    }
+    if (!g_noalloc_ptr[dev]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, qz_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            set_error(QZ_ERR_CUDA, "cuda_gemv_noalloc: cudaGetSymbolAddress failed");
+            return nullptr;
+        }
+        g_noalloc_ptr[dev] = (unsigned char *)p;
+    }
+    return g_noalloc_ptr[dev];
+}
+
+template <class F>
+static void launch_noalloc(const GemvArgs &a, int T)
+{
+    const int sms = sm_count();
+    int R = 4;
+    while (R > 1 && (long long)(a.N + a.RP * R - 1) / (a.RP * R) < 2LL * sms) R >>= 1;
+    const int ntiles = (a.N + a.RP * R - 1) / (a.RP * R);
+    const int per_sm = (T <= 256) ? 2 : 1;
+    int gx = ntiles < sms * per_sm ? ntiles : sms * per_sm;
+    if (gx < 1) gx = 1;
+    if (R == 4) gemv_stream_kernel<F, 4><<<gx, T, 0, g_stream>>>(a);
+    else if (R == 2) gemv_stream_kernel<F, 2><<<gx, T, 0, g_stream>>>(a);
+    else gemv_stream_kernel<F, 1><<<gx, T, 0, g_stream>>>(a);
+    QZ_LAUNCH_CHECK();
+}
+
+static void gemv_noalloc(uint32_t t, const uint8_t *W, const float *x, float *y, int K, int N)
+{
+    const FormatInfo fi = format_info(t);
+    if (fi.block_elems == 0) {
+        set_error(QZ_ERR_UNSUPPORTED_TYPE, "cuda_gemv_noalloc: unsupported ggml_type");
+        return;
+    }
+    if (!check_shape(t, K, N, "cuda_gemv_noalloc: in_dim must be a positive multiple of the block size")) return;
+    if (K > QZ_NOALLOC_MAX_K) {
+        set_error(QZ_ERR_TOO_LARGE, "cuda_gemv_noalloc: in_dim exceeds the 32768 the built-in scratch holds");
+        return;
+    }
+    if (N == 0) return;
+    if (!tables_ready(t)) {
+        set_error(QZ_ERR_MISSING_TABLE, "IQ codebook not uploaded (cuda_set_*_grid)");
+        return;
+    }
+    bool planes = false;
+    if (const Range *r = find_range(W)) {
+        if (r->type != t || r->K != K) {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_gemv_noalloc: pointer lies in a repacked range of another type/in_dim");
+            return;
+        }
+        planes = true;
+    }
+    const int want = stream_layout(t);
+    const size_t row_bytes = (size_t)(K / fi.block_elems) * fi.block_bytes;
+    const bool streamable = want && K % 64 == 0 && row_bytes % 16 == 0 && !((uintptr_t)W & 15) &&
+                            !((uintptr_t)x & 3) && ((want == 2) == planes);
+    if (!streamable) {
+        launch_generic(t, planes, W, x, y, K, N);   // needs no scratch at all
+        return;
+    }
+    unsigned char *base = noalloc_scratch_ptr();
+    if (!base) return;
+    // nothing in the scratch has to start at zero: the conversion below rewrites every byte
+    // of [0, K) that the GEMV kernel reads, whatever an earlier call left there
+    XQMut q;
+    q.xl = (int8_t *)base;
+    q.xh = (int8_t *)(base + QZ_NOALLOC_MAX_K);
+    q.xs = (float *)(base + 2 * (size_t)QZ_NOALLOC_MAX_K);
+    q.xsum = (float *)(base + 2 * (size_t)QZ_NOALLOC_MAX_K + QZ_NOALLOC_MAX_K / 8);
+    launch_quantize(x, q, K);
+    GemvArgs a;
+    a.K = K;
+    a.N = N;
+    a.U = K / 64;
+    if (a.U < 32) {
+        int p = 1;
+        while (p < a.U) p <<= 1;
+        a.Upad = p;
+    } else {
+        a.Upad = (a.U + 31) & ~31;
+    }
+    a.RP = a.Upad >= 256 ? 1 : 256 / a.Upad;
+    for (int i = 0; i < 4; i++) {
+        a.W[i] = W;
+        a.y[i] = y;
+        a.xq[i] = XQ{q.xl, q.xh, q.xs, q.xsum};
+    }
+    const int T = a.Upad * a.RP;
+    switch (t) {
+    case T_Q4_K: launch_noalloc<StreamQ4K>(a, T); break;
+    case T_Q6_K: launch_noalloc<StreamQ6K>(a, T); break;
+    case T_Q8_0: launch_noalloc<StreamQ8_0>(a, T); break;
+    default: launch_generic(t, planes, W, x, y, K, N); break;
+    }
+}
+
 }  // namespace qz
 
 using namespace qz;
@@ -709,6 +830,12 @@ int cuda_unpack_weights(void *d_data)
 void cuda_dequant(uint32_t ggml_type, const uint8_t *d_data, float *d_out, int in_dim, long long n_rows)
 {
     dequant_rows(ggml_type, d_data, d_out, in_dim, n_rows);
+}
+
+void cuda_gemv_noalloc(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int in_dim,
+                       int out_dim)
+{
+    gemv_noalloc(ggml_type, d_data, d_x, d_y, in_dim, out_dim);
 }
 
 void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,
