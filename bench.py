@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="profiling case: lm_head cut to 40080 rows (134 MB, still larger than L2; ~0.3 GB on the device)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode-step section")
     return ap.parse_args()
 
 
@@ -176,6 +177,64 @@ def run_reference(args):
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+def decode_section(q, args, torch, np, want_parity):
+    """Full batch-1 decode step of a random-init Llama-3-8B-architecture model in the fixed
+    Q4_K_M-style layout (q/k/v/o/gate/up Q4_K, down + output head Q6_K), f32 KV cache pre-filled
+    with N(0,1) at context 1024, decoding position 1024."""
+    from saient_quartz_b200.host_model import HostModel, LLAMA3_8B
+    L = q.lib()
+    t0 = time.perf_counter()
+    m = HostModel(keep_host=want_parity, **LLAMA3_8B)
+    m.fill_synthetic()
+    kv = m.fill_kv(1024, keep=want_parity)
+    build_s = time.perf_counter() - t0
+    token, pos = 4242, 1024
+    kv_bytes = 32 * 2 * 1025 * 1024 * 4
+    bytes_per_token = m.weight_bytes + kv_bytes
+    out = {"model": "llama-3-8b architecture, random init, Q4_K_M-style layout", "context": 1024,
+           "bytes_per_token": bytes_per_token, "build_s": round(build_s, 1)}
+    peak, _ = peaks()
+    for name, fused in (("fused_graph", True), ("reference_sequence", False)):
+        for _ in range(3):
+            m.step_device(token, pos, fused)
+        torch.cuda.synchronize()
+        n = max(5, min(args.steps, 20))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            m.step_device(token, pos, fused)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        out[name] = {"tok_s": 1e3 / ms, "ms_per_token": ms, "launches_per_token": m.launches(),
+                     "gbs": bytes_per_token / (ms * 1e-3) / 1e9,
+                     "frac_of_measured_hbm": bytes_per_token / (ms * 1e-3) / 1e9 / peak}
+        q.check_error("decode " + name)
+    # end to end as the host sees it: token in, 513 KB of logits out, per step
+    n = 5
+    t1 = time.perf_counter()
+    for _ in range(n):
+        logits = m.step(token, pos, fused=True)
+    out["e2e_tok_s"] = n / (time.perf_counter() - t1)
+    if want_parity:
+        import oracle
+        from oracle.forward_ref import RefModel
+        from saient_quartz_b200.iq_tables import load_tables
+        oracle.set_tables(load_tables())
+        r = RefModel(m.cfg, m.host)
+        for l, (k, v) in enumerate(kv):
+            r.set_kv(l, k, v)
+        t2 = time.perf_counter()
+        want = r.forward(token, pos)
+        cpu_s = time.perf_counter() - t2
+        rel = float(np.abs(logits.astype(np.float64) - want).max() / np.abs(want).max())
+        out["parity_max_rel_err_vs_cpu_oracle"] = rel
+        out["cpu_oracle_tok_s"] = 1.0 / cpu_s
+        assert rel < 5e-3, f"decode-step logits differ from the CPU oracle: {rel}"
+    m.close()
+    return out
 
 
 def main():
@@ -331,6 +390,10 @@ def main():
         tol = oracle.tolerance(mats["w"][i], t, K, N, xs[i])
         assert np.all(np.abs(got - ref) <= tol), "bench output failed the parity bound"
 
+    decode = None
+    if rank == 0 and world == 1 and not args.small and not args.no_decode:
+        decode = decode_section(q, args, torch, np, want_parity=not args.no_cpu_baseline)
+
     if rank == 0:
         launches_per_step = 0
         for (label, t, K, N) in shapes:
@@ -352,6 +415,7 @@ def main():
                                     "d2h_bytes_per_step": 0, "note": "multi-GPU: operands resident"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
+            "decode": decode,
         }
         print(json.dumps(line))
     if world > 1:

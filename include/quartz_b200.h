@@ -95,6 +95,9 @@ void quartz_clear_error(void);
  * the reference's behaviour, src/cuda_kernels.cu launches with <<<g,b>>> only). */
 void quartz_set_stream(void *cuda_stream);
 
+/* Number of kernels this library has launched (or recorded into a graph) so far. */
+long long quartz_launch_count(void);
+
 /* Which streaming GEMV serves the formats that have one: 0 = TMA-staged shared-memory ring
  * (default), 1 = register-streaming 128-bit loads.  For A/B measurements; results are
  * bit-identical.  The environment variable QUARTZ_GEMV_IMPL=ldg selects 1 at start-up. */
@@ -133,6 +136,43 @@ void cuda_dequant(uint32_t ggml_type, const uint8_t *d_data, float *d_out, int i
  *     calls -- each call rewrites what it reads. */
 void cuda_gemv_noalloc(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int in_dim,
                        int out_dim);
+
+/* ---- fused decode-step entry points (no counterparts in the reference, which issues these
+ * steps as separate launches, src/cuda.rs:548-823).  The streaming GEMVs consume activations
+ * in a 16-bit block-fixed-point form held in library scratch "slots" 0..3; these producers
+ * write a slot directly, so the separate conversion launch of cuda_gemv disappears. ---- */
+/* convert d_x[0..n) into slot */
+void cuda_quantize_x(const float *d_x, int n, int slot);
+/* cuda_rms_norm whose result lands in `slot` (and in out_f32 when not NULL) */
+void cuda_rms_norm_q(const float *x, const float *w, int n, int slot, float *out_f32);
+/* cuda_swiglu (oai = 0) / cuda_swiglu_oai (oai = 1) whose result lands in `slot` */
+void cuda_swiglu_q(const float *gate, const float *up, int n, int slot, int oai);
+/* 1 if (type, in_dim, pointer/layout) is served by the streaming kernel, else 0 */
+int cuda_gemv_q_supported(uint32_t ggml_type, const uint8_t *d_data, int in_dim);
+/* n_mats <= 8 same-shape GEMVs in ONE launch: d_y[i] (+)= W[i] * slot[slots[i]].  d_w, slots, d_y
+ * are HOST arrays (of device pointers / slot numbers).  accumulate = 1 adds into d_y (residual
+ * epilogue).  Generalises cuda_gemv_moe4; fused q/k/v is six 1024-row slices of three tensors. */
+void cuda_gemv_q(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, const int *slots, float *const *d_y,
+                 int in_dim, int out_dim, int accumulate);
+/* cuda_rope_yarn on q and k + cuda_kv_append (src/cuda.rs:601-613) in one launch */
+void cuda_rope_kv(float *q, float *k, const float *v, float *k_cache, float *v_cache, int n_heads, int n_kv_heads,
+                  int head_dim, int pos, float theta, float yarn_scale, int yarn_orig_ctx, int neox);
+/* cuda_attn_score_all + cuda_softmax_sink_all + cuda_attn_values_all (src/cuda.rs:627-645) as a
+ * split-KV decode attention (K and V read once for all query heads of a kv head); sinks may be
+ * NULL; out_slot >= 0 also writes the result's activation form for the output projection. */
+void cuda_attn_decode(float *out, const float *q, const float *k_cache, const float *v_cache, int n_heads,
+                      int n_kv_heads, int seq_len, int head_dim, int kv_dim, float scale, const float *sinks,
+                      int out_slot);
+
+/* CUDA-graph helpers (no counterpart in the reference, which launches ~670 kernels per token one
+ * by one, src/cuda.rs:548-843).  Between begin and end every call of this library is recorded
+ * instead of executed; copies and cuda_sync must stay outside, and every scratch buffer must
+ * already exist (run the sequence once eagerly first).  end returns an executable graph (NULL on
+ * failure); launch replays it, ordered with the default stream. */
+int quartz_graph_begin(void);
+void *quartz_graph_end(void);
+void quartz_graph_launch(void *graph_exec);
+void quartz_graph_destroy(void *graph_exec);
 
 /* Batched form: Y[m, out_dim] = X[m, in_dim] * W^T, token-major like the reference's CPU
  * gemm() (src/dequant.rs:143-200).  The reference has no GPU counterpart. */

@@ -60,10 +60,24 @@ _SIGS = {
     "quartz_clear_error": (None, []),
     "quartz_set_stream": (None, [C.c_void_p]),
     "quartz_set_gemv_impl": (None, [C.c_int]),
+    "quartz_launch_count": (C.c_longlong, []),
     "cuda_set_iq3xxs_grid": (None, [C.c_void_p]),
     "cuda_repack_weights": (C.c_int, [C.c_uint32, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_unpack_weights": (C.c_int, [C.c_void_p]),
     "cuda_dequant": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong]),
+    "cuda_quantize_x": (None, [C.c_void_p, C.c_int, C.c_int]),
+    "cuda_rms_norm_q": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "cuda_swiglu_q": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "cuda_gemv_q_supported": (C.c_int, [C.c_uint32, C.c_void_p, C.c_int]),
+    "cuda_gemv_q": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "cuda_rope_kv": (None, [C.c_void_p] * 5 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int,
+                            C.c_int]),
+    "cuda_attn_decode": (None, [C.c_void_p] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float,
+                                C.c_void_p, C.c_int]),
+    "quartz_graph_begin": (C.c_int, []),
+    "quartz_graph_end": (C.c_void_p, []),
+    "quartz_graph_launch": (None, [C.c_void_p]),
+    "quartz_graph_destroy": (None, [C.c_void_p]),
     "cuda_gemv_noalloc": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "cuda_gemm": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
 }

@@ -1,4 +1,5 @@
-"""Build the CUDA library in-tree: saient-quartz_b200/libquartz_b200.so (sm_100a only)."""
+"""Build in-tree: saient-quartz_b200/libquartz_b200.so (the CUDA library, sm_100a only) and
+saient-quartz_b200/libquartz_host.so (the C++ host side of the decode step, a pure client of the C ABI)."""
 import os
 import subprocess
 import sys
@@ -6,6 +7,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libquartz_b200.so")
+HOST_LIB = os.path.join(HERE, "libquartz_host.so")
+HOST_SRC = os.path.join(HERE, "host", "forward_state.cpp")
 
 
 def sources():
@@ -20,8 +23,20 @@ def up_to_date():
     return all(os.path.getmtime(s) <= t for s in sources() + [hdr])
 
 
+def build_host(force=False):
+    hdrs = [os.path.join(HERE, "host", "forward_state.h"), os.path.join(HERE, "..", "include", "quartz_b200.h")]
+    if (not force and os.path.exists(HOST_LIB)
+            and all(os.path.getmtime(p) <= os.path.getmtime(HOST_LIB) for p in [HOST_SRC, LIB] + hdrs)):
+        return HOST_LIB
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", HOST_LIB, HOST_SRC, "-L" + HERE, "-lquartz_b200",
+           "-Wl,-rpath,$ORIGIN"]
+    subprocess.check_call(cmd)
+    return HOST_LIB
+
+
 def build(force=False, verbose=False):
     if not force and up_to_date():
+        build_host()
         return LIB
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
     arch = os.environ.get("QUARTZ_CUDA_ARCH", "sm_100a")   # same variable as the reference's build.rs:33
@@ -32,6 +47,7 @@ def build(force=False, verbose=False):
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     subprocess.check_call(cmd)
+    build_host(force=True)
     return LIB
 
 

@@ -29,7 +29,12 @@ int sm_count();
         if (e__ != cudaSuccess) ::qz::set_error(QZ_ERR_CUDA, cudaGetErrorString(e__)); \
     } while (0)
 
-#define QZ_LAUNCH_CHECK() QZ_CUDA_CHECK(cudaGetLastError())
+extern long long g_launch_count;   // kernels launched by this library so far
+#define QZ_LAUNCH_CHECK()                  \
+    do {                                   \
+        ::qz::g_launch_count++;            \
+        QZ_CUDA_CHECK(cudaGetLastError()); \
+    } while (0)
 
 __device__ __forceinline__ float h2f(uint16_t bits)
 {

@@ -1,0 +1,234 @@
+// Fused decode-step kernels (additions; the reference runs these as separate launches,
+// src/cuda.rs:548-823): producers that emit the block-fixed-point activation form the
+// streaming GEMVs consume, RoPE+KV-append in one launch, and split-KV decode attention.
+#pragma once
+
+#include "decode_ops.cuh"
+#include "gemv_stream.cuh"
+
+namespace qz {
+
+struct XQOut {
+    int8_t *xl, *xh;
+    float *xs, *xsum;
+};
+
+// Convert four consecutive values (elements 4t .. 4t+3, t = global thread-of-4 index) exactly
+// as quantize_x_kernel does.  All 32 lanes of the warp must call it (shuffles inside); lanes
+// past the end pass valid = false.
+__device__ __forceinline__ void quantize4_store(const float v[4], int t, bool valid, const XQOut &o)
+{
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float sum = (v[0] + v[1]) + (v[2] + v[3]);
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    if (!valid) return;
+    const float inv = amax > 0.f ? XQ_RANGE / amax : 0.f;
+    uint32_t wl = 0, wh = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int X = __float2int_rn(v[i] * inv);
+        int l = ((X + 128) & 0xFF) - 128;
+        int h = (X - l) >> 8;
+        wl |= (uint32_t)(l & 0xFF) << (8 * i);
+        wh |= (uint32_t)(h & 0xFF) << (8 * i);
+    }
+    ((uint32_t *)o.xl)[t] = wl;
+    ((uint32_t *)o.xh)[t] = wh;
+    if ((t & 7) == 0) o.xs[t >> 3] = amax / XQ_RANGE;
+    if ((t & 3) == 0) o.xsum[t >> 2] = sum;
+}
+
+// RMSNorm (src/cuda_kernels.cu:563-575) whose result goes straight into activation form;
+// optionally also stored as f32.  One CTA; n is a multiple of 4.
+__global__ void rms_norm_q_kernel(const float *__restrict__ x, const float *__restrict__ w, int n, XQOut o,
+                                  float *__restrict__ out_f32)
+{
+    __shared__ float sm[32];
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+    ss = block_reduce<false>(ss, sm);
+    const float r = rsqrtf(ss / (float)n + 1e-5f);
+    const int n4 = n >> 2;
+    for (int t0 = 0; t0 < n4; t0 += blockDim.x) {
+        const int t = t0 + threadIdx.x;
+        const bool valid = t < n4;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (valid) {
+            const float4 a = *(const float4 *)(x + 4 * t), b = *(const float4 *)(w + 4 * t);
+            v[0] = a.x * r * b.x; v[1] = a.y * r * b.y; v[2] = a.z * r * b.z; v[3] = a.w * r * b.w;
+            if (out_f32) *(float4 *)(out_f32 + 4 * t) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        quantize4_store(v, t, valid, o);
+    }
+}
+
+// SwiGLU (src/cuda_kernels.cu:683-698) into activation form.
+__global__ void swiglu_q_kernel(const float *__restrict__ gate, const float *__restrict__ up, int n, int oai, XQOut o)
+{
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = 4 * t < n;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (valid) {
+        const float4 g = *(const float4 *)(gate + 4 * t), u = *(const float4 *)(up + 4 * t);
+        const float gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (oai) {
+                const float a = fminf(gg[i], 7.f), b = fmaxf(-7.f, fminf(7.f, uu[i]));
+                v[i] = (a / (1.f + expf(-1.702f * a))) * (b + 1.f);
+            } else {
+                v[i] = (gg[i] / (1.f + expf(-gg[i]))) * uu[i];
+            }
+        }
+    }
+    quantize4_store(v, t, valid, o);
+}
+
+// RoPE on q (n_heads) and k (n_kv_heads) in place, then append k, v to the caches at `pos`:
+// cuda_rope_yarn x2 + cuda_kv_append (src/cuda.rs:601-613) as one launch.  grid = n_heads +
+// n_kv_heads, block = head_dim/2 rounded up to a warp.
+__global__ void rope_kv_kernel(float *q, float *k, const float *__restrict__ v, float *__restrict__ k_cache,
+                               float *__restrict__ v_cache, int n_heads, int head_dim, int pos, float theta,
+                               float yarn_scale, int yarn_orig_ctx, int neox, int kv_dim)
+{
+    const int i = threadIdx.x, half = head_dim >> 1;
+    const bool is_k = (int)blockIdx.x >= n_heads;
+    const int head = is_k ? blockIdx.x - n_heads : blockIdx.x;
+    float *xh = (is_k ? k : q) + (size_t)head * head_dim;
+    if (i < half) {
+        const float PI = 3.14159265358979f;
+        float inv = 1.f / powf(theta, 2.f * (float)i / (float)head_dim);
+        float eff = inv;
+        if (yarn_scale > 1.f && yarn_orig_ctx > 0) {
+            float hi_w = (float)yarn_orig_ctx / 32.f, lo_w = (float)yarn_orig_ctx / 1.f;
+            float wavelen = 2.f * PI / inv;
+            float ramp = fmaxf(0.f, fminf(1.f, (lo_w - wavelen) / (lo_w - hi_w)));
+            eff = ramp * inv + (1.f - ramp) * (inv / yarn_scale);
+        }
+        float s, c;
+        sincosf((float)pos * eff, &s, &c);
+        const int i0 = neox ? i : 2 * i, i1 = neox ? i + half : 2 * i + 1;
+        const float a = xh[i0], b = xh[i1];
+        const float r0 = a * c - b * s, r1 = a * s + b * c;
+        xh[i0] = r0;
+        xh[i1] = r1;
+        if (is_k) {
+            float *kc = k_cache + (size_t)pos * kv_dim + (size_t)head * head_dim;
+            kc[i0] = r0;
+            kc[i1] = r1;
+        }
+    }
+    if (is_k) {
+        const float *vh = v + (size_t)head * head_dim;
+        float *vc = v_cache + (size_t)pos * kv_dim + (size_t)head * head_dim;
+        for (int j = i; j < head_dim; j += blockDim.x) vc[j] = vh[j];
+    }
+}
+
+// ---- split-KV decode attention -------------------------------------------------------------
+// softmax(q K^T * scale [+ sink]) V for one new token, all heads (the three launches of
+// src/cuda.rs:627-645 as two).  grid = (n_kv_heads, n_splits): a CTA stages CHUNK key rows and
+// value rows of its kv head in shared memory once and serves every query head that maps to
+// that kv head (GQA: head*n_kv/n_heads), so K and V are read from HBM exactly once.  Warp w
+// handles query heads w, w+4, ...  Each (head, split) leaves (max, sum, unnormalised out[hd])
+// in a scratch buffer; attn_combine_kernel merges the splits.
+constexpr int ATT_CHUNK = 32;
+constexpr int ATT_MAX_HD = 128;
+
+__global__ void __launch_bounds__(128) attn_partial_kernel(float *__restrict__ part, const float *__restrict__ q,
+                                                           const float *__restrict__ k_cache,
+                                                           const float *__restrict__ v_cache, int n_heads, int n_kv_heads,
+                                                           int seq_len, int head_dim, int kv_dim, float scale)
+{
+    __shared__ float ks[ATT_CHUNK][ATT_MAX_HD + 1];
+    __shared__ float vs[ATT_CHUNK][ATT_MAX_HD];
+    __shared__ float qs[4][ATT_MAX_HD];
+    __shared__ float ps[4][ATT_CHUNK];
+    const int kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
+    const int t0 = split * ATT_CHUNK;
+    const int nt = min(ATT_CHUNK, seq_len - t0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // stage K and V rows [t0, t0+nt) of this kv head
+    const int hd4 = head_dim >> 2;
+    for (int idx = threadIdx.x; idx < nt * hd4; idx += blockDim.x) {
+        const int t = idx / hd4, c = idx % hd4;
+        const size_t g = (size_t)(t0 + t) * kv_dim + (size_t)kvh * head_dim + 4 * c;
+        const float4 kk = *(const float4 *)(k_cache + g), vv = *(const float4 *)(v_cache + g);
+        ks[t][4 * c] = kk.x; ks[t][4 * c + 1] = kk.y; ks[t][4 * c + 2] = kk.z; ks[t][4 * c + 3] = kk.w;
+        *(float4 *)&vs[t][4 * c] = vv;
+    }
+    // query heads of this kv head: those with (head * n_kv_heads) / n_heads == kvh
+    const int h_lo = (kvh * n_heads + n_kv_heads - 1) / n_kv_heads;
+    const int h_hi = ((kvh + 1) * n_heads + n_kv_heads - 1) / n_kv_heads;
+    for (int hb = h_lo; hb < h_hi; hb += 4) {
+        const int head = hb + warp;
+        const bool live = head < h_hi;
+        __syncthreads();   // staging done / previous round's qs no longer read
+        if (live)
+            for (int i = lane; i < head_dim; i += 32) qs[warp][i] = q[(size_t)head * head_dim + i];
+        __syncthreads();
+        if (!live) continue;
+        // one key position per lane
+        float sc = 0.f;
+        for (int i = 0; i < head_dim; i++) sc = fmaf(qs[warp][i], ks[lane][i], sc);
+        sc = lane < nt ? sc * scale : -INFINITY;
+        float mx = sc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        const float p = lane < nt ? expf(sc - mx) : 0.f;
+        float sum = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+        ps[warp][lane] = p;
+        __syncwarp();
+        float *dst = part + ((size_t)head * n_splits + split) * (head_dim + 2);
+        for (int i = lane; i < head_dim; i += 32) {
+            float acc = 0.f;
+            for (int t = 0; t < nt; t++) acc = fmaf(ps[warp][t], vs[t][i], acc);
+            dst[2 + i] = acc;
+        }
+        if (lane == 0) {
+            dst[0] = mx;
+            dst[1] = sum;
+        }
+        __syncwarp();
+    }
+}
+
+// Merge the splits of every head; optionally emit the activation form for the output
+// projection.  grid = n_heads, block = head_dim (a multiple of 32, <= 128).
+__global__ void attn_combine_kernel(float *__restrict__ out, const float *__restrict__ part, int n_splits, int head_dim,
+                                    const float *__restrict__ sinks, XQOut o, int emit_q)
+{
+    const int head = blockIdx.x, i = threadIdx.x;
+    const float *p = part + (size_t)head * n_splits * (head_dim + 2);
+    const float sink = sinks ? sinks[head] : -INFINITY;
+    const bool has_sink = sink > -1e29f;
+    float mx = has_sink ? sink : -1e30f;
+    for (int s = 0; s < n_splits; s++) mx = fmaxf(mx, p[(size_t)s * (head_dim + 2)]);
+    float total = has_sink ? expf(sink - mx) : 0.f, acc = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        const float *ps_ = p + (size_t)s * (head_dim + 2);
+        const float f = expf(ps_[0] - mx);
+        total += f * ps_[1];
+        acc = fmaf(f, ps_[2 + i], acc);
+    }
+    const float r = acc / total;
+    out[(size_t)head * head_dim + i] = r;
+    if (emit_q) {
+        // four consecutive outputs per converting thread: gather through shuffles
+        const int lane = i & 31;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = __shfl_sync(0xFFFFFFFFu, r, (4 * lane + j) & 31);
+        // lanes 0..7 of each warp own the warp's 32 outputs as 8 groups of 4
+        const int base = (head * head_dim + (i & ~31)) >> 2;
+        quantize4_store(v, base + (lane & 7), lane < 8, o);
+    }
+}
+
+}  // namespace qz

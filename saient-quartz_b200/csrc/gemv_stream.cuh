@@ -102,11 +102,14 @@ struct LdGlobal {
     __device__ static uint32_t u16(const uint8_t *p) { return ld_stream_u16(p); }
 };
 
+constexpr int QZ_MAX_MATS = 8;   // (weights, activation, output) triples one launch can serve
+
 struct GemvArgs {
-    const uint8_t *W[4];
-    XQ xq[4];
-    float *y[4];
+    const uint8_t *W[QZ_MAX_MATS];
+    XQ xq[QZ_MAX_MATS];
+    float *y[QZ_MAX_MATS];
     int K, N;
+    int accumulate;   // 1: y += W x (residual epilogue), 0: y = W x
     int U;       // 64-weight units per row
     int Upad;    // threads per row: U rounded up to a power of two (<32) or a multiple of 32
     int RP;      // rows per pass = blockDim.x / Upad
@@ -379,7 +382,7 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
                 float v = acc[i];
                 for (int off = a.Upad >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
                 const int row = row0 + i * a.RP;
-                if (u == 0 && row < a.N) y[row] = v;
+                if (u == 0 && row < a.N) y[row] = a.accumulate ? y[row] + v : v;
             }
         } else {
 #pragma unroll
@@ -389,7 +392,7 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
 #pragma unroll
                     for (int i = 0; i < R; i++) {
                         const int row = row0 + i * a.RP;
-                        if (row < a.N) y[row] = acc[i];
+                        if (row < a.N) y[row] = a.accumulate ? y[row] + acc[i] : acc[i];
                     }
                 }
             } else {
@@ -403,7 +406,7 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
                     float v = 0.f;
                     for (int k = 0; k < wpr; k++) v += part_w[parity][(rl2 * R + i2) * 16 + k];
                     const int row = tile * rows_per_tile + i2 * a.RP + rl2;
-                    if (row < a.N) y[row] = v;
+                    if (row < a.N) y[row] = a.accumulate ? y[row] + v : v;
                 }
             }
         }

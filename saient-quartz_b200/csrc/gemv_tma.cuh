@@ -27,10 +27,11 @@ constexpr int TMA_CONSUMERS = 512;
 constexpr long long TMA_WAIT_CYCLES = 2000000000LL;   // ~1 s at 1.9 GHz
 
 struct TmaArgs {
-    const uint8_t *W[4];
-    XQ xq[4];
-    float *y[4];
+    const uint8_t *W[QZ_MAX_MATS];
+    XQ xq[QZ_MAX_MATS];
+    float *y[QZ_MAX_MATS];
     int K, N;
+    int accumulate;          // 1: y += W x
     int U, Upad, RP;         // units per row, threads per row, rows per stage
     int n_mats;
     int stage_bytes;         // RP * row_bytes, a multiple of 16
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
                 float v = active ? acc[j] : 0.f;
                 for (int o = a.Upad >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
                 const int row = row_j0 + j * row_step;
-                if (u == 0 && t0 + j < my_tiles && row < a.N) y[row] = v;
+                if (u == 0 && t0 + j < my_tiles && row < a.N) y[row] = a.accumulate ? y[row] + v : v;
             }
         } else {
             const float v = warp_sum4(active ? acc[0] : 0.f, active ? acc[1] : 0.f, active ? acc[2] : 0.f,
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             const int j = lane >> 3;   // which of the four rows this lane's total belongs to
             if (MODE == 1) {
                 const int row = row_j0 + j * row_step;
-                if ((lane & 7) == 0 && t0 + j < my_tiles && row < a.N) y[row] = v;
+                if ((lane & 7) == 0 && t0 + j < my_tiles && row < a.N) y[row] = a.accumulate ? y[row] + v : v;
             } else {
                 // the row's warps meet at their own named barrier; its first warp finishes the sums
                 float *p = part[(t0 >> 2) & 1] + rl * wpr * 4;
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
                     float t = 0.f;
                     for (int k = 0; k < wpr; k++) t += p[lane * wpr + k];
                     const int row = row_j0 + lane * row_step;
-                    if (t0 + lane < my_tiles && row < a.N) y[row] = t;
+                    if (t0 + lane < my_tiles && row < a.N) y[row] = a.accumulate ? y[row] + t : t;
                 }
             }
         }

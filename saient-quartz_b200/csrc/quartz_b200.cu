@@ -17,6 +17,7 @@
 #include "gemv_stream.cuh"
 #include "gemv_tma.cuh"
 #include "decode_ops.cuh"
+#include "fused_ops.cuh"
 
 namespace qz {
 
@@ -25,6 +26,7 @@ static cudaStream_t g_stream = 0;
 static int g_err = QZ_OK;
 static std::string g_err_msg;
 static int g_sm_count = 0;
+long long g_launch_count = 0;
 
 void set_error(int code, const char *what)
 {
@@ -87,7 +89,7 @@ static bool ensure_xq(int K)
     }
     size_t cap = (size_t)K < 32768 ? 32768 : (size_t)K;
     size_t sb = xq_slot_bytes(cap);
-    if (cudaMalloc(&g_xq.base, 4 * sb) != cudaSuccess) {
+    if (cudaMalloc(&g_xq.base, 8 * sb) != cudaSuccess) {   // slots 0-3: cuda_gemv & co; 4-7: the *_q entry points
         cudaGetLastError();
         set_error(QZ_ERR_CUDA, "cudaMalloc of the activation scratch failed");
         return false;
@@ -225,7 +227,8 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     const FormatInfo fi = format_info(F::TYPE);
     const size_t row_bytes = (size_t)(g.K / fi.block_elems) * fi.block_bytes;
     TmaArgs a;
-    for (int i = 0; i < 4; i++) { a.W[i] = g.W[i]; a.xq[i] = g.xq[i]; a.y[i] = g.y[i]; }
+    for (int i = 0; i < QZ_MAX_MATS; i++) { a.W[i] = g.W[i]; a.xq[i] = g.xq[i]; a.y[i] = g.y[i]; }
+    a.accumulate = g.accumulate;
     a.K = g.K; a.N = g.N; a.U = g.U; a.Upad = g.Upad; a.n_mats = n_mats;
     a.RP = g.Upad >= TMA_CONSUMERS ? 1 : TMA_CONSUMERS / g.Upad;
     const int sms = sm_count();
@@ -277,25 +280,22 @@ static void launch_stream_r(const GemvArgs &a, int n_mats, int T)
     QZ_LAUNCH_CHECK();
 }
 
-// Streaming path for up to four same-shape GEMVs.  Returns false when the shape or the
-// pointers do not qualify (the caller then falls back to the any-shape kernels).
-static bool try_stream(uint32_t t, int n, const uint8_t *const *W, const float *const *x, float *const *y, int K,
-                       int N, const bool *planes)
+static bool stream_shape_ok(uint32_t t, int K)
 {
-    const int want = stream_layout(t);
-    if (!want || K % 64 != 0 || K / 64 > 512) return false;
+    if (!stream_layout(t) || K % 64 != 0 || K / 64 > 512) return false;
     const FormatInfo fi = format_info(t);
-    const size_t row_bytes = (size_t)(K / fi.block_elems) * fi.block_bytes;
-    if (row_bytes % 16 != 0) return false;
-    for (int i = 0; i < n; i++) {
-        if (((uintptr_t)W[i] & 15) || ((uintptr_t)x[i] & 3)) return false;
-        if ((want == 2) != planes[i]) return false;
-    }
-    if (!ensure_xq(K)) return false;
+    return ((size_t)(K / fi.block_elems) * fi.block_bytes) % 16 == 0;
+}
 
+// Launch the streaming GEMV for n same-shape matrices whose activations already sit in the
+// scratch slots slot_of[i].
+static bool stream_core(uint32_t t, int n, const uint8_t *const *W, const int *slot_of, float *const *y, int K, int N,
+                        int accumulate)
+{
     GemvArgs a;
     a.K = K;
     a.N = N;
+    a.accumulate = accumulate;
     a.U = K / 64;
     if (a.U < 32) {
         int p = 1;
@@ -306,21 +306,7 @@ static bool try_stream(uint32_t t, int n, const uint8_t *const *W, const float *
     }
     a.RP = a.Upad >= 256 ? 1 : 256 / a.Upad;
     const int T = a.Upad * a.RP;
-
-    // quantize each distinct activation vector once
-    int slot_of[4];
-    int n_slots = 0;
-    for (int i = 0; i < n; i++) {
-        int s = -1;
-        for (int j = 0; j < i; j++)
-            if (x[j] == x[i]) { s = slot_of[j]; break; }
-        if (s < 0) {
-            s = n_slots++;
-            launch_quantize(x[i], xq_slot(g_xq.base, g_xq.slot_bytes, s, g_xq.cap_k), K);
-        }
-        slot_of[i] = s;
-    }
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < QZ_MAX_MATS; i++) {
         int j = i < n ? i : 0;
         XQMut q = xq_slot(g_xq.base, g_xq.slot_bytes, slot_of[j], g_xq.cap_k);
         a.W[i] = W[j];
@@ -344,6 +330,34 @@ static bool try_stream(uint32_t t, int n, const uint8_t *const *W, const float *
     default: return false;
     }
     return true;
+}
+
+// Streaming path for up to four same-shape GEMVs.  Returns false when the shape or the
+// pointers do not qualify (the caller then falls back to the any-shape kernels).
+static bool try_stream(uint32_t t, int n, const uint8_t *const *W, const float *const *x, float *const *y, int K,
+                       int N, const bool *planes)
+{
+    if (!stream_shape_ok(t, K)) return false;
+    const int want = stream_layout(t);
+    for (int i = 0; i < n; i++) {
+        if (((uintptr_t)W[i] & 15) || ((uintptr_t)x[i] & 3)) return false;
+        if ((want == 2) != planes[i]) return false;
+    }
+    if (!ensure_xq(K)) return false;
+    // quantize each distinct activation vector once
+    int slot_of[4];
+    int n_slots = 0;
+    for (int i = 0; i < n; i++) {
+        int s = -1;
+        for (int j = 0; j < i; j++)
+            if (x[j] == x[i]) { s = slot_of[j]; break; }
+        if (s < 0) {
+            s = n_slots++;
+            launch_quantize(x[i], xq_slot(g_xq.base, g_xq.slot_bytes, s, g_xq.cap_k), K);
+        }
+        slot_of[i] = s;
+    }
+    return stream_core(t, n, W, slot_of, y, K, N, 0);
 }
 
 static bool check_shape(uint32_t t, int K, int N, const char *who)
@@ -538,7 +552,8 @@ static void gemv_noalloc(uint32_t t, const uint8_t *W, const float *x, float *y,
         a.Upad = (a.U + 31) & ~31;
     }
     a.RP = a.Upad >= 256 ? 1 : 256 / a.Upad;
-    for (int i = 0; i < 4; i++) {
+    a.accumulate = 0;
+    for (int i = 0; i < QZ_MAX_MATS; i++) {
         a.W[i] = W;
         a.y[i] = y;
         a.xq[i] = XQ{q.xl, q.xh, q.xs, q.xsum};
@@ -775,6 +790,7 @@ void quartz_clear_error(void)
     g_err_msg.clear();
 }
 void quartz_set_stream(void *s) { g_stream = (cudaStream_t)s; }
+long long quartz_launch_count(void) { return g_launch_count; }
 void quartz_set_gemv_impl(int impl) { g_use_tma = impl == 1 ? 0 : 1; }
 
 int cuda_repack_weights(uint32_t ggml_type, void *d_data, int in_dim, int out_dim, int n_mats)
@@ -836,6 +852,182 @@ void cuda_gemv_noalloc(uint32_t ggml_type, const uint8_t *d_data, const float *d
                        int out_dim)
 {
     gemv_noalloc(ggml_type, d_data, d_x, d_y, in_dim, out_dim);
+}
+
+// ---- fused decode-step entry points (activation slots 0..3 map to scratch slots 4..7) ----
+static bool user_slot(int slot, int n, XQOut *o)
+{
+    if (slot < 0 || slot > 3 || n <= 0 || n % 4 != 0) {
+        set_error(QZ_ERR_BAD_SHAPE, "activation slot must be 0..3 and n a positive multiple of 4");
+        return false;
+    }
+    if (!ensure_xq(n)) return false;
+    XQMut q = xq_slot(g_xq.base, g_xq.slot_bytes, 4 + slot, g_xq.cap_k);
+    *o = XQOut{q.xl, q.xh, q.xs, q.xsum};
+    return true;
+}
+
+void cuda_quantize_x(const float *d_x, int n, int slot)
+{
+    XQOut o;
+    if (!user_slot(slot, n, &o)) return;
+    launch_quantize(d_x, XQMut{o.xl, o.xh, o.xs, o.xsum}, n);
+}
+
+void cuda_rms_norm_q(const float *x, const float *w, int n, int slot, float *out_f32)
+{
+    XQOut o;
+    if (!user_slot(slot, n, &o)) return;
+    rms_norm_q_kernel<<<1, 1024, 0, g_stream>>>(x, w, n, o, out_f32);
+    QZ_LAUNCH_CHECK();
+}
+
+void cuda_swiglu_q(const float *gate, const float *up, int n, int slot, int oai)
+{
+    XQOut o;
+    if (!user_slot(slot, n, &o)) return;
+    const int threads = n / 4;
+    swiglu_q_kernel<<<(threads + 255) / 256, 256, 0, g_stream>>>(gate, up, n, oai, o);
+    QZ_LAUNCH_CHECK();
+}
+
+int cuda_gemv_q_supported(uint32_t ggml_type, const uint8_t *d_data, int in_dim)
+{
+    if (!stream_shape_ok(ggml_type, in_dim) || ((uintptr_t)d_data & 15)) return 0;
+    const Range *r = find_range(d_data);
+    const bool planes = r && r->type == ggml_type && r->K == in_dim;
+    return ((stream_layout(ggml_type) == 2) == planes) ? 1 : 0;
+}
+
+void cuda_gemv_q(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, const int *slots, float *const *d_y,
+                 int in_dim, int out_dim, int accumulate)
+{
+    if (n_mats <= 0 || out_dim <= 0) return;
+    if (n_mats > QZ_MAX_MATS) {
+        set_error(QZ_ERR_TOO_LARGE, "cuda_gemv_q: at most 8 matrices per call");
+        return;
+    }
+    int slot_of[QZ_MAX_MATS];
+    for (int i = 0; i < n_mats; i++) {
+        if (slots[i] < 0 || slots[i] > 3 || !cuda_gemv_q_supported(ggml_type, d_w[i], in_dim)) {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_gemv_q: type/shape/layout has no streaming kernel (ask cuda_gemv_q_supported)");
+            return;
+        }
+        slot_of[i] = 4 + slots[i];
+    }
+    if (!ensure_xq(in_dim)) return;
+    stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
+}
+
+void cuda_rope_kv(float *q, float *k, const float *v, float *k_cache, float *v_cache, int n_heads, int n_kv_heads,
+                  int head_dim, int pos, float theta, float yarn_scale, int yarn_orig_ctx, int neox)
+{
+    if (n_heads <= 0 || n_kv_heads <= 0 || head_dim < 2) return;
+    const int bs = ((head_dim / 2) + 31) & ~31;
+    rope_kv_kernel<<<n_heads + n_kv_heads, bs, 0, g_stream>>>(q, k, v, k_cache, v_cache, n_heads, head_dim, pos, theta,
+                                                            yarn_scale, yarn_orig_ctx, neox, n_kv_heads * head_dim);
+    QZ_LAUNCH_CHECK();
+}
+
+static float *g_attn_part = nullptr;
+static size_t g_attn_part_floats = 0;
+
+void cuda_attn_decode(float *out, const float *q, const float *k_cache, const float *v_cache, int n_heads,
+                      int n_kv_heads, int seq_len, int head_dim, int kv_dim, float scale, const float *sinks,
+                      int out_slot)
+{
+    if (n_heads <= 0 || seq_len <= 0) return;
+    if (head_dim > ATT_MAX_HD || head_dim % 32 != 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_attn_decode: head_dim must be a multiple of 32 up to 128, n_heads a multiple of n_kv_heads");
+        return;
+    }
+    const int n_splits = (seq_len + ATT_CHUNK - 1) / ATT_CHUNK;
+    const size_t need = (size_t)n_heads * n_splits * (head_dim + 2);
+    if (need > g_attn_part_floats) {
+        if (g_attn_part) {
+            cudaStreamSynchronize(g_stream);
+            cudaFree(g_attn_part);
+        }
+        size_t cap = need < (size_t)(1 << 20) ? (size_t)(1 << 20) : need * 2;   // room for longer contexts
+        if (cudaMalloc(&g_attn_part, cap * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            g_attn_part = nullptr;
+            g_attn_part_floats = 0;
+            set_error(QZ_ERR_CUDA, "cudaMalloc of the attention scratch failed");
+            return;
+        }
+        g_attn_part_floats = cap;
+    }
+    XQOut o{nullptr, nullptr, nullptr, nullptr};
+    if (out_slot >= 0 && !user_slot(out_slot, n_heads * head_dim, &o)) return;
+    attn_partial_kernel<<<dim3(n_kv_heads, n_splits), 128, 0, g_stream>>>(g_attn_part, q, k_cache, v_cache, n_heads,
+                                                                         n_kv_heads, seq_len, head_dim, kv_dim, scale);
+    QZ_LAUNCH_CHECK();
+    attn_combine_kernel<<<n_heads, head_dim, 0, g_stream>>>(out, g_attn_part, n_splits, head_dim, sinks, o,
+                                                            out_slot >= 0 ? 1 : 0);
+    QZ_LAUNCH_CHECK();
+}
+
+// ---- CUDA-graph helpers: record a sequence of this library's calls once, replay it per token ----
+static cudaStream_t g_graph_stream = nullptr, g_saved_stream = nullptr;
+static bool g_capturing = false;
+
+int quartz_graph_begin(void)
+{
+    if (g_capturing) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_graph_begin: a capture is already open");
+        return 0;
+    }
+    if (!g_graph_stream) {
+        // a blocking stream: it stays ordered with the legacy default stream the copies use
+        if (cudaStreamCreate(&g_graph_stream) != cudaSuccess) {
+            cudaGetLastError();
+            set_error(QZ_ERR_CUDA, "quartz_graph_begin: cudaStreamCreate failed");
+            return 0;
+        }
+    }
+    if (cudaStreamBeginCapture(g_graph_stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "quartz_graph_begin: cudaStreamBeginCapture failed");
+        return 0;
+    }
+    g_saved_stream = g_stream;
+    g_stream = g_graph_stream;
+    g_capturing = true;
+    return 1;
+}
+
+void *quartz_graph_end(void)
+{
+    if (!g_capturing) return nullptr;
+    g_capturing = false;
+    g_stream = g_saved_stream;
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamEndCapture(g_graph_stream, &graph) != cudaSuccess || !graph) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "quartz_graph_end: capture failed (a captured call synchronised or allocated?)");
+        return nullptr;
+    }
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "quartz_graph_end: cudaGraphInstantiate failed");
+        return nullptr;
+    }
+    return (void *)exec;
+}
+
+void quartz_graph_launch(void *graph_exec)
+{
+    if (!graph_exec) return;
+    QZ_CUDA_CHECK(cudaGraphLaunch((cudaGraphExec_t)graph_exec, g_graph_stream));
+}
+
+void quartz_graph_destroy(void *graph_exec)
+{
+    if (graph_exec) QZ_CUDA_CHECK(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
 }
 
 void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,

@@ -1,0 +1,524 @@
+// Host side of the decode step over the C ABI (see forward_state.h).
+#include "forward_state.h"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <utility>
+#include <vector>
+
+#include "../../include/quartz_b200.h"
+
+extern "C" long long quartz_launch_count(void);
+
+namespace {
+
+// src/gguf.rs:172-191 (+ the three extension ids); 0 = unknown
+size_t ggml_type_size(uint32_t t, size_t n)
+{
+    switch (t) {
+    case 0: return n * 4;
+    case 1: case 30: return n * 2;
+    case 2: return n / 32 * 18;
+    case 3: return n / 32 * 20;
+    case 6: return n / 32 * 22;
+    case 7: return n / 32 * 24;
+    case 8: return n / 32 * 34;
+    case 20: return n / 32 * 18;
+    case 10: return n / 256 * 84;
+    case 12: return n / 256 * 144;
+    case 13: return n / 256 * 176;
+    case 14: return n / 256 * 210;
+    case 16: return n / 256 * 66;
+    case 17: return n / 256 * 74;
+    case 18: return n / 256 * 98;
+    case 21: return n / 256 * 110;
+    case 22: return n / 256 * 82;
+    default: return 0;
+    }
+}
+
+// src/cuda.rs:59-90: owns one device allocation
+struct GpuBuf {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    uint32_t ggml_type = 0;
+    GpuBuf() = default;
+    GpuBuf(const GpuBuf &) = delete;
+    GpuBuf &operator=(const GpuBuf &) = delete;
+    GpuBuf(GpuBuf &&o) noexcept { *this = std::move(o); }
+    GpuBuf &operator=(GpuBuf &&o) noexcept
+    {
+        drop();
+        ptr = o.ptr; bytes = o.bytes; ggml_type = o.ggml_type;
+        o.ptr = nullptr;
+        return *this;
+    }
+    ~GpuBuf() { drop(); }
+    void drop()
+    {
+        if (ptr) cuda_drop(ptr);
+        ptr = nullptr;
+    }
+    bool upload(const void *data, size_t n)
+    {
+        drop();
+        ptr = cuda_alloc(n ? n : 1);
+        if (!ptr) return false;
+        bytes = n;
+        if (n) cuda_h2d(ptr, data, n);
+        return true;
+    }
+    bool alloc_f32(size_t n)
+    {
+        drop();
+        ptr = cuda_alloc(n ? n * 4 : 4);
+        bytes = n * 4;
+        return ptr != nullptr;
+    }
+    bool empty() const { return ptr == nullptr; }
+    float *f() const { return (float *)ptr; }
+    const uint8_t *u8() const { return (const uint8_t *)ptr; }
+};
+
+struct Layer {
+    GpuBuf q, k, v, o, gate, up, down;
+    GpuBuf attn_norm, ffn_norm, q_norm, k_norm;
+    size_t q_norm_len = 0, k_norm_len = 0;
+    GpuBuf q_bias, k_bias, v_bias, o_bias, sinks;
+    bool has_qkv_bias = false;
+    GpuBuf moe_gate, moe_up, moe_down, router_w;
+    std::vector<float> router_b;
+    GpuBuf moe_gate_bias, moe_up_bias, moe_down_bias;
+};
+
+}  // namespace
+
+struct qh_model {
+    qh_config c;
+    std::vector<Layer> L;
+    GpuBuf embed, lm_head, final_norm;
+    // scratch (src/cuda.rs:312-354)
+    GpuBuf d_hidden, d_norm_out, d_q, d_k, d_v, d_attn_out, d_scores, d_gate, d_up, d_expert_out, d_expert_acc;
+    GpuBuf d_gate_all, d_up_all, d_expert_out_all, d_down_all, d_router_logits, d_logits;
+    std::vector<GpuBuf> kv_k, kv_v;
+    bool finalized = false;
+    long long last_launches = 0;
+    std::map<std::pair<int, int>, void *> graphs;   // (pos, need_logits) -> recorded step
+    int q_d() const { return c.n_heads * c.head_dim; }
+    int kv_d() const { return c.n_kv_heads * c.head_dim; }
+};
+
+extern "C" {
+
+qh_model *qh_create(const qh_config *cfg)
+{
+    if (!cfg || cfg->n_layers <= 0 || cfg->embed_dim <= 0) return nullptr;
+    qh_model *m = new qh_model();
+    m->c = *cfg;
+    m->L.resize(cfg->n_layers);
+    return m;
+}
+
+void qh_destroy(qh_model *m)
+{
+    if (!m) return;
+    for (auto &g : m->graphs) quartz_graph_destroy(g.second);
+    delete m;
+}
+
+int qh_set_tensor(qh_model *m, int role, int layer, uint32_t t, const void *host, size_t bytes, int repack)
+{
+    if (!m) return -1;
+    const qh_config &c = m->c;
+    GpuBuf *dst = nullptr;
+    int K = 0, N = 0, mats = 1;
+    const int d = c.embed_dim, fd = c.ffn_dim;
+    if (role == QH_EMBED) { dst = &m->embed; K = d; N = c.vocab_size; }
+    else if (role == QH_LM_HEAD) { dst = &m->lm_head; K = d; N = c.vocab_size; }
+    else if (role == QH_FINAL_NORM) dst = &m->final_norm;
+    else {
+        if (layer < 0 || layer >= c.n_layers) return -2;
+        Layer &l = m->L[layer];
+        switch (role) {
+        case QH_Q: dst = &l.q; K = d; N = m->q_d(); break;
+        case QH_K: dst = &l.k; K = d; N = m->kv_d(); break;
+        case QH_V: dst = &l.v; K = d; N = m->kv_d(); break;
+        case QH_O: dst = &l.o; K = m->q_d(); N = d; break;
+        case QH_GATE: dst = &l.gate; K = d; N = fd; break;
+        case QH_UP: dst = &l.up; K = d; N = fd; break;
+        case QH_DOWN: dst = &l.down; K = fd; N = d; break;
+        case QH_ATTN_NORM: dst = &l.attn_norm; break;
+        case QH_FFN_NORM: dst = &l.ffn_norm; break;
+        case QH_Q_NORM: dst = &l.q_norm; l.q_norm_len = bytes / 4; break;
+        case QH_K_NORM: dst = &l.k_norm; l.k_norm_len = bytes / 4; break;
+        case QH_Q_BIAS: dst = &l.q_bias; l.has_qkv_bias = true; break;
+        case QH_K_BIAS: dst = &l.k_bias; l.has_qkv_bias = true; break;
+        case QH_V_BIAS: dst = &l.v_bias; l.has_qkv_bias = true; break;
+        case QH_O_BIAS: dst = &l.o_bias; break;
+        case QH_SINKS: dst = &l.sinks; break;
+        case QH_MOE_GATE: dst = &l.moe_gate; K = d; N = fd; mats = c.n_experts; break;
+        case QH_MOE_UP: dst = &l.moe_up; K = d; N = fd; mats = c.n_experts; break;
+        case QH_MOE_DOWN: dst = &l.moe_down; K = fd; N = d; mats = c.n_experts; break;
+        case QH_ROUTER_W: dst = &l.router_w; break;
+        case QH_ROUTER_B:
+            l.router_b.assign((const float *)host, (const float *)host + bytes / 4);
+            return 0;
+        case QH_MOE_GATE_BIAS: dst = &l.moe_gate_bias; break;
+        case QH_MOE_UP_BIAS: dst = &l.moe_up_bias; break;
+        case QH_MOE_DOWN_BIAS: dst = &l.moe_down_bias; break;
+        default: return -3;
+        }
+    }
+    if (K > 0) {   // a quantized matrix: size must match the GGUF blob size (src/gguf.rs:172-191)
+        if (ggml_type_size(t, (size_t)K * N * mats) != bytes) return -4;
+    }
+    if (!dst->upload(host, bytes)) return -5;   // cudaMalloc failed (src/cuda.rs:79)
+    dst->ggml_type = t;
+    // the one-line addition to upload_ti (src/cuda.rs:170-172): the embedding table stays raw
+    if (K > 0 && repack && role != QH_EMBED) cuda_repack_weights(t, dst->ptr, K, N, mats);
+    return 0;
+}
+
+int qh_finalize(qh_model *m)
+{
+    if (!m) return -1;
+    const qh_config &c = m->c;
+    const int d = c.embed_dim, q_d = m->q_d(), kv_d = m->kv_d(), fd = c.ffn_dim, nh = c.n_heads;
+    const size_t mseq = c.max_seq;
+    bool ok = m->d_hidden.alloc_f32(d) && m->d_norm_out.alloc_f32(d) && m->d_q.alloc_f32(q_d) &&
+              m->d_k.alloc_f32(kv_d) && m->d_v.alloc_f32(kv_d) && m->d_attn_out.alloc_f32(q_d) &&
+              m->d_scores.alloc_f32(nh * mseq) && m->d_gate.alloc_f32(fd) && m->d_up.alloc_f32(fd) &&
+              m->d_expert_out.alloc_f32(fd) && m->d_expert_acc.alloc_f32(d) && m->d_gate_all.alloc_f32(4 * (size_t)fd) &&
+              m->d_up_all.alloc_f32(4 * (size_t)fd) && m->d_expert_out_all.alloc_f32(4 * (size_t)fd) &&
+              m->d_down_all.alloc_f32(4 * (size_t)d) && m->d_router_logits.alloc_f32(std::max(c.n_experts, 1)) &&
+              m->d_logits.alloc_f32(c.vocab_size);
+    if (!ok) return -2;
+    m->kv_k.resize(c.n_layers);
+    m->kv_v.resize(c.n_layers);
+    std::vector<float> zeros(std::max(q_d, kv_d), 0.f), no_sink(nh, -INFINITY);
+    for (int l = 0; l < c.n_layers; l++) {
+        if (!m->kv_k[l].alloc_f32(mseq * kv_d) || !m->kv_v[l].alloc_f32(mseq * kv_d)) return -3;
+        Layer &L = m->L[l];
+        // absent q/k/v biases are uploaded as zero vectors and added anyway (src/main.rs:366-368)
+        if (L.q_bias.empty()) L.q_bias.upload(zeros.data(), (size_t)q_d * 4);
+        if (L.k_bias.empty()) L.k_bias.upload(zeros.data(), (size_t)kv_d * 4);
+        if (L.v_bias.empty()) L.v_bias.upload(zeros.data(), (size_t)kv_d * 4);
+        if (L.sinks.empty()) L.sinks.upload(no_sink.data(), (size_t)nh * 4);   // src/cuda.rs:456-464
+    }
+    cuda_sync();
+    m->finalized = true;
+    return quartz_last_error() == 0 ? 0 : -4;
+}
+
+int qh_set_kv(qh_model *m, int layer, const float *k, const float *v, int n_pos)
+{
+    if (!m || !m->finalized || layer < 0 || layer >= m->c.n_layers || n_pos > m->c.max_seq) return -1;
+    cuda_h2d(m->kv_k[layer].ptr, k, (size_t)n_pos * m->kv_d() * 4);
+    cuda_h2d(m->kv_v[layer].ptr, v, (size_t)n_pos * m->kv_d() * 4);
+    return 0;
+}
+
+static int attn_start(const qh_config &c, int layer, int pos)   // src/main.rs:231-237
+{
+    if (c.swa_window > 0 && layer % 2 == 0) return std::max(0, pos + 1 - c.swa_window);
+    return 0;
+}
+
+static float attn_scale(const qh_config &c)   // src/cuda.rs:532-536
+{
+    float mscale2 = 1.f;
+    if (c.yarn_scale > 1.f && c.yarn_orig_ctx > 0) {
+        float ms = 1.f + 0.1f * logf(c.yarn_scale);
+        mscale2 = ms * ms;
+    }
+    return (1.f / sqrtf((float)c.head_dim)) * mscale2;
+}
+
+// Router: logits to host, top-k, softmax weights (src/cuda.rs:673-701)
+static void route(qh_model *m, int l, std::vector<std::pair<int, float>> &top, std::vector<float> &rw)
+{
+    const qh_config &c = m->c;
+    Layer &L = m->L[l];
+    const int ne = c.n_experts, d = c.embed_dim;
+    cuda_gemv(0, L.router_w.u8(), m->d_norm_out.f(), m->d_router_logits.f(), d, ne);
+    std::vector<float> logits(ne);
+    cuda_d2h(logits.data(), m->d_router_logits.ptr, (size_t)ne * 4);
+    cuda_sync();
+    for (size_t i = 0; i < L.router_b.size() && i < (size_t)ne; i++) logits[i] += L.router_b[i];
+    std::vector<std::pair<int, float>> idx(ne);
+    for (int i = 0; i < ne; i++) idx[i] = {i, logits[i]};
+    std::stable_sort(idx.begin(), idx.end(), [](const std::pair<int, float> &a, const std::pair<int, float> &b) { return a.second > b.second; });
+    top.assign(idx.begin(), idx.begin() + c.n_experts_used);
+    std::vector<float> e(top.size());
+    float denom = 0.f;
+    if (c.moe_renorm) {
+        float mx = -INFINITY;
+        for (auto &p : top) mx = std::max(mx, p.second);
+        for (size_t i = 0; i < top.size(); i++) { e[i] = expf(top[i].second - mx); denom += e[i]; }
+    } else {
+        float mx = -INFINITY;
+        for (float v : logits) mx = std::max(mx, v);
+        for (float v : logits) denom += expf(v - mx);
+        for (size_t i = 0; i < top.size(); i++) e[i] = expf(top[i].second - mx);
+    }
+    rw.resize(top.size());
+    for (size_t i = 0; i < top.size(); i++) rw[i] = e[i] / denom;
+}
+
+// MoE FFN of one layer on d_norm_out -> d_expert_acc (src/cuda.rs:667-798)
+static void moe_ffn(qh_model *m, int l)
+{
+    const qh_config &c = m->c;
+    Layer &L = m->L[l];
+    const int d = c.embed_dim, fd = c.ffn_dim;
+    std::vector<std::pair<int, float>> top;
+    std::vector<float> rw;
+    route(m, l, top, rw);
+    cuda_vec_zero(m->d_expert_acc.f(), d);
+    const uint32_t tg = L.moe_gate.ggml_type, tu = L.moe_up.ggml_type, td = L.moe_down.ggml_type;
+    const size_t sg = ggml_type_size(tg, (size_t)d * fd), su = ggml_type_size(tu, (size_t)d * fd),
+                 sd = ggml_type_size(td, (size_t)fd * d);
+    const float *xn = m->d_norm_out.f();
+    const int n_act = (int)top.size();
+    if (n_act == 4) {
+        // four experts per launch (src/cuda.rs:714-761)
+        const uint8_t *gp[4], *up[4], *dp[4];
+        for (int k = 0; k < 4; k++) {
+            gp[k] = L.moe_gate.u8() + top[k].first * sg;
+            up[k] = L.moe_up.u8() + top[k].first * su;
+            dp[k] = L.moe_down.u8() + top[k].first * sd;
+        }
+        float *go = m->d_gate_all.f(), *uo = m->d_up_all.f(), *eo = m->d_expert_out_all.f(), *doo = m->d_down_all.f();
+        cuda_gemv_moe4(tg, gp[0], gp[1], gp[2], gp[3], xn, xn, xn, xn, go, go + fd, go + 2 * fd, go + 3 * fd, 4, d, fd);
+        cuda_gemv_moe4(tu, up[0], up[1], up[2], up[3], xn, xn, xn, xn, uo, uo + fd, uo + 2 * fd, uo + 3 * fd, 4, d, fd);
+        for (int k = 0; k < 4; k++) {
+            const int e = top[k].first;
+            if (!L.moe_gate_bias.empty()) cuda_vec_add(go + (size_t)k * fd, L.moe_gate_bias.f() + (size_t)e * fd, fd);
+            if (!L.moe_up_bias.empty()) cuda_vec_add(uo + (size_t)k * fd, L.moe_up_bias.f() + (size_t)e * fd, fd);
+            if (c.clamped_swiglu) cuda_swiglu_oai(eo + (size_t)k * fd, go + (size_t)k * fd, uo + (size_t)k * fd, fd);
+            else cuda_swiglu(eo + (size_t)k * fd, go + (size_t)k * fd, uo + (size_t)k * fd, fd);
+        }
+        cuda_gemv_moe4(td, dp[0], dp[1], dp[2], dp[3], eo, eo + fd, eo + 2 * fd, eo + 3 * fd, doo, doo + d, doo + 2 * d,
+                       doo + 3 * d, 4, fd, d);
+        for (int k = 0; k < 4; k++) {
+            if (!L.moe_down_bias.empty()) cuda_vec_add(doo + (size_t)k * d, L.moe_down_bias.f() + (size_t)top[k].first * d, d);
+            cuda_vec_scale_add(m->d_expert_acc.f(), doo + (size_t)k * d, rw[k], d);
+        }
+    } else {
+        // any active-expert count, one expert at a time (src/cuda.rs:762-794)
+        float *g1 = m->d_gate.f(), *u1 = m->d_up.f(), *e1 = m->d_expert_out.f(), *dn = m->d_down_all.f();
+        for (int k = 0; k < n_act; k++) {
+            const int e = top[k].first;
+            cuda_gemv(tg, L.moe_gate.u8() + e * sg, xn, g1, d, fd);
+            if (!L.moe_gate_bias.empty()) cuda_vec_add(g1, L.moe_gate_bias.f() + (size_t)e * fd, fd);
+            cuda_gemv(tu, L.moe_up.u8() + e * su, xn, u1, d, fd);
+            if (!L.moe_up_bias.empty()) cuda_vec_add(u1, L.moe_up_bias.f() + (size_t)e * fd, fd);
+            if (c.clamped_swiglu) cuda_swiglu_oai(e1, g1, u1, fd);
+            else cuda_swiglu(e1, g1, u1, fd);
+            cuda_gemv(td, L.moe_down.u8() + e * sd, e1, dn, fd, d);
+            if (!L.moe_down_bias.empty()) cuda_vec_add(dn, L.moe_down_bias.f() + (size_t)e * d, d);
+            cuda_vec_scale_add(m->d_expert_acc.f(), dn, rw[k], d);
+        }
+    }
+}
+
+// The reference sequence (src/cuda.rs:538-843), on-device part.
+static void step_reference(qh_model *m, int token, int pos, bool need_logits)
+{
+    const qh_config &c = m->c;
+    const int d = c.embed_dim, h = c.n_heads, kv = c.n_kv_heads, hd = c.head_dim, q_d = m->q_d(), kv_d = m->kv_d(),
+              fd = c.ffn_dim, seq = pos + 1;
+    const float scale = attn_scale(c);
+    // The reference dequantizes the embedding row on the CPU and uploads it (src/cuda.rs:538-545);
+    // here the table is resident and cuda_embed_lookup produces the same f32 row bit for bit.
+    cuda_embed_lookup(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, token, d);
+    for (int l = 0; l < c.n_layers; l++) {
+        Layer &L = m->L[l];
+        cuda_rms_norm(m->d_norm_out.f(), m->d_hidden.f(), L.attn_norm.f(), d);
+        cuda_gemv(L.q.ggml_type, L.q.u8(), m->d_norm_out.f(), m->d_q.f(), d, q_d);
+        cuda_gemv(L.k.ggml_type, L.k.u8(), m->d_norm_out.f(), m->d_k.f(), d, kv_d);
+        cuda_gemv(L.v.ggml_type, L.v.u8(), m->d_norm_out.f(), m->d_v.f(), d, kv_d);
+        cuda_vec_add(m->d_q.f(), L.q_bias.f(), q_d);
+        cuda_vec_add(m->d_k.f(), L.k_bias.f(), kv_d);
+        cuda_vec_add(m->d_v.f(), L.v_bias.f(), kv_d);
+        if (!L.q_norm.empty()) {   // QK-norm before RoPE (src/cuda.rs:576-599)
+            if ((int)L.q_norm_len == hd) for (int hh = 0; hh < h; hh++) cuda_rms_norm(m->d_q.f() + hh * hd, m->d_q.f() + hh * hd, L.q_norm.f(), hd);
+            else cuda_rms_norm(m->d_q.f(), m->d_q.f(), L.q_norm.f(), q_d);
+        }
+        if (!L.k_norm.empty()) {
+            if ((int)L.k_norm_len == hd) for (int hh = 0; hh < kv; hh++) cuda_rms_norm(m->d_k.f() + hh * hd, m->d_k.f() + hh * hd, L.k_norm.f(), hd);
+            else cuda_rms_norm(m->d_k.f(), m->d_k.f(), L.k_norm.f(), kv_d);
+        }
+        cuda_rope_yarn(m->d_q.f(), h, hd, pos, c.rope_theta, c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
+        cuda_rope_yarn(m->d_k.f(), kv, hd, pos, c.rope_theta, c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
+        cuda_kv_append(m->kv_k[l].f(), m->kv_v[l].f(), m->d_k.f(), m->d_v.f(), pos, kv_d);
+        const int k_start = attn_start(c, l, pos), seq_a = seq - k_start;
+        const float *kc = m->kv_k[l].f() + (size_t)k_start * kv_d, *vc = m->kv_v[l].f() + (size_t)k_start * kv_d;
+        cuda_attn_score_all(m->d_scores.f(), m->d_q.f(), kc, h, kv, seq_a, hd, kv_d, c.max_seq, scale);
+        cuda_softmax_sink_all(m->d_scores.f(), h, seq_a, c.max_seq, L.sinks.f());
+        cuda_attn_values_all(m->d_attn_out.f(), m->d_scores.f(), vc, h, kv, seq_a, hd, kv_d, c.max_seq);
+        cuda_gemv(L.o.ggml_type, L.o.u8(), m->d_attn_out.f(), m->d_norm_out.f(), q_d, d);
+        if (!L.o_bias.empty()) cuda_vec_add(m->d_norm_out.f(), L.o_bias.f(), d);
+        cuda_vec_add(m->d_hidden.f(), m->d_norm_out.f(), d);
+        cuda_rms_norm(m->d_norm_out.f(), m->d_hidden.f(), L.ffn_norm.f(), d);
+        if (c.n_experts > 0) {
+            moe_ffn(m, l);
+            cuda_vec_add(m->d_hidden.f(), m->d_expert_acc.f(), d);
+        } else {
+            cuda_gemv(L.gate.ggml_type, L.gate.u8(), m->d_norm_out.f(), m->d_gate.f(), d, fd);
+            cuda_gemv(L.up.ggml_type, L.up.u8(), m->d_norm_out.f(), m->d_up.f(), d, fd);
+            cuda_swiglu(m->d_expert_out.f(), m->d_gate.f(), m->d_up.f(), fd);
+            cuda_gemv(L.down.ggml_type, L.down.u8(), m->d_expert_out.f(), m->d_norm_out.f(), fd, d);
+            cuda_vec_add(m->d_hidden.f(), m->d_norm_out.f(), d);
+        }
+    }
+    if (!need_logits) return;
+    cuda_rms_norm(m->d_norm_out.f(), m->d_hidden.f(), m->final_norm.f(), d);
+    cuda_gemv(m->lm_head.ggml_type, m->lm_head.u8(), m->d_norm_out.f(), m->d_logits.f(), d, c.vocab_size);
+}
+
+// Can this model take the fused sequence?  Dense FFN, no QK-norm, no biases to add (absent
+// biases are zero vectors in the reference, so skipping them changes nothing), every
+// projection served by the streaming kernel, q rows splittable into kv-sized slices.
+static bool fusable(qh_model *m)
+{
+    const qh_config &c = m->c;
+    if (c.n_experts > 0 || c.head_dim > 128 || c.head_dim % 32 || c.embed_dim % 64 || c.ffn_dim % 64) return false;
+    if (m->q_d() % m->kv_d() != 0 || m->q_d() / m->kv_d() + 2 > 8) return false;
+    for (auto &L : m->L) {
+        if (!L.q_norm.empty() || !L.k_norm.empty() || L.has_qkv_bias || !L.o_bias.empty()) return false;
+        if (L.q.ggml_type != L.k.ggml_type || L.q.ggml_type != L.v.ggml_type || L.gate.ggml_type != L.up.ggml_type) return false;
+        if (!cuda_gemv_q_supported(L.q.ggml_type, L.q.u8(), c.embed_dim) || !cuda_gemv_q_supported(L.k.ggml_type, L.k.u8(), c.embed_dim) ||
+            !cuda_gemv_q_supported(L.v.ggml_type, L.v.u8(), c.embed_dim) || !cuda_gemv_q_supported(L.o.ggml_type, L.o.u8(), m->q_d()) ||
+            !cuda_gemv_q_supported(L.gate.ggml_type, L.gate.u8(), c.embed_dim) || !cuda_gemv_q_supported(L.up.ggml_type, L.up.u8(), c.embed_dim) ||
+            !cuda_gemv_q_supported(L.down.ggml_type, L.down.u8(), c.ffn_dim))
+            return false;
+    }
+    return cuda_gemv_q_supported(m->lm_head.ggml_type, m->lm_head.u8(), c.embed_dim) != 0;
+}
+
+// The fused sequence: ten launches per layer instead of twenty-one (+ seven conversions).
+static void step_fused(qh_model *m, int token, int pos, bool need_logits)
+{
+    const qh_config &c = m->c;
+    const int d = c.embed_dim, h = c.n_heads, kv = c.n_kv_heads, hd = c.head_dim, q_d = m->q_d(), kv_d = m->kv_d(),
+              fd = c.ffn_dim, seq = pos + 1;
+    const float scale = attn_scale(c);
+    const int q_slices = q_d / kv_d;
+    const size_t q_slice_bytes = ggml_type_size(m->L[0].q.ggml_type, (size_t)d * kv_d);
+    cuda_embed_lookup(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, token, d);
+    for (int l = 0; l < c.n_layers; l++) {
+        Layer &L = m->L[l];
+        cuda_rms_norm_q(m->d_hidden.f(), L.attn_norm.f(), d, 0, nullptr);
+        // q (as kv_d-row slices), k and v in one launch
+        const uint8_t *W[8];
+        float *Y[8];
+        int S[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int n = 0;
+        for (int s = 0; s < q_slices; s++) { W[n] = L.q.u8() + s * q_slice_bytes; Y[n] = m->d_q.f() + (size_t)s * kv_d; n++; }
+        W[n] = L.k.u8(); Y[n] = m->d_k.f(); n++;
+        W[n] = L.v.u8(); Y[n] = m->d_v.f(); n++;
+        cuda_gemv_q(L.q.ggml_type, n, W, S, Y, d, kv_d, 0);
+        cuda_rope_kv(m->d_q.f(), m->d_k.f(), m->d_v.f(), m->kv_k[l].f(), m->kv_v[l].f(), h, kv, hd, pos, c.rope_theta,
+                     c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
+        const int k_start = attn_start(c, l, pos), seq_a = seq - k_start;
+        cuda_attn_decode(m->d_attn_out.f(), m->d_q.f(), m->kv_k[l].f() + (size_t)k_start * kv_d,
+                         m->kv_v[l].f() + (size_t)k_start * kv_d, h, kv, seq_a, hd, kv_d, scale, L.sinks.f(), 1);
+        {   // output projection, residual added in the epilogue
+            const uint8_t *w1[1] = {L.o.u8()};
+            float *y1[1] = {m->d_hidden.f()};
+            int s1[1] = {1};
+            cuda_gemv_q(L.o.ggml_type, 1, w1, s1, y1, q_d, d, 1);
+        }
+        cuda_rms_norm_q(m->d_hidden.f(), L.ffn_norm.f(), d, 0, nullptr);
+        {
+            const uint8_t *w2[2] = {L.gate.u8(), L.up.u8()};
+            float *y2[2] = {m->d_gate.f(), m->d_up.f()};
+            int s2[2] = {0, 0};
+            cuda_gemv_q(L.gate.ggml_type, 2, w2, s2, y2, d, fd, 0);
+        }
+        cuda_swiglu_q(m->d_gate.f(), m->d_up.f(), fd, 2, 0);
+        {
+            const uint8_t *w1[1] = {L.down.u8()};
+            float *y1[1] = {m->d_hidden.f()};
+            int s1[1] = {2};
+            cuda_gemv_q(L.down.ggml_type, 1, w1, s1, y1, fd, d, 1);
+        }
+    }
+    if (!need_logits) return;
+    cuda_rms_norm_q(m->d_hidden.f(), m->final_norm.f(), d, 0, nullptr);
+    const uint8_t *w1[1] = {m->lm_head.u8()};
+    float *y1[1] = {m->d_logits.f()};
+    int s1[1] = {0};
+    cuda_gemv_q(m->lm_head.ggml_type, 1, w1, s1, y1, d, c.vocab_size, 0);
+}
+
+int qh_step_device(qh_model *m, int token, int pos, int fused)
+{
+    if (!m || !m->finalized || token < 0 || token >= m->c.vocab_size) return -1;
+    if (pos >= m->c.max_seq) {   // src/cuda.rs:517-520: clamp with a warning, never write out of bounds
+        fprintf(stderr, "KV cache full at pos %d (max_seq=%d); clamping to avoid OOB\n", pos, m->c.max_seq);
+        pos = m->c.max_seq - 1;
+    }
+    const long long before = quartz_launch_count();
+    if (!fused || !fusable(m)) {
+        step_reference(m, token, pos, true);
+        m->last_launches = quartz_launch_count() - before;
+        return 0;
+    }
+    // one recorded graph per (token-independent) position; the embedding row is looked up outside
+    auto key = std::make_pair(pos, token);
+    auto it = m->graphs.find(key);
+    if (it == m->graphs.end()) {
+        step_fused(m, token, pos, true);   // eager once: creates every scratch buffer, warms the kernels
+        cuda_sync();
+        const long long b2 = quartz_launch_count();
+        if (!quartz_graph_begin()) return -2;
+        step_fused(m, token, pos, true);
+        void *g = quartz_graph_end();
+        if (!g) return -3;
+        m->last_launches = quartz_launch_count() - b2;
+        if (m->graphs.size() > 64) {
+            for (auto &old : m->graphs) quartz_graph_destroy(old.second);
+            m->graphs.clear();
+        }
+        it = m->graphs.emplace(key, g).first;
+    }
+    quartz_graph_launch(it->second);
+    return 0;
+}
+
+static int step_host(qh_model *m, int token, int pos, int need_logits, float *logits_host, int fused)
+{
+    int rc = qh_step_device(m, token, pos, fused);
+    if (rc) return rc;
+    if (need_logits && logits_host) cuda_d2h(logits_host, m->d_logits.ptr, (size_t)m->c.vocab_size * 4);
+    cuda_sync();
+    return quartz_last_error() == 0 ? 0 : -10;
+}
+
+int qh_forward_step(qh_model *m, int token, int pos, int need_logits, float *logits_host)
+{
+    return step_host(m, token, pos, need_logits, logits_host, 0);
+}
+
+int qh_forward_step_fused(qh_model *m, int token, int pos, int need_logits, float *logits_host)
+{
+    return step_host(m, token, pos, need_logits, logits_host, 1);
+}
+
+int qh_read_hidden(qh_model *m, float *host)
+{
+    if (!m || !m->finalized) return -1;
+    cuda_d2h(host, m->d_hidden.ptr, (size_t)m->c.embed_dim * 4);
+    cuda_sync();
+    return 0;
+}
+
+long long qh_launches_last_step(qh_model *m) { return m ? m->last_launches : 0; }
+
+}  // extern "C"

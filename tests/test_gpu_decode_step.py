@@ -1,0 +1,216 @@
+"""GPU tests of the decode step: the C++ host mirror of GpuForwardState::forward_gpu_step
+(src/cuda.rs:507-851) over the C ABI -- reference sequence and fused/graph sequence -- against the
+numpy restatement of the reference's CPU forward (src/main.rs:1045-1120).
+
+Bar: logits within 5e-3 of max|logit| (the end-to-end analogue of the reference's --verify-gemv
+relative check, src/main.rs:2653-2659, with room for 2 x n_layers chained f32 GEMVs); the fused
+sequence and the reference sequence agree to 1e-3 of max|logit|."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float(np.abs(a.astype(np.float64) - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def _tiny_dense(gpu, repack=True, types=None, **over):
+    """Llama-shaped miniature.  Q6_K planes need in_dim % 2048 == 0, hence 2048 / 4096."""
+    from saient_quartz_b200.host_model import HostModel, Q4K_M_TYPES
+    cfg = dict(vocab_size=320, embed_dim=2048, n_heads=16, n_kv_heads=4, n_layers=3, ffn_dim=4096, head_dim=128,
+               rope_theta=500000.0, max_seq=96)
+    cfg.update(over)
+    m = HostModel(repack=repack, keep_host=True, types=types or Q4K_M_TYPES, **cfg)
+    m.fill_synthetic()
+    return m
+
+
+def _ref_for(m, oracle_mod, kv):
+    from oracle.forward_ref import RefModel
+    r = RefModel(m.cfg, m.host)
+    for l, (k, v) in enumerate(kv):
+        r.set_kv(l, k, v)
+    return r
+
+
+@pytest.mark.parametrize("repack", [True, False])
+def test_tiny_dense_model_both_sequences(gpu, oracle_mod, repack):
+    m = _tiny_dense(gpu, repack=repack)
+    kv = m.fill_kv(40, keep=True)
+    ref = _ref_for(m, oracle_mod, kv)
+    want = ref.forward(17, 40)
+    got = m.step(17, 40, fused=False)
+    assert _rel(got, want) < 5e-3
+    n_ref = m.launches()
+    got_f = m.step(17, 40, fused=True)
+    assert _rel(got_f, want) < 5e-3
+    assert _rel(got_f, got) < 1e-3
+    if repack:
+        assert m.launches() < n_ref          # the fused sequence needs fewer launches
+    # the recorded graph replays to the same numbers
+    again = m.step(17, 40, fused=True)
+    assert np.array_equal(again, got_f)
+    gpu.check_error()
+
+
+def test_small_dims_q4k_q8_0(gpu, oracle_mod):
+    """Rows narrower than a warp of 64-weight units (in_dim 512 / 1024): the sub-warp row mode."""
+    types = dict(Q=12, K=12, V=12, O=12, GATE=12, UP=12, DOWN=8, LM_HEAD=8, EMBED=14)
+    m = _tiny_dense(gpu, types=types, embed_dim=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=1024)
+    kv = m.fill_kv(33, keep=True)
+    want = _ref_for(m, oracle_mod, kv).forward(5, 33)
+    got, n_ref = m.step(5, 33, fused=False), m.launches()
+    got_f = m.step(5, 33, fused=True)
+    assert _rel(got, want) < 5e-3 and _rel(got_f, want) < 5e-3
+    assert m.launches() < n_ref
+    gpu.check_error()
+
+
+def test_decode_several_positions_and_neox(gpu, oracle_mod):
+    m = _tiny_dense(gpu, rope_neox=1)
+    kv = m.fill_kv(5, keep=True)
+    ref = _ref_for(m, oracle_mod, kv)
+    for pos, tok in ((5, 3), (6, 300), (7, 0)):
+        want = ref.forward(tok, pos)
+        got = m.step(tok, pos, fused=(pos % 2 == 0))
+        assert _rel(got, want) < 5e-3, pos
+    gpu.check_error()
+
+
+def test_first_token_empty_cache(gpu, oracle_mod):
+    m = _tiny_dense(gpu)
+    ref = _ref_for(m, oracle_mod, [])
+    assert _rel(m.step(9, 0, fused=False), ref.forward(9, 0)) < 5e-3
+    m2 = _tiny_dense(gpu)
+    assert _rel(m2.step(9, 0, fused=True), _ref_for(m2, oracle_mod, []).forward(9, 0)) < 5e-3
+
+
+@pytest.mark.parametrize("n_used", [2, 4])
+def test_tiny_moe_model(gpu, oracle_mod, n_used):
+    """MoE branch (src/cuda.rs:667-798): general path (top-2) and the four-expert launch (top-4),
+    biases, sinks, QK-norm, YaRN and a sliding window switched on together."""
+    from saient_quartz_b200 import synth
+    from saient_quartz_b200.host_model import HostModel
+    cfg = dict(vocab_size=256, embed_dim=256, n_heads=4, n_kv_heads=2, n_layers=2, ffn_dim=512, head_dim=64,
+               rope_theta=150000.0, max_seq=64, n_experts=6, n_experts_used=n_used, moe_renorm=int(n_used == 2),
+               clamped_swiglu=int(n_used == 4), swa_window=8, rope_neox=1, yarn_scale=4.0, yarn_orig_ctx=32)
+    m = HostModel(keep_host=True, **cfg)
+    rng = np.random.Generator(np.random.PCG64([77, n_used]))
+    d, fd, q_d, kv_d, ne = 256, 512, 256, 128, 6
+    tid = [500]
+
+    def w(role, l, t, K, N):
+        tid[0] += 1
+        m.set(role, l, t, synth.make_weights(t, K, N, tensor_id=tid[0]))
+
+    def f(role, l, n, scale=1.0, base=0.0):
+        m.set(role, l, 0, (base + scale * rng.standard_normal(n)).astype(np.float32))
+
+    w("EMBED", 0, 7, d, 256)
+    for l in range(2):
+        w("Q", l, 12, d, q_d); w("K", l, 14, d, kv_d); w("V", l, 8, d, kv_d); w("O", l, 7, q_d, d)
+        f("ATTN_NORM", l, d, 0.1, 1.0); f("FFN_NORM", l, d, 0.1, 1.0)
+        f("Q_NORM", l, 64, 0.1, 1.0); f("K_NORM", l, kv_d, 0.1, 1.0)
+        f("Q_BIAS", l, q_d, 0.01); f("K_BIAS", l, kv_d, 0.01); f("V_BIAS", l, kv_d, 0.01); f("O_BIAS", l, d, 0.01)
+        f("SINKS", l, 4)
+        w("MOE_GATE", l, 17 if l else 12, d, fd * ne); w("MOE_UP", l, 12, d, fd * ne); w("MOE_DOWN", l, 14, fd, d * ne)
+        f("ROUTER_W", l, ne * d, 0.2); f("ROUTER_B", l, ne, 0.1)
+        f("MOE_GATE_BIAS", l, ne * fd, 0.01); f("MOE_UP_BIAS", l, ne * fd, 0.01); f("MOE_DOWN_BIAS", l, ne * d, 0.01)
+    f("FINAL_NORM", 0, d, 0.1, 1.0)
+    w("LM_HEAD", 0, 30, d, 256)
+    m.finalize()
+    kv = m.fill_kv(20, keep=True)
+    ref = _ref_for(m, oracle_mod, kv)
+    for pos, tok in ((20, 11), (21, 200)):
+        want = ref.forward(tok, pos)
+        got = m.step(tok, pos, fused=True)   # not fusable: must fall back to the reference sequence
+        assert _rel(got, want) < 5e-3, (n_used, pos)
+    gpu.check_error()
+
+
+def test_fused_entry_points_match_unfused(gpu):
+    """cuda_rms_norm_q / cuda_swiglu_q / cuda_quantize_x + cuda_gemv_q reproduce cuda_rms_norm /
+    cuda_swiglu + cuda_gemv bit for bit (same conversion, same kernels); accumulate adds."""
+    import ctypes as C
+    from saient_quartz_b200 import synth
+    L = gpu.lib()
+    K, N = 4096, 1024
+    w = synth.make_weights(12, K, 2 * N, tensor_id=601)
+    dw = gpu.GpuBuf.upload(w)
+    x, g = synth.make_x(K, tensor_id=602), synth.make_x(K, tensor_id=603)
+    nw = (1.0 + 0.1 * synth.make_x(K, tensor_id=604)).astype(np.float32)
+    dx, dg, dn = gpu.GpuBuf.upload(x), gpu.GpuBuf.upload(g), gpu.GpuBuf.upload(nw)
+    dt, dy, dy2 = gpu.GpuBuf.alloc_f32(K), gpu.GpuBuf.alloc_f32(2 * N), gpu.GpuBuf.alloc_f32(2 * N)
+    half = synth.type_size(12, K * N)
+
+    def gemv_q(slot, acc):
+        W = (C.c_void_p * 2)(dw.ptr, dw.ptr + half)
+        Y = (C.c_void_p * 2)(dy2.ptr, dy2.ptr + 4 * N)
+        S = (C.c_int * 2)(slot, slot)
+        L.cuda_gemv_q(12, 2, W, S, Y, K, N, acc)
+
+    for mode in ("norm", "swiglu", "plain"):
+        if mode == "norm":
+            L.cuda_rms_norm(dt.ptr, dx.ptr, dn.ptr, K)
+            L.cuda_rms_norm_q(dx.ptr, dn.ptr, K, 1, None)
+        elif mode == "swiglu":
+            L.cuda_swiglu(dt.ptr, dg.ptr, dx.ptr, K)
+            L.cuda_swiglu_q(dg.ptr, dx.ptr, K, 1, 0)
+        else:
+            L.cuda_vec_zero(dt.ptr, K)
+            L.cuda_vec_add(dt.ptr, dx.ptr, K)
+            L.cuda_quantize_x(dx.ptr, K, 1)
+        L.cuda_gemv(12, dw.ptr, dt.ptr, dy.ptr, K, 2 * N)
+        gemv_q(1, 0)
+        a, b = dy.download(), dy2.download()
+        assert np.array_equal(a, b), mode
+        gemv_q(1, 1)
+        assert np.array_equal(dy2.download(), b + b), mode
+    gpu.check_error()
+
+
+def test_attn_decode_matches_three_kernel_attention(gpu):
+    L = gpu.lib()
+    r = np.random.Generator(np.random.PCG64([0xA77]))
+    for (nh, nkv, hd, seq, max_seq, sink) in [(32, 8, 128, 1025, 1100, False), (8, 8, 64, 33, 64, True),
+                                              (12, 2, 96, 70, 128, True), (4, 1, 128, 1, 16, False)]:
+        kv_dim = nkv * hd
+        kc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+        vc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+        q = r.standard_normal(nh * hd, dtype=np.float32)
+        sinks = r.standard_normal(nh, dtype=np.float32) if sink else np.full(nh, -np.inf, np.float32)
+        dk, dv, dq, ds = gpu.GpuBuf.upload(kc), gpu.GpuBuf.upload(vc), gpu.GpuBuf.upload(q), gpu.GpuBuf.upload(sinks)
+        dsc, d1, d2 = gpu.GpuBuf.alloc_f32(nh * max_seq), gpu.GpuBuf.alloc_f32(nh * hd), gpu.GpuBuf.alloc_f32(nh * hd)
+        scale = np.float32(1.0 / np.sqrt(hd))
+        L.cuda_attn_score_all(dsc.ptr, dq.ptr, dk.ptr, nh, nkv, seq, hd, kv_dim, max_seq, scale)
+        L.cuda_softmax_sink_all(dsc.ptr, nh, seq, max_seq, ds.ptr)
+        L.cuda_attn_values_all(d1.ptr, dsc.ptr, dv.ptr, nh, nkv, seq, hd, kv_dim, max_seq)
+        L.cuda_attn_decode(d2.ptr, dq.ptr, dk.ptr, dv.ptr, nh, nkv, seq, hd, kv_dim, scale, ds.ptr, -1)
+        a, b = d1.download(), d2.download()
+        assert np.abs(a - b).max() <= 2e-5 * max(np.abs(a).max(), 1e-30)
+    gpu.check_error()
+
+
+def test_rope_kv_matches_separate_calls(gpu):
+    L = gpu.lib()
+    r = np.random.Generator(np.random.PCG64([0xB0B]))
+    for (nh, nkv, hd, pos, neox, ys, yo) in [(32, 8, 128, 1024, 0, 1.0, 0), (8, 2, 64, 7, 1, 8.0, 64)]:
+        kv_dim = nkv * hd
+        q, k, v = (r.standard_normal(n, dtype=np.float32) for n in (nh * hd, kv_dim, kv_dim))
+        dq1, dk1, dv1 = gpu.GpuBuf.upload(q), gpu.GpuBuf.upload(k), gpu.GpuBuf.upload(v)
+        dq2, dk2 = gpu.GpuBuf.upload(q), gpu.GpuBuf.upload(k)
+        kc1, vc1 = gpu.GpuBuf.alloc_f32((pos + 1) * kv_dim), gpu.GpuBuf.alloc_f32((pos + 1) * kv_dim)
+        kc2, vc2 = gpu.GpuBuf.alloc_f32((pos + 1) * kv_dim), gpu.GpuBuf.alloc_f32((pos + 1) * kv_dim)
+        for b in (kc1, vc1, kc2, vc2):
+            L.cuda_vec_zero(b.ptr, (pos + 1) * kv_dim)
+        L.cuda_rope_yarn(dq1.ptr, nh, hd, pos, np.float32(5e5), np.float32(ys), yo, neox)
+        L.cuda_rope_yarn(dk1.ptr, nkv, hd, pos, np.float32(5e5), np.float32(ys), yo, neox)
+        L.cuda_kv_append(kc1.ptr, vc1.ptr, dk1.ptr, dv1.ptr, pos, kv_dim)
+        L.cuda_rope_kv(dq2.ptr, dk2.ptr, dv1.ptr, kc2.ptr, vc2.ptr, nh, nkv, hd, pos, np.float32(5e5), np.float32(ys),
+                       yo, neox)
+        assert np.array_equal(dq1.download(), dq2.download())
+        assert np.array_equal(dk1.download(), dk2.download())
+        assert np.array_equal(kc1.download(), kc2.download())
+        assert np.array_equal(vc1.download(), vc2.download())
+    gpu.check_error()
