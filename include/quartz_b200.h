@@ -169,6 +169,10 @@ void cuda_attn_decode(float *out, const float *q, const float *k_cache, const fl
  * instead of executed; copies and cuda_sync must stay outside, and every scratch buffer must
  * already exist (run the sequence once eagerly first).  end returns an executable graph (NULL on
  * failure); launch replays it, ordered with the default stream. */
+/* 1 (default): kernels recorded into a graph are launched as programmatic dependents, so each
+ * may begin (and a GEMV may start streaming its weights) while its predecessor drains; 0: plain
+ * serial edges.  Results are identical. */
+void quartz_set_pdl(int on);
 int quartz_graph_begin(void);
 void *quartz_graph_end(void);
 void quartz_graph_launch(void *graph_exec);

@@ -74,6 +74,7 @@ _SIGS = {
                             C.c_int]),
     "cuda_attn_decode": (None, [C.c_void_p] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float,
                                 C.c_void_p, C.c_int]),
+    "quartz_set_pdl": (None, [C.c_int]),
     "quartz_graph_begin": (C.c_int, []),
     "quartz_graph_end": (C.c_void_p, []),
     "quartz_graph_launch": (None, [C.c_void_p]),

@@ -36,6 +36,14 @@ extern long long g_launch_count;   // kernels launched by this library so far
         QZ_CUDA_CHECK(cudaGetLastError()); \
     } while (0)
 
+// Programmatic dependent launch: a kernel launched with the "programmatic stream serialization"
+// attribute may begin while its predecessor in the stream is still running; pdl_wait() blocks until
+// the predecessor has completed and its writes are visible (a no-op for ordinary launches), and
+// pdl_trigger() lets the successor begin.  Code before pdl_wait() may touch only data no kernel writes
+// (weights, codebooks).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float h2f(uint16_t bits)
 {
     return __half2float(__ushort_as_half(bits));

@@ -48,6 +48,8 @@ __global__ void rms_norm_q_kernel(const float *__restrict__ x, const float *__re
                                   float *__restrict__ out_f32)
 {
     __shared__ float sm[32];
+    pdl_wait();
+    pdl_trigger();
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
     ss = block_reduce<false>(ss, sm);
@@ -69,6 +71,8 @@ __global__ void rms_norm_q_kernel(const float *__restrict__ x, const float *__re
 // SwiGLU (src/cuda_kernels.cu:683-698) into activation form.
 __global__ void swiglu_q_kernel(const float *__restrict__ gate, const float *__restrict__ up, int n, int oai, XQOut o)
 {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     const bool valid = 4 * t < n;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -95,6 +99,8 @@ __global__ void rope_kv_kernel(float *q, float *k, const float *__restrict__ v, 
                                float *__restrict__ v_cache, int n_heads, int head_dim, int pos, float theta,
                                float yarn_scale, int yarn_orig_ctx, int neox, int kv_dim)
 {
+    pdl_wait();
+    pdl_trigger();
     const int i = threadIdx.x, half = head_dim >> 1;
     const bool is_k = (int)blockIdx.x >= n_heads;
     const int head = is_k ? blockIdx.x - n_heads : blockIdx.x;
@@ -148,18 +154,35 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(float *__restrict__ p
     __shared__ float vs[ATT_CHUNK][ATT_MAX_HD];
     __shared__ float qs[4][ATT_MAX_HD];
     __shared__ float ps[4][ATT_CHUNK];
+    pdl_wait();
+    pdl_trigger();
     const int kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
     const int t0 = split * ATT_CHUNK;
     const int nt = min(ATT_CHUNK, seq_len - t0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // stage K and V rows [t0, t0+nt) of this kv head
+    // stage K and V rows [t0, t0+nt) of this kv head: all of a thread's loads are issued before
+    // the first shared-memory store, so the CTA pays one DRAM round trip, not one per row
     const int hd4 = head_dim >> 2;
-    for (int idx = threadIdx.x; idx < nt * hd4; idx += blockDim.x) {
-        const int t = idx / hd4, c = idx % hd4;
-        const size_t g = (size_t)(t0 + t) * kv_dim + (size_t)kvh * head_dim + 4 * c;
-        const float4 kk = *(const float4 *)(k_cache + g), vv = *(const float4 *)(v_cache + g);
-        ks[t][4 * c] = kk.x; ks[t][4 * c + 1] = kk.y; ks[t][4 * c + 2] = kk.z; ks[t][4 * c + 3] = kk.w;
-        *(float4 *)&vs[t][4 * c] = vv;
+    constexpr int MAX_IT = ATT_CHUNK * (ATT_MAX_HD / 4) / 128;   // 8 float4 pairs per thread
+    float4 kreg[MAX_IT], vreg[MAX_IT];
+#pragma unroll
+    for (int it = 0; it < MAX_IT; it++) {
+        const int idx = threadIdx.x + it * 128;
+        if (idx < nt * hd4) {
+            const int t = idx / hd4, c = idx - t * hd4;
+            const size_t g = (size_t)(t0 + t) * kv_dim + (size_t)kvh * head_dim + 4 * c;
+            kreg[it] = __ldg((const float4 *)(k_cache + g));
+            vreg[it] = __ldg((const float4 *)(v_cache + g));
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < MAX_IT; it++) {
+        const int idx = threadIdx.x + it * 128;
+        if (idx < nt * hd4) {
+            const int t = idx / hd4, c = idx - t * hd4;
+            ks[t][4 * c] = kreg[it].x; ks[t][4 * c + 1] = kreg[it].y; ks[t][4 * c + 2] = kreg[it].z; ks[t][4 * c + 3] = kreg[it].w;
+            *(float4 *)&vs[t][4 * c] = vreg[it];
+        }
     }
     // query heads of this kv head: those with (head * n_kv_heads) / n_heads == kvh
     const int h_lo = (kvh * n_heads + n_kv_heads - 1) / n_kv_heads;
@@ -173,8 +196,14 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(float *__restrict__ p
         __syncthreads();
         if (!live) continue;
         // one key position per lane
-        float sc = 0.f;
-        for (int i = 0; i < head_dim; i++) sc = fmaf(qs[warp][i], ks[lane][i], sc);
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+        for (int i = 0; i < head_dim; i += 4) {
+            c0 = fmaf(qs[warp][i], ks[lane][i], c0);
+            c1 = fmaf(qs[warp][i + 1], ks[lane][i + 1], c1);
+            c2 = fmaf(qs[warp][i + 2], ks[lane][i + 2], c2);
+            c3 = fmaf(qs[warp][i + 3], ks[lane][i + 3], c3);
+        }
+        float sc = (c0 + c1) + (c2 + c3);
         sc = lane < nt ? sc * scale : -INFINITY;
         float mx = sc;
 #pragma unroll
@@ -186,11 +215,19 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(float *__restrict__ p
         ps[warp][lane] = p;
         __syncwarp();
         float *dst = part + ((size_t)head * n_splits + split) * (head_dim + 2);
-        for (int i = lane; i < head_dim; i += 32) {
-            float acc = 0.f;
-            for (int t = 0; t < nt; t++) acc = fmaf(ps[warp][t], vs[t][i], acc);
-            dst[2 + i] = acc;
+        // lane owns outputs lane, lane+32, lane+64, lane+96 (four independent chains)
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        for (int t = 0; t < nt; t++) {
+            const float pt = ps[warp][t];
+            o0 = fmaf(pt, vs[t][lane], o0);
+            if (head_dim > 32) o1 = fmaf(pt, vs[t][lane + 32], o1);
+            if (head_dim > 64) o2 = fmaf(pt, vs[t][lane + 64], o2);
+            if (head_dim > 96) o3 = fmaf(pt, vs[t][lane + 96], o3);
         }
+        dst[2 + lane] = o0;
+        if (head_dim > 32) dst[2 + lane + 32] = o1;
+        if (head_dim > 64) dst[2 + lane + 64] = o2;
+        if (head_dim > 96) dst[2 + lane + 96] = o3;
         if (lane == 0) {
             dst[0] = mx;
             dst[1] = sum;
@@ -204,19 +241,37 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(float *__restrict__ p
 __global__ void attn_combine_kernel(float *__restrict__ out, const float *__restrict__ part, int n_splits, int head_dim,
                                     const float *__restrict__ sinks, XQOut o, int emit_q)
 {
+    __shared__ float sm[32];
+    extern __shared__ float fs[];   // n_splits rescale factors
+    pdl_wait();
+    pdl_trigger();
     const int head = blockIdx.x, i = threadIdx.x;
-    const float *p = part + (size_t)head * n_splits * (head_dim + 2);
+    const int stride = head_dim + 2;
+    const float *p = part + (size_t)head * n_splits * stride;
     const float sink = sinks ? sinks[head] : -INFINITY;
     const bool has_sink = sink > -1e29f;
+    // every thread takes a strided share of the splits' (max, sum) pairs
     float mx = has_sink ? sink : -1e30f;
-    for (int s = 0; s < n_splits; s++) mx = fmaxf(mx, p[(size_t)s * (head_dim + 2)]);
-    float total = has_sink ? expf(sink - mx) : 0.f, acc = 0.f;
-    for (int s = 0; s < n_splits; s++) {
-        const float *ps_ = p + (size_t)s * (head_dim + 2);
-        const float f = expf(ps_[0] - mx);
-        total += f * ps_[1];
-        acc = fmaf(f, ps_[2 + i], acc);
+    for (int s = i; s < n_splits; s += blockDim.x) mx = fmaxf(mx, p[(size_t)s * stride]);
+    mx = block_reduce<true>(mx, sm);
+    float tot = 0.f;
+    for (int s = i; s < n_splits; s += blockDim.x) {
+        const float f = expf(p[(size_t)s * stride] - mx);
+        fs[s] = f;
+        tot = fmaf(f, p[(size_t)s * stride + 1], tot);
     }
+    tot = block_reduce<false>(tot, sm);   // (its barriers also publish fs)
+    const float total = tot + (has_sink ? expf(sink - mx) : 0.f);
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int s = 0;
+    for (; s + 4 <= n_splits; s += 4) {
+        a0 = fmaf(fs[s], p[(size_t)s * stride + 2 + i], a0);
+        a1 = fmaf(fs[s + 1], p[(size_t)(s + 1) * stride + 2 + i], a1);
+        a2 = fmaf(fs[s + 2], p[(size_t)(s + 2) * stride + 2 + i], a2);
+        a3 = fmaf(fs[s + 3], p[(size_t)(s + 3) * stride + 2 + i], a3);
+    }
+    for (; s < n_splits; s++) a0 = fmaf(fs[s], p[(size_t)s * stride + 2 + i], a0);
+    const float acc = (a0 + a1) + (a2 + a3);
     const float r = acc / total;
     out[(size_t)head * head_dim + i] = r;
     if (emit_q) {

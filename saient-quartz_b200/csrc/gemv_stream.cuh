@@ -45,6 +45,8 @@ constexpr float XQ_RANGE = 32512.0f;   // 127 * 256: h, l both fit int8
 __global__ void quantize_x_kernel(const float *__restrict__ x, int8_t *__restrict__ xl, int8_t *__restrict__ xh,
                                   float *__restrict__ xs, float *__restrict__ xsum, int K)
 {
+    pdl_wait();
+    pdl_trigger();
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     int k = 4 * t;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -354,6 +356,8 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
     const int wpr = a.Upad >> 5;                 // warps per row (0 when Upad < 32)
     const int wir = (threadIdx.x >> 5) % (wpr > 0 ? wpr : 1);   // warp index inside the row
 
+    pdl_wait();
+    pdl_trigger();
     typename F::XRegs xr;
     if (active) F::load_x(xr, a.xq[m], u);
     const typename F::Off off = F::make_off(nb, u);

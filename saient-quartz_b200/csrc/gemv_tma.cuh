@@ -37,6 +37,7 @@ struct TmaArgs {
     int stage_bytes;         // RP * row_bytes, a multiple of 16
     int n_stages;
     int *status;             // device status word (0 = ok)
+    int probe;               // measurement aid: 1 = consumers release stages without computing (streaming ceiling)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
 {
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ uint64_t full_bar[TMA_MAX_STAGES], empty_bar[TMA_MAX_STAGES];
-    __shared__ float part[2][64];
+    __shared__ float part[2][4 * (TMA_CONSUMERS / 32)];
 
     const int m = blockIdx.x % a.n_mats;
     const int cta = blockIdx.x / a.n_mats, n_cta = gridDim.x / a.n_mats;
@@ -170,9 +171,12 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    pdl_trigger();
 
     if (threadIdx.x >= TMA_CONSUMERS) {
         // ---------------- producer ----------------
+        // Weights are written by no kernel, so streaming starts at once, even while the kernel
+        // that produces this GEMV's activations is still running.
         if (threadIdx.x != TMA_CONSUMERS) return;
         const uint8_t *W = a.W[m];
         int it = 0, s = 0;
@@ -211,6 +215,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
 
     // Padding lanes (u >= U) run on unit 0's bytes and are masked out of the sums; rows past
     // N in the last tile are computed from stale shared memory and simply never stored.
+    pdl_wait();   // activations (and, for the accumulate epilogue, y) come from the preceding kernels
     typename F::XRegs xr;
     F::load_x(xr, a.xq[m], active ? u : 0);
     const typename F::Off off = F::make_off(nb, active ? u : 0);
@@ -232,9 +237,11 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
                     atomicExch(a.status, QZ_ERR_TIMEOUT);
                     return;
                 }
-                typename F::WRegs w;
-                F::template load_w<LdSharedAddr>(w, sp, off);
-                acc[j] = F::dot(w, xr, off);
+                if (!a.probe) {
+                    typename F::WRegs w;
+                    F::template load_w<LdSharedAddr>(w, sp, off);
+                    acc[j] = F::dot(w, xr, off);
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive_addr(empty0 + bar_off);   // this warp no longer reads the stage
                 sp += stage_bytes;

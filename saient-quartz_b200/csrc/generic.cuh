@@ -16,6 +16,8 @@ template <uint32_t T, bool PLANES>
 __global__ void dequant_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, int K, long long n_sub)
 {
     const FormatInfo fi = format_info(T);
+    pdl_wait();
+    pdl_trigger();
     long long gs = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gs >= n_sub) return;
     const int subs_per_row = K / 32;

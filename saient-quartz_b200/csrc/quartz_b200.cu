@@ -47,6 +47,31 @@ int sm_count()
     return g_sm_count;
 }
 
+// ---- launch helper: ordinary launch, or programmatic dependent launch when enabled ----------
+static bool g_pdl = false;
+
+template <class... KArgs, class... Args>
+static void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args)
+{
+    g_launch_count++;
+    if (g_pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = g_stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        QZ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    } else {
+        kernel<<<grid, block, smem, g_stream>>>(KArgs(args)...);
+        QZ_CUDA_CHECK(cudaGetLastError());
+    }
+}
+
 // ---- registry of repacked byte ranges ---------------------------------------------
 struct Range {
     uintptr_t end;
@@ -118,8 +143,7 @@ static void launch_quantize(const float *x, const XQMut &q, int K)
 {
     int threads = K / 4;
     int bs = 256, gs = (threads + bs - 1) / bs;
-    quantize_x_kernel<<<gs, bs, 0, g_stream>>>(x, q.xl, q.xh, q.xs, q.xsum, K);
-    QZ_LAUNCH_CHECK();
+    launch(quantize_x_kernel, dim3(gs), dim3(bs), 0, x, q.xl, q.xh, q.xs, q.xsum, K);
 }
 
 // ---- one-time init: default sign table ------------------------------------------------
@@ -211,6 +235,7 @@ static void poll_status()
     }
 }
 
+static int g_probe = 0;
 static int g_use_tma = -1;
 static bool use_tma()
 {
@@ -246,6 +271,7 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     a.n_stages = stages;
     a.status = status_word();
     if (!a.status) return false;
+    a.probe = g_probe;
     static bool attr_set = false;
     if (!attr_set) {
         QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget));
@@ -255,10 +281,9 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     }
     const dim3 grid(n_cta * n_mats), block(TMA_CONSUMERS + 32);
     const size_t smem = (size_t)stages * a.stage_bytes;
-    if (g.Upad < 32) gemv_tma_kernel<F, 0><<<grid, block, smem, g_stream>>>(a);
-    else if (g.Upad == 32) gemv_tma_kernel<F, 1><<<grid, block, smem, g_stream>>>(a);
-    else gemv_tma_kernel<F, 2><<<grid, block, smem, g_stream>>>(a);
-    QZ_LAUNCH_CHECK();
+    if (g.Upad < 32) launch(gemv_tma_kernel<F, 0>, grid, block, smem, a);
+    else if (g.Upad == 32) launch(gemv_tma_kernel<F, 1>, grid, block, smem, a);
+    else launch(gemv_tma_kernel<F, 2>, grid, block, smem, a);
     return true;
 }
 
@@ -274,10 +299,9 @@ static void launch_stream_r(const GemvArgs &a, int n_mats, int T)
     int gx = ntiles < sms * per_sm ? ntiles : sms * per_sm;
     if (gx < 1) gx = 1;
     dim3 grid(gx, n_mats), block(T);
-    if (R == 4) gemv_stream_kernel<F, 4><<<grid, block, 0, g_stream>>>(a);
-    else if (R == 2) gemv_stream_kernel<F, 2><<<grid, block, 0, g_stream>>>(a);
-    else gemv_stream_kernel<F, 1><<<grid, block, 0, g_stream>>>(a);
-    QZ_LAUNCH_CHECK();
+    if (R == 4) launch(gemv_stream_kernel<F, 4>, grid, block, 0, a);
+    else if (R == 2) launch(gemv_stream_kernel<F, 2>, grid, block, 0, a);
+    else launch(gemv_stream_kernel<F, 1>, grid, block, 0, a);
 }
 
 static bool stream_shape_ok(uint32_t t, int K)
@@ -791,7 +815,11 @@ void quartz_clear_error(void)
 }
 void quartz_set_stream(void *s) { g_stream = (cudaStream_t)s; }
 long long quartz_launch_count(void) { return g_launch_count; }
-void quartz_set_gemv_impl(int impl) { g_use_tma = impl == 1 ? 0 : 1; }
+void quartz_set_gemv_impl(int impl)
+{
+    g_probe = impl == 2 ? 1 : 0;   // 2: streaming-ceiling probe (outputs are meaningless)
+    g_use_tma = impl == 1 ? 0 : 1;
+}
 
 int cuda_repack_weights(uint32_t ggml_type, void *d_data, int in_dim, int out_dim, int n_mats)
 {
@@ -878,8 +906,7 @@ void cuda_rms_norm_q(const float *x, const float *w, int n, int slot, float *out
 {
     XQOut o;
     if (!user_slot(slot, n, &o)) return;
-    rms_norm_q_kernel<<<1, 1024, 0, g_stream>>>(x, w, n, o, out_f32);
-    QZ_LAUNCH_CHECK();
+    launch(rms_norm_q_kernel, dim3(1), dim3(1024), 0, x, w, n, o, out_f32);
 }
 
 void cuda_swiglu_q(const float *gate, const float *up, int n, int slot, int oai)
@@ -887,8 +914,7 @@ void cuda_swiglu_q(const float *gate, const float *up, int n, int slot, int oai)
     XQOut o;
     if (!user_slot(slot, n, &o)) return;
     const int threads = n / 4;
-    swiglu_q_kernel<<<(threads + 255) / 256, 256, 0, g_stream>>>(gate, up, n, oai, o);
-    QZ_LAUNCH_CHECK();
+    launch(swiglu_q_kernel, dim3((threads + 255) / 256), dim3(256), 0, gate, up, n, oai, o);
 }
 
 int cuda_gemv_q_supported(uint32_t ggml_type, const uint8_t *d_data, int in_dim)
@@ -924,9 +950,8 @@ void cuda_rope_kv(float *q, float *k, const float *v, float *k_cache, float *v_c
 {
     if (n_heads <= 0 || n_kv_heads <= 0 || head_dim < 2) return;
     const int bs = ((head_dim / 2) + 31) & ~31;
-    rope_kv_kernel<<<n_heads + n_kv_heads, bs, 0, g_stream>>>(q, k, v, k_cache, v_cache, n_heads, head_dim, pos, theta,
-                                                            yarn_scale, yarn_orig_ctx, neox, n_kv_heads * head_dim);
-    QZ_LAUNCH_CHECK();
+    launch(rope_kv_kernel, dim3(n_heads + n_kv_heads), dim3(bs), 0, q, k, v, k_cache, v_cache, n_heads, head_dim, pos,
+           theta, yarn_scale, yarn_orig_ctx, neox, n_kv_heads * head_dim);
 }
 
 static float *g_attn_part = nullptr;
@@ -960,16 +985,15 @@ void cuda_attn_decode(float *out, const float *q, const float *k_cache, const fl
     }
     XQOut o{nullptr, nullptr, nullptr, nullptr};
     if (out_slot >= 0 && !user_slot(out_slot, n_heads * head_dim, &o)) return;
-    attn_partial_kernel<<<dim3(n_kv_heads, n_splits), 128, 0, g_stream>>>(g_attn_part, q, k_cache, v_cache, n_heads,
-                                                                         n_kv_heads, seq_len, head_dim, kv_dim, scale);
-    QZ_LAUNCH_CHECK();
-    attn_combine_kernel<<<n_heads, head_dim, 0, g_stream>>>(out, g_attn_part, n_splits, head_dim, sinks, o,
-                                                            out_slot >= 0 ? 1 : 0);
-    QZ_LAUNCH_CHECK();
+    launch(attn_partial_kernel, dim3(n_kv_heads, n_splits), dim3(128), 0, g_attn_part, q, k_cache, v_cache, n_heads,
+           n_kv_heads, seq_len, head_dim, kv_dim, scale);
+    launch(attn_combine_kernel, dim3(n_heads), dim3(head_dim), (size_t)n_splits * sizeof(float), out,
+           (const float *)g_attn_part, n_splits, head_dim, sinks, o, out_slot >= 0 ? 1 : 0);
 }
 
 // ---- CUDA-graph helpers: record a sequence of this library's calls once, replay it per token ----
 static cudaStream_t g_graph_stream = nullptr, g_saved_stream = nullptr;
+static bool g_pdl_in_graphs = true;
 static bool g_capturing = false;
 
 int quartz_graph_begin(void)
@@ -994,6 +1018,7 @@ int quartz_graph_begin(void)
     g_saved_stream = g_stream;
     g_stream = g_graph_stream;
     g_capturing = true;
+    g_pdl = g_pdl_in_graphs;   // recorded kernels become programmatic dependents of one another
     return 1;
 }
 
@@ -1002,6 +1027,7 @@ void *quartz_graph_end(void)
     if (!g_capturing) return nullptr;
     g_capturing = false;
     g_stream = g_saved_stream;
+    g_pdl = false;
     cudaGraph_t graph = nullptr;
     if (cudaStreamEndCapture(g_graph_stream, &graph) != cudaSuccess || !graph) {
         cudaGetLastError();
@@ -1018,6 +1044,8 @@ void *quartz_graph_end(void)
     }
     return (void *)exec;
 }
+
+void quartz_set_pdl(int on) { g_pdl_in_graphs = on != 0; }
 
 void quartz_graph_launch(void *graph_exec)
 {
