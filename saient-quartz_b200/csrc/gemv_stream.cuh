@@ -122,6 +122,12 @@ struct GemvArgs {
 // inside a row (Off: they depend on the unit only, never on the row), one row's bytes
 // for the slice (WRegs), the loads, and the integer dot product.
 
+// policies without a codebook
+struct NoTable {
+    static constexpr int TABLE_BYTES = 0;
+    __device__ static void load_table(uint8_t *, int, int) {}
+};
+
 __device__ __forceinline__ void load_x64(uint32_t *xl, uint32_t *xh, const XQ &q, int at)
 {
     const uint4 *pl = (const uint4 *)(q.xl + at), *ph = (const uint4 *)(q.xh + at);
@@ -142,7 +148,7 @@ __device__ __forceinline__ int sext_byte(uint32_t v, uint32_t selector)
     return d;
 }
 
-struct StreamQ4K {
+struct StreamQ4K : NoTable {
     static constexpr uint32_t TYPE = T_Q4_K;
     static constexpr bool PLANES = false;
     struct XRegs { uint32_t xl[16], xh[16]; float s0, s1, sum0, sum1; };
@@ -177,7 +183,7 @@ struct StreamQ4K {
         w.q0 = LD::v4(row + o.qs);
         w.q1 = LD::v4(row + o.qs + 16);
     }
-    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &o)
+    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &o, const uint8_t *)
     {
         const uint32_t q[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
         int a0h = 0, a0l = 0, a1h = 0, a1l = 0;
@@ -203,7 +209,7 @@ struct StreamQ4K {
     }
 };
 
-struct StreamQ6K {
+struct StreamQ6K : NoTable {
     static constexpr uint32_t TYPE = T_Q6_K;
     static constexpr bool PLANES = true;
     // unit u -> block u/4, half n = (u>>1)&1, 16-lane group g = u&1; run k holds the
@@ -251,7 +257,7 @@ struct StreamQ6K {
         w.sc = LD::v2(row + o.sc);
         w.d = LD::u16(row + o.d);
     }
-    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &o)
+    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &o, const uint8_t *)
     {
         const uint32_t a0[4] = {w.ql0.x, w.ql0.y, w.ql0.z, w.ql0.w};
         const uint32_t a1[4] = {w.ql1.x, w.ql1.y, w.ql1.z, w.ql1.w};
@@ -280,7 +286,7 @@ struct StreamQ6K {
     }
 };
 
-struct StreamQ8_0 {
+struct StreamQ8_0 : NoTable {
     static constexpr uint32_t TYPE = T_Q8_0;
     static constexpr bool PLANES = true;
     // unit u -> blocks 2u and 2u+1
@@ -302,7 +308,7 @@ struct StreamQ8_0 {
         for (int i = 0; i < 4; i++) w.q[i] = LD::v4(row + o.qs + 16 * i);
         w.d2 = LD::u32(row + o.d);
     }
-    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &)
+    __device__ static float dot(const WRegs &w, const XRegs &x, const Off &, const uint8_t *)
     {
         int h0 = 0, l0 = 0, h1 = 0, l1 = 0;
 #pragma unroll
@@ -341,6 +347,9 @@ template <class F, int R>
 __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
 {
     __shared__ float part_w[2][4 * R * 16];   // [parity][(row-in-pass * R + i) * 16 + warp of the row]
+    __shared__ __align__(16) uint8_t tbl[F::TABLE_BYTES > 0 ? F::TABLE_BYTES : 16];
+    F::load_table(tbl, threadIdx.x, blockDim.x);   // codebooks are written by no kernel: before pdl_wait
+    if (F::TABLE_BYTES > 0) __syncthreads();
 
     const int m = blockIdx.y;
     const uint8_t *__restrict__ W = a.W[m];
@@ -377,7 +386,7 @@ __global__ void __launch_bounds__(512) gemv_stream_kernel(const GemvArgs a)
 #pragma unroll
         for (int i = 0; i < R; i++) {
             const int row = row0 + i * a.RP;
-            acc[i] = (active && row < a.N) ? F::dot(w[i], xr, off) : 0.f;
+            acc[i] = (active && row < a.N) ? F::dot(w[i], xr, off, tbl) : 0.f;
         }
         if (wpr == 0) {
             // several rows per warp: butterfly inside the row's Upad lanes

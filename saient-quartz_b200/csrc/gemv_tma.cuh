@@ -18,7 +18,8 @@
 // copies (bounded) before it exits.
 #pragma once
 
-#include "gemv_stream.cuh"
+#include "gemv_formats_iq.cuh"
+#include "gemv_formats_k.cuh"
 
 namespace qz {
 
@@ -162,6 +163,8 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     const int ntiles = (a.N + a.RP - 1) / a.RP;
     const int n_consumers = a.Upad * a.RP;
 
+    uint8_t *tbl = ring + (size_t)a.n_stages * a.stage_bytes;   // codebook copy, behind the ring
+    F::load_table(tbl, threadIdx.x, blockDim.x);
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.n_stages; s++) {
             mbar_init(&full_bar[s], 1);
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
                 if (!a.probe) {
                     typename F::WRegs w;
                     F::template load_w<LdSharedAddr>(w, sp, off);
-                    acc[j] = F::dot(w, xr, off);
+                    acc[j] = F::dot(w, xr, off, tbl);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive_addr(empty0 + bar_off);   // this warp no longer reads the stage

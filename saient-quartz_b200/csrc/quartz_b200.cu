@@ -203,12 +203,18 @@ static void launch_generic(uint32_t t, bool planes, const uint8_t *W, const floa
 static int stream_layout(uint32_t t)
 {
     switch (t) {
-    case T_Q4_K: return 1;
-    case T_Q6_K: return 2;
-    case T_Q8_0: return 2;
+    case T_Q4_K: case T_Q5_K: return 1;
+    case T_Q6_K: case T_Q8_0: case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1:
+    case T_IQ2_XXS: case T_IQ2_XS: case T_IQ2_S: case T_IQ3_XXS: case T_IQ3_S: case T_Q2_K: case T_IQ4_NL: return 2;
     default: return 0;
     }
 }
+
+#define QZ_FOR_STREAM_TYPES(X)                                                                              \
+    X(T_Q4_K, StreamQ4K) X(T_Q6_K, StreamQ6K) X(T_Q8_0, StreamQ8_0) X(T_Q4_0, StreamQ4_0) X(T_Q4_1, StreamQ4_1) \
+    X(T_Q5_0, StreamQ5_0) X(T_Q5_1, StreamQ5_1) X(T_IQ2_XXS, StreamIQ2XXS) X(T_IQ2_XS, StreamIQ2XS)          \
+    X(T_IQ2_S, StreamIQ2S) X(T_IQ3_XXS, StreamIQ3XXS) X(T_IQ3_S, StreamIQ3S) X(T_Q5_K, StreamQ5K)               \
+    X(T_Q2_K, StreamQ2K) X(T_IQ4_NL, StreamIQ4NL)
 
 // ---- device status word written by kernels whose bounded waits gave up ------------------
 static int *g_status = nullptr;
@@ -259,7 +265,7 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     const int sms = sm_count();
     const int ctas_per_mat = sms / n_mats > 0 ? sms / n_mats : 1;
     a.stage_bytes = (int)((size_t)a.RP * row_bytes);
-    const int ring_budget = 200 * 1024;
+    const int ring_budget = 200 * 1024;   // + up to 8 KB of codebook behind it
     if (a.stage_bytes * 2 > ring_budget) return false;
     const int ntiles = (g.N + a.RP - 1) / a.RP;
     const int n_cta = ntiles < ctas_per_mat ? ntiles : ctas_per_mat;
@@ -274,13 +280,13 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     a.probe = g_probe;
     static bool attr_set = false;
     if (!attr_set) {
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget));
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget));
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + F::TABLE_BYTES));
         attr_set = true;
     }
     const dim3 grid(n_cta * n_mats), block(TMA_CONSUMERS + 32);
-    const size_t smem = (size_t)stages * a.stage_bytes;
+    const size_t smem = (size_t)stages * a.stage_bytes + F::TABLE_BYTES;
     if (g.Upad < 32) launch(gemv_tma_kernel<F, 0>, grid, block, smem, a);
     else if (g.Upad == 32) launch(gemv_tma_kernel<F, 1>, grid, block, smem, a);
     else launch(gemv_tma_kernel<F, 2>, grid, block, smem, a);
@@ -340,17 +346,17 @@ static bool stream_core(uint32_t t, int n, const uint8_t *const *W, const int *s
     if (use_tma()) {
         bool done = false;
         switch (t) {
-        case T_Q4_K: done = launch_tma<StreamQ4K>(a, n); break;
-        case T_Q6_K: done = launch_tma<StreamQ6K>(a, n); break;
-        case T_Q8_0: done = launch_tma<StreamQ8_0>(a, n); break;
+#define X(TT, POL) case TT: done = launch_tma<POL>(a, n); break;
+            QZ_FOR_STREAM_TYPES(X)
+#undef X
         default: break;
         }
         if (done) return true;
     }
     switch (t) {
-    case T_Q4_K: launch_stream_r<StreamQ4K>(a, n, T); break;
-    case T_Q6_K: launch_stream_r<StreamQ6K>(a, n, T); break;
-    case T_Q8_0: launch_stream_r<StreamQ8_0>(a, n, T); break;
+#define X(TT, POL) case TT: launch_stream_r<POL>(a, n, T); break;
+        QZ_FOR_STREAM_TYPES(X)
+#undef X
     default: return false;
     }
     return true;

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "dequant_golden.npz")
 ALL_TYPES = [0, 1, 30, 2, 3, 6, 7, 8, 20, 10, 12, 13, 14, 16, 17, 18, 21, 22]
-STREAM_TYPES = [12, 14, 8]
+STREAM_TYPES = [12, 14, 8, 2, 3, 6, 7, 16, 17, 22, 18, 21, 13, 10, 20]
 
 
 def _check_gemv(oracle_mod, y, x, w, t, K, N, verify_bar=1e-3):
