@@ -141,10 +141,8 @@ def make_host_tensors(shapes, rank=0, world=1):
 
 
 def shard_rows(N, rank, world):
-    """Row range of `rank` when N output rows are split over `world` ranks (equal, last rank takes the rest)."""
-    per = (N + world - 1) // world
-    n0 = min(rank * per, N)
-    return n0, min(n0 + per, N)
+    from saient_quartz_b200.shard import shard_rows as _sr
+    return _sr(N, rank, world)[:2]
 
 
 def run_reference(args):

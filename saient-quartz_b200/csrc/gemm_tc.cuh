@@ -1,0 +1,373 @@
+// Batched dequant-GEMM on the 5th-generation tensor cores (tcgen05 + TMEM):
+//   Y[m, n] = sum_k X[m, k] * W[n, k],  W quantized (any supported format), X/Y f32.
+//
+// The reference has no batched GPU path at all (its GPU prefill is token-by-token GEMV,
+// src/main.rs:1410-1416); its CPU form is dequant::gemm (src/dequant.rs:143-200).
+//
+// One CTA owns a tile of 128 weight rows (the UMMA M dimension) x up to 256 tokens (the UMMA N
+// dimension) x one K split.  Per 64-wide K step:
+//   * eight producer warps dequantize the 128x64 weight tile to bf16 straight into shared
+//     memory in the K-major 128-byte-swizzled layout tcgen05.mma reads (two threads per row,
+//     32 weights each; Q4_K / Q6_K use packed bf16x2 arithmetic: nibble|0x4300 is the bf16
+//     128+q, an exact HSUB2 removes the 128, one HFMA2 applies scale and min), and copy the
+//     matching 64 columns of the bf16 activation tile beside it;
+//   * they fence the generic->async proxy and arrive on the stage's "full" mbarrier;
+//   * one elected thread issues four tcgen05.mma (K=16 each, kind::f16, bf16 x bf16 -> f32 in
+//     TMEM) and a tcgen05.commit that arrives on the stage's "empty" mbarrier when the tensor
+//     core has finished reading the stage.
+// A 4-stage ring lets dequantization run ahead of the MMAs.  The epilogue reads the
+// accumulator with tcgen05.ld (32 lanes x 8 columns per instruction), one weight row per
+// thread, and stores (or, with K splits, atomically adds) into the token-major output.
+//
+// Within every group of four consecutive k the tile order is (0,2,1,3) for BOTH operands: that
+// is the order byte->bf16x2 unpacking produces for free, and a contraction does not care about
+// a permutation applied to both sides.  The activation tile is converted f32->bf16 (and
+// permuted) once per call by convert_x_bf16_kernel.
+//
+// Every mbarrier wait is bounded (~1 s); a timeout sets the status word, the loops are left,
+// and the CTA still reaches the common exit where the allocating warp frees its TMEM columns.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "formats.cuh"
+#include "gemv_tma.cuh"
+
+namespace qz {
+
+constexpr int GEMM_ROWS = 128;       // UMMA M
+constexpr int GEMM_KSTEP = 64;       // one 128-byte swizzle atom of bf16
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_PRODUCERS = 256;
+constexpr int GEMM_MAX_TOKENS = 256; // UMMA N per CTA
+
+struct GemmArgs {
+    const uint8_t *W;
+    const __nv_bfloat16 *Xb;   // [m_pad, K] bf16, k permuted (0,2,1,3) inside every 4
+    float *Y;                  // [M, N] token-major
+    int M, K, N;
+    int planes;                // weight layout
+    int n_tok_tiles, tok_tile; // tokens per CTA (multiple of 16, <= 256)
+    int k_splits, ksteps_per_split;
+    int *status;
+};
+
+// ---- f32 [M,K] -> bf16 [m_pad,K], (0,2,1,3) inside every four k ----
+__global__ void convert_x_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, int M, int K, int m_pad)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per 4 elements
+    const long long total = (long long)m_pad * K / 4;
+    if (i >= total) return;
+    const long long row = (i * 4) / K;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < M) v = *(const float4 *)(x + i * 4);
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.z), b = __floats2bfloat162_rn(v.y, v.w);
+    uint2 o;
+    o.x = *(uint32_t *)&a;
+    o.y = *(uint32_t *)&b;
+    *(uint2 *)(out + i * 4) = o;
+}
+
+// ---- tcgen05 / TMEM primitives ----
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t *r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);    // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                        // layout type: SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int n)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(GEMM_ROWS >> 4) << 24);
+}
+
+// position of 16-byte chunk c of row r inside a [rows x 128 B] swizzled tile
+__device__ __forceinline__ uint32_t sw128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+// four bytes (values < 128) -> two bf16x2 registers holding (b0, b2) and (b1, b3) minus `bias`,
+// times `scale`, minus `sub` (all packed bf16x2 constants)
+__device__ __forceinline__ void bytes4_to_bf16(uint32_t v, __nv_bfloat162 bias, __nv_bfloat162 scale, __nv_bfloat162 sub,
+                                               uint32_t &o02, uint32_t &o13)
+{
+    uint32_t t02 = (v & 0x00FF00FFu) | 0x43004300u, t13 = ((v >> 8) & 0x00FF00FFu) | 0x43004300u;
+    __nv_bfloat162 a = __hsub2(*(__nv_bfloat162 *)&t02, bias), b = __hsub2(*(__nv_bfloat162 *)&t13, bias);
+    a = __hfma2(a, scale, sub);
+    b = __hfma2(b, scale, sub);
+    o02 = *(uint32_t *)&a;
+    o13 = *(uint32_t *)&b;
+}
+
+// ---- A-tile producers: thread (row r, half h) writes weights [32h, 32h+32) of the K step ----
+// Generic: any format, either layout, through the bit-exact decoder (f32 -> bf16 rounding).
+template <uint32_t T, bool PLANES>
+__device__ __forceinline__ void produce_a_generic(uint8_t *As, const uint8_t *rowp, int nb, int kstep, int r, int h)
+{
+    const FormatInfo fi = format_info(T);
+    const int elem0 = kstep * GEMM_KSTEP + 32 * h;
+    float w[32];
+    if (rowp) {
+        Fields F = block_fields<PLANES>(fi, rowp, nb, elem0 / fi.block_elems);
+        decode32<T>(F, (elem0 % fi.block_elems) / 32, w);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) w[i] = 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(w[8 * c + 4 * j], w[8 * c + 4 * j + 2]);
+            __nv_bfloat162 b = __floats2bfloat162_rn(w[8 * c + 4 * j + 1], w[8 * c + 4 * j + 3]);
+            o[2 * j] = *(uint32_t *)&a;
+            o[2 * j + 1] = *(uint32_t *)&b;
+        }
+        *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// Q4_K, raw layout: K step = sub-block pair p of block b; half h = sub-block 2p + h
+__device__ __forceinline__ void produce_a_q4k(uint8_t *As, const uint8_t *rowp, int kstep, int r, int h)
+{
+    uint32_t q[8];
+    __nv_bfloat162 scale = __floats2bfloat162_rn(0.f, 0.f), sub = scale;
+    if (rowp) {
+        const uint8_t *blk = rowp + (size_t)(kstep >> 2) * 144;
+        const int p = kstep & 3, j = 2 * p + h;
+        const uint4 hdr = __ldg((const uint4 *)blk);
+        const uint4 q0 = __ldg((const uint4 *)(blk + 16 + 32 * p)), q1 = __ldg((const uint4 *)(blk + 32 + 32 * p));
+        q[0] = q0.x; q[1] = q0.y; q[2] = q0.z; q[3] = q0.w; q[4] = q1.x; q[5] = q1.y; q[6] = q1.z; q[7] = q1.w;
+        const uint8_t *s = (const uint8_t *)&hdr.y;   // the 12 packed 6-bit codes
+        int sc, mn;
+        if (j < 4) {
+            sc = s[j] & 63;
+            mn = s[j + 4] & 63;
+        } else {
+            sc = (s[j + 4] & 0x0F) | ((s[j - 4] >> 6) << 4);
+            mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+        }
+        const float2 dm = __half22float2(*(const __half2 *)&hdr.x);
+        const float d1 = dm.x * (float)sc, m1 = dm.y * (float)mn;
+        scale = __floats2bfloat162_rn(d1, d1);
+        sub = __floats2bfloat162_rn(-m1, -m1);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) q[i] = 0;
+    }
+    const __nv_bfloat162 bias = __floats2bfloat162_rn(128.f, 128.f);
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t o[4];
+#pragma unroll
+        for (int jj = 0; jj < 2; jj++) {
+            const uint32_t v = (h ? (q[2 * c + jj] >> 4) : q[2 * c + jj]) & 0x0F0F0F0Fu;
+            bytes4_to_bf16(v, bias, scale, sub, o[2 * jj], o[2 * jj + 1]);
+        }
+        *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// Q6_K, plane layout: K step = (block b, half n, pair hh); half h selects k = 2hh + h
+__device__ __forceinline__ void produce_a_q6k(uint8_t *As, const uint8_t *rowp, int nb, int kstep, int r, int h)
+{
+    uint32_t ql[8], qh[8];
+    __nv_bfloat162 sc_lo = __floats2bfloat162_rn(0.f, 0.f), sc_hi = sc_lo;
+    const int b = kstep >> 2, n = (kstep >> 1) & 1, hh = kstep & 1, k = 2 * hh + h;
+    if (rowp) {
+        const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n + 32 * h;
+        const uint8_t *ph = rowp + (size_t)nb * 128 + (size_t)b * 64 + 32 * n;
+        const uint4 a0 = __ldg((const uint4 *)pl), a1 = __ldg((const uint4 *)(pl + 16));
+        const uint4 h0 = __ldg((const uint4 *)ph), h1 = __ldg((const uint4 *)(ph + 16));
+        ql[0] = a0.x; ql[1] = a0.y; ql[2] = a0.z; ql[3] = a0.w; ql[4] = a1.x; ql[5] = a1.y; ql[6] = a1.z; ql[7] = a1.w;
+        qh[0] = h0.x; qh[1] = h0.y; qh[2] = h0.z; qh[3] = h0.w; qh[4] = h1.x; qh[5] = h1.y; qh[6] = h1.z; qh[7] = h1.w;
+        const int8_t *sc = (const int8_t *)(rowp + (size_t)nb * 192 + (size_t)b * 16 + 8 * n + 2 * k);
+        const float d = h2f(*(const uint16_t *)(rowp + (size_t)nb * 208 + (size_t)b * 2));
+        const float s0 = d * (float)sc[0], s1 = d * (float)sc[1];
+        sc_lo = __floats2bfloat162_rn(s0, s0);
+        sc_hi = __floats2bfloat162_rn(s1, s1);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) ql[i] = qh[i] = 0;
+    }
+    const __nv_bfloat162 bias = __floats2bfloat162_rn(160.f, 160.f);   // the bf16 magic 128 plus Q6_K's own 32
+    const __nv_bfloat162 zero = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t o[4];
+#pragma unroll
+        for (int jj = 0; jj < 2; jj++) {
+            const int i = 2 * c + jj;   // word i = weights l = 4i .. 4i+3; l < 16 <=> i < 4
+            const uint32_t v = ((ql[i] >> (4 * hh)) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * k)) & 0x03030303u) << 4);
+            bytes4_to_bf16(v, bias, i < 4 ? sc_lo : sc_hi, zero, o[2 * jj], o[2 * jj + 1]);
+        }
+        *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+template <uint32_t T, bool PLANES>
+__device__ __forceinline__ void produce_a(uint8_t *As, const uint8_t *rowp, int nb, int kstep, int r, int h)
+{
+    if (T == T_Q4_K && !PLANES) produce_a_q4k(As, rowp, kstep, r, h);
+    else if (T == T_Q6_K && PLANES) produce_a_q6k(As, rowp, nb, kstep, r, h);
+    else produce_a_generic<T, PLANES>(As, rowp, nb, kstep, r, h);
+}
+
+// ---- the kernel: grid = (row tiles, token tiles, K splits), 288 threads ----
+template <uint32_t T, bool PLANES>
+__global__ void __launch_bounds__(GEMM_PRODUCERS + 32, 1) gemm_tc_kernel(const GemmArgs a)
+{
+    extern __shared__ __align__(1024) uint8_t gsm[];
+    __shared__ uint64_t full_bar[GEMM_STAGES], empty_bar[GEMM_STAGES], done_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const FormatInfo fi = format_info(T);
+    const int nb = a.K / fi.block_elems;
+    const size_t row_bytes = (size_t)nb * fi.block_bytes;
+    const int row0 = blockIdx.x * GEMM_ROWS;
+    const int tok0 = blockIdx.y * a.tok_tile;
+    const int ntok = a.tok_tile;                              // UMMA N (multiple of 16)
+    const int ks0 = blockIdx.z * a.ksteps_per_split;
+    const int ks1 = min(ks0 + a.ksteps_per_split, a.K / GEMM_KSTEP);
+    const int nsteps = ks1 - ks0;
+    const int a_bytes = GEMM_ROWS * 128, b_bytes = ntok * 128;
+    const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = ntok <= 32 ? 32 : (ntok <= 64 ? 64 : (ntok <= 128 ? 128 : 256));
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GEMM_STAGES; s++) {
+            mbar_init(&full_bar[s], GEMM_PRODUCERS / 32);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&done_bar, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == GEMM_PRODUCERS / 32) tmem_alloc(&tmem_base_s, tmem_cols);   // one full warp allocates
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp < GEMM_PRODUCERS / 32) {
+        // ---------------- producers ----------------
+        const int r = threadIdx.x >> 1, h = threadIdx.x & 1;
+        const uint8_t *rowp = (row0 + r < a.N) ? a.W + (size_t)(row0 + r) * row_bytes : nullptr;
+        for (int it = 0; it < nsteps; it++) {
+            const int s = it % GEMM_STAGES;
+            const uint32_t round = it / GEMM_STAGES;
+            if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+                atomicExch(a.status, QZ_ERR_TIMEOUT);
+                abort_s = 1;
+                break;
+            }
+            if (*(volatile int *)&abort_s) break;
+            uint8_t *As = gsm + (size_t)s * stage_bytes, *Bs = As + a_bytes;
+            produce_a<T, PLANES>(As, rowp, nb, ks0 + it, r, h);
+            // activation tile: ntok rows x 8 chunks of 16 bytes
+            const __nv_bfloat16 *xk = a.Xb + (size_t)tok0 * a.K + (size_t)(ks0 + it) * GEMM_KSTEP;
+            for (int idx = threadIdx.x; idx < ntok * 8; idx += GEMM_PRODUCERS) {
+                const int tr = idx >> 3, c = idx & 7;
+                *(uint4 *)(Bs + sw128(tr, c)) = __ldg((const uint4 *)(xk + (size_t)tr * a.K + 8 * c));
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[s]);
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = umma_idesc_bf16(ntok);
+        bool ok = true;
+        for (int it = 0; it < nsteps && ok; it++) {
+            const int s = it % GEMM_STAGES;
+            const uint32_t round = it / GEMM_STAGES;
+            ok = mbar_wait(&full_bar[s], round & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(gsm + (size_t)s * stage_bytes), b_addr = a_addr + a_bytes;
+#pragma unroll
+            for (int k = 0; k < GEMM_KSTEP / 16; k++) {
+                // advancing K by 16 bf16 inside the swizzle atom = +32 bytes on the start address
+                tc_mma_bf16(tmem_base, umma_desc_sw128(a_addr + 32 * k), umma_desc_sw128(b_addr + 32 * k), idesc,
+                            (it > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(&empty_bar[s]);   // arrives once the MMAs above have consumed the stage
+        }
+        if (ok) tc_commit(&done_bar);
+        else {
+            atomicExch(a.status, QZ_ERR_TIMEOUT);
+            abort_s = 1;
+        }
+    }
+
+    // ---------------- epilogue: warps 0-3, one weight row per thread ----------------
+    if (warp < 4) {
+        bool ok = nsteps > 0 && !*(volatile int *)&abort_s;
+        if (ok) ok = mbar_wait(&done_bar, 0);
+        if (ok) {
+            tc_fence_after();
+            const int row = row0 + 32 * warp + lane;
+            for (int c0 = 0; c0 < ntok; c0 += 8) {
+                uint32_t v[8];
+                tc_ld8(tmem_base + ((uint32_t)(32 * warp) << 16) + (uint32_t)c0, v);
+                if (row < a.N) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int tok = tok0 + c0 + j;
+                        if (tok < a.M) {
+                            float *dst = a.Y + (size_t)tok * a.N + row;
+                            if (a.k_splits > 1) atomicAdd(dst, __uint_as_float(v[j]));
+                            else *dst = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+        } else if (nsteps > 0) {
+            atomicExch(a.status, QZ_ERR_TIMEOUT);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == GEMM_PRODUCERS / 32) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+}  // namespace qz

@@ -18,6 +18,7 @@
 #include "gemv_tma.cuh"
 #include "decode_ops.cuh"
 #include "fused_ops.cuh"
+#include "gemm_tc.cuh"
 
 namespace qz {
 
@@ -597,6 +598,105 @@ static void gemv_noalloc(uint32_t t, const uint8_t *W, const float *x, float *y,
     }
 }
 
+// ---- batched GEMM on tcgen05 ------------------------------------------------------------------
+static __nv_bfloat16 *g_xb = nullptr;   // bf16 copy of the activation tile (library scratch, grows)
+static size_t g_xb_elems = 0;
+
+template <uint32_t T, bool PLANES>
+static void launch_gemm(const GemmArgs &a, dim3 grid, size_t smem)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<T, PLANES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           GEMM_STAGES * (GEMM_ROWS * 128 + GEMM_MAX_TOKENS * 128)));
+        attr_set = true;
+    }
+    gemm_tc_kernel<T, PLANES><<<grid, GEMM_PRODUCERS + 32, smem, g_stream>>>(a);
+    QZ_LAUNCH_CHECK();
+}
+
+static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y, int M, int K, int N)
+{
+    if (M <= 0 || N <= 0) return;
+    const FormatInfo fi = format_info(t);
+    // n == 1 is the GEMV (src/dequant.rs:151-153); shapes/types the tensor-core kernel does not take
+    // run token by token (what the reference's GPU prefill does, src/main.rs:1410-1416)
+    const bool tc_ok = fi.block_elems >= 32 && K > 0 && K % GEMM_KSTEP == 0 && !((uintptr_t)W & 15) &&
+                       !((uintptr_t)x & 15) && (((size_t)(K / fi.block_elems) * fi.block_bytes) % 16 == 0);
+    if (M == 1 || !tc_ok) {
+        for (int tkn = 0; tkn < M; tkn++) {
+            const uint8_t *Wp[1] = {W};
+            const float *xp[1] = {x + (size_t)tkn * K};
+            float *yp[1] = {y + (size_t)tkn * N};
+            gemv_n(t, 1, Wp, xp, yp, K, N);
+        }
+        return;
+    }
+    if (!tables_ready(t)) {
+        QZ_CUDA_CHECK(cudaMemsetAsync(y, 0, (size_t)M * N * sizeof(float), g_stream));
+        set_error(QZ_ERR_MISSING_TABLE, "IQ codebook not uploaded (cuda_set_*_grid)");
+        return;
+    }
+    bool planes = false;
+    if (const Range *r = find_range(W)) {
+        if (r->type != t || r->K != K) {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_gemm: pointer lies in a repacked range of another type/in_dim");
+            return;
+        }
+        planes = true;
+    }
+    GemmArgs a;
+    a.W = W; a.Y = y; a.M = M; a.K = K; a.N = N; a.planes = planes;
+    a.tok_tile = M >= GEMM_MAX_TOKENS ? GEMM_MAX_TOKENS : ((M + 15) & ~15);
+    a.n_tok_tiles = (M + a.tok_tile - 1) / a.tok_tile;
+    const int m_pad = a.n_tok_tiles * a.tok_tile;
+    const size_t need = (size_t)m_pad * K;
+    if (need > g_xb_elems) {
+        if (g_xb) {
+            cudaStreamSynchronize(g_stream);
+            cudaFree(g_xb);
+        }
+        if (cudaMalloc(&g_xb, need * sizeof(__nv_bfloat16)) != cudaSuccess) {
+            cudaGetLastError();
+            g_xb = nullptr;
+            g_xb_elems = 0;
+            set_error(QZ_ERR_CUDA, "cudaMalloc of the bf16 activation scratch failed");
+            return;
+        }
+        g_xb_elems = need;
+    }
+    a.Xb = g_xb;
+    const long long quads = (long long)need / 4;
+    convert_x_bf16_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, g_stream>>>(x, g_xb, M, K, m_pad);
+    QZ_LAUNCH_CHECK();
+    const int row_tiles = (N + GEMM_ROWS - 1) / GEMM_ROWS, ksteps = K / GEMM_KSTEP;
+    int splits = 1;
+    const int ctas = row_tiles * a.n_tok_tiles;
+    if (ctas < sm_count()) {
+        splits = (sm_count() + ctas - 1) / ctas;
+        if (splits > ksteps / 8) splits = ksteps / 8;
+        if (splits > 8) splits = 8;
+        if (splits < 1) splits = 1;
+    }
+    a.ksteps_per_split = (ksteps + splits - 1) / splits;
+    a.k_splits = (ksteps + a.ksteps_per_split - 1) / a.ksteps_per_split;
+    if (a.k_splits > 1) QZ_CUDA_CHECK(cudaMemsetAsync(y, 0, (size_t)M * N * sizeof(float), g_stream));
+    a.status = status_word();
+    if (!a.status) return;
+    const dim3 grid(row_tiles, a.n_tok_tiles, a.k_splits);
+    const size_t smem = (size_t)GEMM_STAGES * (GEMM_ROWS * 128 + ((a.tok_tile * 128 + 1023) & ~1023));
+    switch (t) {
+#define X(TT)                                                 \
+    case TT:                                                  \
+        if (planes) launch_gemm<TT, true>(a, grid, smem);     \
+        else launch_gemm<TT, false>(a, grid, smem);           \
+        break;
+        QZ_FOR_BLOCK_TYPES(X)
+#undef X
+    default: break;
+    }
+}
+
 }  // namespace qz
 
 using namespace qz;
@@ -1067,9 +1167,7 @@ void quartz_graph_destroy(void *graph_exec)
 void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,
                int out_dim)
 {
-    // first form: token by token (what the reference's GPU prefill does, src/main.rs:1410-1416)
-    for (int t = 0; t < m; t++)
-        cuda_gemv(ggml_type, d_data, d_x + (size_t)t * in_dim, d_y + (size_t)t * out_dim, in_dim, out_dim);
+    gemm_dispatch(ggml_type, d_data, d_x, d_y, m, in_dim, out_dim);
 }
 
 }  // extern "C"
