@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--small", action="store_true", help="profiling case: lm_head cut to 40080 rows (134 MB, still larger than L2; ~0.3 GB on the device)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode-step section")
+    ap.add_argument("--no-gemm", action="store_true", help="skip the batched (prefill) dequant-GEMM section")
     return ap.parse_args()
 
 
@@ -175,6 +176,64 @@ def run_reference(args):
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+def gemm_section(q, args, torch, np, want_parity):
+    """Batched dequant-GEMM for prefill: Q4_K 4096->14336 and Q6_K 14336->4096 times M = 16, 64, 512, 2048
+    f32 activations ~ N(0,1) (bf16 inside the tensor-core tile, f32 accumulation in TMEM)."""
+    from saient_quartz_b200 import synth
+    L = q.lib()
+    peaks_file = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tf_burst, tf_sust = 1590.0, 1400.0
+    if os.path.exists(peaks_file):
+        try:
+            pk = json.load(open(peaks_file))
+            tf_burst, tf_sust = float(pk["bf16_tflops"]), float(pk["bf16_tflops_sustained"])
+        except Exception:
+            pass
+    hbm, _ = peaks()
+    out = []
+    for (t, K, N) in ((12, 4096, 14336), (14, 14336, 4096)):
+        w = synth.make_weights(t, K, N, tensor_id=400 + t)
+        dw = q.GpuBuf.upload(w)
+        L.cuda_repack_weights(t, dw.ptr, K, N, 1)
+        for M in (16, 64, 512, 2048):
+            X = synth.make_x(K, tensor_id=410, rows=M)
+            dx, dy = q.GpuBuf.upload(X), q.GpuBuf.alloc_f32(M * N)
+            for _ in range(2):
+                L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, N)
+            torch.cuda.synchronize()
+            reps = 10 if M <= 64 else 5
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, N)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            q.check_error("gemm")
+            flops = 2.0 * M * K * N
+            nbytes = synth.type_size(t, K * N) + 4.0 * M * K + 4.0 * M * N
+            row = {"format": synth.FORMATS[t][0], "M": M, "K": K, "N": N, "ms": ms, "tflops": flops / ms / 1e9,
+                   "gbs": nbytes / ms / 1e6, "frac_of_measured_bf16_burst": flops / ms / 1e9 / tf_burst,
+                   "frac_of_measured_bf16_sustained": flops / ms / 1e9 / tf_sust,
+                   "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm, "bound": "hbm" if M <= 64 else "tensor"}
+            if want_parity and M in (16, 512):
+                import oracle
+                y = dy.download().reshape(M, N)
+                pick = [0, M - 1]
+                ref = oracle.gemm(X[pick], w, t, K, N, 2)
+                norms = oracle.row_norms(w, t, K, N)
+                worst = 0.0
+                for i, mrow in enumerate(pick):
+                    tol = 1e-3 * norms * float(np.linalg.norm(X[mrow].astype(np.float64)))
+                    worst = max(worst, float(np.max(np.abs(y[mrow].astype(np.float64) - ref[i]) / tol)))
+                row["max_err_over_tolerance"] = worst
+                assert worst <= 1.0, f"GEMM parity failed: {row}"
+            out.append(row)
+            dx.drop(); dy.drop()
+        dw.drop()
+    return out
 
 
 def decode_section(q, args, torch, np, want_parity):
@@ -426,6 +485,10 @@ def main():
     if rank == 0 and world == 1 and not args.small and not args.no_decode:
         decode = decode_section(q, args, torch, np, want_parity=not args.no_cpu_baseline)
 
+    gemm = None
+    if rank == 0 and world == 1 and not args.small and not args.no_gemm:
+        gemm = gemm_section(q, args, torch, np, want_parity=not args.no_cpu_baseline)
+
     if rank == 0:
         launches_per_step = 0
         for (label, t, K, N) in shapes:
@@ -452,6 +515,7 @@ def main():
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "decode": decode,
+            "gemm": gemm,
         }
         print(json.dumps(line))
     if world > 1:

@@ -11,6 +11,7 @@ ALL_BLOCK_TYPES = [2, 3, 6, 7, 8, 20, 10, 12, 13, 14, 16, 17, 18, 21, 22]
 
 def _gemm(gpu, t, w, X, K, N, repack):
     L = gpu.lib()
+    assert X.ndim == 2 and X.shape[1] == K
     M = X.shape[0]
     dw = gpu.GpuBuf.upload(w)
     if repack:
@@ -61,7 +62,7 @@ def test_gemm_m1_is_gemv_and_odd_k_falls_back(gpu, oracle_mod):
     from saient_quartz_b200 import synth
     K, N = 4096, 256
     w = synth.make_weights(12, K, N, tensor_id=721)
-    X = synth.make_x(K, tensor_id=722, rows=1)
+    X = synth.make_x(K, tensor_id=722, rows=1).reshape(1, K)   # make_x returns a vector for rows=1
     y = _gemm(gpu, 12, w, X, K, N, False)
     assert np.array_equal(y[0], gpu.verify_gemv_cuda(X[0], w, 12, K, N))
     K2 = 96                                                   # not a multiple of 64: token-by-token path
