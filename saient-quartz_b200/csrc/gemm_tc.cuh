@@ -6,16 +6,17 @@
 //
 // One CTA owns a tile of 128 weight rows (the UMMA M dimension) x up to 256 tokens (the UMMA N
 // dimension) x one K split.  Per 64-wide K step:
-//   * eight producer warps dequantize the 128x64 weight tile to bf16 straight into shared
-//     memory in the K-major 128-byte-swizzled layout tcgen05.mma reads (two threads per row,
-//     32 weights each; Q4_K / Q6_K use packed bf16x2 arithmetic: nibble|0x4300 is the bf16
+//   * sixteen producer warps dequantize the 128x64 weight tile to bf16 straight into shared
+//     memory in the K-major 128-byte-swizzled layout tcgen05.mma reads (four threads per row,
+//     16 weights each, raw bytes prefetched several K steps ahead with cp.async into a private
+//     shared-memory ring; Q4_K / Q6_K use packed bf16x2 arithmetic: nibble|0x4300 is the bf16
 //     128+q, an exact HSUB2 removes the 128, one HFMA2 applies scale and min), and copy the
 //     matching 64 columns of the bf16 activation tile beside it;
 //   * they fence the generic->async proxy and arrive on the stage's "full" mbarrier;
 //   * one elected thread issues four tcgen05.mma (K=16 each, kind::f16, bf16 x bf16 -> f32 in
 //     TMEM) and a tcgen05.commit that arrives on the stage's "empty" mbarrier when the tensor
 //     core has finished reading the stage.
-// A 4-stage ring lets dequantization run ahead of the MMAs.  The epilogue reads the
+// A 3-4 stage ring lets dequantization run ahead of the MMAs.  The epilogue reads the
 // accumulator with tcgen05.ld (32 lanes x 8 columns per instruction), one weight row per
 // thread, and stores (or, with K splits, atomically adds) into the token-major output.
 //
@@ -38,34 +39,49 @@ namespace qz {
 constexpr int GEMM_ROWS = 128;       // UMMA M
 constexpr int GEMM_KSTEP = 64;       // one 128-byte swizzle atom of bf16
 constexpr int GEMM_STAGES = 4;
-constexpr int GEMM_PRODUCERS = 256;
 constexpr int GEMM_MAX_TOKENS = 256; // UMMA N per CTA
 
 struct GemmArgs {
     const uint8_t *W;
-    const __nv_bfloat16 *Xb;   // [m_pad, K] bf16, k permuted (0,2,1,3) inside every 4
+    const __nv_bfloat16 *Xb;   // bf16 activation tiles, pre-swizzled (see convert_x_bf16_kernel)
     float *Y;                  // [M, N] token-major
     int M, K, N;
     int planes;                // weight layout
     int n_tok_tiles, tok_tile; // tokens per CTA (multiple of 16, <= 256)
     int k_splits, ksteps_per_split;
+    int stages;                // MMA ring depth
     int *status;
 };
 
-// ---- f32 [M,K] -> bf16 [m_pad,K], (0,2,1,3) inside every four k ----
-__global__ void convert_x_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, int M, int K, int m_pad)
+// ---- f32 [M,K] -> bf16 tiles in exactly the shared-memory image the MMA reads: for every (token
+//      tile, K step) a contiguous [tok_tile rows x 128 B] block, 16-byte chunk c of row r stored at
+//      chunk c ^ (r & 7), k order (0,2,1,3) inside every four.  A stage's activation tile is then
+//      ONE bulk async copy.  One thread per 16-byte chunk. ----
+__global__ void convert_x_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, int M, int K,
+                                      int tok_tile, int n_tok_tiles)
 {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per 4 elements
-    const long long total = (long long)m_pad * K / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int ksteps = K / 64;
+    const long long total = (long long)n_tok_tiles * tok_tile * ksteps * 8;
     if (i >= total) return;
-    const long long row = (i * 4) / K;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row < M) v = *(const float4 *)(x + i * 4);
-    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.z), b = __floats2bfloat162_rn(v.y, v.w);
-    uint2 o;
-    o.x = *(uint32_t *)&a;
-    o.y = *(uint32_t *)&b;
-    *(uint2 *)(out + i * 4) = o;
+    const int c = (int)(i & 7);
+    long long rest = i >> 3;
+    const int r = (int)(rest % tok_tile);
+    rest /= tok_tile;
+    const int ks = (int)(rest % ksteps);
+    const int tile = (int)(rest / ksteps);
+    const int tok = tile * tok_tile + r;
+    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+    if (tok < M) {
+        const float *src = x + (size_t)tok * K + (size_t)ks * 64 + 8 * c;
+        v0 = *(const float4 *)src;
+        v1 = *(const float4 *)(src + 4);
+    }
+    __nv_bfloat162 a = __floats2bfloat162_rn(v0.x, v0.z), b = __floats2bfloat162_rn(v0.y, v0.w);
+    __nv_bfloat162 d = __floats2bfloat162_rn(v1.x, v1.z), e = __floats2bfloat162_rn(v1.y, v1.w);
+    uint4 o = make_uint4(*(uint32_t *)&a, *(uint32_t *)&b, *(uint32_t *)&d, *(uint32_t *)&e);
+    uint8_t *tile_base = (uint8_t *)out + ((size_t)tile * ksteps + ks) * ((size_t)tok_tile * 128);
+    *(uint4 *)(tile_base + (size_t)r * 128 + ((c ^ (r & 7)) << 4)) = o;
 }
 
 // ---- tcgen05 / TMEM primitives ----
@@ -135,166 +151,188 @@ __device__ __forceinline__ void bytes4_to_bf16(uint32_t v, __nv_bfloat162 bias, 
     o13 = *(uint32_t *)&b;
 }
 
-// ---- A-tile producers: thread (row r, half h) writes weights [32h, 32h+32) of the K step ----
-// Generic: any format, either layout, through the bit-exact decoder (f32 -> bf16 rounding).
+// ---- A-tile producers: two threads per weight row; thread (row r, half h) owns the 32 weights
+//      [32h, 32h+32) of every K step (16-byte chunks 4h .. 4h+3 of the tile row).  load() only
+//      issues the global loads of a K step into registers, so the NEXT step's bytes are in flight
+//      while the current one is unpacked; store() unpacks to bf16 and writes the swizzled tile. ----
 template <uint32_t T, bool PLANES>
-__device__ __forceinline__ void produce_a_generic(uint8_t *As, const uint8_t *rowp, int nb, int kstep, int r, int h)
-{
-    const FormatInfo fi = format_info(T);
-    const int elem0 = kstep * GEMM_KSTEP + 32 * h;
-    float w[32];
-    if (rowp) {
-        Fields F = block_fields<PLANES>(fi, rowp, nb, elem0 / fi.block_elems);
-        decode32<T>(F, (elem0 % fi.block_elems) / 32, w);
-    } else {
+struct AProd {   // generic: any format, either layout, through the bit-exact decoder; no prefetch
+    struct Raw { int unused; };
+    __device__ static void load(Raw &, const uint8_t *, int, int, int) {}
+    __device__ static void store(uint8_t *As, const Raw &, const uint8_t *rowp, int nb, int kstep, int r, int h)
+    {
+        const FormatInfo fi = format_info(T);
+        const int elem0 = kstep * GEMM_KSTEP + 32 * h;
+        float w[32];
+        if (rowp) {
+            Fields F = block_fields<PLANES>(fi, rowp, nb, elem0 / fi.block_elems);
+            decode32<T>(F, (elem0 % fi.block_elems) / 32, w);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++) w[i] = 0.f;
-    }
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(w[8 * c + 4 * j], w[8 * c + 4 * j + 2]);
-            __nv_bfloat162 b = __floats2bfloat162_rn(w[8 * c + 4 * j + 1], w[8 * c + 4 * j + 3]);
-            o[2 * j] = *(uint32_t *)&a;
-            o[2 * j + 1] = *(uint32_t *)&b;
+            for (int i = 0; i < 32; i++) w[i] = 0.f;
         }
-        *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(w[8 * c + 4 * j], w[8 * c + 4 * j + 2]);
+                __nv_bfloat162 b = __floats2bfloat162_rn(w[8 * c + 4 * j + 1], w[8 * c + 4 * j + 3]);
+                o[2 * j] = *(uint32_t *)&a;
+                o[2 * j + 1] = *(uint32_t *)&b;
+            }
+            *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
     }
-}
+};
 
 // Q4_K, raw layout: K step = sub-block pair p of block b; half h = sub-block 2p + h
-__device__ __forceinline__ void produce_a_q4k(uint8_t *As, const uint8_t *rowp, int kstep, int r, int h)
-{
-    uint32_t q[8];
-    __nv_bfloat162 scale = __floats2bfloat162_rn(0.f, 0.f), sub = scale;
-    if (rowp) {
-        const uint8_t *blk = rowp + (size_t)(kstep >> 2) * 144;
-        const int p = kstep & 3, j = 2 * p + h;
-        const uint4 hdr = __ldg((const uint4 *)blk);
-        const uint4 q0 = __ldg((const uint4 *)(blk + 16 + 32 * p)), q1 = __ldg((const uint4 *)(blk + 32 + 32 * p));
-        q[0] = q0.x; q[1] = q0.y; q[2] = q0.z; q[3] = q0.w; q[4] = q1.x; q[5] = q1.y; q[6] = q1.z; q[7] = q1.w;
-        const uint8_t *s = (const uint8_t *)&hdr.y;   // the 12 packed 6-bit codes
-        int sc, mn;
-        if (j < 4) {
-            sc = s[j] & 63;
-            mn = s[j + 4] & 63;
+template <>
+struct AProd<T_Q4_K, false> {
+    struct Raw { uint4 hdr, q0, q1; };
+    __device__ static void load(Raw &w, const uint8_t *rowp, int, int kstep, int)
+    {
+        if (rowp) {
+            const uint8_t *blk = rowp + (size_t)(kstep >> 2) * 144;
+            const int p = kstep & 3;
+            w.hdr = __ldg((const uint4 *)blk);
+            w.q0 = __ldg((const uint4 *)(blk + 16 + 32 * p));
+            w.q1 = __ldg((const uint4 *)(blk + 32 + 32 * p));
         } else {
-            sc = (s[j + 4] & 0x0F) | ((s[j - 4] >> 6) << 4);
-            mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+            w.hdr = w.q0 = w.q1 = make_uint4(0, 0, 0, 0);
         }
-        const float2 dm = __half22float2(*(const __half2 *)&hdr.x);
-        const float d1 = dm.x * (float)sc, m1 = dm.y * (float)mn;
-        scale = __floats2bfloat162_rn(d1, d1);
-        sub = __floats2bfloat162_rn(-m1, -m1);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) q[i] = 0;
     }
-    const __nv_bfloat162 bias = __floats2bfloat162_rn(128.f, 128.f);
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r, int h)
+    {
+        const uint32_t q[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
+        const int j = 2 * (kstep & 3) + h;
+        // the 12 packed 6-bit codes (src/dequant.rs:1471-1480), as three words
+        const uint32_t s0 = w.hdr.y, s1 = w.hdr.z, s2 = w.hdr.w;
+        const uint32_t scw = j < 4 ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
+        const uint32_t mw = j < 4 ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
+        const int sh = 8 * (j & 3);
+        const float2 dm = __half22float2(*(const __half2 *)&w.hdr.x);
+        const float d1 = dm.x * (float)((scw >> sh) & 0xFF), m1 = dm.y * (float)((mw >> sh) & 0xFF);
+        const __nv_bfloat162 scale = __floats2bfloat162_rn(d1, d1), sub = __floats2bfloat162_rn(-m1, -m1);
+        const __nv_bfloat162 bias = __floats2bfloat162_rn(128.f, 128.f);
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-        uint32_t o[4];
+        for (int c = 0; c < 4; c++) {
+            uint32_t o[4];
 #pragma unroll
-        for (int jj = 0; jj < 2; jj++) {
-            const uint32_t v = (h ? (q[2 * c + jj] >> 4) : q[2 * c + jj]) & 0x0F0F0F0Fu;
-            bytes4_to_bf16(v, bias, scale, sub, o[2 * jj], o[2 * jj + 1]);
+            for (int jj = 0; jj < 2; jj++) {
+                const uint32_t v = (h ? (q[2 * c + jj] >> 4) : q[2 * c + jj]) & 0x0F0F0F0Fu;
+                bytes4_to_bf16(v, bias, scale, sub, o[2 * jj], o[2 * jj + 1]);
+            }
+            *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
-}
+};
 
 // Q6_K, plane layout: K step = (block b, half n, pair hh); half h selects k = 2hh + h
-__device__ __forceinline__ void produce_a_q6k(uint8_t *As, const uint8_t *rowp, int nb, int kstep, int r, int h)
-{
-    uint32_t ql[8], qh[8];
-    __nv_bfloat162 sc_lo = __floats2bfloat162_rn(0.f, 0.f), sc_hi = sc_lo;
-    const int b = kstep >> 2, n = (kstep >> 1) & 1, hh = kstep & 1, k = 2 * hh + h;
-    if (rowp) {
-        const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n + 32 * h;
-        const uint8_t *ph = rowp + (size_t)nb * 128 + (size_t)b * 64 + 32 * n;
-        const uint4 a0 = __ldg((const uint4 *)pl), a1 = __ldg((const uint4 *)(pl + 16));
-        const uint4 h0 = __ldg((const uint4 *)ph), h1 = __ldg((const uint4 *)(ph + 16));
-        ql[0] = a0.x; ql[1] = a0.y; ql[2] = a0.z; ql[3] = a0.w; ql[4] = a1.x; ql[5] = a1.y; ql[6] = a1.z; ql[7] = a1.w;
-        qh[0] = h0.x; qh[1] = h0.y; qh[2] = h0.z; qh[3] = h0.w; qh[4] = h1.x; qh[5] = h1.y; qh[6] = h1.z; qh[7] = h1.w;
-        const int8_t *sc = (const int8_t *)(rowp + (size_t)nb * 192 + (size_t)b * 16 + 8 * n + 2 * k);
-        const float d = h2f(*(const uint16_t *)(rowp + (size_t)nb * 208 + (size_t)b * 2));
-        const float s0 = d * (float)sc[0], s1 = d * (float)sc[1];
-        sc_lo = __floats2bfloat162_rn(s0, s0);
-        sc_hi = __floats2bfloat162_rn(s1, s1);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) ql[i] = qh[i] = 0;
-    }
-    const __nv_bfloat162 bias = __floats2bfloat162_rn(160.f, 160.f);   // the bf16 magic 128 plus Q6_K's own 32
-    const __nv_bfloat162 zero = __floats2bfloat162_rn(0.f, 0.f);
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        uint32_t o[4];
-#pragma unroll
-        for (int jj = 0; jj < 2; jj++) {
-            const int i = 2 * c + jj;   // word i = weights l = 4i .. 4i+3; l < 16 <=> i < 4
-            const uint32_t v = ((ql[i] >> (4 * hh)) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * k)) & 0x03030303u) << 4);
-            bytes4_to_bf16(v, bias, i < 4 ? sc_lo : sc_hi, zero, o[2 * jj], o[2 * jj + 1]);
+template <>
+struct AProd<T_Q6_K, true> {
+    struct Raw { uint4 a0, a1, h0, h1; uint32_t sc, d; };
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep, int h)
+    {
+        if (rowp) {
+            const int b = kstep >> 2, n = (kstep >> 1) & 1, k = 2 * (kstep & 1) + h;
+            const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n + 32 * h;
+            const uint8_t *ph = rowp + (size_t)nb * 128 + (size_t)b * 64 + 32 * n;
+            w.a0 = __ldg((const uint4 *)pl);
+            w.a1 = __ldg((const uint4 *)(pl + 16));
+            w.h0 = __ldg((const uint4 *)ph);
+            w.h1 = __ldg((const uint4 *)(ph + 16));
+            w.sc = __ldg((const uint16_t *)(rowp + (size_t)nb * 192 + (size_t)b * 16 + 8 * n + 2 * k));
+            w.d = __ldg((const uint16_t *)(rowp + (size_t)nb * 208 + (size_t)b * 2));
+        } else {
+            w.a0 = w.a1 = w.h0 = w.h1 = make_uint4(0, 0, 0, 0);
+            w.sc = w.d = 0;
         }
-        *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
-}
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r, int h)
+    {
+        const uint32_t ql[8] = {w.a0.x, w.a0.y, w.a0.z, w.a0.w, w.a1.x, w.a1.y, w.a1.z, w.a1.w};
+        const uint32_t qh[8] = {w.h0.x, w.h0.y, w.h0.z, w.h0.w, w.h1.x, w.h1.y, w.h1.z, w.h1.w};
+        const int hh = kstep & 1, k = 2 * hh + h;
+        const float d = h2f((uint16_t)w.d);
+        const float s0 = d * (float)(int8_t)(w.sc & 0xFF), s1 = d * (float)(int8_t)(w.sc >> 8);
+        const __nv_bfloat162 sc_lo = __floats2bfloat162_rn(s0, s0), sc_hi = __floats2bfloat162_rn(s1, s1);
+        const __nv_bfloat162 bias = __floats2bfloat162_rn(160.f, 160.f);   // the bf16 magic 128 plus Q6_K's own 32
+        const __nv_bfloat162 zero = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint32_t o[4];
+#pragma unroll
+            for (int jj = 0; jj < 2; jj++) {
+                const int i = 2 * c + jj;   // word i = weights l = 4i .. 4i+3; l < 16 <=> i < 4
+                const uint32_t v = ((ql[i] >> (4 * hh)) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * k)) & 0x03030303u) << 4);
+                bytes4_to_bf16(v, bias, i < 4 ? sc_lo : sc_hi, zero, o[2 * jj], o[2 * jj + 1]);
+            }
+            *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+};
 
 template <uint32_t T, bool PLANES>
-__device__ __forceinline__ void produce_a(uint8_t *As, const uint8_t *rowp, int nb, int kstep, int r, int h)
-{
-    if (T == T_Q4_K && !PLANES) produce_a_q4k(As, rowp, kstep, r, h);
-    else if (T == T_Q6_K && PLANES) produce_a_q6k(As, rowp, nb, kstep, r, h);
-    else produce_a_generic<T, PLANES>(As, rowp, nb, kstep, r, h);
-}
+constexpr bool gemm_fast_type() { return (T == T_Q4_K && !PLANES) || (T == T_Q6_K && PLANES); }
 
-// ---- the kernel: grid = (row tiles, token tiles, K splits), 288 threads ----
-template <uint32_t T, bool PLANES>
-__global__ void __launch_bounds__(GEMM_PRODUCERS + 32, 1) gemm_tc_kernel(const GemmArgs a)
+// ---- the kernel: grid = (row tiles, token tiles, K splits).  A CTA owns HALVES x 128 weight rows
+//      (one UMMA M=128 accumulator per half, side by side in TMEM), so an activation tile fetched
+//      from L2 is reused by HALVES x 128 rows.  8 x HALVES producer warps + 1 MMA/TMEM warp. ----
+template <uint32_t T, bool PLANES, int HALVES>
+__global__ void __launch_bounds__(256 * HALVES + 32, (gemm_fast_type<T, PLANES>() && HALVES == 1) ? 2 : 1)
+    gemm_tc_kernel(const GemmArgs a)
 {
     extern __shared__ __align__(1024) uint8_t gsm[];
     __shared__ uint64_t full_bar[GEMM_STAGES], empty_bar[GEMM_STAGES], done_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
+    using P = AProd<T, PLANES>;
+    constexpr int PRODUCERS = 256 * HALVES, PWARPS = PRODUCERS / 32;
 
     const FormatInfo fi = format_info(T);
     const int nb = a.K / fi.block_elems;
     const size_t row_bytes = (size_t)nb * fi.block_bytes;
-    const int row0 = blockIdx.x * GEMM_ROWS;
+    const int row0 = blockIdx.x * (GEMM_ROWS * HALVES);
     const int tok0 = blockIdx.y * a.tok_tile;
     const int ntok = a.tok_tile;                              // UMMA N (multiple of 16)
+    const int ksteps = a.K / GEMM_KSTEP;
     const int ks0 = blockIdx.z * a.ksteps_per_split;
-    const int ks1 = min(ks0 + a.ksteps_per_split, a.K / GEMM_KSTEP);
+    const int ks1 = min(ks0 + a.ksteps_per_split, ksteps);
     const int nsteps = ks1 - ks0;
-    const int a_bytes = GEMM_ROWS * 128, b_bytes = ntok * 128;
+    const int a_bytes = HALVES * GEMM_ROWS * 128, b_bytes = ntok * 128;
     const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tmem_cols = ntok <= 32 ? 32 : (ntok <= 64 ? 64 : (ntok <= 128 ? 128 : 256));
+    const int acc_cols = HALVES * ntok;
+    const uint32_t tmem_cols = acc_cols <= 32 ? 32 : (acc_cols <= 64 ? 64 : (acc_cols <= 128 ? 128 : (acc_cols <= 256 ? 256 : 512)));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) {
-            mbar_init(&full_bar[s], GEMM_PRODUCERS / 32);
+            mbar_init(&full_bar[s], PWARPS + 1);   // the producer warps + the activation copy
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&done_bar, 1);
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == GEMM_PRODUCERS / 32) tmem_alloc(&tmem_base_s, tmem_cols);   // one full warp allocates
+    if (warp == PWARPS) tmem_alloc(&tmem_base_s, tmem_cols);   // one full warp allocates
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
-    if (warp < GEMM_PRODUCERS / 32) {
+    if (warp < PWARPS) {
         // ---------------- producers ----------------
-        const int r = threadIdx.x >> 1, h = threadIdx.x & 1;
+        const int r = threadIdx.x >> 1, h = threadIdx.x & 1;   // tile row (0 .. 128*HALVES-1), half of the K step
         const uint8_t *rowp = (row0 + r < a.N) ? a.W + (size_t)(row0 + r) * row_bytes : nullptr;
+        const uint8_t *xb_tiles = (const uint8_t *)a.Xb + ((size_t)blockIdx.y * ksteps) * (size_t)b_bytes;
+        typename P::Raw cur, nxt;
+        if (nsteps > 0) P::load(cur, rowp, nb, ks0, h);
         for (int it = 0; it < nsteps; it++) {
-            const int s = it % GEMM_STAGES;
-            const uint32_t round = it / GEMM_STAGES;
+            const int s = it % a.stages;
+            const uint32_t round = it / a.stages;
+            if (it + 1 < nsteps) P::load(nxt, rowp, nb, ks0 + it + 1, h);   // in flight while this step is unpacked
             if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
                 atomicExch(a.status, QZ_ERR_TIMEOUT);
                 abort_s = 1;
@@ -302,13 +340,12 @@ __global__ void __launch_bounds__(GEMM_PRODUCERS + 32, 1) gemm_tc_kernel(const G
             }
             if (*(volatile int *)&abort_s) break;
             uint8_t *As = gsm + (size_t)s * stage_bytes, *Bs = As + a_bytes;
-            produce_a<T, PLANES>(As, rowp, nb, ks0 + it, r, h);
-            // activation tile: ntok rows x 8 chunks of 16 bytes
-            const __nv_bfloat16 *xk = a.Xb + (size_t)tok0 * a.K + (size_t)(ks0 + it) * GEMM_KSTEP;
-            for (int idx = threadIdx.x; idx < ntok * 8; idx += GEMM_PRODUCERS) {
-                const int tr = idx >> 3, c = idx & 7;
-                *(uint4 *)(Bs + sw128(tr, c)) = __ldg((const uint4 *)(xk + (size_t)tr * a.K + 8 * c));
+            if (threadIdx.x == 0) {   // the activation tile of this K step: one bulk async copy
+                mbar_arrive_expect_tx(&full_bar[s], (uint32_t)b_bytes);
+                tma_load_1d(Bs, xb_tiles + (size_t)(ks0 + it) * b_bytes, (uint32_t)b_bytes, &full_bar[s]);
             }
+            P::store(As, cur, rowp, nb, ks0 + it, r, h);   // rows >= 128 land in the second half's tile: r * 128
+            cur = nxt;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_bar[s]);
@@ -318,17 +355,20 @@ __global__ void __launch_bounds__(GEMM_PRODUCERS + 32, 1) gemm_tc_kernel(const G
         const uint32_t idesc = umma_idesc_bf16(ntok);
         bool ok = true;
         for (int it = 0; it < nsteps && ok; it++) {
-            const int s = it % GEMM_STAGES;
-            const uint32_t round = it / GEMM_STAGES;
+            const int s = it % a.stages;
+            const uint32_t round = it / a.stages;
             ok = mbar_wait(&full_bar[s], round & 1);
             if (!ok) break;
             tc_fence_after();
             const uint32_t a_addr = smem_u32(gsm + (size_t)s * stage_bytes), b_addr = a_addr + a_bytes;
 #pragma unroll
-            for (int k = 0; k < GEMM_KSTEP / 16; k++) {
-                // advancing K by 16 bf16 inside the swizzle atom = +32 bytes on the start address
-                tc_mma_bf16(tmem_base, umma_desc_sw128(a_addr + 32 * k), umma_desc_sw128(b_addr + 32 * k), idesc,
-                            (it > 0 || k > 0) ? 1u : 0u);
+            for (int hf = 0; hf < HALVES; hf++) {
+#pragma unroll
+                for (int k = 0; k < GEMM_KSTEP / 16; k++) {
+                    // advancing K by 16 bf16 inside the swizzle atom = +32 bytes on the start address
+                    tc_mma_bf16(tmem_base + (uint32_t)(hf * ntok), umma_desc_sw128(a_addr + hf * (GEMM_ROWS * 128) + 32 * k),
+                                umma_desc_sw128(b_addr + 32 * k), idesc, (it > 0 || k > 0) ? 1u : 0u);
+                }
             }
             tc_commit(&empty_bar[s]);   // arrives once the MMAs above have consumed the stage
         }
@@ -339,16 +379,18 @@ __global__ void __launch_bounds__(GEMM_PRODUCERS + 32, 1) gemm_tc_kernel(const G
         }
     }
 
-    // ---------------- epilogue: warps 0-3, one weight row per thread ----------------
-    if (warp < 4) {
+    // ---------------- epilogue: four warps per half (a warp reads the TMEM lanes 32*(warp%4)..),
+    //                  one weight row per thread ----------------
+    if (warp < 4 * HALVES) {
         bool ok = nsteps > 0 && !*(volatile int *)&abort_s;
         if (ok) ok = mbar_wait(&done_bar, 0);
         if (ok) {
             tc_fence_after();
-            const int row = row0 + 32 * warp + lane;
+            const int hf = warp >> 2, quad = warp & 3;
+            const int row = row0 + GEMM_ROWS * hf + 32 * quad + lane;
             for (int c0 = 0; c0 < ntok; c0 += 8) {
                 uint32_t v[8];
-                tc_ld8(tmem_base + ((uint32_t)(32 * warp) << 16) + (uint32_t)c0, v);
+                tc_ld8(tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(hf * ntok + c0), v);
                 if (row < a.N) {
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
@@ -367,7 +409,7 @@ __global__ void __launch_bounds__(GEMM_PRODUCERS + 32, 1) gemm_tc_kernel(const G
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == GEMM_PRODUCERS / 32) tmem_dealloc(tmem_base, tmem_cols);
+    if (warp == PWARPS) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 }  // namespace qz

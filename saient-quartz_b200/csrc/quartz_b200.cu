@@ -602,17 +602,38 @@ static void gemv_noalloc(uint32_t t, const uint8_t *W, const float *x, float *y,
 static __nv_bfloat16 *g_xb = nullptr;   // bf16 copy of the activation tile (library scratch, grows)
 static size_t g_xb_elems = 0;
 
-template <uint32_t T, bool PLANES>
-static void launch_gemm(const GemmArgs &a, dim3 grid, size_t smem)
+template <uint32_t T, bool PLANES, int HALVES>
+static void launch_gemm(GemmArgs a)
 {
+    // shared-memory plan: as many ring stages as fit (at most GEMM_STAGES).  Small token tiles stay
+    // under half an SM's shared memory so that two CTAs are resident (the unpack is ALU-heavy and
+    // wants the warps); large tiles take the SM.
+    const int stage_bytes = HALVES * GEMM_ROWS * 128 + ((a.tok_tile * 128 + 1023) & ~1023);
+    const int budget = (HALVES == 1 && a.tok_tile <= 64 ? 110 : 200) * 1024;
+    a.stages = budget / stage_bytes;
+    if (a.stages > GEMM_STAGES) a.stages = GEMM_STAGES;
+    const size_t smem = (size_t)a.stages * stage_bytes;
     static bool attr_set = false;
     if (!attr_set) {
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<T, PLANES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           GEMM_STAGES * (GEMM_ROWS * 128 + GEMM_MAX_TOKENS * 128)));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<T, PLANES, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           216 * 1024));
         attr_set = true;
     }
-    gemm_tc_kernel<T, PLANES><<<grid, GEMM_PRODUCERS + 32, smem, g_stream>>>(a);
+    const dim3 grid((a.N + HALVES * GEMM_ROWS - 1) / (HALVES * GEMM_ROWS), a.n_tok_tiles, a.k_splits);
+    gemm_tc_kernel<T, PLANES, HALVES><<<grid, 256 * HALVES + 32, smem, g_stream>>>(a);
     QZ_LAUNCH_CHECK();
+}
+
+template <uint32_t T, bool PLANES>
+static void launch_gemm_type(const GemmArgs &a, int halves)
+{
+    if constexpr (gemm_fast_type<T, PLANES>()) {
+        if (halves == 2) {
+            launch_gemm<T, PLANES, 2>(a);
+            return;
+        }
+    }
+    launch_gemm<T, PLANES, 1>(a);
 }
 
 static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y, int M, int K, int N)
@@ -666,10 +687,15 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y
         g_xb_elems = need;
     }
     a.Xb = g_xb;
-    const long long quads = (long long)need / 4;
-    convert_x_bf16_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, g_stream>>>(x, g_xb, M, K, m_pad);
+    const long long chunks = (long long)need / 8;   // one thread per 16-byte chunk
+    convert_x_bf16_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, g_stream>>>(x, g_xb, M, K, a.tok_tile,
+                                                                                  a.n_tok_tiles);
     QZ_LAUNCH_CHECK();
-    const int row_tiles = (N + GEMM_ROWS - 1) / GEMM_ROWS, ksteps = K / GEMM_KSTEP;
+    // 256-row CTA tiles (two accumulators) halve the activation bytes each CTA pulls from L2 per
+    // flop; they pay off once the token tile is wide enough for that traffic to matter
+    const bool fast = (t == T_Q4_K && !planes) || (t == T_Q6_K && planes);
+    const int halves = (fast && a.tok_tile >= 128) ? 2 : 1;
+    const int row_tiles = (N + halves * GEMM_ROWS - 1) / (halves * GEMM_ROWS), ksteps = K / GEMM_KSTEP;
     int splits = 1;
     const int ctas = row_tiles * a.n_tok_tiles;
     if (ctas < sm_count()) {
@@ -683,13 +709,11 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y
     if (a.k_splits > 1) QZ_CUDA_CHECK(cudaMemsetAsync(y, 0, (size_t)M * N * sizeof(float), g_stream));
     a.status = status_word();
     if (!a.status) return;
-    const dim3 grid(row_tiles, a.n_tok_tiles, a.k_splits);
-    const size_t smem = (size_t)GEMM_STAGES * (GEMM_ROWS * 128 + ((a.tok_tile * 128 + 1023) & ~1023));
     switch (t) {
-#define X(TT)                                                 \
-    case TT:                                                  \
-        if (planes) launch_gemm<TT, true>(a, grid, smem);     \
-        else launch_gemm<TT, false>(a, grid, smem);           \
+#define X(TT)                                              \
+    case TT:                                               \
+        if (planes) launch_gemm_type<TT, true>(a, halves); \
+        else launch_gemm_type<TT, false>(a, halves);       \
         break;
         QZ_FOR_BLOCK_TYPES(X)
 #undef X
