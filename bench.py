@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode-step section")
     ap.add_argument("--no-gemm", action="store_true", help="skip the batched (prefill) dequant-GEMM section")
+    ap.add_argument("--gemm-only", default=None, metavar="FORMAT:M",
+                    help="profiling case: run only this dequant-GEMM case (e.g. Q4_K:2048) and print its row")
     return ap.parse_args()
 
 
@@ -178,7 +180,7 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def gemm_section(q, args, torch, np, want_parity):
+def gemm_section(q, args, torch, np, want_parity, only=None):
     """Batched dequant-GEMM for prefill: Q4_K 4096->14336 and Q6_K 14336->4096 times M = 16, 64, 512, 2048
     f32 activations ~ N(0,1) (bf16 inside the tensor-core tile, f32 accumulation in TMEM)."""
     from saient_quartz_b200 import synth
@@ -194,10 +196,14 @@ def gemm_section(q, args, torch, np, want_parity):
     hbm, _ = peaks()
     out = []
     for (t, K, N) in ((12, 4096, 14336), (14, 14336, 4096)):
+        if only and synth.FORMATS[t][0] != only[0]:
+            continue
         w = synth.make_weights(t, K, N, tensor_id=400 + t)
         dw = q.GpuBuf.upload(w)
         L.cuda_repack_weights(t, dw.ptr, K, N, 1)
         for M in (16, 64, 512, 2048):
+            if only and M != only[1]:
+                continue
             X = synth.make_x(K, tensor_id=410, rows=M)
             dx, dy = q.GpuBuf.upload(X), q.GpuBuf.alloc_f32(M * N)
             for _ in range(2):
@@ -318,6 +324,10 @@ def main():
     from saient_quartz_b200 import synth
     L = q.lib()
     torch.cuda.set_device(0)
+    if args.gemm_only:
+        name, m = args.gemm_only.split(":")
+        print(json.dumps({"gemm": gemm_section(q, args, torch, np, False, only=(name, int(m)))}))
+        return
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda:0"))

@@ -48,7 +48,7 @@ struct GemmArgs {
     int M, K, N;
     int planes;                // weight layout
     int n_tok_tiles, tok_tile; // tokens per CTA (multiple of 16, <= 256)
-    int k_splits, ksteps_per_split;
+    long long units, units_per_cta;   // (tile, K step) units in all, and per CTA
     int stages;                // MMA ring depth
     int *status;
 };
@@ -118,6 +118,19 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t *r)
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Bounded mbarrier wait that sleeps between polls: the waiting warps (producers ahead of the tensor
+// core, epilogue warps idle for a whole tile) leave the issue slots to the warps that unpack.
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t *bar, uint32_t parity, unsigned ns)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    do {
+        __nanosleep(ns);
+        if (mbar_try_wait(bar, parity)) return true;
+    } while (clock64() - t0 <= TMA_WAIT_CYCLES);
+    return false;
+}
+
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr)
 {
@@ -151,46 +164,51 @@ __device__ __forceinline__ void bytes4_to_bf16(uint32_t v, __nv_bfloat162 bias, 
     o13 = *(uint32_t *)&b;
 }
 
-// ---- A-tile producers: two threads per weight row; thread (row r, half h) owns the 32 weights
-//      [32h, 32h+32) of every K step (16-byte chunks 4h .. 4h+3 of the tile row).  load() only
-//      issues the global loads of a K step into registers, so the NEXT step's bytes are in flight
-//      while the current one is unpacked; store() unpacks to bf16 and writes the swizzled tile. ----
+// ---- A-tile producers: one thread per weight row and K step (64 weights = the tile row's eight
+//      16-byte chunks).  load() only issues the global loads of a K step into registers, so they
+//      are in flight while the thread's previous step is unpacked; store() unpacks to bf16 and
+//      writes the swizzled tile row. ----
 template <uint32_t T, bool PLANES>
 struct AProd {   // generic: any format, either layout, through the bit-exact decoder; no prefetch
     struct Raw { int unused; };
-    __device__ static void load(Raw &, const uint8_t *, int, int, int) {}
-    __device__ static void store(uint8_t *As, const Raw &, const uint8_t *rowp, int nb, int kstep, int r, int h)
+    static constexpr bool TWO_SETS = false;
+    __device__ static void load(Raw &, const uint8_t *, int, int) {}
+    __device__ static void store(uint8_t *As, const Raw &, const uint8_t *rowp, int nb, int kstep, int r)
     {
         const FormatInfo fi = format_info(T);
-        const int elem0 = kstep * GEMM_KSTEP + 32 * h;
-        float w[32];
-        if (rowp) {
-            Fields F = block_fields<PLANES>(fi, rowp, nb, elem0 / fi.block_elems);
-            decode32<T>(F, (elem0 % fi.block_elems) / 32, w);
-        } else {
+#pragma unroll 1
+        for (int h = 0; h < 2; h++) {
+            const int elem0 = kstep * GEMM_KSTEP + 32 * h;
+            float w[32];
+            if (rowp) {
+                Fields F = block_fields<PLANES>(fi, rowp, nb, elem0 / fi.block_elems);
+                decode32<T>(F, (elem0 % fi.block_elems) / 32, w);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 32; i++) w[i] = 0.f;
-        }
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                __nv_bfloat162 a = __floats2bfloat162_rn(w[8 * c + 4 * j], w[8 * c + 4 * j + 2]);
-                __nv_bfloat162 b = __floats2bfloat162_rn(w[8 * c + 4 * j + 1], w[8 * c + 4 * j + 3]);
-                o[2 * j] = *(uint32_t *)&a;
-                o[2 * j + 1] = *(uint32_t *)&b;
+                for (int i = 0; i < 32; i++) w[i] = 0.f;
             }
-            *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    __nv_bfloat162 a = __floats2bfloat162_rn(w[8 * c + 4 * j], w[8 * c + 4 * j + 2]);
+                    __nv_bfloat162 b = __floats2bfloat162_rn(w[8 * c + 4 * j + 1], w[8 * c + 4 * j + 3]);
+                    o[2 * j] = *(uint32_t *)&a;
+                    o[2 * j + 1] = *(uint32_t *)&b;
+                }
+                *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
         }
     }
 };
 
-// Q4_K, raw layout: K step = sub-block pair p of block b; half h = sub-block 2p + h
+// Q4_K, raw layout: K step = sub-block pair p of block b (low nibbles: sub-block 2p, high: 2p+1)
 template <>
 struct AProd<T_Q4_K, false> {
     struct Raw { uint4 hdr, q0, q1; };
-    __device__ static void load(Raw &w, const uint8_t *rowp, int, int kstep, int)
+    static constexpr bool TWO_SETS = true;
+    __device__ static void load(Raw &w, const uint8_t *rowp, int, int kstep)
     {
         if (rowp) {
             const uint8_t *blk = rowp + (size_t)(kstep >> 2) * 144;
@@ -202,73 +220,84 @@ struct AProd<T_Q4_K, false> {
             w.hdr = w.q0 = w.q1 = make_uint4(0, 0, 0, 0);
         }
     }
-    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r, int h)
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r)
     {
         const uint32_t q[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
-        const int j = 2 * (kstep & 3) + h;
+        const int p = kstep & 3;
         // the 12 packed 6-bit codes (src/dequant.rs:1471-1480), as three words
         const uint32_t s0 = w.hdr.y, s1 = w.hdr.z, s2 = w.hdr.w;
-        const uint32_t scw = j < 4 ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
-        const uint32_t mw = j < 4 ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
-        const int sh = 8 * (j & 3);
+        const uint32_t scw = p < 2 ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
+        const uint32_t mw = p < 2 ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
+        const int sh = 16 * (p & 1);
         const float2 dm = __half22float2(*(const __half2 *)&w.hdr.x);
-        const float d1 = dm.x * (float)((scw >> sh) & 0xFF), m1 = dm.y * (float)((mw >> sh) & 0xFF);
-        const __nv_bfloat162 scale = __floats2bfloat162_rn(d1, d1), sub = __floats2bfloat162_rn(-m1, -m1);
         const __nv_bfloat162 bias = __floats2bfloat162_rn(128.f, 128.f);
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            uint32_t o[4];
+        for (int h = 0; h < 2; h++) {
+            const float d1 = dm.x * (float)((scw >> (sh + 8 * h)) & 0xFF), m1 = dm.y * (float)((mw >> (sh + 8 * h)) & 0xFF);
+            const __nv_bfloat162 scale = __floats2bfloat162_rn(d1, d1), sub = __floats2bfloat162_rn(-m1, -m1);
 #pragma unroll
-            for (int jj = 0; jj < 2; jj++) {
-                const uint32_t v = (h ? (q[2 * c + jj] >> 4) : q[2 * c + jj]) & 0x0F0F0F0Fu;
-                bytes4_to_bf16(v, bias, scale, sub, o[2 * jj], o[2 * jj + 1]);
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int jj = 0; jj < 2; jj++) {
+                    const uint32_t v = (h ? (q[2 * c + jj] >> 4) : q[2 * c + jj]) & 0x0F0F0F0Fu;
+                    bytes4_to_bf16(v, bias, scale, sub, o[2 * jj], o[2 * jj + 1]);
+                }
+                *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
-            *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 };
 
-// Q6_K, plane layout: K step = (block b, half n, pair hh); half h selects k = 2hh + h
+// Q6_K, plane layout: K step = (block b, half n, pair hh) = the 32-weight runs k = 2hh, 2hh + 1
 template <>
 struct AProd<T_Q6_K, true> {
-    struct Raw { uint4 a0, a1, h0, h1; uint32_t sc, d; };
-    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep, int h)
+    struct Raw { uint4 a[4], h0, h1; uint32_t sc, d; };
+    static constexpr bool TWO_SETS = false;
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
     {
         if (rowp) {
-            const int b = kstep >> 2, n = (kstep >> 1) & 1, k = 2 * (kstep & 1) + h;
-            const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n + 32 * h;
+            const int b = kstep >> 2, n = (kstep >> 1) & 1, hh = kstep & 1;
+            const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n;
             const uint8_t *ph = rowp + (size_t)nb * 128 + (size_t)b * 64 + 32 * n;
-            w.a0 = __ldg((const uint4 *)pl);
-            w.a1 = __ldg((const uint4 *)(pl + 16));
+#pragma unroll
+            for (int i = 0; i < 4; i++) w.a[i] = __ldg((const uint4 *)(pl + 16 * i));
             w.h0 = __ldg((const uint4 *)ph);
             w.h1 = __ldg((const uint4 *)(ph + 16));
-            w.sc = __ldg((const uint16_t *)(rowp + (size_t)nb * 192 + (size_t)b * 16 + 8 * n + 2 * k));
+            w.sc = __ldg((const uint32_t *)(rowp + (size_t)nb * 192 + (size_t)b * 16 + 8 * n + 4 * hh));
             w.d = __ldg((const uint16_t *)(rowp + (size_t)nb * 208 + (size_t)b * 2));
         } else {
-            w.a0 = w.a1 = w.h0 = w.h1 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int i = 0; i < 4; i++) w.a[i] = make_uint4(0, 0, 0, 0);
+            w.h0 = w.h1 = make_uint4(0, 0, 0, 0);
             w.sc = w.d = 0;
         }
     }
-    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r, int h)
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r)
     {
-        const uint32_t ql[8] = {w.a0.x, w.a0.y, w.a0.z, w.a0.w, w.a1.x, w.a1.y, w.a1.z, w.a1.w};
         const uint32_t qh[8] = {w.h0.x, w.h0.y, w.h0.z, w.h0.w, w.h1.x, w.h1.y, w.h1.z, w.h1.w};
-        const int hh = kstep & 1, k = 2 * hh + h;
+        const int hh = kstep & 1;
         const float d = h2f((uint16_t)w.d);
-        const float s0 = d * (float)(int8_t)(w.sc & 0xFF), s1 = d * (float)(int8_t)(w.sc >> 8);
-        const __nv_bfloat162 sc_lo = __floats2bfloat162_rn(s0, s0), sc_hi = __floats2bfloat162_rn(s1, s1);
         const __nv_bfloat162 bias = __floats2bfloat162_rn(160.f, 160.f);   // the bf16 magic 128 plus Q6_K's own 32
         const __nv_bfloat162 zero = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            uint32_t o[4];
+        for (int h = 0; h < 2; h++) {
+            const uint32_t ql[8] = {w.a[2 * h].x, w.a[2 * h].y, w.a[2 * h].z, w.a[2 * h].w,
+                                    w.a[2 * h + 1].x, w.a[2 * h + 1].y, w.a[2 * h + 1].z, w.a[2 * h + 1].w};
+            const int k = 2 * hh + h;
+            const float s0 = d * (float)(int8_t)((w.sc >> (16 * h)) & 0xFF), s1 = d * (float)(int8_t)((w.sc >> (16 * h + 8)) & 0xFF);
+            const __nv_bfloat162 sc_lo = __floats2bfloat162_rn(s0, s0), sc_hi = __floats2bfloat162_rn(s1, s1);
 #pragma unroll
-            for (int jj = 0; jj < 2; jj++) {
-                const int i = 2 * c + jj;   // word i = weights l = 4i .. 4i+3; l < 16 <=> i < 4
-                const uint32_t v = ((ql[i] >> (4 * hh)) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * k)) & 0x03030303u) << 4);
-                bytes4_to_bf16(v, bias, i < 4 ? sc_lo : sc_hi, zero, o[2 * jj], o[2 * jj + 1]);
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int jj = 0; jj < 2; jj++) {
+                    const int i = 2 * c + jj;   // word i = weights l = 4i .. 4i+3; l < 16 <=> i < 4
+                    const uint32_t v = ((ql[i] >> (4 * hh)) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * k)) & 0x03030303u) << 4);
+                    bytes4_to_bf16(v, bias, i < 4 ? sc_lo : sc_hi, zero, o[2 * jj], o[2 * jj + 1]);
+                }
+                *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
-            *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 };
@@ -276,31 +305,54 @@ struct AProd<T_Q6_K, true> {
 template <uint32_t T, bool PLANES>
 constexpr bool gemm_fast_type() { return (T == T_Q4_K && !PLANES) || (T == T_Q6_K && PLANES); }
 
-// ---- the kernel: grid = (row tiles, token tiles, K splits).  A CTA owns HALVES x 128 weight rows
-//      (one UMMA M=128 accumulator per half, side by side in TMEM), so an activation tile fetched
-//      from L2 is reused by HALVES x 128 rows.  8 x HALVES producer warps + 1 MMA/TMEM warp. ----
+template <int HALVES>
+constexpr int gemm_threads() { return 2 * 128 * HALVES + 32 + 128 * HALVES; }   // producers, MMA warp, epilogue warps
+
+// ---- zero the output tiles that more than one CTA contributes to (their partial sums are added
+//      atomically).  One block per CTA of the GEMM grid: a CTA whose first unit lies strictly inside
+//      a tile's K range marks that tile as shared. ----
+__global__ void gemm_zero_split_tiles_kernel(float *__restrict__ Y, int M, int N, int ksteps, int n_tok_tiles, int tok_tile,
+                                             int cta_rows, long long units, long long units_per_cta)
+{
+    const long long u0 = (long long)blockIdx.x * units_per_cta;
+    if (u0 >= units || u0 % ksteps == 0) return;
+    const int tile = (int)(u0 / ksteps);
+    const int row0 = (tile / n_tok_tiles) * cta_rows, tok0 = (tile % n_tok_tiles) * tok_tile;
+    const int rows = min(cta_rows, N - row0), toks = min(tok_tile, M - tok0);
+    for (int i = threadIdx.x; i < rows * toks; i += blockDim.x) {
+        const int tk = i / rows, rr = i - tk * rows;
+        Y[(size_t)(tok0 + tk) * N + row0 + rr] = 0.f;
+    }
+}
+
+// ---- the kernel.  Persistent: the (row tile, token tile, K step) units of the whole problem, tile-major,
+//      are cut into one contiguous, equally long range per CTA, so every SM gets the same amount of
+//      work whatever the tile count; a CTA's range may end inside a tile and the next CTA continues
+//      it.  A tile a single CTA covers completely is stored; a shared one is added atomically onto
+//      zeros.  A CTA owns HALVES x 128 weight rows of a tile (one UMMA M=128 accumulator per half,
+//      side by side in TMEM), so an activation tile fetched from L2 feeds HALVES x 128 rows.
+//      Warps: 8 x HALVES producers | 1 MMA issuer + TMEM owner | 4 x HALVES epilogue. ----
 template <uint32_t T, bool PLANES, int HALVES>
-__global__ void __launch_bounds__(256 * HALVES + 32, (gemm_fast_type<T, PLANES>() && HALVES == 1) ? 2 : 1)
+__global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLANES>() && HALVES == 1) ? 2 : 1)
     gemm_tc_kernel(const GemmArgs a)
 {
     extern __shared__ __align__(1024) uint8_t gsm[];
-    __shared__ uint64_t full_bar[GEMM_STAGES], empty_bar[GEMM_STAGES], done_bar;
+    __shared__ uint64_t full_bar[GEMM_STAGES], empty_bar[GEMM_STAGES], done_bar, acc_free_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     using P = AProd<T, PLANES>;
-    constexpr int PRODUCERS = 256 * HALVES, PWARPS = PRODUCERS / 32;
+    constexpr int PRODUCERS = 256 * HALVES, PWARPS = PRODUCERS / 32, CTA_ROWS = GEMM_ROWS * HALVES;
 
     const FormatInfo fi = format_info(T);
     const int nb = a.K / fi.block_elems;
     const size_t row_bytes = (size_t)nb * fi.block_bytes;
-    const int row0 = blockIdx.x * (GEMM_ROWS * HALVES);
-    const int tok0 = blockIdx.y * a.tok_tile;
     const int ntok = a.tok_tile;                              // UMMA N (multiple of 16)
     const int ksteps = a.K / GEMM_KSTEP;
-    const int ks0 = blockIdx.z * a.ksteps_per_split;
-    const int ks1 = min(ks0 + a.ksteps_per_split, ksteps);
-    const int nsteps = ks1 - ks0;
-    const int a_bytes = HALVES * GEMM_ROWS * 128, b_bytes = ntok * 128;
+    const long long u_begin = (long long)blockIdx.x * a.units_per_cta;
+    const long long u_end = min(u_begin + a.units_per_cta, a.units);
+    const int nunits = u_end > u_begin ? (int)(u_end - u_begin) : 0;
+    const int tile_begin = (int)(u_begin / ksteps), ks_begin = (int)(u_begin - (long long)tile_begin * ksteps);
+    const int a_bytes = CTA_ROWS * 128, b_bytes = ntok * 128;
     const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int acc_cols = HALVES * ntok;
@@ -308,10 +360,11 @@ __global__ void __launch_bounds__(256 * HALVES + 32, (gemm_fast_type<T, PLANES>(
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) {
-            mbar_init(&full_bar[s], PWARPS + 1);   // the producer warps + the activation copy
+            mbar_init(&full_bar[s], PWARPS / 2 + 1);   // one group's producer warps + the activation copy
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&done_bar, 1);
+        mbar_init(&acc_free_bar, 4 * HALVES);
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -323,71 +376,135 @@ __global__ void __launch_bounds__(256 * HALVES + 32, (gemm_fast_type<T, PLANES>(
     const uint32_t tmem_base = tmem_base_s;
 
     if (warp < PWARPS) {
-        // ---------------- producers ----------------
-        const int r = threadIdx.x >> 1, h = threadIdx.x & 1;   // tile row (0 .. 128*HALVES-1), half of the K step
-        const uint8_t *rowp = (row0 + r < a.N) ? a.W + (size_t)(row0 + r) * row_bytes : nullptr;
-        const uint8_t *xb_tiles = (const uint8_t *)a.Xb + ((size_t)blockIdx.y * ksteps) * (size_t)b_bytes;
-        typename P::Raw cur, nxt;
-        if (nsteps > 0) P::load(cur, rowp, nb, ks0, h);
-        for (int it = 0; it < nsteps; it++) {
-            const int s = it % a.stages;
-            const uint32_t round = it / a.stages;
-            if (it + 1 < nsteps) P::load(nxt, rowp, nb, ks0 + it + 1, h);   // in flight while this step is unpacked
-            if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+        // ---------------- producers: two groups of CTA_ROWS threads; group g unpacks the units
+        //                  i = g, g + 2, ... (one thread per tile row), so two units are always in
+        //                  the making and one group's load latency hides behind the other's work ----
+        const int r = threadIdx.x % CTA_ROWS, g = threadIdx.x / CTA_ROWS;
+        struct Cursor { int tile, ks; const uint8_t *rowp; };
+        auto rowp_of = [&](int tile) -> const uint8_t * {
+            const int row = (tile / a.n_tok_tiles) * CTA_ROWS + r;
+            return row < a.N ? a.W + (size_t)row * row_bytes : nullptr;
+        };
+        auto advance = [&](Cursor &c, int by) {
+            c.ks += by;
+            while (c.ks >= ksteps) {
+                c.ks -= ksteps;
+                c.tile++;
+                c.rowp = rowp_of(c.tile);
+            }
+        };
+        Cursor ld{tile_begin, ks_begin, nullptr}, st;
+        ld.rowp = rowp_of(ld.tile);
+        advance(ld, g);
+        st = ld;
+        int s = g % a.stages;
+        uint32_t round = g / a.stages;
+        bool live = true;
+        // one unit: start the loads of this thread's next unit (into the other register set; formats
+        // whose raw bytes are too many registers for two sets reload the one set right after unpacking),
+        // wait for the stage, unpack into it
+        auto produce = [&](typename P::Raw &use, typename P::Raw &pre, int i) {
+            if (P::TWO_SETS && i + 2 < nunits) {
+                advance(ld, 2);
+                P::load(pre, ld.rowp, nb, ld.ks);
+            }
+            if (round > 0 && !mbar_wait_sleep(&empty_bar[s], (round - 1) & 1, 32)) {
+                atomicExch(a.status, QZ_ERR_TIMEOUT);
+                abort_s = 1;
+                live = false;
+                return;
+            }
+            if (*(volatile int *)&abort_s) {
+                live = false;
+                return;
+            }
+            uint8_t *As = gsm + (size_t)s * stage_bytes;
+            if (r == 0) {   // the activation tile of this unit: one bulk async copy
+                const uint8_t *src = (const uint8_t *)a.Xb + ((size_t)(st.tile % a.n_tok_tiles) * ksteps + st.ks) * (size_t)b_bytes;
+                mbar_arrive_expect_tx(&full_bar[s], (uint32_t)b_bytes);
+                tma_load_1d(As + a_bytes, src, (uint32_t)b_bytes, &full_bar[s]);
+            }
+            P::store(As, use, st.rowp, nb, st.ks, r);   // rows >= 128 land in the second half's tile (r * 128)
+            if (!P::TWO_SETS && i + 2 < nunits) {
+                advance(ld, 2);
+                P::load(use, ld.rowp, nb, ld.ks);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[s]);
+            st = ld;
+            s += 2;
+            while (s >= a.stages) {
+                s -= a.stages;
+                round++;
+            }
+        };
+        typename P::Raw r0, r1;
+        if (g < nunits) P::load(r0, ld.rowp, nb, ld.ks);
+        if (P::TWO_SETS) {
+            for (int i = g; i < nunits && live; i += 4) {
+                produce(r0, r1, i);
+                if (i + 2 < nunits && live) produce(r1, r0, i + 2);
+            }
+        } else {
+            for (int i = g; i < nunits && live; i += 2) produce(r0, r0, i);
+        }
+    } else if (warp == PWARPS) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(ntok);
+            int ks = ks_begin, s = 0, seg = 0;
+            uint32_t round = 0;
+            bool ok = true, first = true;
+            for (int i = 0; i < nunits && ok; i++) {
+                ok = mbar_wait(&full_bar[s], round & 1);
+                if (ok && first && seg > 0) ok = mbar_wait(&acc_free_bar, (seg - 1) & 1);   // accumulator drained
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(gsm + (size_t)s * stage_bytes), b_addr = a_addr + a_bytes;
+#pragma unroll
+                for (int hf = 0; hf < HALVES; hf++) {
+#pragma unroll
+                    for (int k = 0; k < GEMM_KSTEP / 16; k++) {
+                        // advancing K by 16 bf16 inside the swizzle atom = +32 bytes on the start address
+                        tc_mma_bf16(tmem_base + (uint32_t)(hf * ntok), umma_desc_sw128(a_addr + hf * (GEMM_ROWS * 128) + 32 * k),
+                                    umma_desc_sw128(b_addr + 32 * k), idesc, (!first || k > 0) ? 1u : 0u);
+                    }
+                }
+                tc_commit(&empty_bar[s]);   // arrives once the MMAs above have consumed the stage
+                first = false;
+                if (++ks == ksteps || i + 1 == nunits) {   // the tile's last unit in this CTA's range
+                    tc_commit(&done_bar);
+                    ks = 0;
+                    seg++;
+                    first = true;
+                }
+                if (++s == a.stages) {
+                    s = 0;
+                    round++;
+                }
+            }
+            if (!ok) {
+                atomicExch(a.status, QZ_ERR_TIMEOUT);
+                abort_s = 1;
+            }
+        }
+    } else {
+        // ---------------- epilogue: four warps per half (a warp reads TMEM lanes 32 * (warp % 4) ..),
+        //                  one weight row per thread ----------------
+        const int hf = (warp - PWARPS - 1) >> 2, quad = warp & 3;
+        int tile = tile_begin, ks0 = ks_begin, left = nunits, seg = 0;
+        while (left > 0) {
+            const int len = min(ksteps - ks0, left);
+            if (*(volatile int *)&abort_s || !mbar_wait_sleep(&done_bar, seg & 1, 500)) {
                 atomicExch(a.status, QZ_ERR_TIMEOUT);
                 abort_s = 1;
                 break;
             }
-            if (*(volatile int *)&abort_s) break;
-            uint8_t *As = gsm + (size_t)s * stage_bytes, *Bs = As + a_bytes;
-            if (threadIdx.x == 0) {   // the activation tile of this K step: one bulk async copy
-                mbar_arrive_expect_tx(&full_bar[s], (uint32_t)b_bytes);
-                tma_load_1d(Bs, xb_tiles + (size_t)(ks0 + it) * b_bytes, (uint32_t)b_bytes, &full_bar[s]);
-            }
-            P::store(As, cur, rowp, nb, ks0 + it, r, h);   // rows >= 128 land in the second half's tile: r * 128
-            cur = nxt;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full_bar[s]);
-        }
-    } else if (lane == 0) {
-        // ---------------- MMA issuer ----------------
-        const uint32_t idesc = umma_idesc_bf16(ntok);
-        bool ok = true;
-        for (int it = 0; it < nsteps && ok; it++) {
-            const int s = it % a.stages;
-            const uint32_t round = it / a.stages;
-            ok = mbar_wait(&full_bar[s], round & 1);
-            if (!ok) break;
             tc_fence_after();
-            const uint32_t a_addr = smem_u32(gsm + (size_t)s * stage_bytes), b_addr = a_addr + a_bytes;
-#pragma unroll
-            for (int hf = 0; hf < HALVES; hf++) {
-#pragma unroll
-                for (int k = 0; k < GEMM_KSTEP / 16; k++) {
-                    // advancing K by 16 bf16 inside the swizzle atom = +32 bytes on the start address
-                    tc_mma_bf16(tmem_base + (uint32_t)(hf * ntok), umma_desc_sw128(a_addr + hf * (GEMM_ROWS * 128) + 32 * k),
-                                umma_desc_sw128(b_addr + 32 * k), idesc, (it > 0 || k > 0) ? 1u : 0u);
-                }
-            }
-            tc_commit(&empty_bar[s]);   // arrives once the MMAs above have consumed the stage
-        }
-        if (ok) tc_commit(&done_bar);
-        else {
-            atomicExch(a.status, QZ_ERR_TIMEOUT);
-            abort_s = 1;
-        }
-    }
-
-    // ---------------- epilogue: four warps per half (a warp reads the TMEM lanes 32*(warp%4)..),
-    //                  one weight row per thread ----------------
-    if (warp < 4 * HALVES) {
-        bool ok = nsteps > 0 && !*(volatile int *)&abort_s;
-        if (ok) ok = mbar_wait(&done_bar, 0);
-        if (ok) {
-            tc_fence_after();
-            const int hf = warp >> 2, quad = warp & 3;
-            const int row = row0 + GEMM_ROWS * hf + 32 * quad + lane;
+            const bool whole = len == ksteps;
+            const int row = (tile / a.n_tok_tiles) * CTA_ROWS + GEMM_ROWS * hf + 32 * quad + lane;
+            const int tok0 = (tile % a.n_tok_tiles) * ntok;
             for (int c0 = 0; c0 < ntok; c0 += 8) {
                 uint32_t v[8];
                 tc_ld8(tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(hf * ntok + c0), v);
@@ -397,15 +514,25 @@ __global__ void __launch_bounds__(256 * HALVES + 32, (gemm_fast_type<T, PLANES>(
                         const int tok = tok0 + c0 + j;
                         if (tok < a.M) {
                             float *dst = a.Y + (size_t)tok * a.N + row;
-                            if (a.k_splits > 1) atomicAdd(dst, __uint_as_float(v[j]));
-                            else *dst = __uint_as_float(v[j]);
+                            if (whole) *dst = __uint_as_float(v[j]);
+                            else atomicAdd(dst, __uint_as_float(v[j]));
                         }
                     }
                 }
             }
-        } else if (nsteps > 0) {
-            atomicExch(a.status, QZ_ERR_TIMEOUT);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_free_bar);
+            left -= len;
+            ks0 = 0;
+            tile++;
+            seg++;
         }
+    }
+    if (threadIdx.x == 0 && *(volatile int *)&abort_s) {
+        // gave up: let this thread's own bulk copies land before the shared memory goes away
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) {}
     }
     tc_fence_before();
     __syncthreads();

@@ -609,7 +609,8 @@ static void launch_gemm(GemmArgs a)
     // under half an SM's shared memory so that two CTAs are resident (the unpack is ALU-heavy and
     // wants the warps); large tiles take the SM.
     const int stage_bytes = HALVES * GEMM_ROWS * 128 + ((a.tok_tile * 128 + 1023) & ~1023);
-    const int budget = (HALVES == 1 && a.tok_tile <= 64 ? 110 : 200) * 1024;
+    const bool two = gemm_fast_type<T, PLANES>() && HALVES == 1 && a.tok_tile <= 64;
+    const int budget = (two ? 110 : 200) * 1024;
     a.stages = budget / stage_bytes;
     if (a.stages > GEMM_STAGES) a.stages = GEMM_STAGES;
     const size_t smem = (size_t)a.stages * stage_bytes;
@@ -619,8 +620,18 @@ static void launch_gemm(GemmArgs a)
                                            216 * 1024));
         attr_set = true;
     }
-    const dim3 grid((a.N + HALVES * GEMM_ROWS - 1) / (HALVES * GEMM_ROWS), a.n_tok_tiles, a.k_splits);
-    gemm_tc_kernel<T, PLANES, HALVES><<<grid, 256 * HALVES + 32, smem, g_stream>>>(a);
+    // one equal share of the (tile, K step) units per resident CTA; at least 8 units each
+    const int cta_rows = HALVES * GEMM_ROWS, ksteps = a.K / GEMM_KSTEP;
+    const long long tiles = (long long)((a.N + cta_rows - 1) / cta_rows) * a.n_tok_tiles;
+    a.units = tiles * ksteps;
+    long long ctas = (long long)sm_count() * (two ? 2 : 1);
+    if (ctas > (a.units + 7) / 8) ctas = (a.units + 7) / 8;
+    a.units_per_cta = (a.units + ctas - 1) / ctas;
+    ctas = (a.units + a.units_per_cta - 1) / a.units_per_cta;
+    gemm_zero_split_tiles_kernel<<<(unsigned)ctas, 256, 0, g_stream>>>(a.Y, a.M, a.N, ksteps, a.n_tok_tiles, a.tok_tile, cta_rows,
+                                                                    a.units, a.units_per_cta);
+    QZ_LAUNCH_CHECK();
+    gemm_tc_kernel<T, PLANES, HALVES><<<(unsigned)ctas, gemm_threads<HALVES>(), smem, g_stream>>>(a);
     QZ_LAUNCH_CHECK();
 }
 
@@ -695,18 +706,6 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y
     // flop; they pay off once the token tile is wide enough for that traffic to matter
     const bool fast = (t == T_Q4_K && !planes) || (t == T_Q6_K && planes);
     const int halves = (fast && a.tok_tile >= 128) ? 2 : 1;
-    const int row_tiles = (N + halves * GEMM_ROWS - 1) / (halves * GEMM_ROWS), ksteps = K / GEMM_KSTEP;
-    int splits = 1;
-    const int ctas = row_tiles * a.n_tok_tiles;
-    if (ctas < sm_count()) {
-        splits = (sm_count() + ctas - 1) / ctas;
-        if (splits > ksteps / 8) splits = ksteps / 8;
-        if (splits > 8) splits = 8;
-        if (splits < 1) splits = 1;
-    }
-    a.ksteps_per_split = (ksteps + splits - 1) / splits;
-    a.k_splits = (ksteps + a.ksteps_per_split - 1) / a.ksteps_per_split;
-    if (a.k_splits > 1) QZ_CUDA_CHECK(cudaMemsetAsync(y, 0, (size_t)M * N * sizeof(float), g_stream));
     a.status = status_word();
     if (!a.status) return;
     switch (t) {
