@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode-step section")
     ap.add_argument("--no-gemm", action="store_true", help="skip the batched (prefill) dequant-GEMM section")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="profiling case: run only the fused decode-step section (no CPU parity pass) and print it")
     ap.add_argument("--gemm-only", default=None, metavar="FORMAT:M",
                     help="profiling case: run only this dequant-GEMM case (e.g. Q4_K:2048) and print its row")
     return ap.parse_args()
@@ -242,7 +244,7 @@ def gemm_section(q, args, torch, np, want_parity, only=None):
     return out
 
 
-def decode_section(q, args, torch, np, want_parity):
+def decode_section(q, args, torch, np, want_parity, fused_only=False):
     """Full batch-1 decode step of a random-init Llama-3-8B-architecture model in the fixed
     Q4_K_M-style layout (q/k/v/o/gate/up Q4_K, down + output head Q6_K), f32 KV cache pre-filled
     with N(0,1) at context 1024, decoding position 1024."""
@@ -260,6 +262,8 @@ def decode_section(q, args, torch, np, want_parity):
            "bytes_per_token": bytes_per_token, "build_s": round(build_s, 1)}
     peak, _ = peaks()
     for name, fused in (("fused_graph", True), ("reference_sequence", False)):
+        if fused_only and not fused:
+            continue
         for _ in range(3):
             m.step_device(token, pos, fused)
         torch.cuda.synchronize()
@@ -275,6 +279,9 @@ def decode_section(q, args, torch, np, want_parity):
                      "gbs": bytes_per_token / (ms * 1e-3) / 1e9,
                      "frac_of_measured_hbm": bytes_per_token / (ms * 1e-3) / 1e9 / peak}
         q.check_error("decode " + name)
+    if fused_only:
+        m.close()
+        return out
     # end to end as the host sees it: token in, 513 KB of logits out, per step
     n = 5
     t1 = time.perf_counter()
@@ -324,6 +331,9 @@ def main():
     from saient_quartz_b200 import synth
     L = q.lib()
     torch.cuda.set_device(0)
+    if args.decode_only:
+        print(json.dumps({"decode": decode_section(q, args, torch, np, False, fused_only=True)}))
+        return
     if args.gemm_only:
         name, m = args.gemm_only.split(":")
         print(json.dumps({"gemm": gemm_section(q, args, torch, np, False, only=(name, int(m)))}))

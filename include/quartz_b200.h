@@ -183,6 +183,37 @@ void quartz_graph_destroy(void *graph_exec);
 void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,
                int out_dim);
 
+/* ---- Row-sharded layers over the GPUs of one box (one process per GPU).  No counterpart in the
+ * reference, which drives a single device (src/cuda.rs:301-358).  A layer's weight rows are split
+ * over the ranks (the loader uploads rows [n0, n1) of each matrix on rank r); every rank computes
+ * its slice of y and stores it, from the GEMV's own epilogue, into the "window" of every rank over
+ * NVLink peer mappings, so that after quartz_mgpu_wait() each rank holds the complete vector.
+ *
+ *   quartz_set_device       select the CUDA device of this process (before any other call)
+ *   quartz_mgpu_init        allocate this rank's window (data_bytes of f32 payload) and write its
+ *                           inter-process handle (quartz_mgpu_handle_bytes() bytes) to handle_out
+ *   quartz_mgpu_attach      handles = the handles of all ranks, in rank order, concatenated (the
+ *                           host exchanges them by whatever means it has); maps the peers' windows
+ *   quartz_mgpu_data        device pointer to this rank's payload area (read complete vectors here)
+ *   cuda_gemv_push          cuda_gemv whose out_dim rows land at payload[dst_off + j] of EVERY rank
+ *   cuda_push_rows          the same exchange for an [m x n_local] block already in device memory
+ *                           (GEMM outputs): element (i, j) lands at payload[dst_off + i*dst_ld + j]
+ *   quartz_mgpu_wait        enqueue the wait for the current exchange: every rank's slice has landed
+ *                           when it completes (bounded: QZ_ERR_TIMEOUT after ~0.5 s)
+ * Each rank must issue the same sequence of pushes and waits (one wait per push).  A payload region
+ * may be overwritten only after an exchange into another region has completed in between.  All
+ * return 0 on success, -1 on failure (see quartz_last_error). */
+size_t quartz_mgpu_handle_bytes(void);
+int quartz_set_device(int device);
+int quartz_mgpu_init(int rank, int world, size_t data_bytes, void *handle_out);
+int quartz_mgpu_attach(const void *handles);
+float *quartz_mgpu_data(void);
+void cuda_gemv_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, size_t dst_off, int in_dim,
+                    int out_dim);
+void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size_t dst_ld);
+void quartz_mgpu_wait(void);
+void quartz_mgpu_shutdown(void);
+
 #ifdef __cplusplus
 }
 #endif

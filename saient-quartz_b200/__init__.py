@@ -81,6 +81,15 @@ _SIGS = {
     "quartz_graph_destroy": (None, [C.c_void_p]),
     "cuda_gemv_noalloc": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "cuda_gemm": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "quartz_mgpu_handle_bytes": (C.c_size_t, []),
+    "quartz_set_device": (C.c_int, [C.c_int]),
+    "quartz_mgpu_init": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
+    "quartz_mgpu_attach": (C.c_int, [C.c_void_p]),
+    "quartz_mgpu_data": (C.c_void_p, []),
+    "cuda_gemv_push": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int]),
+    "cuda_push_rows": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t]),
+    "quartz_mgpu_wait": (None, []),
+    "quartz_mgpu_shutdown": (None, []),
 }
 
 # The 28 symbols the reference's Rust host binds (src/cuda.rs:6-55).

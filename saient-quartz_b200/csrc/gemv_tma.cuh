@@ -20,6 +20,7 @@
 
 #include "gemv_formats_iq.cuh"
 #include "gemv_formats_k.cuh"
+#include "mgpu.cuh"
 
 namespace qz {
 
@@ -39,6 +40,7 @@ struct TmaArgs {
     int n_stages;
     int *status;             // device status word (0 = ok)
     int probe;               // measurement aid: 1 = consumers release stages without computing (streaming ceiling)
+    PushArgs push;           // push.n > 0: rows go to every rank's window instead of y (single matrix)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -215,6 +217,15 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     const int wpr = a.Upad >> 5;
     const int wir = MODE == 2 ? (threadIdx.x >> 5) % wpr : 0;
     float *__restrict__ y = a.y[m];
+    // the row's result: a local store, or (row-sharded layers) a store into every rank's window
+    auto store_y = [&](int row, float v) {
+        if (a.push.n == 0) {
+            y[row] = a.accumulate ? y[row] + v : v;
+        } else {
+            for (int r = 0; r < a.push.n; r++) a.push.data[r][a.push.dst_off + row] = v;
+        }
+    };
+    bool dead = false;
 
     // Padding lanes (u >= U) run on unit 0's bytes and are masked out of the sums; rows past
     // N in the last tile are computed from stale shared memory and simply never stored.
@@ -230,15 +241,16 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     uint32_t sp = row_base, bar_off = 0, parity = 0;
     int s = 0;
-    for (int t0 = 0; t0 < my_tiles; t0 += 4) {
+    for (int t0 = 0; t0 < my_tiles && !dead; t0 += 4) {
         float acc[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             acc[j] = 0.f;
             if (t0 + j < my_tiles) {
-                if (!mbar_wait_addr(full0 + bar_off, parity)) {
-                    atomicExch(a.status, QZ_ERR_TIMEOUT);
-                    return;
+                if (dead || !mbar_wait_addr(full0 + bar_off, parity)) {
+                    if (!dead) atomicExch(a.status, QZ_ERR_TIMEOUT);
+                    dead = true;   // the whole CTA waits on the same barriers: every warp gives up here
+                    continue;
                 }
                 if (!a.probe) {
                     typename F::WRegs w;
@@ -252,6 +264,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
                 if (++s == n_stages) { s = 0; sp = row_base; bar_off = 0; parity ^= 1; }
             }
         }
+        if (dead) break;
         // ---- reduce the group's (up to) four rows ----
         // row of group member j: tile (cta + (t0 + j) * n_cta), thread-row rl
         const int row_j0 = (cta + t0 * n_cta) * a.RP + rl, row_step = n_cta * a.RP;
@@ -261,7 +274,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
                 float v = active ? acc[j] : 0.f;
                 for (int o = a.Upad >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
                 const int row = row_j0 + j * row_step;
-                if (u == 0 && t0 + j < my_tiles && row < a.N) y[row] = a.accumulate ? y[row] + v : v;
+                if (u == 0 && t0 + j < my_tiles && row < a.N) store_y(row, v);
             }
         } else {
             const float v = warp_sum4(active ? acc[0] : 0.f, active ? acc[1] : 0.f, active ? acc[2] : 0.f,
@@ -269,7 +282,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             const int j = lane >> 3;   // which of the four rows this lane's total belongs to
             if (MODE == 1) {
                 const int row = row_j0 + j * row_step;
-                if ((lane & 7) == 0 && t0 + j < my_tiles && row < a.N) y[row] = a.accumulate ? y[row] + v : v;
+                if ((lane & 7) == 0 && t0 + j < my_tiles && row < a.N) store_y(row, v);
             } else {
                 // the row's warps meet at their own named barrier; its first warp finishes the sums
                 float *p = part[(t0 >> 2) & 1] + rl * wpr * 4;
@@ -279,10 +292,16 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
                     float t = 0.f;
                     for (int k = 0; k < wpr; k++) t += p[lane * wpr + k];
                     const int row = row_j0 + lane * row_step;
-                    if (t0 + lane < my_tiles && row < a.N) y[row] = a.accumulate ? y[row] + t : t;
+                    if (t0 + lane < my_tiles && row < a.N) store_y(row, t);
                 }
             }
         }
+    }
+    if (a.push.n > 0 && !dead) {
+        // all of this CTA's remote stores are out: fence them, meet, and let one thread count the CTA in
+        __threadfence_system();
+        named_bar_sync(15, n_consumers);
+        if (threadIdx.x == 0) push_publish(a.push, gridDim.x);
     }
 }
 

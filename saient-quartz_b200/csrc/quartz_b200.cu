@@ -244,6 +244,9 @@ static void poll_status()
 
 static int g_probe = 0;
 static int g_use_tma = -1;
+// set by cuda_gemv_push around its GEMV: the TMA kernel takes it as its epilogue and clears `pending`
+static PushArgs g_push_args;
+static bool g_push_pending = false;
 static bool use_tma()
 {
     if (g_use_tma < 0) {
@@ -279,6 +282,11 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     a.status = status_word();
     if (!a.status) return false;
     a.probe = g_probe;
+    a.push.n = 0;
+    if (g_push_pending && n_mats == 1 && !g.accumulate) {
+        a.push = g_push_args;
+        g_push_pending = false;
+    }
     static bool attr_set = false;
     if (!attr_set) {
         QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + F::TABLE_BYTES));
@@ -1191,6 +1199,163 @@ void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, floa
                int out_dim)
 {
     gemm_dispatch(ggml_type, d_data, d_x, d_y, m, in_dim, out_dim);
+}
+
+// ======================= row-sharded layers: peer windows =======================
+static uint8_t *g_win = nullptr;          // this rank's window (control words + data)
+static size_t g_win_data_bytes = 0;
+static int g_mg_rank = 0, g_mg_world = 0;
+static void *g_peer_base[MGPU_MAX_RANKS] = {};
+static bool g_mg_attached = false;
+
+size_t quartz_mgpu_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+int quartz_set_device(int device)
+{
+    if (cudaSetDevice(device) != cudaSuccess) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "quartz_set_device: cudaSetDevice failed");
+        return -1;
+    }
+    g_sm_count = 0;
+    return 0;
+}
+
+int quartz_mgpu_init(int rank, int world, size_t data_bytes, void *handle_out)
+{
+    if (g_win || rank < 0 || world < 1 || world > MGPU_MAX_RANKS || rank >= world || !handle_out) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_mgpu_init: bad rank/world, or already initialised");
+        return -1;
+    }
+    data_bytes = (data_bytes + 255) & ~(size_t)255;
+    if (cudaMalloc(&g_win, MGPU_CTRL_BYTES + data_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        g_win = nullptr;
+        set_error(QZ_ERR_CUDA, "quartz_mgpu_init: cudaMalloc of the window failed");
+        return -1;
+    }
+    QZ_CUDA_CHECK(cudaMemset(g_win, 0, MGPU_CTRL_BYTES + data_bytes));
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, g_win) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(g_win);
+        g_win = nullptr;
+        set_error(QZ_ERR_CUDA, "quartz_mgpu_init: cudaIpcGetMemHandle failed");
+        return -1;
+    }
+    memcpy(handle_out, &h, sizeof(h));
+    g_win_data_bytes = data_bytes;
+    g_mg_rank = rank;
+    g_mg_world = world;
+    g_mg_attached = false;
+    return 0;
+}
+
+int quartz_mgpu_attach(const void *handles)
+{
+    if (!g_win || !handles) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_mgpu_attach: call quartz_mgpu_init first");
+        return -1;
+    }
+    for (int r = 0; r < g_mg_world; r++) {
+        if (r == g_mg_rank) {
+            g_peer_base[r] = g_win;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + (size_t)r * sizeof(h), sizeof(h));
+        void *p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess || !p) {
+            cudaGetLastError();
+            set_error(QZ_ERR_CUDA, "quartz_mgpu_attach: cudaIpcOpenMemHandle failed (no peer access between the GPUs?)");
+            return -1;
+        }
+        g_peer_base[r] = p;
+    }
+    g_mg_attached = true;
+    return 0;
+}
+
+float *quartz_mgpu_data(void) { return g_win ? (float *)(g_win + MGPU_CTRL_BYTES) : nullptr; }
+
+static bool fill_push(PushArgs &p, size_t dst_off, size_t elems)
+{
+    if (!g_mg_attached) {
+        set_error(QZ_ERR_BAD_SHAPE, "push: the windows are not attached (quartz_mgpu_init / quartz_mgpu_attach)");
+        return false;
+    }
+    if ((dst_off + elems) * sizeof(float) > g_win_data_bytes) {
+        set_error(QZ_ERR_BAD_SHAPE, "push: the slice does not fit the window");
+        return false;
+    }
+    for (int r = 0; r < MGPU_MAX_RANKS; r++) {
+        uint8_t *b = (uint8_t *)g_peer_base[r < g_mg_world ? r : g_mg_rank];
+        p.ctrl[r] = (MgpuCtrl *)b;
+        p.data[r] = (float *)(b + MGPU_CTRL_BYTES);
+    }
+    p.n = g_mg_world;
+    p.rank = g_mg_rank;
+    p.dst_off = (long long)dst_off;
+    return true;
+}
+
+void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size_t dst_ld)
+{
+    // an empty slice (a rank that owns no rows) still takes part in the exchange: it only publishes
+    if (m < 0) m = 0;
+    if (n_local < 0) n_local = 0;
+    PushArgs p;
+    const long long total = (long long)m * n_local;
+    if (!fill_push(p, dst_off, total ? (size_t)(m - 1) * dst_ld + n_local : 0)) return;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > sm_count()) blocks = sm_count();
+    if (blocks < 1) blocks = 1;
+    mgpu_push_rows_kernel<<<blocks, 256, 0, g_stream>>>(d_src, m, n_local, (long long)dst_ld, p);
+    QZ_LAUNCH_CHECK();
+}
+
+void cuda_gemv_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, size_t dst_off, int in_dim, int out_dim)
+{
+    if (out_dim <= 0) {
+        cuda_push_rows(nullptr, 0, 0, dst_off, 0);
+        return;
+    }
+    if (!fill_push(g_push_args, dst_off, (size_t)out_dim)) return;
+    // the streaming kernel stores into every window from its epilogue; any other kernel writes the
+    // local window and the slice is pushed by a copy kernel
+    float *local = quartz_mgpu_data() + dst_off;
+    g_push_pending = true;
+    gemv_n(ggml_type, 1, &d_data, &d_x, &local, in_dim, out_dim);
+    if (g_push_pending) {
+        g_push_pending = false;
+        cuda_push_rows(local, 1, out_dim, dst_off, (size_t)out_dim);
+    }
+}
+
+void quartz_mgpu_wait(void)
+{
+    if (!g_mg_attached) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_mgpu_wait: the windows are not attached");
+        return;
+    }
+    int *st = status_word();
+    if (!st) return;
+    mgpu_wait_kernel<<<1, 32, 0, g_stream>>>((MgpuCtrl *)g_win, g_mg_world, st);
+    QZ_LAUNCH_CHECK();
+}
+
+void quartz_mgpu_shutdown(void)
+{
+    if (!g_win) return;
+    cudaDeviceSynchronize();
+    for (int r = 0; r < g_mg_world; r++)
+        if (r != g_mg_rank && g_peer_base[r]) cudaIpcCloseMemHandle(g_peer_base[r]);
+    cudaFree(g_win);
+    cudaGetLastError();
+    g_win = nullptr;
+    g_mg_attached = false;
+    g_mg_world = 0;
+    for (int r = 0; r < MGPU_MAX_RANKS; r++) g_peer_base[r] = nullptr;
 }
 
 }  // extern "C"

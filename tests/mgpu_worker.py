@@ -1,0 +1,107 @@
+"""One rank of the row-sharded exchange test; launched by test_gpu_mgpu.py (one process per GPU) as
+    python -m torch.distributed.run --nproc-per-node G tests/mgpu_worker.py
+Every rank uploads its row shard of each matrix, runs cuda_gemv_push + quartz_mgpu_wait, and checks the
+COMPLETE vector in its own window against the CPU oracle.  Then a batched block goes through
+cuda_gemm + cuda_push_rows, and last a wait that nobody answers must come back with QZ_ERR_TIMEOUT."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    q = entry.load_package()
+    from saient_quartz_b200 import synth
+    from saient_quartz_b200.shard import PeerWindow, shard_rows, shard_bytes
+    from saient_quartz_b200.iq_tables import load_tables
+    import oracle
+    oracle.set_tables(load_tables())
+    L = q.lib()
+    torch.cuda.set_device(local)
+    assert L.quartz_set_device(local) == 0
+    if world > 1:
+        dist.init_process_group("gloo")
+    q.ensure_iq_grids()
+    win = PeerWindow(L, rank, world, 4 << 20, dist if world > 1 else None)
+
+    def download(off, n):
+        out = np.empty(n, dtype=np.float32)
+        L.cuda_d2h(out.ctypes.data, win.data_ptr + 4 * off, 4 * n)
+        return out
+
+    # (type, K, N, repack): streaming kernels with the fused push epilogue, a raw-layout matrix, and an
+    # F16 matrix that takes the any-shape kernel + copy push; two alternating window regions
+    cases = [(12, 4096, 14336, True), (14, 14336, 4096, True), (8, 4096, 4096, True), (17, 4096, 1536, True),
+             (12, 4096, 1000, False), (1, 512, 301, False)]
+    region = [0, 32768]
+    for i, (t, K, N, repack) in enumerate(cases):
+        w = synth.make_weights(t, K, N, tensor_id=900 + i)
+        x = synth.make_x(K, tensor_id=950 + i).reshape(-1)
+        n0, n1, per = shard_rows(N, rank, world)
+        b0, b1 = shard_bytes(t, K, N, rank, world)
+        dw = q.GpuBuf.upload(w[b0:b1]) if n1 > n0 else None
+        if repack and dw is not None:
+            L.cuda_repack_weights(t, dw.ptr, K, n1 - n0, 1)
+        dx = q.GpuBuf.upload(x)
+        off = region[i & 1]
+        for rep in range(2):   # twice: the counters advance, the result must not change
+            if dw is not None:
+                win.gemv_push(t, dw.ptr, dx.ptr, off + n0, K, n1 - n0)
+            else:
+                win.gemv_push(t, 0, dx.ptr, off + n0, K, 0)
+            win.wait()
+            L.cuda_sync()
+            q.check_error("gemv_push")
+            y = download(off, N)
+            ref = oracle.gemv(x, w, t, K, N)
+            tol = 1e-3 * oracle.row_norms(w, t, K, N) * float(np.linalg.norm(x.astype(np.float64)))
+            err = np.abs(y.astype(np.float64) - ref)
+            assert np.all(err <= tol), f"rank {rank} case {i} rep {rep}: err/tol {np.max(err / np.maximum(tol, 1e-30))}"
+            # the exchange is not allowed to run ahead into the region just read: alternate regions
+            off = region[(i + rep + 1) & 1]
+        if dw is not None:
+            dw.drop()
+        dx.drop()
+
+    # batched block: Y[M, N] column-sharded, pushed with cuda_push_rows
+    t, K, N, M = 12, 2048, 768, 24
+    w = synth.make_weights(t, K, N, tensor_id=990)
+    X = synth.make_x(K, tensor_id=991, rows=M)
+    n0, n1, per = shard_rows(N, rank, world)
+    b0, b1 = shard_bytes(t, K, N, rank, world)
+    dw, dx = q.GpuBuf.upload(w[b0:b1]), q.GpuBuf.upload(X)
+    dy = q.GpuBuf.alloc_f32(M * (n1 - n0))
+    L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, n1 - n0)
+    win.push_rows(dy.ptr, M, n1 - n0, 65536 + n0, N)
+    win.wait()
+    L.cuda_sync()
+    q.check_error("gemm push")
+    Y = download(65536, M * N).reshape(M, N)
+    ref = oracle.gemm(X, w, t, K, N, M)
+    norms = oracle.row_norms(w, t, K, N)
+    for m in range(M):
+        tol = 1e-3 * norms * float(np.linalg.norm(X[m].astype(np.float64)))
+        assert np.all(np.abs(Y[m].astype(np.float64) - ref[m]) <= tol), f"rank {rank} gemm token {m}"
+
+    if world > 1:
+        dist.barrier()
+        # a wait that no push answers runs out (bounded) and reports it; nothing hangs
+        win.wait()
+        L.cuda_sync()
+        assert L.quartz_last_error() == 7, L.quartz_last_error()   # QZ_ERR_TIMEOUT
+        L.quartz_clear_error()
+        dist.barrier()
+    win.close()
+    print(f"rank {rank}/{world}: ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()
