@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--small", action="store_true", help="profiling case: lm_head cut to 40080 rows (134 MB, still larger than L2; ~0.3 GB on the device)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode-step section")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the 70B-shaped row-sharded pair section")
     ap.add_argument("--no-gemm", action="store_true", help="skip the batched (prefill) dequant-GEMM section")
     ap.add_argument("--decode-only", action="store_true",
                     help="profiling case: run only the fused decode-step section (no CPU parity pass) and print it")
@@ -307,6 +308,106 @@ def decode_section(q, args, torch, np, want_parity, fused_only=False):
     return out
 
 
+def sharded70b_section(q, L, torch, win, rank, world, dist, steps):
+    """Llama-3-70B-shaped FFN pair, row-sharded over the ranks: Q4_K 8192->28672 whose complete output
+    (gathered in every rank's window by the GEMV's own peer stores) is the activation of Q6_K
+    28672->8192.  Batch 1 through cuda_gemv_push, batch 32 through cuda_gemm + cuda_push_rows; the
+    NCCL all-gather form of batch 1 is timed beside it.  Times are max over ranks, on the device."""
+    from saient_quartz_b200 import synth
+    from saient_quartz_b200.shard import shard_rows as sr, shard_bytes
+    K1, N1, N2 = 8192, 28672, 8192
+    out = {"shapes": "Q4_K 8192->28672 -> Q6_K 28672->8192", "n_gpus": world}
+    w1, w2 = synth.make_weights(12, K1, N1, tensor_id=300), synth.make_weights(14, N1, N2, tensor_id=301)
+    a0, a1, per1 = sr(N1, rank, world)
+    b0, b1, per2 = sr(N2, rank, world)
+    s0, s1 = shard_bytes(12, K1, N1, rank, world)
+    d1 = q.GpuBuf.upload(w1[s0:s1])
+    s0, s1 = shard_bytes(14, N1, N2, rank, world)
+    d2 = q.GpuBuf.upload(w2[s0:s1])
+    del w1, w2
+    L.cuda_repack_weights(12, d1.ptr, K1, a1 - a0, 1)
+    L.cuda_repack_weights(14, d2.ptr, N1, b1 - b0, 1)
+    total = synth.algorithmic_bytes(12, K1, N1) + synth.algorithmic_bytes(14, N1, N2)
+    M = 32
+    X = synth.make_x(K1, tensor_id=302, rows=M)
+    dx = q.GpuBuf.upload(X)
+    A, B = 0, M * N1                       # window regions (floats): Y1 [M x N1], Y2 [M x N2]
+    base = win.data_ptr
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        if world > 1:
+            tt = torch.tensor([ms], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        q.check_error("sharded 70B-shaped pair")
+        return ms
+
+    def chain1():
+        # the wait for an exchange runs inside the activation conversion of the GEMV that consumes it (the first
+        # GEMV of an iteration thereby also completes the previous iteration's second exchange)
+        win.wait(fused=True)
+        win.gemv_push(12, d1.ptr, dx.ptr, A + a0, K1, a1 - a0)
+        win.wait(fused=True)
+        win.gemv_push(14, d2.ptr, base + 4 * A, B + b0, N1, b1 - b0)
+
+    fn = chain1
+    g = None
+    if L.quartz_graph_begin():
+        chain1()
+        g = L.quartz_graph_end()
+        q.check_error("sharded graph capture")
+        if g:
+            fn = lambda: L.quartz_graph_launch(g)   # noqa: E731
+    n = max(10, min(steps, 50))
+    ms = timed(fn, n)
+    win.wait()
+    out["batch1_push"] = {"ms": ms, "gbs": total / (ms * 1e-3) / 1e9, "launch": "graph replay" if g else "eager",
+                          "exchange": "peer stores from the GEMV epilogue; flag wait fused into the consumer's activation conversion"}
+    if g:
+        L.quartz_graph_destroy(g)
+
+    if world > 1:
+        y1 = torch.zeros(per1 * world, dtype=torch.float32, device="cuda")
+        y2 = torch.zeros(per2 * world, dtype=torch.float32, device="cuda")
+
+        def chain_nccl():
+            L.cuda_gemv(12, d1.ptr, dx.ptr, y1.data_ptr() + 4 * rank * per1, K1, a1 - a0)
+            dist.all_gather_into_tensor(y1, y1[rank * per1:(rank + 1) * per1])
+            L.cuda_gemv(14, d2.ptr, y1.data_ptr(), y2.data_ptr() + 4 * rank * per2, N1, b1 - b0)
+            dist.all_gather_into_tensor(y2, y2[rank * per2:(rank + 1) * per2])
+        ms = timed(chain_nccl, n)
+        out["batch1_nccl_allgather"] = {"ms": ms, "gbs": total / (ms * 1e-3) / 1e9, "launch": "eager"}
+
+    dy1 = q.GpuBuf.alloc_f32(M * (a1 - a0))
+    dy2 = q.GpuBuf.alloc_f32(M * (b1 - b0))
+
+    def chain32():
+        L.cuda_gemm(12, d1.ptr, dx.ptr, dy1.ptr, M, K1, a1 - a0)
+        win.push_rows(dy1.ptr, M, a1 - a0, A + a0, N1)
+        win.wait()
+        L.cuda_gemm(14, d2.ptr, base + 4 * A, dy2.ptr, M, N1, b1 - b0)
+        win.push_rows(dy2.ptr, M, b1 - b0, B + b0, N2)
+        win.wait()
+    ms = timed(chain32, max(5, n // 2))
+    flops = 2.0 * M * (K1 * N1 + N1 * N2)
+    out["batch32_push"] = {"ms": ms, "gbs": total / (ms * 1e-3) / 1e9, "tflops": flops / ms / 1e9, "launch": "eager"}
+    for b in (d1, d2, dx, dy1, dy2):
+        b.drop()
+    return out
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -315,22 +416,23 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        # one GPU per process, visible as device 0 to both torch and the C library
-        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
-        ids = vis.split(",") if vis else [str(i) for i in range(world)]
-        os.environ["CUDA_VISIBLE_DEVICES"] = ids[local_rank]
-        phys_index = ids[local_rank]
-    else:
-        phys_index = (os.environ.get("CUDA_VISIBLE_DEVICES") or "0").split(",")[0]
+    # one GPU per process; every GPU of the box stays visible so that peers' windows can be mapped
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    ids = vis.split(",") if vis else None
+    dev = local_rank if world > 1 else 0
+    phys_index = ids[dev] if ids and dev < len(ids) else str(dev)
 
+    if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"   # NCCL's version banner goes to stdout, which carries the JSON line
     import numpy as np
     import torch
     import __graft_entry__ as entry
     q = entry.load_package()
     from saient_quartz_b200 import synth
     L = q.lib()
-    torch.cuda.set_device(0)
+    torch.cuda.set_device(dev)
+    if L.quartz_set_device(dev) != 0:
+        q.check_error("quartz_set_device")
     if args.decode_only:
         print(json.dumps({"decode": decode_section(q, args, torch, np, False, fused_only=True)}))
         return
@@ -340,14 +442,18 @@ def main():
         return
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda:0"))
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{dev}"))
+    else:
+        dist = None
+    from saient_quartz_b200.shard import PeerWindow
 
     shapes = sweep(args.small)
     mats, xs = make_host_tensors(shapes, rank, world)
     total_bytes = sum(synth.algorithmic_bytes(t, K, N) for (_, t, K, N) in shapes)
 
     # device residency: weights (repacked once, as the loader would), x, y
-    d_w, d_x, y_full, rows = [], [], [], []
+    d_w, d_x, y_full, rows, y_off = [], [], [], [], []
+    off = 0
     for (label, t, K, N), w, x in zip(shapes, mats["w"], xs):
         n0, n1 = shard_rows(N, rank, world)
         buf = q.GpuBuf.upload(w)
@@ -357,15 +463,37 @@ def main():
         per = (N + world - 1) // world
         y_full.append(torch.zeros(per * world, dtype=torch.float32, device="cuda"))
         rows.append((n0, n1, per))
+        y_off.append(off)            # this shape's region of the exchange window, in floats
+        off += (N + 63) & ~63
+    # exchange window: the six output vectors (sweep) or the 70B-shaped pair at batch 32, whichever is larger
+    half = off
+    win_floats = max(2 * half, 32 * (28672 + 8192))
+    win = PeerWindow(L, rank, world, 4 * win_floats, dist) if (world > 1 or not args.small) else None
     L.cuda_sync()
     q.check_error("setup")
 
-    def step():
+    def step_nccl():
         for i, (label, t, K, N) in enumerate(shapes):
             n0, n1, per = rows[i]
             L.cuda_gemv(t, d_w[i].ptr, d_x[i].ptr, y_full[i].data_ptr() + 4 * rank * per, K, n1 - n0)
             if world > 1:
                 dist.all_gather_into_tensor(y_full[i], y_full[i][rank * per:(rank + 1) * per])
+
+    step_no = [0]
+
+    def step_push(parity=None):
+        # every rank's slice lands in every rank's window from the GEMV's own epilogue; the six GEMVs of a
+        # step do not depend on one another, so one wait at the end of the step covers the six exchanges.
+        # Two sets of regions alternate from step to step: a rank one step ahead never writes what a slower
+        # rank may still be reading.
+        par = step_no[0] & 1 if parity is None else parity
+        step_no[0] += 1
+        for i, (label, t, K, N) in enumerate(shapes):
+            n0, n1, per = rows[i]
+            win.gemv_push(t, d_w[i].ptr, d_x[i].ptr, par * half + y_off[i] + n0, K, n1 - n0)
+        win.wait()
+
+    step = step_push if world > 1 else step_nccl
 
     def sync_all():
         torch.cuda.synchronize()
@@ -378,21 +506,29 @@ def main():
     sync_all()
     q.check_error("warmup")
     graph = None
-    if world == 1:
-        # what a host would do with a fixed call sequence: record the six cuda_gemv calls once
-        # (quartz_graph_begin/end) and replay them; kernels become programmatic dependents
+    if True:
+        # what a host would do with a fixed call sequence: record the six GEMV calls (and, sharded, their
+        # exchanges) once (quartz_graph_begin/end) and replay them; kernels become programmatic dependents
+        graph2 = None
         if L.quartz_graph_begin():
-            step()
+            step(0) if world > 1 else step()
             graph = L.quartz_graph_end()
+        if graph and world > 1 and L.quartz_graph_begin():
+            step(1)
+            graph2 = L.quartz_graph_end()
         q.check_error("graph capture")
-        if graph:
+        if graph and (world == 1 or graph2):
             eager_step = step
+            replay_no = [0]
 
             def step():   # noqa: F811
-                L.quartz_graph_launch(graph)
-            for _ in range(3):
+                L.quartz_graph_launch(graph2 if (graph2 and replay_no[0] & 1) else graph)
+                replay_no[0] += 1
+            for _ in range(4):
                 step()
             sync_all()
+        else:
+            graph = None
 
     sampler = ClockSampler(phys_index)
     if rank == 0:
@@ -478,7 +614,76 @@ def main():
                "d2h_bytes_per_step": sum(4 * N for (_, _, _, N) in shapes), "ms_per_step": e2e_ms}
         q.check_error("e2e")
 
+    nccl_variant = None
+    if world > 1:
+        # end to end, sharded: every rank copies the step's activations in, and reads the complete outputs
+        # back from its window (pinned host buffers, synchronous copies as in GpuScratch::gemv)
+        pinned = [torch.from_numpy(x).pin_memory() for x in xs]
+        hx = [p_.numpy() for p_ in pinned]
+        hy = [torch.empty(N, dtype=torch.float32).pin_memory().numpy() for (_, _, _, N) in shapes]
+
+        e2e_no = [0]
+
+        def e2e_step():
+            for i, (label, t, K, N) in enumerate(shapes):
+                n0, n1, per = rows[i]
+                L.cuda_h2d(d_x[i].ptr, hx[i].ctypes.data, 4 * K)
+                par = (e2e_no[0] + i) & 1   # alternate regions from exchange to exchange
+                win.gemv_push(t, d_w[i].ptr, d_x[i].ptr, par * half + y_off[i] + n0, K, n1 - n0)
+                win.wait()
+                L.cuda_d2h(hy[i].ctypes.data, win.data_ptr + 4 * (par * half + y_off[i]), 4 * N)
+            e2e_no[0] += 1
+        for _ in range(3):
+            e2e_step()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(5, args.steps // 2)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        sync_all()
+        tt = torch.tensor([e0.elapsed_time(e1) / n_e2e], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item())
+        e2e = {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": sum(4 * K for (_, _, K, _) in shapes),
+               "d2h_bytes_per_step": sum(4 * N for (_, _, _, N) in shapes), "ms_per_step": e2e_ms,
+               "note": "per rank; every rank holds the complete outputs"}
+        q.check_error("e2e sharded")
+        # parity of what was timed: the complete vector in this rank's window against the CPU oracle
+        if rank == 0:
+            import oracle
+            from saient_quartz_b200.iq_tables import load_tables
+            oracle.set_tables(load_tables())
+            i = 1
+            _, t, K, N = shapes[i]
+            wfull = synth.make_weights(t, K, N, tensor_id=100 + i)
+            ref = oracle.gemv(xs[i].reshape(-1), wfull, t, K, N)
+            tol = oracle.tolerance(wfull, t, K, N, xs[i].reshape(-1))
+            assert np.all(np.abs(hy[i] - ref) <= tol), "sharded bench output failed the parity bound"
+        # the same step with NCCL's all-gather as the exchange (eager launches)
+        for _ in range(3):
+            step_nccl()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step_nccl()
+        e1.record()
+        sync_all()
+        tt = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        nccl_ms = float(tt.item())
+        nccl_variant = {"ms_per_step": nccl_ms, "value": total_bytes / (nccl_ms * 1e-3) / 1e9, "unit": UNIT,
+                        "exchange": "ncclAllGather of the f32 slices after every GEMV, eager launches"}
+        q.check_error("nccl variant")
+
     clocks = sampler.stop() if rank == 0 else None
+
+    sharded = None
+    if win is not None and not args.small and not args.no_sharded:
+        sharded = sharded70b_section(q, L, torch, win, rank, world, dist, args.steps)
 
     # ---- parity spot check of what was just timed (rank 0, smallest shape) + CPU baseline ----
     cpu = None
@@ -513,13 +718,15 @@ def main():
         launches_per_step = 0
         for (label, t, K, N) in shapes:
             launches_per_step += 2   # activation conversion + streaming GEMV
+        if world > 1:
+            launches_per_step += 1   # the step's exchange wait
         line = {
             "metric": METRIC, "value": total_bytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "i8 dp4a + f32", "data": "synthetic",
             "config": {"workload": WORKLOAD + (" [small]" if args.small else ""),
                        "launch": ("CUDA graph replay of the six cuda_gemv calls" if graph else "eager launches"),
-                       "parallelism": "single GPU" if world == 1 else f"row-sharded x{world} + NCCL all-gather of f32 outputs",
+                       "parallelism": "single GPU" if world == 1 else f"row-sharded x{world}; output slices exchanged by peer stores from the GEMV epilogue (NVLink), one flag wait per step",
                        "l2": "inputs larger than L2: each step streams 543 MB of distinct weights (> 126 MB L2); the roofline loop alternates two 431 MB copies of the matrix",
                        "pct_of_8TBs_nominal": 100.0 * total_bytes / (ms * 1e-3) / 8e12},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -536,8 +743,12 @@ def main():
             "clocks": clocks,
             "decode": decode,
             "gemm": gemm,
+            "sharded70b": sharded,
+            "nccl_allgather_variant": nccl_variant,
         }
         print(json.dumps(line))
+    if win is not None:
+        win.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -198,11 +198,14 @@ void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, floa
  *   cuda_gemv_push          cuda_gemv whose out_dim rows land at payload[dst_off + j] of EVERY rank
  *   cuda_push_rows          the same exchange for an [m x n_local] block already in device memory
  *                           (GEMM outputs): element (i, j) lands at payload[dst_off + i*dst_ld + j]
- *   quartz_mgpu_wait        enqueue the wait for the current exchange: every rank's slice has landed
- *                           when it completes (bounded: QZ_ERR_TIMEOUT after ~0.5 s)
- * Each rank must issue the same sequence of pushes and waits (one wait per push).  A payload region
- * may be overwritten only after an exchange into another region has completed in between.  All
- * return 0 on success, -1 on failure (see quartz_last_error). */
+ *   quartz_mgpu_wait        enqueue the wait for ALL exchanges pushed so far: every rank's slices have
+ *                           landed when it completes (bounded: QZ_ERR_TIMEOUT after ~0.5 s)
+ *   quartz_mgpu_fuse_next_wait  the same wait, but carried out by the activation-conversion kernel of
+ *                           the next cuda_gemv / cuda_gemv_push / cuda_quantize_x call instead of a
+ *                           launch of its own; that GEMV's weight stream starts while it waits
+ * Every rank must issue the same sequence of pushes.  A payload region may be overwritten only after a
+ * wait that followed an exchange into another region.  The int functions return 0 on success, -1 on
+ * failure (see quartz_last_error). */
 size_t quartz_mgpu_handle_bytes(void);
 int quartz_set_device(int device);
 int quartz_mgpu_init(int rank, int world, size_t data_bytes, void *handle_out);
@@ -212,6 +215,7 @@ void cuda_gemv_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x,
                     int out_dim);
 void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size_t dst_ld);
 void quartz_mgpu_wait(void);
+void quartz_mgpu_fuse_next_wait(void);
 void quartz_mgpu_shutdown(void);
 
 #ifdef __cplusplus

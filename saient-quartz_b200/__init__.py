@@ -89,6 +89,7 @@ _SIGS = {
     "cuda_gemv_push": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int]),
     "cuda_push_rows": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t]),
     "quartz_mgpu_wait": (None, []),
+    "quartz_mgpu_fuse_next_wait": (None, []),
     "quartz_mgpu_shutdown": (None, []),
 }
 

@@ -27,6 +27,7 @@
 #pragma once
 
 #include "formats.cuh"
+#include "mgpu.cuh"
 
 namespace qz {
 
@@ -42,11 +43,19 @@ struct XQ {
 constexpr float XQ_RANGE = 32512.0f;   // 127 * 256: h, l both fit int8
 
 // one thread per 4 values; 8 threads share a 32-run
+// With `ctrl` set, x is (part of) a row-sharded vector whose slices other ranks push into this
+// rank's window: every CTA first waits for the exchange to complete.  The dependent GEMV has been
+// released by then and streams its weights meanwhile.
 __global__ void quantize_x_kernel(const float *__restrict__ x, int8_t *__restrict__ xl, int8_t *__restrict__ xh,
-                                  float *__restrict__ xs, float *__restrict__ xsum, int K)
+                                  float *__restrict__ xs, float *__restrict__ xsum, int K, const MgpuCtrl *ctrl,
+                                  int n_ranks, int *status)
 {
     pdl_wait();
     pdl_trigger();
+    if (ctrl) {
+        mgpu_poll(ctrl, n_ranks, status);
+        __syncthreads();
+    }
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     int k = 4 * t;
     float v[4] = {0.f, 0.f, 0.f, 0.f};

@@ -298,8 +298,8 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
         }
     }
     if (a.push.n > 0 && !dead) {
-        // all of this CTA's remote stores are out: fence them, meet, and let one thread count the CTA in
-        __threadfence_system();
+        // all of this CTA's remote stores are issued: meet, then one thread fences them (the barrier
+        // makes the fence cumulative over the other threads' stores) and counts the CTA in
         named_bar_sync(15, n_consumers);
         if (threadIdx.x == 0) push_publish(a.push, gridDim.x);
     }

@@ -10,14 +10,16 @@
 //          window (its own included), fences at system scope, and the last CTA to finish bumps
 //          this rank's push counter and stores it, with release semantics, into slot [r] of every
 //          rank's flag array.
-//   wait:  a one-CTA kernel on each rank bumps its own wait counter and polls its local flag array
-//          until every slot has reached that count: all slices of the current exchange have landed.
-//          The poll is bounded; when it runs out the status word is set and the kernel returns.
+//   wait:  every rank issues the same sequence of pushes, so "all slices of the exchanges I have
+//          pushed so far have landed" is: every slot of my flag array has reached MY OWN push
+//          counter.  The poll runs in a one-CTA kernel, or in the prologue of the kernel that
+//          consumes the data (the activation conversion of the next GEMV, whose weight stream has
+//          then already started).  It is bounded; when it runs out the status word is set and the
+//          kernel carries on to its end.
 //
-// Both counters live in device memory, so a recorded graph can be replayed: the n-th wait always
-// pairs with the n-th push of every rank.  A region of the window may be rewritten only after an
-// exchange into a different region has completed in between (ranks run at most one exchange
-// ahead of one another, because the next push depends on data of the previous wait).
+// The counters live in device memory, so a recorded graph can be replayed.  A region of the window
+// may be rewritten only after a wait that followed an exchange into a different region (a rank
+// can run at most one wait ahead of the slowest one).
 #pragma once
 
 #include "common.cuh"
@@ -25,14 +27,13 @@
 namespace qz {
 
 constexpr int MGPU_MAX_RANKS = 8;
-constexpr int MGPU_CTRL_BYTES = 256;   // flags[8] | cta counter | pushes | waits
+constexpr int MGPU_CTRL_BYTES = 256;   // flags[8] | cta counter | pushes
 constexpr long long MGPU_WAIT_CYCLES = 1000000000LL;   // ~0.5 s
 
 struct MgpuCtrl {
     int flags[MGPU_MAX_RANKS];   // flags[r] = number of exchanges rank r has completed into this window
     int cta_counter;             // CTAs of the running push kernel that have finished
     int pushes;                  // exchanges this rank has pushed
-    int waits;                   // exchanges this rank has waited for
 };
 
 struct PushArgs {
@@ -54,15 +55,17 @@ __device__ __forceinline__ void st_release_sys(int *p, int v)
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Called by ONE thread of a CTA after all of the CTA's remote stores were followed by
-// __threadfence_system() and a CTA-level barrier.  The last CTA publishes the exchange.
+// Called by ONE thread of a CTA after a CTA-level barrier that follows all of the CTA's remote
+// stores.  The count is a release/acquire read-modify-write at GPU scope: through the barrier it is
+// cumulative over the other threads' stores, and the last CTA to count in has thereby acquired every
+// CTA's stores.  That CTA publishes the exchange with system-scope release stores of the new
+// counter, which carry all of it to the peers.
 __device__ __forceinline__ void push_publish(const PushArgs &p, int total_ctas)
 {
     MgpuCtrl *mine = p.ctrl[p.rank];
-    __threadfence();
-    const int prev = atomicAdd(&mine->cta_counter, 1);
+    int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(&mine->cta_counter) : "memory");
     if (prev == total_ctas - 1) {
-        __threadfence_system();
         mine->cta_counter = 0;
         const int e = mine->pushes + 1;
         mine->pushes = e;
@@ -81,30 +84,30 @@ __global__ void mgpu_push_rows_kernel(const float *__restrict__ src, int M, int 
         const float v = src[i];
         for (int r = 0; r < p.n; r++) p.data[r][p.dst_off + m * dst_ld + j] = v;
     }
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) push_publish(p, gridDim.x);
 }
 
-// One CTA, one lane per rank.
-__global__ void mgpu_wait_kernel(MgpuCtrl *mine, int n, int *status)
+// Lanes 0..n-1 of the calling CTA poll this rank's flags until every rank has published as many
+// exchanges as this rank has pushed; the caller follows with __syncthreads().
+__device__ __forceinline__ void mgpu_poll(const MgpuCtrl *mine, int n, int *status)
 {
-    __shared__ int expected;
-    if (threadIdx.x == 0) {
-        expected = mine->waits + 1;
-        mine->waits = expected;
-    }
-    __syncthreads();
     if ((int)threadIdx.x < n) {
+        const int expected = *(volatile const int *)&mine->pushes;
         const long long t0 = clock64();
         while (ld_acquire_sys(&mine->flags[threadIdx.x]) < expected) {
             if (clock64() - t0 > MGPU_WAIT_CYCLES) {
                 atomicExch(status, QZ_ERR_TIMEOUT);
                 break;
             }
-            __nanosleep(100);
+            __nanosleep(64);
         }
     }
+}
+
+__global__ void mgpu_wait_kernel(const MgpuCtrl *mine, int n, int *status)
+{
+    mgpu_poll(mine, n, status);
 }
 
 }  // namespace qz

@@ -140,11 +140,20 @@ static XQMut xq_slot(uint8_t *base, size_t slot_bytes, int slot, size_t cap_k)
     return q;
 }
 
+// set by quartz_mgpu_fuse_next_wait: the next activation conversion first waits for the exchange
+static const MgpuCtrl *g_wait_ctrl = nullptr;
+static int g_wait_ranks = 0;
+static int *status_word();
+
 static void launch_quantize(const float *x, const XQMut &q, int K)
 {
     int threads = K / 4;
     int bs = 256, gs = (threads + bs - 1) / bs;
-    launch(quantize_x_kernel, dim3(gs), dim3(bs), 0, x, q.xl, q.xh, q.xs, q.xsum, K);
+    const MgpuCtrl *ctrl = g_wait_ctrl;
+    int *st = ctrl ? status_word() : nullptr;
+    if (ctrl && !st) ctrl = nullptr;
+    g_wait_ctrl = nullptr;
+    launch(quantize_x_kernel, dim3(gs), dim3(bs), 0, x, q.xl, q.xh, q.xs, q.xsum, K, ctrl, g_wait_ranks, st);
 }
 
 // ---- one-time init: default sign table ------------------------------------------------
@@ -439,6 +448,14 @@ static void gemv_n(uint32_t t, int n, const uint8_t *const *W, const float *cons
         }
     }
     if (!is_plain(t) && try_stream(t, n, W, x, y, K, N, planes)) return;
+    if (g_wait_ctrl) {   // a fused wait was asked for, but this path converts no activations: wait in a kernel of its own
+        int *st = status_word();
+        if (st) {
+            mgpu_wait_kernel<<<1, 32, 0, g_stream>>>(g_wait_ctrl, g_wait_ranks, st);
+            QZ_LAUNCH_CHECK();
+        }
+        g_wait_ctrl = nullptr;
+    }
     for (int i = 0; i < n; i++) launch_generic(t, planes[i], W[i], x[i], y[i], K, N);
 }
 
@@ -1340,8 +1357,18 @@ void quartz_mgpu_wait(void)
     }
     int *st = status_word();
     if (!st) return;
-    mgpu_wait_kernel<<<1, 32, 0, g_stream>>>((MgpuCtrl *)g_win, g_mg_world, st);
+    mgpu_wait_kernel<<<1, 32, 0, g_stream>>>((const MgpuCtrl *)g_win, g_mg_world, st);
     QZ_LAUNCH_CHECK();
+}
+
+void quartz_mgpu_fuse_next_wait(void)
+{
+    if (!g_mg_attached) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_mgpu_fuse_next_wait: the windows are not attached");
+        return;
+    }
+    g_wait_ctrl = (const MgpuCtrl *)g_win;
+    g_wait_ranks = g_mg_world;
 }
 
 void quartz_mgpu_shutdown(void)

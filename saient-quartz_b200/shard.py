@@ -66,8 +66,13 @@ class PeerWindow:
     def push_rows(self, d_src, m, n_local, dst_off, dst_ld):
         self.lib.cuda_push_rows(d_src, m, n_local, dst_off, dst_ld)
 
-    def wait(self):
-        self.lib.quartz_mgpu_wait()
+    def wait(self, fused=False):
+        """All exchanges pushed so far are complete after this: as a kernel of its own, or (fused) inside the
+        activation conversion of the next GEMV call."""
+        if fused:
+            self.lib.quartz_mgpu_fuse_next_wait()
+        else:
+            self.lib.quartz_mgpu_wait()
 
     def close(self):
         self.lib.quartz_mgpu_shutdown()

@@ -91,13 +91,43 @@ def main():
         tol = 1e-3 * norms * float(np.linalg.norm(X[m].astype(np.float64)))
         assert np.all(np.abs(Y[m].astype(np.float64) - ref[m]) <= tol), f"rank {rank} gemm token {m}"
 
-    if world > 1:
-        dist.barrier()
-        # a wait that no push answers runs out (bounded) and reports it; nothing hangs
+    # a chain whose second GEMV reads the first one's gathered output, the wait fused into its conversion
+    K, N1, N2 = 2048, 4096, 1024
+    wa, wb = synth.make_weights(12, K, N1, tensor_id=970), synth.make_weights(14, N1, N2, tensor_id=971)
+    x = synth.make_x(K, tensor_id=972).reshape(-1)
+    a0, a1, _ = shard_rows(N1, rank, world)
+    c0, c1, _ = shard_rows(N2, rank, world)
+    s0, s1 = shard_bytes(12, K, N1, rank, world)
+    da = q.GpuBuf.upload(wa[s0:s1])
+    s0, s1 = shard_bytes(14, N1, N2, rank, world)
+    db = q.GpuBuf.upload(wb[s0:s1])
+    L.cuda_repack_weights(14, db.ptr, N1, c1 - c0, 1)
+    dx = q.GpuBuf.upload(x)
+    RA, RB = 200000, 210000
+    for rep in range(3):
+        win.gemv_push(12, da.ptr, dx.ptr, RA + a0, K, a1 - a0)
+        win.wait(fused=True)
+        win.gemv_push(14, db.ptr, win.data_ptr + 4 * RA, RB + c0, N1, c1 - c0)
         win.wait()
         L.cuda_sync()
-        assert L.quartz_last_error() == 7, L.quartz_last_error()   # QZ_ERR_TIMEOUT
-        L.quartz_clear_error()
+        q.check_error("chain")
+        y1 = download(RA, N1)
+        y2 = download(RB, N2)
+        ref1 = oracle.gemv(x, wa, 12, K, N1)
+        tol1 = 1e-3 * oracle.row_norms(wa, 12, K, N1) * float(np.linalg.norm(x.astype(np.float64)))
+        assert np.all(np.abs(y1 - ref1) <= tol1), f"rank {rank} chain y1"
+        ref2 = oracle.gemv(y1, wb, 14, N1, N2)
+        tol2 = 1e-3 * oracle.row_norms(wb, 14, N1, N2) * float(np.linalg.norm(y1.astype(np.float64)))
+        assert np.all(np.abs(y2 - ref2) <= tol2), f"rank {rank} chain y2"
+    if world > 1:
+        dist.barrier()
+        # rank 0 pushes once more and waits, nobody answers: the bounded wait runs out and reports it
+        if rank == 0:
+            win.gemv_push(12, 0, dx.ptr, 0, 2048, 0)
+            win.wait()
+            L.cuda_sync()
+            assert L.quartz_last_error() == 7, L.quartz_last_error()   # QZ_ERR_TIMEOUT
+            L.quartz_clear_error()
         dist.barrier()
     win.close()
     print(f"rank {rank}/{world}: ok", flush=True)
