@@ -164,6 +164,17 @@ void cuda_attn_decode(float *out, const float *q, const float *k_cache, const fl
                       int n_kv_heads, int seq_len, int head_dim, int kv_dim, float scale, const float *sinks,
                       int out_slot);
 
+/* cuda_gemv_q whose activation vector is computed by the GEMV kernel itself, in its prologue, while its
+ * weight pipeline fills: y_i (+)= W_i * rmsnorm(x, norm_w)  (cuda_rms_norm + cuda_gemv, src/cuda.rs:556-597
+ * and :760-775) and y_i (+)= W_i * swiglu(gate, up)  (cuda_swiglu / cuda_swiglu_oai + cuda_gemv,
+ * src/cuda.rs:777-800).  eps is 1e-5 as in the reference kernel.  Same type/shape/layout conditions as
+ * cuda_gemv_q (cuda_gemv_q_supported); in_dim floats of d_x / d_norm_w / d_gate / d_up, 16-byte aligned
+ * for the fused form (otherwise the two-launch form runs and uses the caller's scratch slot 3). */
+void cuda_gemv_rmsnorm(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_x,
+                       const float *d_norm_w, int in_dim, int out_dim, int accumulate);
+void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_gate,
+                      const float *d_up, int oai, int in_dim, int out_dim, int accumulate);
+
 /* CUDA-graph helpers (no counterpart in the reference, which launches ~670 kernels per token one
  * by one, src/cuda.rs:548-843).  Between begin and end every call of this library is recorded
  * instead of executed; copies and cuda_sync must stay outside, and every scratch buffer must

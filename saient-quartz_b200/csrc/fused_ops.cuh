@@ -8,40 +8,6 @@
 
 namespace qz {
 
-struct XQOut {
-    int8_t *xl, *xh;
-    float *xs, *xsum;
-};
-
-// Convert four consecutive values (elements 4t .. 4t+3, t = global thread-of-4 index) exactly
-// as quantize_x_kernel does.  All 32 lanes of the warp must call it (shuffles inside); lanes
-// past the end pass valid = false.
-__device__ __forceinline__ void quantize4_store(const float v[4], int t, bool valid, const XQOut &o)
-{
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    float sum = (v[0] + v[1]) + (v[2] + v[3]);
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-    if (!valid) return;
-    const float inv = amax > 0.f ? XQ_RANGE / amax : 0.f;
-    uint32_t wl = 0, wh = 0;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        int X = __float2int_rn(v[i] * inv);
-        int l = ((X + 128) & 0xFF) - 128;
-        int h = (X - l) >> 8;
-        wl |= (uint32_t)(l & 0xFF) << (8 * i);
-        wh |= (uint32_t)(h & 0xFF) << (8 * i);
-    }
-    ((uint32_t *)o.xl)[t] = wl;
-    ((uint32_t *)o.xh)[t] = wh;
-    if ((t & 7) == 0) o.xs[t >> 3] = amax / XQ_RANGE;
-    if ((t & 3) == 0) o.xsum[t >> 2] = sum;
-}
-
 // RMSNorm (src/cuda_kernels.cu:563-575) whose result goes straight into activation form;
 // optionally also stored as f32.  One CTA; n is a multiple of 4.
 __global__ void rms_norm_q_kernel(const float *__restrict__ x, const float *__restrict__ w, int n, XQOut o,

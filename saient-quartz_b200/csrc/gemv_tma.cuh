@@ -28,6 +28,17 @@ constexpr int TMA_MAX_STAGES = 16;
 constexpr int TMA_CONSUMERS = 512;
 constexpr long long TMA_WAIT_CYCLES = 2000000000LL;   // ~1 s at 1.9 GHz
 
+// Where the activation vector comes from.  mode 0: already converted (xq).  mode 1: RMSNorm of the
+// f32 vector a with weights b (src/cuda_kernels.cu:563-575, eps 1e-5 as there), mode 2: SwiGLU of
+// gate a and up b (src/cuda_kernels.cu:683-698; oai = the clamped variant).  For modes 1 and 2 every
+// CTA converts the vector itself, into shared memory, while its weight pipeline fills: the producer of
+// the activations needs no kernel of its own.
+struct XSrc {
+    int mode;
+    const float *a, *b;
+    int oai;
+};
+
 struct TmaArgs {
     const uint8_t *W[QZ_MAX_MATS];
     XQ xq[QZ_MAX_MATS];
@@ -41,6 +52,7 @@ struct TmaArgs {
     int *status;             // device status word (0 = ok)
     int probe;               // measurement aid: 1 = consumers release stages without computing (streaming ceiling)
     PushArgs push;           // push.n > 0: rows go to every rank's window instead of y (single matrix)
+    XSrc xsrc;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -156,6 +168,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ uint64_t full_bar[TMA_MAX_STAGES], empty_bar[TMA_MAX_STAGES];
     __shared__ float part[2][4 * (TMA_CONSUMERS / 32)];
+    __shared__ float xred[TMA_CONSUMERS / 32];
 
     const int m = blockIdx.x % a.n_mats;
     const int cta = blockIdx.x / a.n_mats, n_cta = gridDim.x / a.n_mats;
@@ -231,7 +244,54 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     // N in the last tile are computed from stale shared memory and simply never stored.
     pdl_wait();   // activations (and, for the accumulate epilogue, y) come from the preceding kernels
     typename F::XRegs xr;
-    F::load_x(xr, a.xq[m], active ? u : 0);
+    XQ xq = a.xq[m];
+    if (a.xsrc.mode) {
+        // the activation form of the whole vector, built by this CTA's consumers behind ring and codebook
+        int8_t *sxl = (int8_t *)(tbl + ((F::TABLE_BYTES + 15) & ~15));
+        int8_t *sxh = sxl + a.K;
+        float *sxs = (float *)(sxh + a.K), *sxsum = sxs + (a.K >> 5);
+        const XQOut o{sxl, sxh, sxs, sxsum};
+        const float *__restrict__ pa = a.xsrc.a, *__restrict__ pb = a.xsrc.b;
+        const int n4 = a.K >> 2;
+        float r = 1.f;
+        if (a.xsrc.mode == 1) {
+            float ss = 0.f;
+            for (int t = threadIdx.x; t < n4; t += n_consumers) {
+                const float4 v = *(const float4 *)(pa + 4 * t);
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            }
+            for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o2);
+            if (lane == 0) xred[threadIdx.x >> 5] = ss;
+            named_bar_sync(14, n_consumers);
+            ss = 0.f;
+            for (int w = 0; w < (n_consumers >> 5); w++) ss += xred[w];
+            r = rsqrtf(ss / (float)a.K + 1e-5f);
+        }
+        for (int t0 = 0; t0 < n4; t0 += n_consumers) {
+            const int t = t0 + threadIdx.x;
+            const bool valid = t < n4;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (valid) {
+                const float4 x4 = *(const float4 *)(pa + 4 * t), y4 = *(const float4 *)(pb + 4 * t);
+                const float xx[4] = {x4.x, x4.y, x4.z, x4.w}, yy[4] = {y4.x, y4.y, y4.z, y4.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (a.xsrc.mode == 1) {
+                        v[i] = xx[i] * r * yy[i];
+                    } else if (a.xsrc.oai) {
+                        const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
+                        v[i] = (g / (1.f + expf(-1.702f * g))) * (up + 1.f);
+                    } else {
+                        v[i] = (xx[i] / (1.f + expf(-xx[i]))) * yy[i];
+                    }
+                }
+            }
+            quantize4_store(v, t, valid, o);
+        }
+        named_bar_sync(14, n_consumers);
+        xq = XQ{sxl, sxh, sxs, sxsum};
+    }
+    F::load_x(xr, xq, active ? u : 0);
     const typename F::Off off = F::make_off(nb, active ? u : 0);
 
     const int my_tiles = (ntiles - cta + n_cta - 1) / n_cta;

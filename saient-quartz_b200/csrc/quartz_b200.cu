@@ -256,6 +256,9 @@ static int g_use_tma = -1;
 // set by cuda_gemv_push around its GEMV: the TMA kernel takes it as its epilogue and clears `pending`
 static PushArgs g_push_args;
 static bool g_push_pending = false;
+// set by cuda_gemv_rmsnorm / cuda_gemv_swiglu around their GEMV: the TMA kernel converts the activations itself
+static XSrc g_xsrc = {0, nullptr, nullptr, 0};
+static bool g_xsrc_pending = false;
 static bool use_tma()
 {
     if (g_use_tma < 0) {
@@ -278,7 +281,10 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     const int sms = sm_count();
     const int ctas_per_mat = sms / n_mats > 0 ? sms / n_mats : 1;
     a.stage_bytes = (int)((size_t)a.RP * row_bytes);
-    const int ring_budget = 200 * 1024;   // + up to 8 KB of codebook behind it
+    const int smem_budget = 200 * 1024;   // + up to 8 KB of codebook behind it
+    // a fused activation source keeps the converted vector (2 K + 3 K / 8 bytes) behind the codebook
+    const int x_bytes = g_xsrc_pending ? (int)((2 * (size_t)g.K + g.K / 8 + g.K / 4 + 31) & ~(size_t)15) : 0;
+    const int ring_budget = smem_budget - x_bytes;
     if (a.stage_bytes * 2 > ring_budget) return false;
     const int ntiles = (g.N + a.RP - 1) / a.RP;
     const int n_cta = ntiles < ctas_per_mat ? ntiles : ctas_per_mat;
@@ -296,15 +302,20 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
         a.push = g_push_args;
         g_push_pending = false;
     }
+    a.xsrc.mode = 0;
+    if (g_xsrc_pending) {
+        a.xsrc = g_xsrc;
+        g_xsrc_pending = false;
+    }
     static bool attr_set = false;
     if (!attr_set) {
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + F::TABLE_BYTES));
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + F::TABLE_BYTES));
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_budget + 16 + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_budget + 16 + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_budget + 16 + F::TABLE_BYTES));
         attr_set = true;
     }
     const dim3 grid(n_cta * n_mats), block(TMA_CONSUMERS + 32);
-    const size_t smem = (size_t)stages * a.stage_bytes + F::TABLE_BYTES;
+    const size_t smem = (size_t)stages * a.stage_bytes + ((F::TABLE_BYTES + 15) & ~15) + x_bytes;
     if (g.Upad < 32) launch(gemv_tma_kernel<F, 0>, grid, block, smem, a);
     else if (g.Upad == 32) launch(gemv_tma_kernel<F, 1>, grid, block, smem, a);
     else launch(gemv_tma_kernel<F, 2>, grid, block, smem, a);
@@ -371,6 +382,7 @@ static bool stream_core(uint32_t t, int n, const uint8_t *const *W, const int *s
         }
         if (done) return true;
     }
+    if (g_xsrc_pending) return false;   // only the TMA kernel converts activations itself: let the caller do it
     switch (t) {
 #define X(TT, POL) case TT: launch_stream_r<POL>(a, n, T); break;
         QZ_FOR_STREAM_TYPES(X)
@@ -1097,6 +1109,52 @@ void cuda_gemv_q(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, cons
     }
     if (!ensure_xq(in_dim)) return;
     stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
+}
+
+// The GEMVs whose activation vector is the RMSNorm of x / the SwiGLU of (gate, up): the streaming kernel
+// converts it in its own prologue; where that kernel does not apply, the two-launch form runs instead.
+static void gemv_xsrc(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, XSrc src, int in_dim,
+                      int out_dim, int accumulate, const char *who)
+{
+    if (n_mats <= 0 || out_dim <= 0) return;
+    if (n_mats > QZ_MAX_MATS) {
+        set_error(QZ_ERR_TOO_LARGE, "fused GEMV: at most 8 matrices per call");
+        return;
+    }
+    int slot_of[QZ_MAX_MATS];
+    for (int i = 0; i < n_mats; i++) {
+        if (!cuda_gemv_q_supported(ggml_type, d_w[i], in_dim)) {
+            set_error(QZ_ERR_BAD_SHAPE, who);
+            return;
+        }
+        slot_of[i] = 7;   // the caller's slot 3: used only if the fused prologue is not taken
+    }
+    if (!ensure_xq(in_dim)) return;
+    if (use_tma() && ((uintptr_t)src.a & 15) == 0 && ((uintptr_t)src.b & 15) == 0) {
+        g_xsrc = src;
+        g_xsrc_pending = true;
+        const bool ok = stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
+        const bool consumed = !g_xsrc_pending;
+        g_xsrc_pending = false;
+        if (ok && consumed) return;
+    }
+    if (src.mode == 1) cuda_rms_norm_q(src.a, src.b, in_dim, 3, nullptr);
+    else cuda_swiglu_q(src.a, src.b, in_dim, 3, src.oai);
+    stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
+}
+
+void cuda_gemv_rmsnorm(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_x,
+                       const float *d_norm_w, int in_dim, int out_dim, int accumulate)
+{
+    gemv_xsrc(ggml_type, n_mats, d_w, d_y, XSrc{1, d_x, d_norm_w, 0}, in_dim, out_dim, accumulate,
+              "cuda_gemv_rmsnorm: type/shape/layout has no streaming kernel (ask cuda_gemv_q_supported)");
+}
+
+void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_gate,
+                      const float *d_up, int oai, int in_dim, int out_dim, int accumulate)
+{
+    gemv_xsrc(ggml_type, n_mats, d_w, d_y, XSrc{2, d_gate, d_up, oai}, in_dim, out_dim, accumulate,
+              "cuda_gemv_swiglu: type/shape/layout has no streaming kernel (ask cuda_gemv_q_supported)");
 }
 
 void cuda_rope_kv(float *q, float *k, const float *v, float *k_cache, float *v_cache, int n_heads, int n_kv_heads,

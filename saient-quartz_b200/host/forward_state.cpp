@@ -401,7 +401,7 @@ static bool fusable(qh_model *m)
     return cuda_gemv_q_supported(m->lm_head.ggml_type, m->lm_head.u8(), c.embed_dim) != 0;
 }
 
-// The fused sequence: ten launches per layer instead of twenty-one (+ seven conversions).
+// The fused sequence: seven launches per layer instead of twenty-one (+ seven conversions).
 static void step_fused(qh_model *m, int token, int pos, bool need_logits)
 {
     const qh_config &c = m->c;
@@ -413,16 +413,14 @@ static void step_fused(qh_model *m, int token, int pos, bool need_logits)
     cuda_embed_lookup(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, token, d);
     for (int l = 0; l < c.n_layers; l++) {
         Layer &L = m->L[l];
-        cuda_rms_norm_q(m->d_hidden.f(), L.attn_norm.f(), d, 0, nullptr);
-        // q (as kv_d-row slices), k and v in one launch
+        // q (as kv_d-row slices), k and v in one launch that normalises the hidden state in its prologue
         const uint8_t *W[8];
         float *Y[8];
-        int S[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         int n = 0;
         for (int s = 0; s < q_slices; s++) { W[n] = L.q.u8() + s * q_slice_bytes; Y[n] = m->d_q.f() + (size_t)s * kv_d; n++; }
         W[n] = L.k.u8(); Y[n] = m->d_k.f(); n++;
         W[n] = L.v.u8(); Y[n] = m->d_v.f(); n++;
-        cuda_gemv_q(L.q.ggml_type, n, W, S, Y, d, kv_d, 0);
+        cuda_gemv_rmsnorm(L.q.ggml_type, n, W, Y, m->d_hidden.f(), L.attn_norm.f(), d, kv_d, 0);
         cuda_rope_kv(m->d_q.f(), m->d_k.f(), m->d_v.f(), m->kv_k[l].f(), m->kv_v[l].f(), h, kv, hd, pos, c.rope_theta,
                      c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
         const int k_start = attn_start(c, l, pos), seq_a = seq - k_start;
@@ -434,27 +432,21 @@ static void step_fused(qh_model *m, int token, int pos, bool need_logits)
             int s1[1] = {1};
             cuda_gemv_q(L.o.ggml_type, 1, w1, s1, y1, q_d, d, 1);
         }
-        cuda_rms_norm_q(m->d_hidden.f(), L.ffn_norm.f(), d, 0, nullptr);
         {
             const uint8_t *w2[2] = {L.gate.u8(), L.up.u8()};
             float *y2[2] = {m->d_gate.f(), m->d_up.f()};
-            int s2[2] = {0, 0};
-            cuda_gemv_q(L.gate.ggml_type, 2, w2, s2, y2, d, fd, 0);
+            cuda_gemv_rmsnorm(L.gate.ggml_type, 2, w2, y2, m->d_hidden.f(), L.ffn_norm.f(), d, fd, 0);
         }
-        cuda_swiglu_q(m->d_gate.f(), m->d_up.f(), fd, 2, 0);
-        {
+        {   // down projection of swiglu(gate, up), computed in its prologue; residual added in the epilogue
             const uint8_t *w1[1] = {L.down.u8()};
             float *y1[1] = {m->d_hidden.f()};
-            int s1[1] = {2};
-            cuda_gemv_q(L.down.ggml_type, 1, w1, s1, y1, fd, d, 1);
+            cuda_gemv_swiglu(L.down.ggml_type, 1, w1, y1, m->d_gate.f(), m->d_up.f(), 0, fd, d, 1);
         }
     }
     if (!need_logits) return;
-    cuda_rms_norm_q(m->d_hidden.f(), m->final_norm.f(), d, 0, nullptr);
     const uint8_t *w1[1] = {m->lm_head.u8()};
     float *y1[1] = {m->d_logits.f()};
-    int s1[1] = {0};
-    cuda_gemv_q(m->lm_head.ggml_type, 1, w1, s1, y1, d, c.vocab_size, 0);
+    cuda_gemv_rmsnorm(m->lm_head.ggml_type, 1, w1, y1, m->d_hidden.f(), m->final_norm.f(), d, c.vocab_size, 0);
 }
 
 int qh_step_device(qh_model *m, int token, int pos, int fused)

@@ -170,6 +170,44 @@ def test_fused_entry_points_match_unfused(gpu):
     gpu.check_error()
 
 
+@pytest.mark.parametrize("t,K,N", [(12, 4096, 1024), (14, 14336, 512), (8, 2048, 300), (12, 512, 256)])
+def test_gemv_with_fused_norm_and_swiglu(gpu, t, K, N):
+    """cuda_gemv_rmsnorm / cuda_gemv_swiglu (activation computed in the GEMV's prologue) against the
+    two-launch forms cuda_rms_norm_q / cuda_swiglu_q + cuda_gemv_q.  SwiGLU converts element by element,
+    so results are identical; the norm's sum of squares is reduced in another order (1e-5 relative)."""
+    import ctypes as C
+    from saient_quartz_b200 import synth
+    L = gpu.lib()
+    w = synth.make_weights(t, K, 2 * N, tensor_id=611)
+    dw = gpu.GpuBuf.upload(w)
+    L.cuda_repack_weights(t, dw.ptr, K, 2 * N, 1)
+    assert L.cuda_gemv_q_supported(t, dw.ptr, K)
+    x, g = synth.make_x(K, tensor_id=612), synth.make_x(K, tensor_id=613)
+    nw = (1.0 + 0.1 * synth.make_x(K, tensor_id=614)).astype(np.float32)
+    dx, dg, dn = gpu.GpuBuf.upload(x), gpu.GpuBuf.upload(g), gpu.GpuBuf.upload(nw)
+    dy, dy2 = gpu.GpuBuf.alloc_f32(2 * N), gpu.GpuBuf.alloc_f32(2 * N)
+    half = synth.type_size(t, K * N)
+    W = (C.c_void_p * 2)(dw.ptr, dw.ptr + half)
+    Y = (C.c_void_p * 2)(dy.ptr, dy.ptr + 4 * N)
+    Y2 = (C.c_void_p * 2)(dy2.ptr, dy2.ptr + 4 * N)
+    S = (C.c_int * 2)(1, 1)
+    for acc in (0, 1):
+        L.cuda_vec_zero(dy.ptr, 2 * N)
+        L.cuda_vec_zero(dy2.ptr, 2 * N)
+        L.cuda_rms_norm_q(dx.ptr, dn.ptr, K, 1, None)
+        L.cuda_gemv_q(t, 2, W, S, Y, K, N, acc)
+        L.cuda_gemv_rmsnorm(t, 2, W, Y2, dx.ptr, dn.ptr, K, N, acc)
+        a, b = dy.download(), dy2.download()
+        assert np.abs(a - b).max() <= 2e-5 * np.abs(a).max(), ("norm", acc)
+        L.cuda_vec_zero(dy.ptr, 2 * N)
+        L.cuda_vec_zero(dy2.ptr, 2 * N)
+        L.cuda_swiglu_q(dg.ptr, dx.ptr, K, 1, 0)
+        L.cuda_gemv_q(t, 2, W, S, Y, K, N, acc)
+        L.cuda_gemv_swiglu(t, 2, W, Y2, dg.ptr, dx.ptr, 0, K, N, acc)
+        assert np.array_equal(dy.download(), dy2.download()), ("swiglu", acc)
+    gpu.check_error()
+
+
 def test_attn_decode_matches_three_kernel_attention(gpu):
     L = gpu.lib()
     r = np.random.Generator(np.random.PCG64([0xA77]))
