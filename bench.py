@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--small", action="store_true", help="profiling case: lm_head cut to 40080 rows (134 MB, still larger than L2; ~0.3 GB on the device)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode-step section")
+    ap.add_argument("--no-moe", action="store_true", help="skip the batched MoE FFN section")
     ap.add_argument("--no-sharded", action="store_true", help="skip the 70B-shaped row-sharded pair section")
     ap.add_argument("--no-gemm", action="store_true", help="skip the batched (prefill) dequant-GEMM section")
     ap.add_argument("--decode-only", action="store_true",
@@ -305,6 +306,59 @@ def decode_section(q, args, torch, np, want_parity, fused_only=False):
         out["cpu_oracle_tok_s"] = 1.0 / cpu_s
         assert rel < 5e-3, f"decode-step logits differ from the CPU oracle: {rel}"
     m.close()
+    return out
+
+
+def moe_section(q, args, torch, np):
+    """Mixtral-style MoE FFN, batched: 8 experts, top-2 routing from a softmax over N(0,1) router logits,
+    256 tokens, expert matrices 4096->14336 (gate, up) and 14336->4096 (down) in IQ3_XXS and in IQ2_XS."""
+    from saient_quartz_b200 import synth
+    L = q.lib()
+    q.ensure_iq_grids()
+    K, F, E, top_k, M = 4096, 14336, 8, 2, 256
+    rng = np.random.Generator(np.random.PCG64([0x5EED0001, 77]))
+    logits = rng.standard_normal((M, E)).astype(np.float32)
+    ids = np.ascontiguousarray(np.argsort(-logits, axis=1)[:, :top_k].astype(np.int32))
+    sel = np.take_along_axis(logits, ids, axis=1)
+    w = np.exp(sel - sel.max(axis=1, keepdims=True))
+    w = np.ascontiguousarray((w / w.sum(axis=1, keepdims=True)).astype(np.float32))
+    X = synth.make_x(K, tensor_id=500, rows=M)
+    dx, dout = q.GpuBuf.upload(X), q.GpuBuf.alloc_f32(M * K)
+    hbm, _ = peaks()
+    out = []
+    for t in (18, 17):
+        bufs = []
+        for which, (kk, nn) in enumerate(((K, F), (K, F), (F, K))):
+            blob = np.concatenate([synth.make_weights(t, kk, nn, tensor_id=510 + 10 * which + e) for e in range(E)])
+            b = q.GpuBuf.upload(blob)
+            L.cuda_repack_weights(t, b.ptr, kk, nn, E)
+            bufs.append(b)
+            del blob
+
+        def call():
+            L.cuda_moe_ffn(t, t, bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, dx.ptr, dout.ptr, M, K, F, E, top_k,
+                           ids.ctypes.data, w.ctypes.data, 0)
+        for _ in range(2):
+            call()
+        torch.cuda.synchronize()
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        q.check_error("moe")
+        wbytes = 3 * E * synth.type_size(t, K * F)
+        flops = 2.0 * M * top_k * K * F * 3
+        out.append({"format": synth.FORMATS[t][0], "tokens": M, "experts": E, "top_k": top_k, "ms": ms,
+                    "weight_bytes": wbytes, "gbs": (wbytes + 8.0 * M * K) / ms / 1e6, "tflops": flops / ms / 1e9,
+                    "frac_of_measured_hbm": (wbytes + 8.0 * M * K) / ms / 1e6 / hbm,
+                    "tokens_per_expert": [int((ids == e).sum()) for e in range(E)]})
+        for b in bufs:
+            b.drop()
+    dx.drop(); dout.drop()
     return out
 
 
@@ -681,6 +735,10 @@ def main():
 
     clocks = sampler.stop() if rank == 0 else None
 
+    moe = None
+    if rank == 0 and world == 1 and not args.small and not args.no_moe:
+        moe = moe_section(q, args, torch, np)
+
     sharded = None
     if win is not None and not args.small and not args.no_sharded:
         sharded = sharded70b_section(q, L, torch, win, rank, world, dist, args.steps)
@@ -743,6 +801,7 @@ def main():
             "clocks": clocks,
             "decode": decode,
             "gemm": gemm,
+            "moe_ffn": moe,
             "sharded70b": sharded,
             "nccl_allgather_variant": nccl_variant,
         }

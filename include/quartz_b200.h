@@ -194,6 +194,22 @@ void quartz_graph_destroy(void *graph_exec);
 void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,
                int out_dim);
 
+/* Batched mixture-of-experts FFN for m tokens:
+ *   out[t] = sum over the top_k experts e of token t of  w(t,e) * down_e( swiglu(gate_e x_t, up_e x_t) )
+ * the batched form of the reference's per-token MoE branch (src/main.rs:941-990; on the GPU every
+ * expert GEMV of every token is its own launch, src/cuda.rs:673-800).  d_gate / d_up / d_down point at
+ * the stacked expert tensors ([in_dim, out_dim, n_experts]: expert e at byte offset e * size(one
+ * matrix), src/main.rs:941-950, src/cuda.rs:250-257); raw or repacked (cuda_repack_weights with
+ * n_mats = n_experts).  Routing is decided by the host, as in the reference (src/cuda.rs:673-701):
+ * h_expert_ids / h_expert_w are HOST arrays of m * top_k entries (token-major), the weights already
+ * normalised.  d_x is [m, embed_dim], d_out [m, embed_dim], both f32 on the device.  The library
+ * groups the assignments by expert, gathers the rows, runs three cuda_gemm per expert and scatters the
+ * weighted results back; the sum over a token's experts is taken in expert order.  oai = 1 selects
+ * the clamped SwiGLU (cuda_swiglu_oai).  Synchronises the stream once (the routing lists are copied). */
+void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
+                  const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim, int n_experts,
+                  int top_k, const int *h_expert_ids, const float *h_expert_w, int oai);
+
 /* ---- Row-sharded layers over the GPUs of one box (one process per GPU).  No counterpart in the
  * reference, which drives a single device (src/cuda.rs:301-358).  A layer's weight rows are split
  * over the ranks (the loader uploads rows [n0, n1) of each matrix on rank r); every rank computes

@@ -84,6 +84,8 @@ _SIGS = {
     "cuda_gemv_rmsnorm": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_gemv_swiglu": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                 C.c_int]),
+    "cuda_moe_ffn": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                            C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
     "quartz_mgpu_handle_bytes": (C.c_size_t, []),
     "quartz_set_device": (C.c_int, [C.c_int]),
     "quartz_mgpu_init": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.c_void_p]),

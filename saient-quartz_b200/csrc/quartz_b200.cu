@@ -19,6 +19,7 @@
 #include "decode_ops.cuh"
 #include "fused_ops.cuh"
 #include "gemm_tc.cuh"
+#include "moe.cuh"
 
 namespace qz {
 
@@ -1274,6 +1275,98 @@ void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, floa
                int out_dim)
 {
     gemm_dispatch(ggml_type, d_data, d_x, d_y, m, in_dim, out_dim);
+}
+
+// ======================= batched mixture-of-experts FFN =======================
+static uint8_t *g_moe = nullptr;   // library scratch: index / weight lists, gathered rows, gate, up, down outputs
+static size_t g_moe_bytes = 0;
+
+void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
+                  const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim, int n_experts,
+                  int top_k, const int *h_expert_ids, const float *h_expert_w, int oai)
+{
+    if (m <= 0) return;
+    const FormatInfo fg = format_info(type_gate_up), fd = format_info(type_down);
+    if (fg.block_elems == 0 || fd.block_elems == 0) {
+        set_error(QZ_ERR_UNSUPPORTED_TYPE, "cuda_moe_ffn: unsupported ggml_type");
+        return;
+    }
+    if (n_experts <= 0 || top_k <= 0 || top_k > n_experts || embed_dim <= 0 || ffn_dim <= 0 || embed_dim % fg.block_elems ||
+        ffn_dim % fd.block_elems || (embed_dim & 3) || (ffn_dim & 3) || !h_expert_ids || !h_expert_w) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_moe_ffn: bad dimensions or routing lists");
+        return;
+    }
+    // group the (token, expert) assignments by expert
+    const int A = m * top_k;
+    std::vector<int> count(n_experts, 0), start(n_experts + 1, 0), rows(A);
+    std::vector<float> wts(A);
+    for (int i = 0; i < A; i++) {
+        const int e = h_expert_ids[i];
+        if (e < 0 || e >= n_experts) {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_moe_ffn: expert id out of range");
+            return;
+        }
+        count[e]++;
+    }
+    for (int e = 0; e < n_experts; e++) start[e + 1] = start[e] + count[e];
+    std::vector<int> fill(start.begin(), start.end() - 1);
+    for (int i = 0; i < A; i++) {
+        const int e = h_expert_ids[i], p = fill[e]++;
+        rows[p] = i / top_k;
+        wts[p] = h_expert_w[i];
+    }
+    const size_t K = (size_t)embed_dim, F = (size_t)ffn_dim;
+    const size_t lists = (((size_t)A * 8) + 255) & ~(size_t)255;
+    const size_t need = lists + (size_t)A * (2 * K + 2 * F) * sizeof(float);
+    if (need > g_moe_bytes) {
+        if (g_moe) {
+            cudaStreamSynchronize(g_stream);
+            cudaFree(g_moe);
+        }
+        if (cudaMalloc(&g_moe, need) != cudaSuccess) {
+            cudaGetLastError();
+            g_moe = nullptr;
+            g_moe_bytes = 0;
+            set_error(QZ_ERR_CUDA, "cuda_moe_ffn: cudaMalloc of the scratch failed");
+            return;
+        }
+        g_moe_bytes = need;
+    }
+    int *d_rows = (int *)g_moe;
+    float *d_wts = (float *)(g_moe + (size_t)A * 4);
+    float *xe = (float *)(g_moe + lists), *g = xe + (size_t)A * K, *u = g + (size_t)A * F, *yd = u + (size_t)A * F;
+    QZ_CUDA_CHECK(cudaMemcpyAsync(d_rows, rows.data(), (size_t)A * 4, cudaMemcpyHostToDevice, g_stream));
+    QZ_CUDA_CHECK(cudaMemcpyAsync(d_wts, wts.data(), (size_t)A * 4, cudaMemcpyHostToDevice, g_stream));
+    QZ_CUDA_CHECK(cudaStreamSynchronize(g_stream));   // the host vectors die with this call
+    QZ_CUDA_CHECK(cudaMemsetAsync(d_out, 0, (size_t)m * K * sizeof(float), g_stream));
+    {
+        const long long n4 = (long long)A * (K / 4);
+        moe_gather_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, g_stream>>>(d_x, xe, d_rows, A, embed_dim);
+        QZ_LAUNCH_CHECK();
+    }
+    const size_t gu_bytes = (K * F / fg.block_elems) * fg.block_bytes, dn_bytes = (F * K / fd.block_elems) * fd.block_bytes;
+    for (int e = 0; e < n_experts; e++) {
+        const int c = count[e];
+        if (!c) continue;
+        const size_t o = (size_t)start[e];
+        gemm_dispatch(type_gate_up, d_gate + e * gu_bytes, xe + o * K, g + o * F, c, embed_dim, ffn_dim);
+        gemm_dispatch(type_gate_up, d_up + e * gu_bytes, xe + o * K, u + o * F, c, embed_dim, ffn_dim);
+    }
+    {
+        const long long n = (long long)A * F;
+        moe_swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, g_stream>>>(g, u, n, oai);
+        QZ_LAUNCH_CHECK();
+    }
+    for (int e = 0; e < n_experts; e++) {
+        const int c = count[e];
+        if (!c) continue;
+        const size_t o = (size_t)start[e];
+        gemm_dispatch(type_down, d_down + e * dn_bytes, g + o * F, yd + o * K, c, ffn_dim, embed_dim);
+        const long long n4 = (long long)c * (K / 4);
+        moe_scatter_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, g_stream>>>(d_out, yd + o * K, d_rows + o, d_wts + o, c,
+                                                                             embed_dim);
+        QZ_LAUNCH_CHECK();
+    }
 }
 
 // ======================= row-sharded layers: peer windows =======================
