@@ -164,6 +164,17 @@ void cuda_attn_decode(float *out, const float *q, const float *k_cache, const fl
                       int n_kv_heads, int seq_len, int head_dim, int kv_dim, float scale, const float *sinks,
                       int out_slot);
 
+/* The whole attention block of one decode step as ONE launch: RoPE on q and k, append of k and v to the
+ * caches at `pos`, attention of all heads over cache positions [k_start, pos], merge of the splits
+ * (cuda_rope_yarn x2 + cuda_kv_append + cuda_attn_score_all + cuda_softmax_sink_all +
+ * cuda_attn_values_all, src/cuda.rs:601-645).  q [n_heads*head_dim], k_new / v_new
+ * [n_kv_heads*head_dim] are the projections BEFORE RoPE and are left untouched; the caches are
+ * [max_seq][n_kv_heads*head_dim].  sinks may be NULL; out_slot >= 0 also writes the result's activation
+ * form for the output projection.  head_dim a multiple of 32 up to 128, at most 64 kv heads. */
+void cuda_attn_block(float *out, const float *q, const float *k_new, const float *v_new, float *k_cache, float *v_cache,
+                     int n_heads, int n_kv_heads, int head_dim, int pos, int k_start, float scale, const float *sinks,
+                     float theta, float yarn_scale, int yarn_orig_ctx, int neox, int out_slot);
+
 /* cuda_gemv_q whose activation vector is computed by the GEMV kernel itself, in its prologue, while its
  * weight pipeline fills: y_i (+)= W_i * rmsnorm(x, norm_w)  (cuda_rms_norm + cuda_gemv, src/cuda.rs:556-597
  * and :760-775) and y_i (+)= W_i * swiglu(gate, up)  (cuda_swiglu / cuda_swiglu_oai + cuda_gemv,

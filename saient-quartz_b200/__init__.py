@@ -84,6 +84,8 @@ _SIGS = {
     "cuda_gemv_rmsnorm": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_gemv_swiglu": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                 C.c_int]),
+    "cuda_attn_block": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                               C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int]),
     "cuda_moe_ffn": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                             C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
     "quartz_mgpu_handle_bytes": (C.c_size_t, []),

@@ -252,4 +252,242 @@ __global__ void attn_combine_kernel(float *__restrict__ out, const float *__rest
     }
 }
 
+// ---- the whole attention block of a decode step in ONE launch ---------------------------------
+// RoPE on q and k, append of k and v at `pos`, split-KV attention over positions [k_start, pos] and
+// the merge of the splits (cuda_rope_yarn x2, cuda_kv_append, cuda_attn_score_all,
+// cuda_softmax_sink_all, cuda_attn_values_all: src/cuda.rs:601-645).  grid = (n_kv_heads,
+// n_splits), 128 threads.  Every CTA rotates the query heads of its kv head itself (from the
+// un-rotated q, into shared memory); the CTA of the last split rotates the new key, writes key and
+// value into the caches and then stages them like any other row.  Partials as in
+// attn_partial_kernel; the CTA that finishes last for a kv head (a counter per kv head) merges that
+// head group's splits and emits the output projection's activation form.
+struct RopeArgs {
+    int pos;
+    float theta, yarn_scale;
+    int yarn_orig_ctx, neox;
+};
+
+// rotation (cos, sin) of pair i, exactly as rope_kv_kernel / src/cuda_kernels.cu:588-620 compute it
+__device__ __forceinline__ void rope_cs(const RopeArgs &r, int i, int head_dim, float &c, float &s)
+{
+    const float PI = 3.14159265358979f;
+    float inv = 1.f / powf(r.theta, 2.f * (float)i / (float)head_dim);
+    float eff = inv;
+    if (r.yarn_scale > 1.f && r.yarn_orig_ctx > 0) {
+        float hi_w = (float)r.yarn_orig_ctx / 32.f, lo_w = (float)r.yarn_orig_ctx / 1.f;
+        float wavelen = 2.f * PI / inv;
+        float ramp = fmaxf(0.f, fminf(1.f, (lo_w - wavelen) / (lo_w - hi_w)));
+        eff = ramp * inv + (1.f - ramp) * (inv / r.yarn_scale);
+    }
+    sincosf((float)r.pos * eff, &s, &c);
+}
+
+// (cos, sin) of every rotation pair at one position: the same for all layers and heads of a decode
+// step, so it is computed once per step instead of in every attention CTA
+__global__ void rope_table_kernel(float2 *__restrict__ tab, RopeArgs r, int head_dim)
+{
+    pdl_wait();
+    pdl_trigger();
+    const int i = threadIdx.x;
+    if (i < (head_dim >> 1)) {
+        float c, s;
+        rope_cs(r, i, head_dim, c, s);
+        tab[i] = make_float2(c, s);
+    }
+}
+
+__global__ void __launch_bounds__(128) attn_fused_kernel(float *__restrict__ out, float *__restrict__ part,
+                                                         int *__restrict__ counters, const float *__restrict__ q,
+                                                         const float *__restrict__ k_new, const float *__restrict__ v_new,
+                                                         float *k_cache, float *v_cache, int n_heads, int n_kv_heads,
+                                                         int k_start, int head_dim, int kv_dim, float scale,
+                                                         const float *__restrict__ sinks, RopeArgs rope,
+                                                         const float2 *__restrict__ rope_tab, XQOut o, int emit_q)
+{
+    __shared__ float ks[ATT_CHUNK][ATT_MAX_HD + 1];
+    __shared__ float vs[ATT_CHUNK][ATT_MAX_HD];
+    __shared__ float qs[4][ATT_MAX_HD];
+    __shared__ float ps[4][ATT_CHUNK];
+    __shared__ int is_last;
+    pdl_wait();
+    pdl_trigger();
+    const int kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
+    const int seq_len = rope.pos - k_start + 1;
+    const int t0 = split * ATT_CHUNK;                 // relative to k_start
+    const int nt = min(ATT_CHUNK, seq_len - t0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = head_dim >> 1;
+    const float *kc = k_cache + (size_t)k_start * kv_dim, *vc = v_cache + (size_t)k_start * kv_dim;
+    const bool has_new = split == n_splits - 1;       // the new position is this CTA's last row
+    const int n_old = has_new ? nt - 1 : nt;          // rows that come from the caches
+    // 1. issue the loads of the cached K and V rows (all of a thread's loads before any use)
+    const int hd4 = head_dim >> 2;
+    constexpr int MAX_IT = ATT_CHUNK * (ATT_MAX_HD / 4) / 128;
+    float4 kreg[MAX_IT], vreg[MAX_IT];
+#pragma unroll
+    for (int it = 0; it < MAX_IT; it++) {
+        const int idx = threadIdx.x + it * 128;
+        if (idx < n_old * hd4) {
+            const int t = idx / hd4, c = idx - t * hd4;
+            const size_t g = (size_t)(t0 + t) * kv_dim + (size_t)kvh * head_dim + 4 * c;
+            kreg[it] = __ldg((const float4 *)(kc + g));
+            vreg[it] = __ldg((const float4 *)(vc + g));
+        }
+    }
+    // 2. while they fly: the new key (rotated) and value go to shared memory and to the caches
+    if (has_new) {
+        const float *kh = k_new + (size_t)kvh * head_dim, *vh = v_new + (size_t)kvh * head_dim;
+        float *kd = k_cache + (size_t)rope.pos * kv_dim + (size_t)kvh * head_dim;
+        float *vd = v_cache + (size_t)rope.pos * kv_dim + (size_t)kvh * head_dim;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float2 cs = rope_tab[i];
+            const int i0 = rope.neox ? i : 2 * i, i1 = rope.neox ? i + half : 2 * i + 1;
+            const float a = kh[i0], b = kh[i1];
+            const float r0 = a * cs.x - b * cs.y, r1 = a * cs.y + b * cs.x;
+            kd[i0] = r0;
+            kd[i1] = r1;
+            ks[nt - 1][i0] = r0;
+            ks[nt - 1][i1] = r1;
+        }
+        for (int j = threadIdx.x; j < head_dim; j += blockDim.x) {
+            const float v = vh[j];
+            vd[j] = v;
+            vs[nt - 1][j] = v;
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < MAX_IT; it++) {
+        const int idx = threadIdx.x + it * 128;
+        if (idx < n_old * hd4) {
+            const int t = idx / hd4, c = idx - t * hd4;
+            ks[t][4 * c] = kreg[it].x; ks[t][4 * c + 1] = kreg[it].y; ks[t][4 * c + 2] = kreg[it].z; ks[t][4 * c + 3] = kreg[it].w;
+            *(float4 *)&vs[t][4 * c] = vreg[it];
+        }
+    }
+    const int h_lo = (kvh * n_heads + n_kv_heads - 1) / n_kv_heads;
+    const int h_hi = ((kvh + 1) * n_heads + n_kv_heads - 1) / n_kv_heads;
+    const int stride = head_dim + 2;
+    for (int hb = h_lo; hb < h_hi; hb += 4) {
+        const int head = hb + warp;
+        const bool live = head < h_hi;
+        __syncthreads();   // staging done / previous round's qs no longer read
+        if (live) {
+            const float *qh = q + (size_t)head * head_dim;
+            for (int i = lane; i < half; i += 32) {
+                const float2 cs = rope_tab[i];
+                const int i0 = rope.neox ? i : 2 * i, i1 = rope.neox ? i + half : 2 * i + 1;
+                const float a = qh[i0], b = qh[i1];
+                qs[warp][i0] = a * cs.x - b * cs.y;
+                qs[warp][i1] = a * cs.y + b * cs.x;
+            }
+        }
+        __syncthreads();
+        if (!live) continue;
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+        for (int i = 0; i < head_dim; i += 4) {
+            c0 = fmaf(qs[warp][i], ks[lane][i], c0);
+            c1 = fmaf(qs[warp][i + 1], ks[lane][i + 1], c1);
+            c2 = fmaf(qs[warp][i + 2], ks[lane][i + 2], c2);
+            c3 = fmaf(qs[warp][i + 3], ks[lane][i + 3], c3);
+        }
+        float sc = (c0 + c1) + (c2 + c3);
+        sc = lane < nt ? sc * scale : -INFINITY;
+        float mx = sc;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+        const float p = lane < nt ? expf(sc - mx) : 0.f;
+        float sum = p;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o2);
+        ps[warp][lane] = p;
+        __syncwarp();
+        float *dst = part + ((size_t)head * n_splits + split) * stride;
+        float o0 = 0.f, o1 = 0.f, o2v = 0.f, o3 = 0.f;
+        for (int t = 0; t < nt; t++) {
+            const float pt = ps[warp][t];
+            o0 = fmaf(pt, vs[t][lane], o0);
+            if (head_dim > 32) o1 = fmaf(pt, vs[t][lane + 32], o1);
+            if (head_dim > 64) o2v = fmaf(pt, vs[t][lane + 64], o2v);
+            if (head_dim > 96) o3 = fmaf(pt, vs[t][lane + 96], o3);
+        }
+        dst[2 + lane] = o0;
+        if (head_dim > 32) dst[2 + lane + 32] = o1;
+        if (head_dim > 64) dst[2 + lane + 64] = o2v;
+        if (head_dim > 96) dst[2 + lane + 96] = o3;
+        if (lane == 0) {
+            dst[0] = mx;
+            dst[1] = sum;
+        }
+        __syncwarp();
+    }
+    // ---- the last CTA of this kv head merges the head group's splits ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(&counters[kvh], 1);
+        is_last = prev == n_splits - 1;
+        if (is_last) counters[kvh] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // Up to four heads at a time: warp w reduces head hb+w's (max, sum) pairs and leaves the splits'
+    // rescale factors in shared memory; then every thread owns output dimension i of all four heads,
+    // so its loads of the four heads' partials are independent and overlap.
+    float *fs = &ks[0][0];                  // [4][n_splits] rescale factors (ks is free now)
+    float *tot_s = &vs[0][0];               // [4] softmax denominators
+    const int i = threadIdx.x;
+    for (int hb = h_lo; hb < h_hi; hb += 4) {
+        const int head_w = hb + warp;
+        __syncthreads();                    // previous round's fs / tot_s no longer read
+        if (head_w < h_hi) {
+            const float *pp = part + (size_t)head_w * n_splits * stride;
+            const float sink = sinks ? sinks[head_w] : -INFINITY;
+            const bool has_sink = sink > -1e29f;
+            float mx = has_sink ? sink : -1e30f;
+            for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, __ldcg(pp + (size_t)s * stride));
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+            float tot = 0.f;
+            for (int s = lane; s < n_splits; s += 32) {
+                const float f = expf(__ldcg(pp + (size_t)s * stride) - mx);
+                fs[warp * n_splits + s] = f;
+                tot = fmaf(f, __ldcg(pp + (size_t)s * stride + 1), tot);
+            }
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) tot += __shfl_xor_sync(0xFFFFFFFFu, tot, o2);
+            if (lane == 0) tot_s[warp] = tot + (has_sink ? expf(sink - mx) : 0.f);
+        }
+        __syncthreads();
+        float r[4] = {0.f, 0.f, 0.f, 0.f};
+        if (i < head_dim) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int s = 0; s < n_splits; s++) {
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (hb + j < h_hi)
+                        acc[j] = fmaf(fs[j * n_splits + s],
+                                      __ldcg(part + ((size_t)(hb + j) * n_splits + s) * stride + 2 + i), acc[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (hb + j < h_hi) {
+                    r[j] = acc[j] / tot_s[j];
+                    out[(size_t)(hb + j) * head_dim + i] = r[j];
+                }
+        }
+        if (emit_q) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (hb + j >= h_hi) break;   // uniform over the block
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) v[e] = __shfl_sync(0xFFFFFFFFu, r[j], (4 * lane + e) & 31);
+                const int base = ((hb + j) * head_dim + (i & ~31)) >> 2;
+                quantize4_store(v, base + (lane & 7), lane < 8 && (i & ~31) < head_dim, o);
+            }
+        }
+    }
+}
+
 }  // namespace qz

@@ -26,6 +26,7 @@ namespace qz {
 
 constexpr int TMA_MAX_STAGES = 16;
 constexpr int TMA_CONSUMERS = 512;
+constexpr int XSRC_MAX_IT = 8;             // float4 loads per consumer thread in the fused activation prologue
 constexpr long long TMA_WAIT_CYCLES = 2000000000LL;   // ~1 s at 1.9 GHz
 
 // Where the activation vector comes from.  mode 0: already converted (xq).  mode 1: RMSNorm of the
@@ -253,13 +254,25 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
         const XQOut o{sxl, sxh, sxs, sxsum};
         const float *__restrict__ pa = a.xsrc.a, *__restrict__ pb = a.xsrc.b;
         const int n4 = a.K >> 2;
+        // all of this thread's loads are issued before anything is computed: one L2 round trip, not one per
+        // pass (the host only takes this path when XSRC_MAX_IT passes cover the vector)
+        float4 xa[XSRC_MAX_IT], xb[XSRC_MAX_IT];
+#pragma unroll
+        for (int it = 0; it < XSRC_MAX_IT; it++) {
+            const int t = it * n_consumers + threadIdx.x;
+            if (t < n4) {
+                xa[it] = __ldcg((const float4 *)(pa + 4 * t));
+                xb[it] = __ldcg((const float4 *)(pb + 4 * t));
+            } else {
+                xa[it] = xb[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
         float r = 1.f;
         if (a.xsrc.mode == 1) {
             float ss = 0.f;
-            for (int t = threadIdx.x; t < n4; t += n_consumers) {
-                const float4 v = *(const float4 *)(pa + 4 * t);
-                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-            }
+#pragma unroll
+            for (int it = 0; it < XSRC_MAX_IT; it++)
+                ss = fmaf(xa[it].x, xa[it].x, fmaf(xa[it].y, xa[it].y, fmaf(xa[it].z, xa[it].z, fmaf(xa[it].w, xa[it].w, ss))));
             for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o2);
             if (lane == 0) xred[threadIdx.x >> 5] = ss;
             named_bar_sync(14, n_consumers);
@@ -267,23 +280,22 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             for (int w = 0; w < (n_consumers >> 5); w++) ss += xred[w];
             r = rsqrtf(ss / (float)a.K + 1e-5f);
         }
-        for (int t0 = 0; t0 < n4; t0 += n_consumers) {
-            const int t = t0 + threadIdx.x;
-            const bool valid = t < n4;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (valid) {
-                const float4 x4 = *(const float4 *)(pa + 4 * t), y4 = *(const float4 *)(pb + 4 * t);
-                const float xx[4] = {x4.x, x4.y, x4.z, x4.w}, yy[4] = {y4.x, y4.y, y4.z, y4.w};
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    if (a.xsrc.mode == 1) {
-                        v[i] = xx[i] * r * yy[i];
-                    } else if (a.xsrc.oai) {
-                        const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
-                        v[i] = (g / (1.f + expf(-1.702f * g))) * (up + 1.f);
-                    } else {
-                        v[i] = (xx[i] / (1.f + expf(-xx[i]))) * yy[i];
-                    }
+        for (int it = 0; it < XSRC_MAX_IT; it++) {
+            if (it * n_consumers >= n4) break;   // uniform over the CTA
+            const int t = it * n_consumers + threadIdx.x;
+            const bool valid = t < n4;
+            const float xx[4] = {xa[it].x, xa[it].y, xa[it].z, xa[it].w}, yy[4] = {xb[it].x, xb[it].y, xb[it].z, xb[it].w};
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (a.xsrc.mode == 1) {
+                    v[i] = xx[i] * r * yy[i];
+                } else if (a.xsrc.oai) {
+                    const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
+                    v[i] = (g / (1.f + expf(-1.702f * g))) * (up + 1.f);
+                } else {
+                    v[i] = (xx[i] / (1.f + expf(-xx[i]))) * yy[i];
                 }
             }
             quantize4_store(v, t, valid, o);

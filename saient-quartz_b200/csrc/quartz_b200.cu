@@ -287,6 +287,7 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     const int x_bytes = g_xsrc_pending ? (int)((2 * (size_t)g.K + g.K / 8 + g.K / 4 + 31) & ~(size_t)15) : 0;
     const int ring_budget = smem_budget - x_bytes;
     if (a.stage_bytes * 2 > ring_budget) return false;
+    if (g_xsrc_pending && g.K / 4 > XSRC_MAX_IT * a.Upad * a.RP) return false;   // the prologue holds the vector in registers
     const int ntiles = (g.N + a.RP - 1) / a.RP;
     const int n_cta = ntiles < ctas_per_mat ? ntiles : ctas_per_mat;
     int stages = ring_budget / a.stage_bytes;
@@ -1170,6 +1171,27 @@ void cuda_rope_kv(float *q, float *k, const float *v, float *k_cache, float *v_c
 static float *g_attn_part = nullptr;
 static size_t g_attn_part_floats = 0;
 
+// attention scratch: 64 counters (zero between launches) followed by the split partials
+static bool ensure_attn_scratch(size_t need_floats)
+{
+    if (need_floats <= g_attn_part_floats) return true;
+    if (g_attn_part) {
+        cudaStreamSynchronize(g_stream);
+        cudaFree(g_attn_part);
+    }
+    size_t cap = need_floats < (size_t)(1 << 20) ? (size_t)(1 << 20) : need_floats * 2;   // room for longer contexts
+    if (cudaMalloc(&g_attn_part, (cap + 64) * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        g_attn_part = nullptr;
+        g_attn_part_floats = 0;
+        set_error(QZ_ERR_CUDA, "cudaMalloc of the attention scratch failed");
+        return false;
+    }
+    cudaMemset(g_attn_part, 0, 64 * sizeof(float));
+    g_attn_part_floats = cap;
+    return true;
+}
+
 void cuda_attn_decode(float *out, const float *q, const float *k_cache, const float *v_cache, int n_heads,
                       int n_kv_heads, int seq_len, int head_dim, int kv_dim, float scale, const float *sinks,
                       int out_slot)
@@ -1180,28 +1202,58 @@ void cuda_attn_decode(float *out, const float *q, const float *k_cache, const fl
         return;
     }
     const int n_splits = (seq_len + ATT_CHUNK - 1) / ATT_CHUNK;
-    const size_t need = (size_t)n_heads * n_splits * (head_dim + 2);
-    if (need > g_attn_part_floats) {
-        if (g_attn_part) {
-            cudaStreamSynchronize(g_stream);
-            cudaFree(g_attn_part);
-        }
-        size_t cap = need < (size_t)(1 << 20) ? (size_t)(1 << 20) : need * 2;   // room for longer contexts
-        if (cudaMalloc(&g_attn_part, cap * sizeof(float)) != cudaSuccess) {
-            cudaGetLastError();
-            g_attn_part = nullptr;
-            g_attn_part_floats = 0;
-            set_error(QZ_ERR_CUDA, "cudaMalloc of the attention scratch failed");
-            return;
-        }
-        g_attn_part_floats = cap;
-    }
+    if (!ensure_attn_scratch((size_t)n_heads * n_splits * (head_dim + 2))) return;
     XQOut o{nullptr, nullptr, nullptr, nullptr};
     if (out_slot >= 0 && !user_slot(out_slot, n_heads * head_dim, &o)) return;
-    launch(attn_partial_kernel, dim3(n_kv_heads, n_splits), dim3(128), 0, g_attn_part, q, k_cache, v_cache, n_heads,
+    float *part = g_attn_part + 64;
+    launch(attn_partial_kernel, dim3(n_kv_heads, n_splits), dim3(128), 0, part, q, k_cache, v_cache, n_heads,
            n_kv_heads, seq_len, head_dim, kv_dim, scale);
     launch(attn_combine_kernel, dim3(n_heads), dim3(head_dim), (size_t)n_splits * sizeof(float), out,
-           (const float *)g_attn_part, n_splits, head_dim, sinks, o, out_slot >= 0 ? 1 : 0);
+           (const float *)part, n_splits, head_dim, sinks, o, out_slot >= 0 ? 1 : 0);
+}
+
+// (cos, sin) table of the current decode position, shared by all layers of a step
+static float2 *g_rope_tab = nullptr;
+static RopeArgs g_rope_key = {-1, 0.f, 0.f, 0, 0};
+static int g_rope_key_hd = 0;
+static bool g_rope_tab_valid = false;   // cleared when a graph recording starts or ends
+
+void cuda_attn_block(float *out, const float *q, const float *k_new, const float *v_new, float *k_cache, float *v_cache,
+                     int n_heads, int n_kv_heads, int head_dim, int pos, int k_start, float scale, const float *sinks,
+                     float theta, float yarn_scale, int yarn_orig_ctx, int neox, int out_slot)
+{
+    if (n_heads <= 0) return;
+    if (head_dim > ATT_MAX_HD || head_dim % 32 != 0 || n_kv_heads <= 0 || n_kv_heads > 64 || n_heads % n_kv_heads != 0 ||
+        pos < 0 || k_start < 0 || k_start > pos) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_attn_block: head_dim must be a multiple of 32 up to 128, n_heads a multiple of n_kv_heads (<= 64 kv heads), 0 <= k_start <= pos");
+        return;
+    }
+    const int seq_len = pos - k_start + 1;
+    const int n_splits = (seq_len + ATT_CHUNK - 1) / ATT_CHUNK;
+    if (n_splits > ATT_CHUNK * ATT_MAX_HD / 4) {
+        set_error(QZ_ERR_TOO_LARGE, "cuda_attn_block: context too long for the single-launch merge");
+        return;
+    }
+    if (!ensure_attn_scratch((size_t)n_heads * n_splits * (head_dim + 2))) return;
+    XQOut o{nullptr, nullptr, nullptr, nullptr};
+    if (out_slot >= 0 && !user_slot(out_slot, n_heads * head_dim, &o)) return;
+    const RopeArgs r{pos, theta, yarn_scale, yarn_orig_ctx, neox};
+    if (!g_rope_tab && cudaMalloc(&g_rope_tab, (ATT_MAX_HD / 2) * sizeof(float2)) != cudaSuccess) {
+        cudaGetLastError();
+        g_rope_tab = nullptr;
+        set_error(QZ_ERR_CUDA, "cudaMalloc of the RoPE table failed");
+        return;
+    }
+    if (!g_rope_tab_valid || g_rope_key.pos != pos || g_rope_key.theta != theta || g_rope_key.yarn_scale != yarn_scale ||
+        g_rope_key.yarn_orig_ctx != yarn_orig_ctx || g_rope_key_hd != head_dim) {
+        launch(rope_table_kernel, dim3(1), dim3(ATT_MAX_HD / 2), 0, g_rope_tab, r, head_dim);
+        g_rope_key = r;
+        g_rope_key_hd = head_dim;
+        g_rope_tab_valid = true;
+    }
+    launch(attn_fused_kernel, dim3(n_kv_heads, n_splits), dim3(128), 0, out, g_attn_part + 64, (int *)g_attn_part, q, k_new,
+           v_new, k_cache, v_cache, n_heads, n_kv_heads, k_start, head_dim, n_kv_heads * head_dim, scale, sinks, r,
+           (const float2 *)g_rope_tab, o, out_slot >= 0 ? 1 : 0);
 }
 
 // ---- CUDA-graph helpers: record a sequence of this library's calls once, replay it per token ----
@@ -1231,6 +1283,7 @@ int quartz_graph_begin(void)
     g_saved_stream = g_stream;
     g_stream = g_graph_stream;
     g_capturing = true;
+    g_rope_tab_valid = false;   // the table launch must be part of the recording
     g_pdl = g_pdl_in_graphs;   // recorded kernels become programmatic dependents of one another
     return 1;
 }
@@ -1239,6 +1292,7 @@ void *quartz_graph_end(void)
 {
     if (!g_capturing) return nullptr;
     g_capturing = false;
+    g_rope_tab_valid = false;   // a recorded launch has not run
     g_stream = g_saved_stream;
     g_pdl = false;
     cudaGraph_t graph = nullptr;

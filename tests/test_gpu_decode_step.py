@@ -230,6 +230,47 @@ def test_attn_decode_matches_three_kernel_attention(gpu):
     gpu.check_error()
 
 
+@pytest.mark.parametrize("neox", [0, 1])
+def test_attn_block_matches_separate_launches(gpu, neox):
+    """cuda_attn_block (RoPE + KV append + attention + merge in one launch) against cuda_rope_kv +
+    cuda_attn_decode: same output, same cache rows, q / k_new left un-rotated; called twice in a row
+    (the per-kv-head counters must have reset themselves)."""
+    L = gpu.lib()
+    r = np.random.Generator(np.random.PCG64([0xA78, neox]))
+    for (nh, nkv, hd, pos, k_start, max_seq, sink) in [(32, 8, 128, 1024, 0, 1100, False), (8, 8, 64, 32, 0, 64, True),
+                                                       (12, 2, 96, 69, 5, 128, True), (4, 1, 128, 0, 0, 16, False),
+                                                       (16, 4, 128, 31, 0, 40, False)]:
+        kv_dim = nkv * hd
+        kc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+        vc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+        q = r.standard_normal(nh * hd, dtype=np.float32)
+        k = r.standard_normal(kv_dim, dtype=np.float32)
+        v = r.standard_normal(kv_dim, dtype=np.float32)
+        sinks = r.standard_normal(nh, dtype=np.float32) if sink else np.full(nh, -np.inf, np.float32)
+        scale = np.float32(1.0 / np.sqrt(hd))
+        theta, ys, yc = np.float32(500000.0), np.float32(1.0), 0
+        seq = pos - k_start + 1
+        # separate launches (they rotate q and k in place)
+        dk1, dv1 = gpu.GpuBuf.upload(kc), gpu.GpuBuf.upload(vc)
+        dq1, dkn1, dvn = gpu.GpuBuf.upload(q), gpu.GpuBuf.upload(k), gpu.GpuBuf.upload(v)
+        ds, o1 = gpu.GpuBuf.upload(sinks), gpu.GpuBuf.alloc_f32(nh * hd)
+        L.cuda_rope_kv(dq1.ptr, dkn1.ptr, dvn.ptr, dk1.ptr, dv1.ptr, nh, nkv, hd, pos, theta, ys, yc, neox)
+        L.cuda_attn_decode(o1.ptr, dq1.ptr, dk1.ptr + 4 * k_start * kv_dim, dv1.ptr + 4 * k_start * kv_dim, nh, nkv, seq, hd,
+                           kv_dim, scale, ds.ptr, -1)
+        want, want_k, want_v = o1.download(), dk1.download(), dv1.download()
+        # one launch
+        dk2, dv2 = gpu.GpuBuf.upload(kc), gpu.GpuBuf.upload(vc)
+        dq2, dkn2, o2 = gpu.GpuBuf.upload(q), gpu.GpuBuf.upload(k), gpu.GpuBuf.alloc_f32(nh * hd)
+        for rep in range(2):
+            L.cuda_attn_block(o2.ptr, dq2.ptr, dkn2.ptr, dvn.ptr, dk2.ptr, dv2.ptr, nh, nkv, hd, pos, k_start, scale, ds.ptr,
+                              theta, ys, yc, neox, -1)
+            got = o2.download()
+            assert np.abs(got - want).max() <= 2e-5 * max(np.abs(want).max(), 1e-30), (nh, hd, pos, rep)
+        assert np.array_equal(dk2.download(), want_k) and np.array_equal(dv2.download(), want_v)
+        assert np.array_equal(dq2.download(), q) and np.array_equal(dkn2.download(), k)
+    gpu.check_error()
+
+
 def test_rope_kv_matches_separate_calls(gpu):
     L = gpu.lib()
     r = np.random.Generator(np.random.PCG64([0xB0B]))
