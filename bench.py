@@ -240,6 +240,11 @@ def gemm_section(q, args, torch, np, want_parity, only=None):
                     worst = max(worst, float(np.max(np.abs(y[mrow].astype(np.float64) - ref[i]) / tol)))
                 row["max_err_over_tolerance"] = worst
                 assert worst <= 1.0, f"GEMM parity failed: {row}"
+                if M == 16:   # the CPU path's gemm() on the same 16 tokens, all host threads
+                    tc0 = time.perf_counter()
+                    oracle.gemm(X, w, t, K, N, M)
+                    row["cpu_oracle_ms"] = (time.perf_counter() - tc0) * 1e3
+                    row["cpu_cores"] = oracle.max_threads()
             out.append(row)
             dx.drop(); dy.drop()
         dw.drop()

@@ -172,8 +172,10 @@ template <uint32_t T, bool PLANES>
 struct AProd {   // generic: any format, either layout, through the bit-exact decoder; no prefetch
     struct Raw { int unused; };
     static constexpr bool TWO_SETS = false;
+    static constexpr int TABLE_BYTES = 0;
+    __device__ static void build_table(uint8_t *, int, int) {}
     __device__ static void load(Raw &, const uint8_t *, int, int) {}
-    __device__ static void store(uint8_t *As, const Raw &, const uint8_t *rowp, int nb, int kstep, int r)
+    __device__ static void store(uint8_t *As, const Raw &, const uint8_t *rowp, int nb, int kstep, int r, const uint8_t *)
     {
         const FormatInfo fi = format_info(T);
 #pragma unroll 1
@@ -208,6 +210,8 @@ template <>
 struct AProd<T_Q4_K, false> {
     struct Raw { uint4 hdr, q0, q1; };
     static constexpr bool TWO_SETS = true;
+    static constexpr int TABLE_BYTES = 0;
+    __device__ static void build_table(uint8_t *, int, int) {}
     __device__ static void load(Raw &w, const uint8_t *rowp, int, int kstep)
     {
         if (rowp) {
@@ -220,7 +224,7 @@ struct AProd<T_Q4_K, false> {
             w.hdr = w.q0 = w.q1 = make_uint4(0, 0, 0, 0);
         }
     }
-    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r)
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r, const uint8_t *)
     {
         const uint32_t q[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
         const int p = kstep & 3;
@@ -254,6 +258,8 @@ template <>
 struct AProd<T_Q6_K, true> {
     struct Raw { uint4 a[4], h0, h1; uint32_t sc, d; };
     static constexpr bool TWO_SETS = false;
+    static constexpr int TABLE_BYTES = 0;
+    __device__ static void build_table(uint8_t *, int, int) {}
     __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
     {
         if (rowp) {
@@ -273,7 +279,7 @@ struct AProd<T_Q6_K, true> {
             w.sc = w.d = 0;
         }
     }
-    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r)
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r, const uint8_t *)
     {
         const uint32_t qh[8] = {w.h0.x, w.h0.y, w.h0.z, w.h0.w, w.h1.x, w.h1.y, w.h1.z, w.h1.w};
         const int hh = kstep & 1;
@@ -302,8 +308,131 @@ struct AProd<T_Q6_K, true> {
     }
 };
 
+// ---- codebook formats: the grids are kept in shared memory already converted to bf16 and already in
+//      tile order ((w0,w2),(w1,w3) per four weights), next to a table of sign-bit masks per 7-bit sign
+//      index in the same order.  Eight weights then cost two table reads, four XORs and four HMUL2s. ----
+__device__ __forceinline__ uint32_t bf16x2_of(float a, float b)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *(uint32_t *)&v;
+}
+// entry i of the sign table: XOR masks for eight weights, words (s0,s2) (s1,s3) (s4,s6) (s5,s7)
+__device__ __forceinline__ void build_sign_table(uint4 *dst, int tid, int n)
+{
+    for (int i = tid; i < 128; i += n) {
+        const uint32_t s = g_ksigns[i];
+        auto m = [&](int a, int b) { return (((s >> a) & 1u) << 15) | (((s >> b) & 1u) << 31); };
+        dst[i] = make_uint4(m(0, 2), m(1, 3), m(4, 6), m(5, 7));
+    }
+}
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, __nv_bfloat162 s)
+{
+    __nv_bfloat162 r = __hmul2(*(__nv_bfloat162 *)&a, s);
+    return *(uint32_t *)&r;
+}
+
+// IQ2_XS, plane layout (d[nb x 2] | qs[nb x 64] | scales[nb x 8]): K step = the 64 weights of pair p
+// of block b: eight u16 (9-bit grid index, 7-bit sign index), two scale bytes (src/dequant.rs:1043-1075)
+template <>
+struct AProd<T_IQ2_XS, true> {
+    struct Raw { uint4 q; uint32_t sc, d; };
+    static constexpr bool TWO_SETS = true;
+    static constexpr int TABLE_BYTES = 512 * 16 + 128 * 16;
+    __device__ static void build_table(uint8_t *tbl, int tid, int n)
+    {
+        uint4 *g = (uint4 *)tbl;
+        for (int i = tid; i < 512; i += n) {
+            const uint64_t v = g_iq2xs_grid[i];
+            auto b = [&](int j) { return (float)(int)(int8_t)(v >> (8 * j)); };
+            g[i] = make_uint4(bf16x2_of(b(0), b(2)), bf16x2_of(b(1), b(3)), bf16x2_of(b(4), b(6)), bf16x2_of(b(5), b(7)));
+        }
+        build_sign_table(g + 512, tid, n);
+    }
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
+    {
+        if (rowp) {
+            const int b = kstep >> 2, p = kstep & 3;
+            w.q = __ldg((const uint4 *)(rowp + (size_t)nb * 2 + (size_t)b * 64 + 16 * p));
+            w.sc = __ldg((const uint16_t *)(rowp + (size_t)nb * 66 + (size_t)b * 8 + 2 * p));
+            w.d = __ldg((const uint16_t *)(rowp + (size_t)b * 2));
+        } else {
+            w.q = make_uint4(0, 0, 0, 0);
+            w.sc = w.d = 0;
+        }
+    }
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int, int r, const uint8_t *tbl)
+    {
+        const uint4 *grid = (const uint4 *)tbl, *sign = grid + 512;
+        const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
+        const float d = 0.25f * h2f((uint16_t)w.d);
+#pragma unroll
+        for (int l = 0; l < 8; l++) {
+            const uint32_t q = (qw[l >> 1] >> (16 * (l & 1))) & 0xFFFF;
+            const uint32_t nib = (w.sc >> (8 * (l >> 2) + 4 * ((l >> 1) & 1))) & 0xF;
+            const float db = d * (0.5f + (float)nib);
+            const __nv_bfloat162 s2 = __floats2bfloat162_rn(db, db);
+            const uint4 g = grid[q & 511], m = sign[q >> 9];
+            *(uint4 *)(As + sw128(r, l)) = make_uint4(hmul2_bits(g.x ^ m.x, s2), hmul2_bits(g.y ^ m.y, s2),
+                                                      hmul2_bits(g.z ^ m.z, s2), hmul2_bits(g.w ^ m.w, s2));
+        }
+    }
+};
+
+// IQ3_XXS, plane layout (d[nb x 2] | qs[nb x 64] | scales_and_signs[nb x 32]): K step = pair p of block b:
+// sixteen grid-index bytes (four weights each) and two u32 (4 x 7 sign bits + 4-bit scale per 32 weights)
+template <>
+struct AProd<T_IQ3_XXS, true> {
+    struct Raw { uint4 q; uint2 sas; uint32_t d; };
+    static constexpr bool TWO_SETS = true;
+    static constexpr int TABLE_BYTES = 256 * 8 + 128 * 16;
+    __device__ static void build_table(uint8_t *tbl, int tid, int n)
+    {
+        uint2 *g = (uint2 *)tbl;
+        for (int i = tid; i < 256; i += n) {
+            const uint32_t v = g_iq3xxs_grid[i];
+            auto b = [&](int j) { return (float)((v >> (8 * j)) & 0xFF); };
+            g[i] = make_uint2(bf16x2_of(b(0), b(2)), bf16x2_of(b(1), b(3)));
+        }
+        build_sign_table((uint4 *)(tbl + 256 * 8), tid, n);
+    }
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
+    {
+        if (rowp) {
+            const int b = kstep >> 2, p = kstep & 3;
+            w.q = __ldg((const uint4 *)(rowp + (size_t)nb * 2 + (size_t)b * 64 + 16 * p));
+            w.sas = __ldg((const uint2 *)(rowp + (size_t)nb * 66 + (size_t)b * 32 + 8 * p));
+            w.d = __ldg((const uint16_t *)(rowp + (size_t)b * 2));
+        } else {
+            w.q = make_uint4(0, 0, 0, 0);
+            w.sas = make_uint2(0, 0);
+            w.d = 0;
+        }
+    }
+    __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int, int r, const uint8_t *tbl)
+    {
+        const uint2 *grid = (const uint2 *)tbl;
+        const uint4 *sign = (const uint4 *)(tbl + 256 * 8);
+        const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
+        const float d = 0.5f * h2f((uint16_t)w.d);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t a1 = h ? w.sas.y : w.sas.x;
+            const float db = d * (0.5f + (float)(a1 >> 28));
+            const __nv_bfloat162 s2 = __floats2bfloat162_rn(db, db);
+#pragma unroll
+            for (int l = 0; l < 4; l++) {
+                const uint32_t two = (qw[2 * h + (l >> 1)] >> (16 * (l & 1))) & 0xFFFF;   // index bytes 2l, 2l+1
+                const uint2 g1 = grid[two & 0xFF], g2 = grid[two >> 8];
+                const uint4 m = sign[(a1 >> (7 * l)) & 127];
+                *(uint4 *)(As + sw128(r, 4 * h + l)) = make_uint4(hmul2_bits(g1.x ^ m.x, s2), hmul2_bits(g1.y ^ m.y, s2),
+                                                                  hmul2_bits(g2.x ^ m.z, s2), hmul2_bits(g2.y ^ m.w, s2));
+            }
+        }
+    }
+};
+
 template <uint32_t T, bool PLANES>
-constexpr bool gemm_fast_type() { return (T == T_Q4_K && !PLANES) || (T == T_Q6_K && PLANES); }
+constexpr bool gemm_fast_type() { return (T == T_Q4_K && !PLANES) || (PLANES && (T == T_Q6_K || T == T_IQ2_XS || T == T_IQ3_XXS)); }
 
 template <int HALVES>
 constexpr int gemm_threads() { return 2 * 128 * HALVES + 32 + 128 * HALVES; }   // producers, MMA warp, epilogue warps
@@ -370,6 +499,8 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == PWARPS) tmem_alloc(&tmem_base_s, tmem_cols);   // one full warp allocates
+    uint8_t *tbl = gsm + (size_t)a.stages * stage_bytes;        // codebook tables of the format, behind the ring
+    P::build_table(tbl, threadIdx.x, blockDim.x);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -424,7 +555,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
                 mbar_arrive_expect_tx(&full_bar[s], (uint32_t)b_bytes);
                 tma_load_1d(As + a_bytes, src, (uint32_t)b_bytes, &full_bar[s]);
             }
-            P::store(As, use, st.rowp, nb, st.ks, r);   // rows >= 128 land in the second half's tile (r * 128)
+            P::store(As, use, st.rowp, nb, st.ks, r, tbl);   // rows >= 128 land in the second half's tile (r * 128)
             if (!P::TWO_SETS && i + 2 < nunits) {
                 advance(ld, 2);
                 P::load(use, ld.rowp, nb, ld.ks);

@@ -649,10 +649,11 @@ static void launch_gemm(GemmArgs a)
     // wants the warps); large tiles take the SM.
     const int stage_bytes = HALVES * GEMM_ROWS * 128 + ((a.tok_tile * 128 + 1023) & ~1023);
     const bool two = gemm_fast_type<T, PLANES>() && HALVES == 1 && a.tok_tile <= 64;
-    const int budget = (two ? 110 : 200) * 1024;
+    constexpr int table_bytes = AProd<T, PLANES>::TABLE_BYTES;
+    const int budget = (two ? 110 : 200) * 1024 - table_bytes;
     a.stages = budget / stage_bytes;
     if (a.stages > GEMM_STAGES) a.stages = GEMM_STAGES;
-    const size_t smem = (size_t)a.stages * stage_bytes;
+    const size_t smem = (size_t)a.stages * stage_bytes + table_bytes;
     static bool attr_set = false;
     if (!attr_set) {
         QZ_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<T, PLANES, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -743,7 +744,7 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y
     QZ_LAUNCH_CHECK();
     // 256-row CTA tiles (two accumulators) halve the activation bytes each CTA pulls from L2 per
     // flop; they pay off once the token tile is wide enough for that traffic to matter
-    const bool fast = (t == T_Q4_K && !planes) || (t == T_Q6_K && planes);
+    const bool fast = (t == T_Q4_K && !planes) || (planes && (t == T_Q6_K || t == T_IQ2_XS || t == T_IQ3_XXS));
     const int halves = (fast && a.tok_tile >= 128) ? 2 : 1;
     a.status = status_word();
     if (!a.status) return;
