@@ -186,9 +186,20 @@ void cuda_gemv_rmsnorm(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w
 void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_gate,
                       const float *d_up, int oai, int in_dim, int out_dim, int accumulate);
 
+/* Asynchronous copies between page-locked host memory and the device, on the library's stream (the
+ * reference's cuda_h2d / cuda_d2h, src/cuda_kernels.cu:1117-1123, are synchronous cudaMemcpy).  They may
+ * be recorded into a graph together with the kernels, so that a whole step (inputs in, kernels,
+ * results out) is one graph launch; the host reads the results after cuda_sync().  cuda_host_alloc
+ * returns page-locked memory (NULL on failure). */
+void cuda_h2d_async(void *d_dst, const void *h_src_pinned, size_t bytes);
+void cuda_d2h_async(void *h_dst_pinned, const void *d_src, size_t bytes);
+void *cuda_host_alloc(size_t bytes);
+void cuda_host_free(void *p);
+
 /* CUDA-graph helpers (no counterpart in the reference, which launches ~670 kernels per token one
  * by one, src/cuda.rs:548-843).  Between begin and end every call of this library is recorded
- * instead of executed; copies and cuda_sync must stay outside, and every scratch buffer must
+ * instead of executed; cuda_h2d / cuda_d2h / cuda_sync must stay outside (cuda_h2d_async and
+ * cuda_d2h_async may be recorded), and every scratch buffer must
  * already exist (run the sequence once eagerly first).  end returns an executable graph (NULL on
  * failure); launch replays it, ordered with the default stream. */
 /* 1 (default): kernels recorded into a graph are launched as programmatic dependents, so each

@@ -84,6 +84,10 @@ _SIGS = {
     "cuda_gemv_rmsnorm": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_gemv_swiglu": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                 C.c_int]),
+    "cuda_h2d_async": (None, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "cuda_d2h_async": (None, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "cuda_host_alloc": (C.c_void_p, [C.c_size_t]),
+    "cuda_host_free": (None, [C.c_void_p]),
     "cuda_attn_block": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int]),
     "cuda_moe_ffn": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,

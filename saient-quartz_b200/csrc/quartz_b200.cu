@@ -863,6 +863,31 @@ void cuda_sync(void)
     poll_status();
 }
 
+// Asynchronous forms of cuda_h2d / cuda_d2h for page-locked host buffers: enqueued on the library's stream, so
+// they are ordered with the kernels and can be recorded into a graph (quartz_graph_begin/end).  The host must
+// not touch the buffer before a later cuda_sync().
+void cuda_h2d_async(void *dst, const void *src_pinned, size_t bytes)
+{
+    QZ_CUDA_CHECK(cudaMemcpyAsync(dst, src_pinned, bytes, cudaMemcpyHostToDevice, g_stream));
+}
+void cuda_d2h_async(void *dst_pinned, const void *src, size_t bytes)
+{
+    QZ_CUDA_CHECK(cudaMemcpyAsync(dst_pinned, src, bytes, cudaMemcpyDeviceToHost, g_stream));
+}
+void *cuda_host_alloc(size_t bytes)
+{
+    void *p = nullptr;
+    if (cudaMallocHost(&p, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+void cuda_host_free(void *p)
+{
+    if (p) QZ_CUDA_CHECK(cudaFreeHost(p));
+}
+
 void cuda_vec_add(float *dst, const float *src, int n)
 {
     if (n <= 0) return;
