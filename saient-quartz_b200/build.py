@@ -24,11 +24,13 @@ def up_to_date():
 
 
 def build_host(force=False):
-    hdrs = [os.path.join(HERE, "host", "forward_state.h"), os.path.join(HERE, "..", "include", "quartz_b200.h")]
+    hdrs = [os.path.join(HERE, "host", "forward_state.h"), os.path.join(HERE, "host", "gguf_loader.h"),
+            os.path.join(HERE, "..", "include", "quartz_b200.h")]
+    srcs = [HOST_SRC, os.path.join(HERE, "host", "gguf_loader.cpp")]
     if (not force and os.path.exists(HOST_LIB)
-            and all(os.path.getmtime(p) <= os.path.getmtime(HOST_LIB) for p in [HOST_SRC, LIB] + hdrs)):
+            and all(os.path.getmtime(p) <= os.path.getmtime(HOST_LIB) for p in srcs + [LIB] + hdrs)):
         return HOST_LIB
-    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", HOST_LIB, HOST_SRC, "-L" + HERE, "-lquartz_b200",
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", HOST_LIB] + srcs + ["-L" + HERE, "-lquartz_b200",
            "-Wl,-rpath,$ORIGIN"]
     subprocess.check_call(cmd)
     return HOST_LIB
