@@ -367,7 +367,7 @@ def moe_section(q, args, torch, np):
     return out
 
 
-def sharded70b_section(q, L, torch, win, rank, world, dist, steps):
+def sharded70b_section(q, L, torch, win, rank, world, dist, steps, cpu_baseline=False):
     """Llama-3-70B-shaped FFN pair, row-sharded over the ranks: Q4_K 8192->28672 whose complete output
     (gathered in every rank's window by the GEMV's own peer stores) is the activation of Q6_K
     28672->8192.  Batch 1 through cuda_gemv_push, batch 32 through cuda_gemm + cuda_push_rows; the
@@ -383,6 +383,18 @@ def sharded70b_section(q, L, torch, win, rank, world, dist, steps):
     d1 = q.GpuBuf.upload(w1[s0:s1])
     s0, s1 = shard_bytes(14, N1, N2, rank, world)
     d2 = q.GpuBuf.upload(w2[s0:s1])
+    if world == 1 and cpu_baseline:
+        # the CPU path's gemv on the same pair, all host threads (second call of each: warm)
+        import oracle
+        x1 = synth.make_x(K1, tensor_id=302).reshape(-1)
+        oracle.gemv(x1, w1, 12, K1, N1)
+        tc = time.perf_counter()
+        h = oracle.gemv(x1, w1, 12, K1, N1)
+        oracle.gemv(h, w2, 14, N1, N2)
+        tc = time.perf_counter() - tc
+        out["batch1_cpu_oracle"] = {"ms": tc * 1e3, "gbs": (synth.algorithmic_bytes(12, K1, N1) +
+                                                             synth.algorithmic_bytes(14, N1, N2)) / tc / 1e9,
+                                    "cores": oracle.max_threads()}
     del w1, w2
     L.cuda_repack_weights(12, d1.ptr, K1, a1 - a0, 1)
     L.cuda_repack_weights(14, d2.ptr, N1, b1 - b0, 1)
@@ -794,7 +806,7 @@ def main():
 
     sharded = None
     if win is not None and not args.small and not args.no_sharded:
-        sharded = sharded70b_section(q, L, torch, win, rank, world, dist, args.steps)
+        sharded = sharded70b_section(q, L, torch, win, rank, world, dist, args.steps, cpu_baseline=not args.no_cpu_baseline)
 
     # ---- parity spot check of what was just timed (rank 0, smallest shape) + CPU baseline ----
     cpu = None

@@ -57,8 +57,11 @@ struct GemmArgs {
 //      tile, K step) a contiguous [tok_tile rows x 128 B] block, 16-byte chunk c of row r stored at
 //      chunk c ^ (r & 7), k order (0,2,1,3) inside every four.  A stage's activation tile is then
 //      ONE bulk async copy.  One thread per 16-byte chunk. ----
+//      perm = 1 (Q6_K weight tiles): position p of K step (block b, j) holds activation
+//      256 b + 128 (j >> 1) + 32 (p >> 4) + 16 (j & 1) + (p & 15): the K order in which the Q6_K producer
+//      emits weights (all four 32-runs of one 16-wide slice, so that every loaded bit is used). ----
 __global__ void convert_x_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, int M, int K,
-                                      int tok_tile, int n_tok_tiles)
+                                      int tok_tile, int n_tok_tiles, int perm)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int ksteps = K / 64;
@@ -73,7 +76,9 @@ __global__ void convert_x_bf16_kernel(const float *__restrict__ x, __nv_bfloat16
     const int tok = tile * tok_tile + r;
     float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
     if (tok < M) {
-        const float *src = x + (size_t)tok * K + (size_t)ks * 64 + 8 * c;
+        const int p = 8 * c;   // first of this chunk's eight tile positions: they stay contiguous in x
+        const int koff = perm ? 256 * (ks >> 2) + 128 * ((ks >> 1) & 1) + 32 * (p >> 4) + 16 * (ks & 1) + (p & 15) : ks * 64 + p;
+        const float *src = x + (size_t)tok * K + koff;
         v0 = *(const float4 *)src;
         v1 = *(const float4 *)(src + 4);
     }
@@ -253,57 +258,56 @@ struct AProd<T_Q4_K, false> {
     }
 };
 
-// Q6_K, plane layout: K step = (block b, half n, pair hh) = the 32-weight runs k = 2hh, 2hh + 1
+// Q6_K, plane layout (ql[nb x 128] | qh[nb x 64] | scales[nb x 16] | d[nb x 2]): weight 128 n + 32 k + l of
+// a block takes the nibble (k >> 1) of ql[64 n + 32 (k & 1) + l], bits 2k, 2k+1 of qh[32 n + l] and scale
+// 8 n + 2 k + l / 16 (src/dequant.rs:1583-1631).  K step j of a block = half n = j >> 1, slice
+// l in [16 (j & 1), +16), ALL four runs k: 16 + 16 bytes of ql (both nibbles used), 16 bytes of qh (all four
+// bit pairs used), one scale per run.  Tile position p = 16 k + (l & 15); the activation tiles are built
+// in the same order (convert_x_bf16_kernel, perm = 1).
 template <>
 struct AProd<T_Q6_K, true> {
-    struct Raw { uint4 a[4], h0, h1; uint32_t sc, d; };
-    static constexpr bool TWO_SETS = false;
+    struct Raw { uint4 a0, a1, h; uint2 sc; uint32_t d; };
+    static constexpr bool TWO_SETS = true;
     static constexpr int TABLE_BYTES = 0;
     __device__ static void build_table(uint8_t *, int, int) {}
     __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
     {
         if (rowp) {
-            const int b = kstep >> 2, n = (kstep >> 1) & 1, hh = kstep & 1;
-            const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n;
-            const uint8_t *ph = rowp + (size_t)nb * 128 + (size_t)b * 64 + 32 * n;
-#pragma unroll
-            for (int i = 0; i < 4; i++) w.a[i] = __ldg((const uint4 *)(pl + 16 * i));
-            w.h0 = __ldg((const uint4 *)ph);
-            w.h1 = __ldg((const uint4 *)(ph + 16));
-            w.sc = __ldg((const uint32_t *)(rowp + (size_t)nb * 192 + (size_t)b * 16 + 8 * n + 4 * hh));
+            const int b = kstep >> 2, n = (kstep >> 1) & 1, lh = kstep & 1;
+            const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n + 16 * lh;
+            w.a0 = __ldg((const uint4 *)pl);            // runs 0 (low nibbles) and 2 (high nibbles)
+            w.a1 = __ldg((const uint4 *)(pl + 32));     // runs 1 and 3
+            w.h = __ldg((const uint4 *)(rowp + (size_t)nb * 128 + (size_t)b * 64 + 32 * n + 16 * lh));
+            w.sc = __ldg((const uint2 *)(rowp + (size_t)nb * 192 + (size_t)b * 16 + 8 * n));
             w.d = __ldg((const uint16_t *)(rowp + (size_t)nb * 208 + (size_t)b * 2));
         } else {
-#pragma unroll
-            for (int i = 0; i < 4; i++) w.a[i] = make_uint4(0, 0, 0, 0);
-            w.h0 = w.h1 = make_uint4(0, 0, 0, 0);
-            w.sc = w.d = 0;
+            w.a0 = w.a1 = w.h = make_uint4(0, 0, 0, 0);
+            w.sc = make_uint2(0, 0);
+            w.d = 0;
         }
     }
     __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int kstep, int r, const uint8_t *)
     {
-        const uint32_t qh[8] = {w.h0.x, w.h0.y, w.h0.z, w.h0.w, w.h1.x, w.h1.y, w.h1.z, w.h1.w};
-        const int hh = kstep & 1;
+        const uint32_t ql[2][4] = {{w.a0.x, w.a0.y, w.a0.z, w.a0.w}, {w.a1.x, w.a1.y, w.a1.z, w.a1.w}};
+        const uint32_t qh[4] = {w.h.x, w.h.y, w.h.z, w.h.w};
+        const int lh = kstep & 1;
         const float d = h2f((uint16_t)w.d);
         const __nv_bfloat162 bias = __floats2bfloat162_rn(160.f, 160.f);   // the bf16 magic 128 plus Q6_K's own 32
         const __nv_bfloat162 zero = __floats2bfloat162_rn(0.f, 0.f);
+        // scale bytes 2k + lh, k = 0..3, of the half's eight
+        const uint32_t s4 = lh ? __byte_perm(w.sc.x, w.sc.y, 0x7531) : __byte_perm(w.sc.x, w.sc.y, 0x6420);
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const uint32_t ql[8] = {w.a[2 * h].x, w.a[2 * h].y, w.a[2 * h].z, w.a[2 * h].w,
-                                    w.a[2 * h + 1].x, w.a[2 * h + 1].y, w.a[2 * h + 1].z, w.a[2 * h + 1].w};
-            const int k = 2 * hh + h;
-            const float s0 = d * (float)(int8_t)((w.sc >> (16 * h)) & 0xFF), s1 = d * (float)(int8_t)((w.sc >> (16 * h + 8)) & 0xFF);
-            const __nv_bfloat162 sc_lo = __floats2bfloat162_rn(s0, s0), sc_hi = __floats2bfloat162_rn(s1, s1);
+        for (int k = 0; k < 4; k++) {
+            const float sk = d * (float)(int8_t)((s4 >> (8 * k)) & 0xFF);
+            const __nv_bfloat162 sc = __floats2bfloat162_rn(sk, sk);
+            uint32_t o[8];
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t o[4];
-#pragma unroll
-                for (int jj = 0; jj < 2; jj++) {
-                    const int i = 2 * c + jj;   // word i = weights l = 4i .. 4i+3; l < 16 <=> i < 4
-                    const uint32_t v = ((ql[i] >> (4 * hh)) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * k)) & 0x03030303u) << 4);
-                    bytes4_to_bf16(v, bias, i < 4 ? sc_lo : sc_hi, zero, o[2 * jj], o[2 * jj + 1]);
-                }
-                *(uint4 *)(As + sw128(r, 4 * h + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int i = 0; i < 4; i++) {
+                const uint32_t v = ((ql[k & 1][i] >> (4 * (k >> 1))) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * k)) & 0x03030303u) << 4);
+                bytes4_to_bf16(v, bias, sc, zero, o[2 * i], o[2 * i + 1]);
             }
+            *(uint4 *)(As + sw128(r, 2 * k)) = make_uint4(o[0], o[1], o[2], o[3]);
+            *(uint4 *)(As + sw128(r, 2 * k + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
         }
     }
 };

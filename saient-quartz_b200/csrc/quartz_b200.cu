@@ -739,8 +739,10 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y
     }
     a.Xb = g_xb;
     const long long chunks = (long long)need / 8;   // one thread per 16-byte chunk
+    // the Q6_K producer emits each block's weights in its own K order; the activation tiles follow it
+    const int perm = (t == T_Q6_K && planes) ? 1 : 0;
     convert_x_bf16_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, g_stream>>>(x, g_xb, M, K, a.tok_tile,
-                                                                                  a.n_tok_tiles);
+                                                                                  a.n_tok_tiles, perm);
     QZ_LAUNCH_CHECK();
     // 256-row CTA tiles (two accumulators) halve the activation bytes each CTA pulls from L2 per
     // flop; they pay off once the token tile is wide enough for that traffic to matter
