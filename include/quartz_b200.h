@@ -164,6 +164,29 @@ void cuda_attn_decode(float *out, const float *q, const float *k_cache, const fl
                       int n_kv_heads, int seq_len, int head_dim, int kv_dim, float scale, const float *sinks,
                       int out_slot);
 
+/* A chain of dependent GEMVs as ONE persistent kernel (one CTA per SM): op k+1's activation vector is
+ * computed from op k's outputs after a grid-wide barrier inside the kernel, while the weight rows of
+ * op k+1 are already streaming.  In the reference every link is a kernel boundary (src/cuda.rs:548-823:
+ * cuda_gemv, cuda_vec_add, cuda_rms_norm, cuda_swiglu one after the other).  Each op is a cuda_gemv_q-style
+ * multi-matrix GEMV  y_i (+)= W_i * f(a, b)  with f = RMSNorm of a with weights b (src_mode 1, eps 1e-5),
+ * SwiGLU of gate a and up b (src_mode 2; oai = clamped variant) or a itself (src_mode 3).  Takes Q4_K,
+ * Q6_K and Q8_0 matrices that cuda_gemv_q_supported accepts, 2048 <= in_dim <= 16384, up to 8 ops;
+ * anything else runs the same GEMVs one launch at a time (cuda_gemv_chain_supported tells which).
+ * The grid barrier's poll is bounded (~0.5 s, QZ_ERR_TIMEOUT).  First call allocates three control words:
+ * make it outside a graph recording. */
+typedef struct qz_chain_op {
+    uint32_t ggml_type;
+    int n_mats;
+    const uint8_t *const *d_w;
+    float *const *d_y;
+    int in_dim, out_dim, accumulate;
+    int src_mode;
+    const float *d_a, *d_b;
+    int oai;
+} qz_chain_op;
+int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops);
+void cuda_gemv_chain(int n_ops, const qz_chain_op *ops);
+
 /* The whole attention block of one decode step as ONE launch: RoPE on q and k, append of k and v to the
  * caches at `pos`, attention of all heads over cache positions [k_start, pos], merge of the splits
  * (cuda_rope_yarn x2 + cuda_kv_append + cuda_attn_score_all + cuda_softmax_sink_all +

@@ -88,6 +88,8 @@ _SIGS = {
     "cuda_d2h_async": (None, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "cuda_host_alloc": (C.c_void_p, [C.c_size_t]),
     "cuda_host_free": (None, [C.c_void_p]),
+    "cuda_gemv_chain_supported": (C.c_int, [C.c_int, C.c_void_p]),
+    "cuda_gemv_chain": (None, [C.c_int, C.c_void_p]),
     "cuda_attn_block": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int]),
     "cuda_moe_ffn": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
@@ -134,6 +136,24 @@ def lib():
             fn.argtypes = args
         _lib = L
     return _lib
+
+
+class ChainOp(C.Structure):
+    """qz_chain_op of include/quartz_b200.h."""
+    _fields_ = [("ggml_type", C.c_uint32), ("n_mats", C.c_int), ("d_w", C.POINTER(C.c_void_p)),
+                ("d_y", C.POINTER(C.c_void_p)), ("in_dim", C.c_int), ("out_dim", C.c_int), ("accumulate", C.c_int),
+                ("src_mode", C.c_int), ("d_a", C.c_void_p), ("d_b", C.c_void_p), ("oai", C.c_int)]
+
+
+def chain_op(ggml_type, w_ptrs, y_ptrs, in_dim, out_dim, accumulate, src_mode, a_ptr, b_ptr=None, oai=0):
+    """Build one ChainOp; the pointer arrays are kept alive on the returned object."""
+    n = len(w_ptrs)
+    W = (C.c_void_p * n)(*w_ptrs)
+    Y = (C.c_void_p * n)(*y_ptrs)
+    op = ChainOp(ggml_type, n, C.cast(W, C.POINTER(C.c_void_p)), C.cast(Y, C.POINTER(C.c_void_p)), in_dim, out_dim,
+                 1 if accumulate else 0, src_mode, a_ptr, b_ptr, oai)
+    op._keep = (W, Y)
+    return op
 
 
 def declared_symbols():

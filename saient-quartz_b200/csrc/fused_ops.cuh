@@ -228,16 +228,25 @@ __global__ void attn_combine_kernel(float *__restrict__ out, const float *__rest
     }
     tot = block_reduce<false>(tot, sm);   // (its barriers also publish fs)
     const float total = tot + (has_sink ? expf(sink - mx) : 0.f);
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    // sixteen independent loads in flight per thread: the splits' rows sit in L2, this loop is pure latency
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
     int s = 0;
-    for (; s + 4 <= n_splits; s += 4) {
-        a0 = fmaf(fs[s], p[(size_t)s * stride + 2 + i], a0);
-        a1 = fmaf(fs[s + 1], p[(size_t)(s + 1) * stride + 2 + i], a1);
-        a2 = fmaf(fs[s + 2], p[(size_t)(s + 2) * stride + 2 + i], a2);
-        a3 = fmaf(fs[s + 3], p[(size_t)(s + 3) * stride + 2 + i], a3);
+    for (; s + 16 <= n_splits; s += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = p[(size_t)(s + j) * stride + 2 + i];
+#pragma unroll
+        for (int j = 0; j < 16; j++) a[j & 3] = fmaf(fs[s + j], v[j], a[j & 3]);
     }
-    for (; s < n_splits; s++) a0 = fmaf(fs[s], p[(size_t)s * stride + 2 + i], a0);
-    const float acc = (a0 + a1) + (a2 + a3);
+    for (; s + 4 <= n_splits; s += 4) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = p[(size_t)(s + j) * stride + 2 + i];
+#pragma unroll
+        for (int j = 0; j < 4; j++) a[j] = fmaf(fs[s + j], v[j], a[j]);
+    }
+    for (; s < n_splits; s++) a[0] = fmaf(fs[s], p[(size_t)s * stride + 2 + i], a[0]);
+    const float acc = (a[0] + a[1]) + (a[2] + a[3]);
     const float r = acc / total;
     out[(size_t)head * head_dim + i] = r;
     if (emit_q) {

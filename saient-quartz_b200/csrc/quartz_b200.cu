@@ -20,6 +20,7 @@
 #include "fused_ops.cuh"
 #include "gemm_tc.cuh"
 #include "moe.cuh"
+#include "gemv_chain.cuh"
 
 namespace qz {
 
@@ -242,6 +243,7 @@ static int *status_word()
     }
     return g_status;
 }
+static GridBarrier *g_grid_barrier = nullptr;   // count / generation / abort words of the chained-GEMV kernel
 static void poll_status()
 {
     if (!g_status) return;
@@ -249,6 +251,7 @@ static void poll_status()
     if (cudaMemcpy(&h, g_status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && h != 0) {
         set_error(h, "a device-side bounded wait gave up");
         cudaMemset(g_status, 0, sizeof(int));
+        if (g_grid_barrier) cudaMemset(g_grid_barrier, 0, sizeof(GridBarrier));
     }
 }
 
@@ -1185,6 +1188,104 @@ void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w,
 {
     gemv_xsrc(ggml_type, n_mats, d_w, d_y, XSrc{2, d_gate, d_up, oai}, in_dim, out_dim, accumulate,
               "cuda_gemv_swiglu: type/shape/layout has no streaming kernel (ask cuda_gemv_q_supported)");
+}
+
+// ---- a chain of dependent GEMVs as one persistent kernel ----
+static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &smem)
+{
+    if (n_ops < 1 || n_ops > CHAIN_MAX_OPS || !use_tma()) return false;
+    const int grid = sm_count();
+    int slot = 0, x_bytes = 0;
+    for (int k = 0; k < n_ops; k++) {
+        const qz_chain_op &o = ops[k];
+        ChainOp &c = a.op[k];
+        if (o.ggml_type != T_Q4_K && o.ggml_type != T_Q6_K && o.ggml_type != T_Q8_0) return false;
+        if (o.n_mats < 1 || o.n_mats > QZ_MAX_MATS || o.n_mats > grid || o.out_dim <= 0) return false;
+        if (o.src_mode < 1 || o.src_mode > 3 || !o.d_a || (o.src_mode != 3 && !o.d_b)) return false;
+        if (((uintptr_t)o.d_a & 15) || (o.src_mode != 3 && ((uintptr_t)o.d_b & 15))) return false;
+        if (o.in_dim < 2048 || o.in_dim % 64 || o.in_dim / 4 > XSRC_MAX_IT * TMA_CONSUMERS) return false;
+        for (int i = 0; i < o.n_mats; i++)
+            if (!cuda_gemv_q_supported(o.ggml_type, o.d_w[i], o.in_dim)) return false;
+        const FormatInfo fi = format_info(o.ggml_type);
+        const int row_bytes = (o.in_dim / fi.block_elems) * fi.block_bytes;
+        c.type = o.ggml_type;
+        c.n_mats = o.n_mats;
+        c.K = o.in_dim;
+        c.N = o.out_dim;
+        c.accumulate = o.accumulate ? 1 : 0;
+        c.U = o.in_dim / 64;
+        c.Upad = (c.U + 31) & ~31;
+        if (c.Upad > TMA_CONSUMERS) return false;
+        c.RP = TMA_CONSUMERS / c.Upad;
+        const int ntiles = (o.out_dim + c.RP - 1) / c.RP;
+        const int per_mat = grid / o.n_mats;
+        c.n_cta = ntiles < per_mat ? ntiles : per_mat;
+        c.xsrc = XSrc{o.src_mode, o.d_a, o.src_mode == 3 ? o.d_a : o.d_b, o.oai};
+        for (int i = 0; i < QZ_MAX_MATS; i++) {
+            c.W[i] = o.d_w[i < o.n_mats ? i : 0];
+            c.y[i] = o.d_y[i < o.n_mats ? i : 0];
+        }
+        const int stage = c.RP * row_bytes;
+        if (stage > slot) slot = stage;
+        const int xb = (int)((2 * (size_t)o.in_dim + o.in_dim / 8 + o.in_dim / 4 + 31) & ~(size_t)15);
+        if (xb > x_bytes) x_bytes = xb;
+    }
+    slot = (slot + 127) & ~127;
+    const int budget = 222 * 1024 - x_bytes;
+    int n_slots = budget / slot;
+    if (n_slots > TMA_MAX_STAGES) n_slots = TMA_MAX_STAGES;
+    if (n_slots < 3) return false;
+    a.n_ops = n_ops;
+    a.slot_bytes = slot;
+    a.n_slots = n_slots;
+    smem = (size_t)n_slots * slot + x_bytes;
+    return true;
+}
+
+int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops)
+{
+    ChainArgs a;
+    size_t smem;
+    return ops && chain_plan(n_ops, ops, a, smem) ? 1 : 0;
+}
+
+void cuda_gemv_chain(int n_ops, const qz_chain_op *ops)
+{
+    if (n_ops <= 0 || !ops) return;
+    static ChainArgs a;   // (large: kept off the stack)
+    size_t smem = 0;
+    if (!chain_plan(n_ops, ops, a, smem)) {
+        // not a chain the persistent kernel takes: the same GEMVs one launch at a time
+        for (int k = 0; k < n_ops; k++) {
+            const qz_chain_op &o = ops[k];
+            if (o.src_mode == 1) cuda_gemv_rmsnorm(o.ggml_type, o.n_mats, o.d_w, o.d_y, o.d_a, o.d_b, o.in_dim, o.out_dim, o.accumulate);
+            else if (o.src_mode == 2) cuda_gemv_swiglu(o.ggml_type, o.n_mats, o.d_w, o.d_y, o.d_a, o.d_b, o.oai, o.in_dim, o.out_dim, o.accumulate);
+            else {
+                int slots[QZ_MAX_MATS] = {3, 3, 3, 3, 3, 3, 3, 3};
+                cuda_quantize_x(o.d_a, o.in_dim, 3);
+                cuda_gemv_q(o.ggml_type, o.n_mats, o.d_w, slots, o.d_y, o.in_dim, o.out_dim, o.accumulate);
+            }
+        }
+        return;
+    }
+    if (!g_grid_barrier) {
+        if (cudaMalloc(&g_grid_barrier, sizeof(GridBarrier)) != cudaSuccess) {
+            cudaGetLastError();
+            g_grid_barrier = nullptr;
+            set_error(QZ_ERR_CUDA, "cudaMalloc of the grid barrier failed");
+            return;
+        }
+        cudaMemset(g_grid_barrier, 0, sizeof(GridBarrier));
+    }
+    a.gb = g_grid_barrier;
+    a.status = status_word();
+    if (!a.status) return;
+    static bool attr_set = false;
+    if (!attr_set) {
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        attr_set = true;
+    }
+    launch(gemv_chain_kernel, dim3(sm_count()), dim3(TMA_CONSUMERS + 32), smem, a);
 }
 
 void cuda_rope_kv(float *q, float *k, const float *v, float *k_cache, float *v_cache, int n_heads, int n_kv_heads,

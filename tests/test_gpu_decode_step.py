@@ -208,6 +208,61 @@ def test_gemv_with_fused_norm_and_swiglu(gpu, t, K, N):
     gpu.check_error()
 
 
+@pytest.mark.parametrize("d,fd", [(4096, 14336), (2048, 4096)])
+def test_gemv_chain_matches_separate_launches(gpu, d, fd):
+    """cuda_gemv_chain (o-projection -> gate/up -> down -> next q/k/v in one persistent kernel, grid-wide
+    barriers between the links) against the same four GEMVs as separate launches.  Run three times: the
+    barrier words must reset themselves."""
+    import ctypes as C
+    from saient_quartz_b200 import synth
+    L = gpu.lib()
+    kvd = d // 4
+
+    def mat(t, K, N, tid):
+        b = gpu.GpuBuf.upload(synth.make_weights(t, K, N, tensor_id=tid))
+        L.cuda_repack_weights(t, b.ptr, K, N, 1)
+        return b
+    wo, wg, wu, wd = mat(12, d, d, 621), mat(12, d, fd, 622), mat(12, d, fd, 623), mat(14, fd, d, 624)
+    wq, wk = mat(12, d, kvd, 625), mat(12, d, kvd, 626)
+    attn = synth.make_x(d, tensor_id=631)
+    hid0 = synth.make_x(d, tensor_id=632)
+    n1 = (1.0 + 0.1 * synth.make_x(d, tensor_id=633)).astype(np.float32)
+    n2 = (1.0 + 0.1 * synth.make_x(d, tensor_id=634)).astype(np.float32)
+    d_attn, d_n1, d_n2 = gpu.GpuBuf.upload(attn), gpu.GpuBuf.upload(n1), gpu.GpuBuf.upload(n2)
+
+    def run(chain):
+        hid = gpu.GpuBuf.upload(hid0)
+        g, u = gpu.GpuBuf.alloc_f32(fd), gpu.GpuBuf.alloc_f32(fd)
+        qo, ko = gpu.GpuBuf.alloc_f32(kvd), gpu.GpuBuf.alloc_f32(kvd)
+        ops = [gpu.chain_op(12, [wo.ptr], [hid.ptr], d, d, 1, 3, d_attn.ptr),
+               gpu.chain_op(12, [wg.ptr, wu.ptr], [g.ptr, u.ptr], d, fd, 0, 1, hid.ptr, d_n1.ptr),
+               gpu.chain_op(14, [wd.ptr], [hid.ptr], fd, d, 1, 2, g.ptr, u.ptr),
+               gpu.chain_op(12, [wq.ptr, wk.ptr], [qo.ptr, ko.ptr], d, kvd, 0, 1, hid.ptr, d_n2.ptr)]
+        arr = (gpu.ChainOp * 4)(*ops)
+        if chain:
+            assert L.cuda_gemv_chain_supported(4, arr) == 1
+            L.cuda_gemv_chain(4, arr)
+        else:
+            for op in ops:
+                one = (gpu.ChainOp * 1)(op)
+                if op.src_mode == 1:
+                    L.cuda_gemv_rmsnorm(op.ggml_type, op.n_mats, op.d_w, op.d_y, op.d_a, op.d_b, op.in_dim, op.out_dim, op.accumulate)
+                elif op.src_mode == 2:
+                    L.cuda_gemv_swiglu(op.ggml_type, op.n_mats, op.d_w, op.d_y, op.d_a, op.d_b, 0, op.in_dim, op.out_dim, op.accumulate)
+                else:
+                    S = (C.c_int * 1)(2)
+                    L.cuda_quantize_x(op.d_a, op.in_dim, 2)
+                    L.cuda_gemv_q(op.ggml_type, 1, op.d_w, S, op.d_y, op.in_dim, op.out_dim, op.accumulate)
+        L.cuda_sync()
+        gpu.check_error("chain" if chain else "separate")
+        return [b.download() for b in (hid, g, u, qo, ko)]
+    want = run(False)
+    for rep in range(3):
+        got = run(True)
+        for name, a, b in zip(("hidden", "gate", "up", "q", "k"), want, got):
+            assert np.abs(a - b).max() <= 5e-5 * max(np.abs(a).max(), 1e-30), (name, rep)
+
+
 def test_attn_decode_matches_three_kernel_attention(gpu):
     L = gpu.lib()
     r = np.random.Generator(np.random.PCG64([0xA77]))
