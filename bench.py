@@ -270,7 +270,7 @@ def decode_section(q, args, torch, np, want_parity, fused_only=False):
     out = {"model": "llama-3-8b architecture, random init, Q4_K_M-style layout", "context": 1024,
            "bytes_per_token": bytes_per_token, "build_s": round(build_s, 1)}
     peak, _ = peaks()
-    for name, fused in (("fused_graph", True), ("reference_sequence", False)):
+    for name, fused in (("chained_graph", 2), ("fused_graph", 1), ("reference_sequence", 0)):
         if fused_only and not fused:
             continue
         for _ in range(3):
@@ -294,9 +294,11 @@ def decode_section(q, args, torch, np, want_parity, fused_only=False):
     # end to end as the host sees it: token in, 513 KB of logits out, per step
     n = 5
     t1 = time.perf_counter()
+    best = 2 if out["chained_graph"]["ms_per_token"] <= out["fused_graph"]["ms_per_token"] else 1
     for _ in range(n):
-        logits = m.step(token, pos, fused=True)
+        logits = m.step(token, pos, fused=best)
     out["e2e_tok_s"] = n / (time.perf_counter() - t1)
+    out["e2e_sequence"] = "chained" if best == 2 else "fused"
     if want_parity:
         import oracle
         from oracle.forward_ref import RefModel

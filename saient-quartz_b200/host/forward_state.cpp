@@ -452,6 +452,87 @@ static void step_fused(qh_model *m, int token, int pos, bool need_logits)
     cuda_gemv_rmsnorm(m->lm_head.ggml_type, 1, w1, y1, m->d_hidden.f(), m->final_norm.f(), d, c.vocab_size, 0);
 }
 
+// The chained sequence: per layer RoPE + KV append, attention (two kernels) and ONE persistent kernel that
+// runs output projection -> gate/up -> down -> the next layer's q/k/v (or the output head) with grid-wide
+// barriers between the links: four launches per layer.
+static bool chainable(qh_model *m)
+{
+    const qh_config &c = m->c;
+    const int d = c.embed_dim, kv_d = m->kv_d(), q_d = m->q_d(), fd = c.ffn_dim;
+    if (q_d % kv_d != 0 || q_d / kv_d + 2 > 8) return false;
+    Layer &L = m->L[0];
+    const uint8_t *w1[1] = {L.o.u8()};
+    const uint8_t *w2[2] = {L.gate.u8(), L.up.u8()};
+    const uint8_t *w3[1] = {L.down.u8()};
+    const uint8_t *w4[1] = {m->lm_head.u8()};
+    float *y1[1] = {m->d_hidden.f()};
+    float *y2[2] = {m->d_gate.f(), m->d_up.f()};
+    float *y4[1] = {m->d_logits.f()};
+    qz_chain_op ops[4] = {
+        {L.o.ggml_type, 1, w1, y1, q_d, d, 1, 3, m->d_attn_out.f(), nullptr, 0},
+        {L.gate.ggml_type, 2, w2, y2, d, fd, 0, 1, m->d_hidden.f(), L.ffn_norm.f(), 0},
+        {L.down.ggml_type, 1, w3, y1, fd, d, 1, 2, m->d_gate.f(), m->d_up.f(), 0},
+        {m->lm_head.ggml_type, 1, w4, y4, d, c.vocab_size, 0, 1, m->d_hidden.f(), m->final_norm.f(), 0}};
+    return cuda_gemv_chain_supported(4, ops) != 0;
+}
+
+static void step_chained(qh_model *m, int token, int pos, bool need_logits)
+{
+    const qh_config &c = m->c;
+    const int d = c.embed_dim, h = c.n_heads, kv = c.n_kv_heads, hd = c.head_dim, q_d = m->q_d(), kv_d = m->kv_d(),
+              fd = c.ffn_dim, seq = pos + 1;
+    const float scale = attn_scale(c);
+    const int q_slices = q_d / kv_d;
+    const size_t q_slice_bytes = ggml_type_size(m->L[0].q.ggml_type, (size_t)d * kv_d);
+    cuda_embed_lookup(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, token, d);
+    auto qkv = [&](Layer &L, const uint8_t **W, float **Y) {
+        int n = 0;
+        for (int s = 0; s < q_slices; s++) { W[n] = L.q.u8() + s * q_slice_bytes; Y[n] = m->d_q.f() + (size_t)s * kv_d; n++; }
+        W[n] = L.k.u8(); Y[n] = m->d_k.f(); n++;
+        W[n] = L.v.u8(); Y[n] = m->d_v.f(); n++;
+        return n;
+    };
+    {
+        const uint8_t *W[8];
+        float *Y[8];
+        const int n = qkv(m->L[0], W, Y);
+        cuda_gemv_rmsnorm(m->L[0].q.ggml_type, n, W, Y, m->d_hidden.f(), m->L[0].attn_norm.f(), d, kv_d, 0);
+    }
+    for (int l = 0; l < c.n_layers; l++) {
+        Layer &L = m->L[l];
+        cuda_rope_kv(m->d_q.f(), m->d_k.f(), m->d_v.f(), m->kv_k[l].f(), m->kv_v[l].f(), h, kv, hd, pos, c.rope_theta,
+                     c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
+        const int k_start = attn_start(c, l, pos), seq_a = seq - k_start;
+        cuda_attn_decode(m->d_attn_out.f(), m->d_q.f(), m->kv_k[l].f() + (size_t)k_start * kv_d,
+                         m->kv_v[l].f() + (size_t)k_start * kv_d, h, kv, seq_a, hd, kv_d, scale, L.sinks.f(), -1);
+        const uint8_t *w1[1] = {L.o.u8()};
+        const uint8_t *w2[2] = {L.gate.u8(), L.up.u8()};
+        const uint8_t *w3[1] = {L.down.u8()};
+        float *y1[1] = {m->d_hidden.f()};
+        float *y2[2] = {m->d_gate.f(), m->d_up.f()};
+        const uint8_t *W4[8];
+        float *Y4[8];
+        qz_chain_op ops[4] = {
+            {L.o.ggml_type, 1, w1, y1, q_d, d, 1, 3, m->d_attn_out.f(), nullptr, 0},
+            {L.gate.ggml_type, 2, w2, y2, d, fd, 0, 1, m->d_hidden.f(), L.ffn_norm.f(), 0},
+            {L.down.ggml_type, 1, w3, y1, fd, d, 1, 2, m->d_gate.f(), m->d_up.f(), 0},
+            {}};
+        int n_ops = 3;
+        if (l + 1 < c.n_layers) {
+            Layer &Nx = m->L[l + 1];
+            const int n = qkv(Nx, W4, Y4);
+            ops[3] = {Nx.q.ggml_type, n, W4, Y4, d, kv_d, 0, 1, m->d_hidden.f(), Nx.attn_norm.f(), 0};
+            n_ops = 4;
+        } else if (need_logits) {
+            W4[0] = m->lm_head.u8();
+            Y4[0] = m->d_logits.f();
+            ops[3] = {m->lm_head.ggml_type, 1, W4, Y4, d, c.vocab_size, 0, 1, m->d_hidden.f(), m->final_norm.f(), 0};
+            n_ops = 4;
+        }
+        cuda_gemv_chain(n_ops, ops);
+    }
+}
+
 int qh_step_device(qh_model *m, int token, int pos, int fused)
 {
     if (!m || !m->finalized || token < 0 || token >= m->c.vocab_size) return -1;
@@ -465,15 +546,18 @@ int qh_step_device(qh_model *m, int token, int pos, int fused)
         m->last_launches = quartz_launch_count() - before;
         return 0;
     }
-    // one recorded graph per (token-independent) position; the embedding row is looked up outside
-    auto key = std::make_pair(pos, token);
+    // fused == 2 asks for the chained sequence (falls back to the fused one where the chain kernel does not apply)
+    const bool chain = fused == 2 && chainable(m);
+    auto step = [&](qh_model *mm, int tk, int ps, bool nl) { chain ? step_chained(mm, tk, ps, nl) : step_fused(mm, tk, ps, nl); };
+    // one recorded graph per (position, token, sequence kind)
+    auto key = std::make_pair(pos, 2 * token + (chain ? 1 : 0));
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
-        step_fused(m, token, pos, true);   // eager once: creates every scratch buffer, warms the kernels
+        step(m, token, pos, true);   // eager once: creates every scratch buffer, warms the kernels
         cuda_sync();
         const long long b2 = quartz_launch_count();
         if (!quartz_graph_begin()) return -2;
-        step_fused(m, token, pos, true);
+        step(m, token, pos, true);
         void *g = quartz_graph_end();
         if (!g) return -3;
         m->last_launches = quartz_launch_count() - b2;
@@ -504,6 +588,11 @@ int qh_forward_step(qh_model *m, int token, int pos, int need_logits, float *log
 int qh_forward_step_fused(qh_model *m, int token, int pos, int need_logits, float *logits_host)
 {
     return step_host(m, token, pos, need_logits, logits_host, 1);
+}
+
+int qh_forward_step_chained(qh_model *m, int token, int pos, int need_logits, float *logits_host)
+{
+    return step_host(m, token, pos, need_logits, logits_host, 2);
 }
 
 int qh_read_hidden(qh_model *m, float *host)

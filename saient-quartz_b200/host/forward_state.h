@@ -53,7 +53,10 @@ int qh_set_kv(qh_model *m, int layer, const float *k, const float *v, int n_pos)
 /* returns 0 on success; logits_host (vocab floats) filled when need_logits */
 int qh_forward_step(qh_model *m, int token, int pos, int need_logits, float *logits_host);
 int qh_forward_step_fused(qh_model *m, int token, int pos, int need_logits, float *logits_host);
-/* device-only variants for timing: no copies, the result stays in the device logits buffer */
+/* as fused, with output projection -> gate/up -> down -> next q/k/v of every layer as one persistent kernel */
+int qh_forward_step_chained(qh_model *m, int token, int pos, int need_logits, float *logits_host);
+/* device-only variants for timing: no copies, the result stays in the device logits buffer; fused: 0 reference
+ * sequence, 1 fused, 2 chained */
 int qh_step_device(qh_model *m, int token, int pos, int fused);
 int qh_read_hidden(qh_model *m, float *host);   /* d_hidden, for layer-level tests */
 long long qh_launches_last_step(qh_model *m);    /* kernel launches issued by the last step (graph nodes if fused) */

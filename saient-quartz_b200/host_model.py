@@ -42,6 +42,7 @@ def host_lib():
         H.qh_set_kv.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
         H.qh_forward_step.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         H.qh_forward_step_fused.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        H.qh_forward_step_chained.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         H.qh_step_device.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
         H.qh_read_hidden.argtypes = [C.c_void_p, C.c_void_p]
         H.qh_launches_last_step.restype = C.c_longlong
@@ -134,7 +135,7 @@ class HostModel:
 
     def step(self, token, pos, fused=False):
         logits = np.empty(self.cfg["vocab_size"], dtype=np.float32)
-        fn = self.H.qh_forward_step_fused if fused else self.H.qh_forward_step
+        fn = (self.H.qh_forward_step_chained if fused == 2 else self.H.qh_forward_step_fused) if fused else self.H.qh_forward_step
         rc = fn(self.m, token, pos, 1, logits.ctypes.data)
         if rc != 0:
             from . import lib

@@ -51,6 +51,12 @@ def test_tiny_dense_model_both_sequences(gpu, oracle_mod, repack):
     # the recorded graph replays to the same numbers
     again = m.step(17, 40, fused=True)
     assert np.array_equal(again, got_f)
+    # the chained sequence (one persistent kernel per layer for the four dependent GEMVs)
+    got_c = m.step(17, 40, fused=2)
+    assert _rel(got_c, want) < 5e-3 and _rel(got_c, got_f) < 1e-3
+    if repack:
+        assert m.launches() < 5 * 3 + 4       # four launches per layer + embedding + first q/k/v
+    assert np.array_equal(m.step(17, 40, fused=2), got_c)
     gpu.check_error()
 
 
