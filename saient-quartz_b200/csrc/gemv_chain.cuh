@@ -273,9 +273,9 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
                         v[i] = xx[i];
                     } else if (op.xsrc.oai) {
                         const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
-                        v[i] = (g / (1.f + expf(-1.702f * g))) * (up + 1.f);
+                        v[i] = __fdividef(g, 1.f + __expf(-1.702f * g)) * (up + 1.f);
                     } else {
-                        v[i] = (xx[i] / (1.f + expf(-xx[i]))) * yy[i];
+                        v[i] = __fdividef(xx[i], 1.f + __expf(-xx[i])) * yy[i];   // fast exp / divide: this runs redundantly in every CTA
                     }
                 }
                 quantize4_store(v, t, valid, o);

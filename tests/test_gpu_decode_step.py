@@ -179,8 +179,8 @@ def test_fused_entry_points_match_unfused(gpu):
 @pytest.mark.parametrize("t,K,N", [(12, 4096, 1024), (14, 14336, 512), (8, 2048, 300), (12, 512, 256)])
 def test_gemv_with_fused_norm_and_swiglu(gpu, t, K, N):
     """cuda_gemv_rmsnorm / cuda_gemv_swiglu (activation computed in the GEMV's prologue) against the
-    two-launch forms cuda_rms_norm_q / cuda_swiglu_q + cuda_gemv_q.  SwiGLU converts element by element,
-    so results are identical; the norm's sum of squares is reduced in another order (1e-5 relative)."""
+    two-launch forms cuda_rms_norm_q / cuda_swiglu_q + cuda_gemv_q.  The norm's sum of squares is reduced in
+    another order and the prologue's SwiGLU uses the fast exponential and divide (2e-5 relative)."""
     import ctypes as C
     from saient_quartz_b200 import synth
     L = gpu.lib()
@@ -210,7 +210,8 @@ def test_gemv_with_fused_norm_and_swiglu(gpu, t, K, N):
         L.cuda_swiglu_q(dg.ptr, dx.ptr, K, 1, 0)
         L.cuda_gemv_q(t, 2, W, S, Y, K, N, acc)
         L.cuda_gemv_swiglu(t, 2, W, Y2, dg.ptr, dx.ptr, 0, K, N, acc)
-        assert np.array_equal(dy.download(), dy2.download()), ("swiglu", acc)
+        a, b = dy.download(), dy2.download()
+        assert np.abs(a - b).max() <= 2e-5 * np.abs(a).max(), ("swiglu", acc)
     gpu.check_error()
 
 
