@@ -186,6 +186,10 @@ typedef struct qz_chain_op {
 } qz_chain_op;
 int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops);
 void cuda_gemv_chain(int n_ops, const qz_chain_op *ops);
+/* The same kernel for GEMVs that do NOT depend on one another (no op reads what another writes): no
+ * barrier between them, the weight stream runs through all of them without a break.  The
+ * generalisation of cuda_gemv_moe4 (src/cuda.rs:39-45) to matrices of different shapes and types. */
+void cuda_gemv_batch(int n_ops, const qz_chain_op *ops);
 
 /* The whole attention block of one decode step as ONE launch: RoPE on q and k, append of k and v to the
  * caches at `pos`, attention of all heads over cache positions [k_start, pos], merge of the splits

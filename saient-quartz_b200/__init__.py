@@ -90,6 +90,7 @@ _SIGS = {
     "cuda_host_free": (None, [C.c_void_p]),
     "cuda_gemv_chain_supported": (C.c_int, [C.c_int, C.c_void_p]),
     "cuda_gemv_chain": (None, [C.c_int, C.c_void_p]),
+    "cuda_gemv_batch": (None, [C.c_int, C.c_void_p]),
     "cuda_attn_block": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int]),
     "cuda_moe_ffn": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,

@@ -41,6 +41,7 @@ struct GridBarrier {
 struct ChainArgs {
     ChainOp op[CHAIN_MAX_OPS];
     int n_ops;
+    int independent;           // 1: no op reads another op's output: no grid barrier between them
     int slot_bytes, n_slots;   // ring geometry: every op's stage fits a slot
     GridBarrier *gb;
     int *status;
@@ -219,7 +220,9 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     bool ok = true;
     for (int k = 0; k < a.n_ops; k++) {
         const ChainOp &op = a.op[k];
-        if (k > 0) {
+        if (k > 0 && a.independent) {
+            named_bar_sync(13, TMA_CONSUMERS);   // every warp has taken its activation registers: the area is free
+        } else if (k > 0) {
             // ---- grid-wide barrier: op k-1's outputs are complete and visible ----
             named_bar_sync(13, TMA_CONSUMERS);
             if (threadIdx.x == 0) cta_ok = (ok && grid_barrier(a.gb, gridDim.x, a.status)) ? 1 : 0;

@@ -1249,7 +1249,12 @@ int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops)
     return ops && chain_plan(n_ops, ops, a, smem) ? 1 : 0;
 }
 
-void cuda_gemv_chain(int n_ops, const qz_chain_op *ops)
+static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent);
+
+void cuda_gemv_chain(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 0); }
+void cuda_gemv_batch(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 1); }
+
+static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent)
 {
     if (n_ops <= 0 || !ops) return;
     static ChainArgs a;   // (large: kept off the stack)
@@ -1278,6 +1283,7 @@ void cuda_gemv_chain(int n_ops, const qz_chain_op *ops)
         cudaMemset(g_grid_barrier, 0, sizeof(GridBarrier));
     }
     a.gb = g_grid_barrier;
+    a.independent = independent;
     a.status = status_word();
     if (!a.status) return;
     static bool attr_set = false;
