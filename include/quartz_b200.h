@@ -191,7 +191,8 @@ void cuda_gemv_chain(int n_ops, const qz_chain_op *ops);
  * generalisation of cuda_gemv_moe4 (src/cuda.rs:39-45) to matrices of different shapes and types. */
 void cuda_gemv_batch(int n_ops, const qz_chain_op *ops);
 
-/* The whole attention block of one decode step as ONE launch: RoPE on q and k, append of k and v to the
+/* The whole attention block of one decode step as ONE launch (two when the context spans more than 8
+ * splits of 32 positions: the merge then gets a launch of its own): RoPE on q and k, append of k and v to the
  * caches at `pos`, attention of all heads over cache positions [k_start, pos], merge of the splits
  * (cuda_rope_yarn x2 + cuda_kv_append + cuda_attn_score_all + cuda_softmax_sink_all +
  * cuda_attn_values_all, src/cuda.rs:601-645).  q [n_heads*head_dim], k_new / v_new

@@ -311,7 +311,8 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(float *__restrict__ out
                                                          float *k_cache, float *v_cache, int n_heads, int n_kv_heads,
                                                          int k_start, int head_dim, int kv_dim, float scale,
                                                          const float *__restrict__ sinks, RopeArgs rope,
-                                                         const float2 *__restrict__ rope_tab, XQOut o, int emit_q)
+                                                         const float2 *__restrict__ rope_tab, XQOut o, int emit_q,
+                                                         int do_merge)
 {
     __shared__ float ks[ATT_CHUNK][ATT_MAX_HD + 1];
     __shared__ float vs[ATT_CHUNK][ATT_MAX_HD];
@@ -429,6 +430,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(float *__restrict__ out
         }
         __syncwarp();
     }
+    if (!do_merge) return;   // the splits are merged by attn_combine_kernel (many splits: more CTAs for the merge)
     // ---- the last CTA of this kv head merges the head group's splits ----
     __threadfence();
     __syncthreads();

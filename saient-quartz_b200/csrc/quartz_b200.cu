@@ -1386,9 +1386,14 @@ void cuda_attn_block(float *out, const float *q, const float *k_new, const float
         g_rope_key_hd = head_dim;
         g_rope_tab_valid = true;
     }
+    // few splits: the last CTA of each kv head merges them in the same launch; many: a second, wider launch
+    const int do_merge = n_splits <= 8 ? 1 : 0;
     launch(attn_fused_kernel, dim3(n_kv_heads, n_splits), dim3(128), 0, out, g_attn_part + 64, (int *)g_attn_part, q, k_new,
            v_new, k_cache, v_cache, n_heads, n_kv_heads, k_start, head_dim, n_kv_heads * head_dim, scale, sinks, r,
-           (const float2 *)g_rope_tab, o, out_slot >= 0 ? 1 : 0);
+           (const float2 *)g_rope_tab, o, out_slot >= 0 ? 1 : 0, do_merge);
+    if (!do_merge)
+        launch(attn_combine_kernel, dim3(n_heads), dim3(head_dim), (size_t)n_splits * sizeof(float), out,
+               (const float *)(g_attn_part + 64), n_splits, head_dim, sinks, o, out_slot >= 0 ? 1 : 0);
 }
 
 // ---- CUDA-graph helpers: record a sequence of this library's calls once, replay it per token ----

@@ -422,8 +422,8 @@ static void step_fused(qh_model *m, int token, int pos, bool need_logits)
         W[n] = L.v.u8(); Y[n] = m->d_v.f(); n++;
         cuda_gemv_rmsnorm(L.q.ggml_type, n, W, Y, m->d_hidden.f(), L.attn_norm.f(), d, kv_d, 0);
         // RoPE + KV append, then split-KV attention and its merge: three launches.  (cuda_attn_block does the
-        // same in one launch; at a context of 1024 its single-CTA-per-kv-head merge makes it the slower choice
-        // inside a replayed graph, 22 us against 19 us.)
+        // same in one or two launches; inside a replayed graph at a context of 1024 it is the slower choice,
+        // 2.15 against 2.06 ms per token: every attention CTA then rotates its own queries.)
         cuda_rope_kv(m->d_q.f(), m->d_k.f(), m->d_v.f(), m->kv_k[l].f(), m->kv_v[l].f(), h, kv, hd, pos, c.rope_theta,
                      c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
         const int k_start = attn_start(c, l, pos), seq_a = seq - k_start;
