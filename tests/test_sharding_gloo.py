@@ -62,3 +62,72 @@ def test_two_gloo_ranks_shard_and_gather(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
                        env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+WINDOW_WORKER = textwrap.dedent("""
+    import ctypes as C, os, sys
+    sys.path.insert(0, {root!r})
+    import numpy as np, torch, torch.distributed as dist
+    import __graft_entry__ as entry
+    entry.load_package()
+    from saient_quartz_b200.shard import PeerWindow, shard_rows
+
+    class FakeLib:
+        '''Stands in for the CUDA library: a "window" is a host array, a "handle" names its owner, and the
+        exchange itself is carried by gloo, so the host-side protocol (init, handle exchange in rank order,
+        attach, push offsets, one wait per exchange) runs without a GPU.'''
+        def __init__(self, rank, world):
+            self.rank, self.world, self.calls = rank, world, []
+            self.window = None
+        def quartz_mgpu_handle_bytes(self):
+            return 64
+        def quartz_mgpu_init(self, rank, world, data_bytes, buf):
+            self.window = np.zeros(data_bytes // 4, dtype=np.float32)
+            C.memmove(buf, (b"rank%02d" % rank).ljust(64, b"."), 64)
+            return 0
+        def quartz_mgpu_attach(self, handles):
+            self.handles = bytes(handles)
+            return 0 if len(self.handles) == 64 * self.world else -1
+        def quartz_mgpu_data(self):
+            return 1234
+        def cuda_gemv_push(self, t, w, x, dst_off, in_dim, rows):
+            self.calls.append(("push", dst_off, rows))
+        def quartz_mgpu_wait(self):
+            self.calls.append(("wait",))
+        def quartz_mgpu_fuse_next_wait(self):
+            self.calls.append(("fuse",))
+        def quartz_mgpu_shutdown(self):
+            self.calls.append(("shutdown",))
+
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    lib = FakeLib(rank, world)
+    win = PeerWindow(lib, rank, world, 4096, dist)
+    ok = win.data_ptr == 1234
+    # every rank received all handles, in rank order
+    ok &= [lib.handles[64 * r:64 * r + 6] for r in range(world)] == [b"rank%02d" % r for r in range(world)]
+    N = 1000
+    n0, n1, per = shard_rows(N, rank, world)
+    win.gemv_push(12, 0, 0, 100 + n0, 4096, n1 - n0)
+    win.wait(fused=True)
+    win.gemv_push(14, 0, 0, 2000 + n0, 4096, n1 - n0)
+    win.wait()
+    win.close()
+    ok &= lib.calls == [("push", 100 + n0, n1 - n0), ("fuse",), ("push", 2000 + n0, n1 - n0), ("wait",), ("shutdown",)]
+    flag = torch.tensor([1 if ok else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+""")
+
+
+def test_two_gloo_ranks_window_protocol(tmp_path):
+    """PeerWindow's host side (handle exchange in rank order, attach, push offsets, waits) over gloo with a
+    stand-in for the CUDA library."""
+    script = tmp_path / "window_worker.py"
+    script.write_text(WINDOW_WORKER.format(root=ROOT))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
