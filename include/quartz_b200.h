@@ -243,6 +243,11 @@ void quartz_graph_destroy(void *graph_exec);
  * gemm() (src/dequant.rs:143-200).  The reference has no GPU counterpart. */
 void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, float *d_y, int m, int in_dim,
                int out_dim);
+/* The same with bf16 activations (raw 16-bit patterns, [m, in_dim]); in_dim a multiple of 64, pointers
+ * 16-byte aligned.  Equal to cuda_gemm on the same values widened to f32 (up to the summation order of
+ * output tiles that two CTAs share). */
+void cuda_gemm_bf16(uint32_t ggml_type, const uint8_t *d_data, const uint16_t *d_x_bf16, float *d_y, int m, int in_dim,
+                    int out_dim);
 
 /* Batched mixture-of-experts FFN for m tokens:
  *   out[t] = sum over the top_k experts e of token t of  w(t,e) * down_e( swiglu(gate_e x_t, up_e x_t) )

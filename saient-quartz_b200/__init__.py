@@ -81,6 +81,7 @@ _SIGS = {
     "quartz_graph_destroy": (None, [C.c_void_p]),
     "cuda_gemv_noalloc": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "cuda_gemm": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "cuda_gemm_bf16": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_gemv_rmsnorm": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_gemv_swiglu": (None, [C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                 C.c_int]),

@@ -60,7 +60,8 @@ struct GemmArgs {
 //      perm = 1 (Q6_K weight tiles): position p of K step (block b, j) holds activation
 //      256 b + 128 (j >> 1) + 32 (p >> 4) + 16 (j & 1) + (p & 15): the K order in which the Q6_K producer
 //      emits weights (all four 32-runs of one 16-wide slice, so that every loaded bit is used). ----
-__global__ void convert_x_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, int M, int K,
+template <bool IN_BF16>
+__global__ void convert_x_bf16_kernel(const void *__restrict__ xin, __nv_bfloat16 *__restrict__ out, int M, int K,
                                       int tok_tile, int n_tok_tiles, int perm)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -74,17 +75,23 @@ __global__ void convert_x_bf16_kernel(const float *__restrict__ x, __nv_bfloat16
     const int ks = (int)(rest % ksteps);
     const int tile = (int)(rest / ksteps);
     const int tok = tile * tok_tile + r;
-    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+    uint4 o = make_uint4(0, 0, 0, 0);
     if (tok < M) {
         const int p = 8 * c;   // first of this chunk's eight tile positions: they stay contiguous in x
         const int koff = perm ? 256 * (ks >> 2) + 128 * ((ks >> 1) & 1) + 32 * (p >> 4) + 16 * (ks & 1) + (p & 15) : ks * 64 + p;
-        const float *src = x + (size_t)tok * K + koff;
-        v0 = *(const float4 *)src;
-        v1 = *(const float4 *)(src + 4);
+        if (IN_BF16) {
+            // eight bf16 values e0..e7 -> words (e0,e2) (e1,e3) (e4,e6) (e5,e7)
+            const uint4 v = *(const uint4 *)((const uint16_t *)xin + (size_t)tok * K + koff);
+            o = make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632), __byte_perm(v.z, v.w, 0x5410),
+                           __byte_perm(v.z, v.w, 0x7632));
+        } else {
+            const float *src = (const float *)xin + (size_t)tok * K + koff;
+            const float4 v0 = *(const float4 *)src, v1 = *(const float4 *)(src + 4);
+            __nv_bfloat162 a = __floats2bfloat162_rn(v0.x, v0.z), b = __floats2bfloat162_rn(v0.y, v0.w);
+            __nv_bfloat162 d = __floats2bfloat162_rn(v1.x, v1.z), e = __floats2bfloat162_rn(v1.y, v1.w);
+            o = make_uint4(*(uint32_t *)&a, *(uint32_t *)&b, *(uint32_t *)&d, *(uint32_t *)&e);
+        }
     }
-    __nv_bfloat162 a = __floats2bfloat162_rn(v0.x, v0.z), b = __floats2bfloat162_rn(v0.y, v0.w);
-    __nv_bfloat162 d = __floats2bfloat162_rn(v1.x, v1.z), e = __floats2bfloat162_rn(v1.y, v1.w);
-    uint4 o = make_uint4(*(uint32_t *)&a, *(uint32_t *)&b, *(uint32_t *)&d, *(uint32_t *)&e);
     uint8_t *tile_base = (uint8_t *)out + ((size_t)tile * ksteps + ks) * ((size_t)tok_tile * 128);
     *(uint4 *)(tile_base + (size_t)r * 128 + ((c ^ (r & 7)) << 4)) = o;
 }

@@ -690,15 +690,20 @@ static void launch_gemm_type(const GemmArgs &a, int halves)
     launch_gemm<T, PLANES, 1>(a);
 }
 
-static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y, int M, int K, int N)
+static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y, int M, int K, int N, bool x_bf16 = false)
 {
+    const float *x = (const float *)xv;   // (bf16 input: only the tensor-core path below reads it)
     if (M <= 0 || N <= 0) return;
     const FormatInfo fi = format_info(t);
     // n == 1 is the GEMV (src/dequant.rs:151-153); shapes/types the tensor-core kernel does not take
     // run token by token (what the reference's GPU prefill does, src/main.rs:1410-1416)
     const bool tc_ok = fi.block_elems >= 32 && K > 0 && K % GEMM_KSTEP == 0 && !((uintptr_t)W & 15) &&
                        !((uintptr_t)x & 15) && (((size_t)(K / fi.block_elems) * fi.block_bytes) % 16 == 0);
-    if (M == 1 || !tc_ok) {
+    if (x_bf16 && !tc_ok) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_gemm_bf16: in_dim must be a multiple of 64 and the pointers 16-byte aligned");
+        return;
+    }
+    if (!x_bf16 && (M == 1 || !tc_ok)) {
         for (int tkn = 0; tkn < M; tkn++) {
             const uint8_t *Wp[1] = {W};
             const float *xp[1] = {x + (size_t)tkn * K};
@@ -744,8 +749,12 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const float *x, float *y
     const long long chunks = (long long)need / 8;   // one thread per 16-byte chunk
     // the Q6_K producer emits each block's weights in its own K order; the activation tiles follow it
     const int perm = (t == T_Q6_K && planes) ? 1 : 0;
-    convert_x_bf16_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, g_stream>>>(x, g_xb, M, K, a.tok_tile,
-                                                                                  a.n_tok_tiles, perm);
+    if (x_bf16)
+        convert_x_bf16_kernel<true><<<(unsigned)((chunks + 255) / 256), 256, 0, g_stream>>>(xv, g_xb, M, K, a.tok_tile,
+                                                                                            a.n_tok_tiles, perm);
+    else
+        convert_x_bf16_kernel<false><<<(unsigned)((chunks + 255) / 256), 256, 0, g_stream>>>(xv, g_xb, M, K, a.tok_tile,
+                                                                                             a.n_tok_tiles, perm);
     QZ_LAUNCH_CHECK();
     // 256-row CTA tiles (two accumulators) halve the activation bytes each CTA pulls from L2 per
     // flop; they pay off once the token tile is wide enough for that traffic to matter
@@ -1469,6 +1478,12 @@ void cuda_gemm(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, floa
                int out_dim)
 {
     gemm_dispatch(ggml_type, d_data, d_x, d_y, m, in_dim, out_dim);
+}
+
+void cuda_gemm_bf16(uint32_t ggml_type, const uint8_t *d_data, const uint16_t *d_x_bf16, float *d_y, int m, int in_dim,
+                    int out_dim)
+{
+    gemm_dispatch(ggml_type, d_data, d_x_bf16, d_y, m, in_dim, out_dim, true);
 }
 
 // ======================= batched mixture-of-experts FFN =======================

@@ -87,3 +87,65 @@ def test_gemm_prefill_shapes(gpu, oracle_mod, t, K, N, M):
         assert np.all(np.abs(y[m].astype(np.float64) - ref[i]) <= tol), (t, M, m)
     # linearity across the batch: a token equal to the sum of two others gives the sum of their rows
     assert np.all(np.isfinite(y))
+
+
+@pytest.mark.parametrize("t,K,N", [(12, 4096, 14336), (14, 14336, 4096)])
+def test_gemm_full_size_prefill_shapes(gpu, oracle_mod, t, K, N):
+    """The prefill shapes at their full size (2048 tokens): sampled tokens against the oracle, exact zeros for
+    a zero activation block, and W(2X) = 2 W(X) within the accumulation-order slack of the shared tiles."""
+    from saient_quartz_b200 import synth
+    L = gpu.lib()
+    M = 2048
+    w = synth.make_weights(t, K, N, tensor_id=731)
+    X = synth.make_x(K, tensor_id=732, rows=M)
+    X[7] = 0.0
+    dw = gpu.GpuBuf.upload(w)
+    L.cuda_repack_weights(t, dw.ptr, K, N, 1)
+    dx, dy = gpu.GpuBuf.upload(X), gpu.GpuBuf.alloc_f32(M * N)
+    L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, N)
+    y = dy.download().reshape(M, N)
+    gpu.check_error("cuda_gemm full size")
+    assert np.all(y[7] == 0.0)
+    pick = [0, 1000, M - 1]
+    ref = oracle_mod.gemm(np.ascontiguousarray(X[pick]), w, t, K, N, len(pick))
+    norms = oracle_mod.row_norms(w, t, K, N)
+    for i, m in enumerate(pick):
+        tol = 1e-3 * norms * float(np.linalg.norm(X[m].astype(np.float64)))
+        assert np.all(np.abs(y[m].astype(np.float64) - ref[i]) <= tol), m
+    dx2 = gpu.GpuBuf.upload((2.0 * X).astype(np.float32))
+    L.cuda_gemm(t, dw.ptr, dx2.ptr, dy.ptr, M, K, N)
+    y2 = dy.download().reshape(M, N)
+    assert np.abs(y2 - 2.0 * y).max() <= 1e-5 * np.abs(y).max()
+    gpu.check_error()
+
+
+@pytest.mark.parametrize("t,repack,M", [(12, False, 40), (14, True, 300), (17, True, 1)])
+def test_gemm_bf16_activations(gpu, t, repack, M):
+    """cuda_gemm_bf16 on bf16 activations equals cuda_gemm on the same values widened to f32.  (Tiles shared
+    by two CTAs are summed atomically, so the comparison allows the accumulation-order slack.)"""
+    from saient_quartz_b200 import synth
+    L = gpu.lib()
+    K, N = 2048, 200
+    w = synth.make_weights(t, K, N, tensor_id=741)
+    X = synth.make_x(K, tensor_id=742, rows=max(M, 2))[:M].reshape(M, K)
+    bits = (X.view(np.uint32) + 0x7FFF + ((X.view(np.uint32) >> 16) & 1)) >> 16   # round to nearest even
+    xb = bits.astype(np.uint16)
+    xf = (bits.astype(np.uint32) << 16).view(np.float32)
+    dw = gpu.GpuBuf.upload(w)
+    if repack:
+        L.cuda_repack_weights(t, dw.ptr, K, N, 1)
+    dxb, dxf = gpu.GpuBuf.upload(xb), gpu.GpuBuf.upload(np.ascontiguousarray(xf))
+    dy1, dy2 = gpu.GpuBuf.alloc_f32(M * N), gpu.GpuBuf.alloc_f32(M * N)
+    L.cuda_gemm_bf16(t, dw.ptr, dxb.ptr, dy1.ptr, M, K, N)
+    if M == 1:
+        X2 = np.concatenate([xf, np.zeros((1, K), np.float32)])     # cuda_gemm routes m = 1 to the GEMV: compare via m = 2
+        dxf = gpu.GpuBuf.upload(X2)
+        dy2 = gpu.GpuBuf.alloc_f32(2 * N)
+        L.cuda_gemm(t, dw.ptr, dxf.ptr, dy2.ptr, 2, K, N)
+        b = dy2.download()[:N]
+    else:
+        L.cuda_gemm(t, dw.ptr, dxf.ptr, dy2.ptr, M, K, N)
+        b = dy2.download()
+    a = dy1.download()
+    gpu.check_error("cuda_gemm_bf16")
+    assert np.abs(a - b).max() <= 1e-5 * max(np.abs(b).max(), 1e-30)
