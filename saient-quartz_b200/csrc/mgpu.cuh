@@ -50,16 +50,16 @@ __device__ __forceinline__ int ld_acquire_sys(const int *p)
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(int *p, int v)
+__device__ __forceinline__ void st_relaxed_sys(int *p, int v)
 {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Called by ONE thread of a CTA after a CTA-level barrier that follows all of the CTA's remote
 // stores.  The count is a release/acquire read-modify-write at GPU scope: through the barrier it is
 // cumulative over the other threads' stores, and the last CTA to count in has thereby acquired every
-// CTA's stores.  That CTA publishes the exchange with system-scope release stores of the new
-// counter, which carry all of it to the peers.
+// CTA's stores.  That CTA publishes the exchange: one system-scope fence, then the new counter
+// stored into every rank's flag array.
 __device__ __forceinline__ void push_publish(const PushArgs &p, int total_ctas)
 {
     MgpuCtrl *mine = p.ctrl[p.rank];
@@ -69,7 +69,10 @@ __device__ __forceinline__ void push_publish(const PushArgs &p, int total_ctas)
         mine->cta_counter = 0;
         const int e = mine->pushes + 1;
         mine->pushes = e;
-        for (int r = 0; r < p.n; r++) st_release_sys(&p.ctrl[r]->flags[p.rank], e);
+        // ONE system-scope fence, then the flag stores: a release store per peer would repeat the fence
+        // (a few microseconds each) once per rank
+        __threadfence_system();
+        for (int r = 0; r < p.n; r++) st_relaxed_sys(&p.ctrl[r]->flags[p.rank], e);
     }
 }
 
