@@ -4,21 +4,25 @@
 // The reference has no batched GPU path at all (its GPU prefill is token-by-token GEMV,
 // src/main.rs:1410-1416); its CPU form is dequant::gemm (src/dequant.rs:143-200).
 //
-// One CTA owns a tile of 128 weight rows (the UMMA M dimension) x up to 256 tokens (the UMMA N
-// dimension) x one K split.  Per 64-wide K step:
-//   * sixteen producer warps dequantize the 128x64 weight tile to bf16 straight into shared
-//     memory in the K-major 128-byte-swizzled layout tcgen05.mma reads (four threads per row,
-//     16 weights each, raw bytes prefetched several K steps ahead with cp.async into a private
-//     shared-memory ring; Q4_K / Q6_K use packed bf16x2 arithmetic: nibble|0x4300 is the bf16
-//     128+q, an exact HSUB2 removes the 128, one HFMA2 applies scale and min), and copy the
-//     matching 64 columns of the bf16 activation tile beside it;
+// Persistent kernel, one CTA per SM (two for narrow token tiles).  The (row tile, token tile, K step)
+// units of the whole problem, tile-major, are cut into one equal contiguous share per CTA; a tile is
+// 128 or 256 weight rows (one or two UMMA M=128 accumulators side by side in TMEM) x up to 256 tokens
+// (the UMMA N dimension).  Per 64-wide K step of a tile:
+//   * producer warps -- two groups that take alternate K steps, one thread per weight row --
+//     dequantize the weight tile to bf16 straight into shared memory in the K-major 128-byte-swizzled
+//     layout tcgen05.mma reads (raw bytes of the thread's next step are loaded into registers while the
+//     current one is unpacked; Q4_K / Q6_K use packed bf16x2 arithmetic: nibble|0x4300 is the bf16
+//     128+q, an exact HSUB2 removes the 128, one HFMA2 applies scale and min; IQ2_XS / IQ3_XXS read
+//     bf16 grids and sign masks from shared-memory tables), and one thread starts the bulk async copy
+//     of the step's pre-swizzled bf16 activation tile;
 //   * they fence the generic->async proxy and arrive on the stage's "full" mbarrier;
-//   * one elected thread issues four tcgen05.mma (K=16 each, kind::f16, bf16 x bf16 -> f32 in
-//     TMEM) and a tcgen05.commit that arrives on the stage's "empty" mbarrier when the tensor
+//   * one elected thread issues four tcgen05.mma per accumulator (K=16 each, kind::f16, bf16 x bf16 ->
+//     f32 in TMEM) and a tcgen05.commit that arrives on the stage's "empty" mbarrier when the tensor
 //     core has finished reading the stage.
-// A 3-4 stage ring lets dequantization run ahead of the MMAs.  The epilogue reads the
-// accumulator with tcgen05.ld (32 lanes x 8 columns per instruction), one weight row per
-// thread, and stores (or, with K splits, atomically adds) into the token-major output.
+// A 3-4 stage ring lets dequantization run ahead of the MMAs.  Dedicated epilogue warps read a finished
+// tile's accumulator with tcgen05.ld (32 lanes x 8 columns per instruction), one weight row per thread,
+// and store it -- or, for a tile that two CTAs share, add it atomically onto zeros -- into the
+// token-major output, then hand the accumulator back to the MMA thread.
 //
 // Within every group of four consecutive k the tile order is (0,2,1,3) for BOTH operands: that
 // is the order byte->bf16x2 unpacking produces for free, and a contraction does not care about
@@ -53,10 +57,10 @@ struct GemmArgs {
     int *status;
 };
 
-// ---- f32 [M,K] -> bf16 tiles in exactly the shared-memory image the MMA reads: for every (token
-//      tile, K step) a contiguous [tok_tile rows x 128 B] block, 16-byte chunk c of row r stored at
-//      chunk c ^ (r & 7), k order (0,2,1,3) inside every four.  A stage's activation tile is then
-//      ONE bulk async copy.  One thread per 16-byte chunk. ----
+// ---- f32 or bf16 [M,K] -> bf16 tiles in exactly the shared-memory image the MMA reads: for every
+//      (token tile, K step) a contiguous [tok_tile rows x 128 B] block, 16-byte chunk c of row r stored
+//      at chunk c ^ (r & 7), k order (0,2,1,3) inside every four.  A stage's activation tile is then
+//      ONE bulk async copy.  One thread per 16-byte chunk.
 //      perm = 1 (Q6_K weight tiles): position p of K step (block b, j) holds activation
 //      256 b + 128 (j >> 1) + 32 (p >> 4) + 16 (j & 1) + (p & 15): the K order in which the Q6_K producer
 //      emits weights (all four 32-runs of one 16-wide slice, so that every loaded bit is used). ----

@@ -31,7 +31,8 @@ constexpr long long TMA_WAIT_CYCLES = 2000000000LL;   // ~1 s at 1.9 GHz
 
 // Where the activation vector comes from.  mode 0: already converted (xq).  mode 1: RMSNorm of the
 // f32 vector a with weights b (src/cuda_kernels.cu:563-575, eps 1e-5 as there), mode 2: SwiGLU of
-// gate a and up b (src/cuda_kernels.cu:683-698; oai = the clamped variant).  For modes 1 and 2 every
+// gate a and up b (src/cuda_kernels.cu:683-698; oai = the clamped variant), mode 3 (gemv_chain_kernel
+// only): the f32 vector a as it is.  For modes 1 to 3 every
 // CTA converts the vector itself, into shared memory, while its weight pipeline fills: the producer of
 // the activations needs no kernel of its own.
 struct XSrc {
