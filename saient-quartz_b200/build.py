@@ -26,7 +26,7 @@ def up_to_date():
 def build_host(force=False):
     hdrs = [os.path.join(HERE, "host", "forward_state.h"), os.path.join(HERE, "host", "gguf_loader.h"),
             os.path.join(HERE, "..", "include", "quartz_b200.h")]
-    srcs = [HOST_SRC, os.path.join(HERE, "host", "gguf_loader.cpp")]
+    srcs = [HOST_SRC, os.path.join(HERE, "host", "gguf_loader.cpp"), os.path.join(HERE, "host", "model_loader.cpp")]
     if (not force and os.path.exists(HOST_LIB)
             and all(os.path.getmtime(p) <= os.path.getmtime(HOST_LIB) for p in srcs + [LIB] + hdrs)):
         return HOST_LIB

@@ -43,6 +43,14 @@ enum qh_role {
 typedef struct qh_model qh_model;
 
 qh_model *qh_create(const qh_config *cfg);
+/* Build a model from a GGUF file: configuration from the metadata as the reference derives it
+ * (Config::from_gguf, src/main.rs:96-215: "<arch>." keys with their fallbacks and defaults), tensors by
+ * the names of src/main.rs:357-414 ("token_embd.weight", "output.weight" or tied, "blk.N.attn_q.weight",
+ * ..., expert tensors "blk.N.ffn_*_exps.weight").  max_seq <= 0 takes the file's context length (capped at
+ * 8192).  Norms, biases, sinks and router weights must be F32 in the file.  NULL on failure
+ * (qh_load_error says why); cfg_out (optional) receives the derived configuration. */
+qh_model *qh_load_gguf(const char *path, int max_seq, int repack, qh_config *cfg_out);
+const char *qh_load_error(void);
 void qh_destroy(qh_model *m);
 /* upload one tensor (raw GGUF bytes, or f32 for norms/biases/router); repack=1 calls the repack hook */
 int qh_set_tensor(qh_model *m, int role, int layer, uint32_t ggml_type, const void *host, size_t bytes, int repack);

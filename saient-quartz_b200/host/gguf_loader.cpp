@@ -305,6 +305,13 @@ const char *qg_meta_str(const qg_file *f, const char *key)
     const MetaValue *v = meta_at(f, key);
     return (v && v->type == VT_STRING) ? v->str.c_str() : nullptr;
 }
+int qg_meta_bool(const qg_file *f, const char *key, int *out)
+{
+    const MetaValue *v = meta_at(f, key);
+    if (!v || v->type != VT_BOOL) return 0;
+    if (out) *out = (v->bits & 0xFF) != 0;
+    return 1;
+}
 int qg_meta_array_len(const qg_file *f, const char *key, uint64_t *out)
 {
     const MetaValue *v = meta_at(f, key);

@@ -47,6 +47,7 @@ int qg_meta_u64(const qg_file *f, const char *key, uint64_t *out);
 int qg_meta_f32(const qg_file *f, const char *key, float *out);
 const char *qg_meta_str(const qg_file *f, const char *key);
 int qg_meta_array_len(const qg_file *f, const char *key, uint64_t *out);
+int qg_meta_bool(const qg_file *f, const char *key, int *out);
 
 /* Allocate device memory for tensor i (cuda_alloc), stream its bytes in through the staging
  * buffers, and (repack != 0, quantized 2-D/3-D tensors) call cuda_repack_weights with

@@ -79,6 +79,25 @@ class HostModel:
         self.seed = seed
         self.weight_bytes = 0
 
+    @classmethod
+    def from_gguf(cls, path, max_seq=0, repack=True):
+        """Load a model from a GGUF file through qh_load_gguf (configuration and tensor names as the reference
+        reads them, src/main.rs:96-215, 357-414)."""
+        from . import ensure_iq_grids
+        ensure_iq_grids()
+        self = cls.__new__(cls)
+        self.H = host_lib()
+        self.H.qh_load_gguf.restype = C.c_void_p
+        self.H.qh_load_gguf.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_void_p]
+        self.H.qh_load_error.restype = C.c_char_p
+        self.c = QhConfig()
+        self.m = self.H.qh_load_gguf(str(path).encode(), max_seq, int(repack), C.byref(self.c))
+        if not self.m:
+            raise RuntimeError("qh_load_gguf failed: " + self.H.qh_load_error().decode())
+        self.cfg = {name: getattr(self.c, name) for name, _ in QhConfig._fields_}
+        self.host, self.repack, self.types, self.weight_bytes = None, repack, None, 0
+        return self
+
     def set(self, role, layer, ggml_type, arr):
         arr = np.ascontiguousarray(arr)
         rc = self.H.qh_set_tensor(self.m, ROLES[role], layer, ggml_type, arr.ctypes.data, arr.nbytes, int(self.repack))

@@ -171,3 +171,86 @@ def test_upload_and_gemv(gpu, oracle_mod, tmp_path):
     gpu.check_error("expert slice")
     Q.cuda_drop(dev)
     L.qg_close(f)
+
+
+_NAMES = {"EMBED": "token_embd.weight", "LM_HEAD": "output.weight", "FINAL_NORM": "output_norm.weight",
+          "Q": "blk.{l}.attn_q.weight", "K": "blk.{l}.attn_k.weight", "V": "blk.{l}.attn_v.weight",
+          "O": "blk.{l}.attn_output.weight", "GATE": "blk.{l}.ffn_gate.weight", "UP": "blk.{l}.ffn_up.weight",
+          "DOWN": "blk.{l}.ffn_down.weight", "ATTN_NORM": "blk.{l}.attn_norm.weight", "FFN_NORM": "blk.{l}.ffn_norm.weight"}
+
+
+def _write_model_gguf(path, m, arch="llama"):
+    """The tensors of a synthetic HostModel (kept on the host) as a GGUF file with the metadata keys the
+    reference reads (src/main.rs:96-215)."""
+    import gguf
+    from saient_quartz_b200 import synth
+    c = m.cfg
+    w = gguf.GGUFWriter(path, arch)
+    w.add_uint32(f"{arch}.embedding_length", c["embed_dim"])
+    w.add_uint32(f"{arch}.attention.head_count", c["n_heads"])
+    w.add_uint32(f"{arch}.attention.head_count_kv", c["n_kv_heads"])
+    w.add_uint32(f"{arch}.block_count", c["n_layers"])
+    w.add_uint32(f"{arch}.feed_forward_length", c["ffn_dim"])
+    w.add_float32(f"{arch}.rope.freq_base", c["rope_theta"])
+    w.add_uint32(f"{arch}.context_length", c["max_seq"])
+    w.add_uint32(f"{arch}.attention.key_length", c["head_dim"])
+    w.add_uint32(f"{arch}.vocab_size", c["vocab_size"])
+    for (role, layer), (t, arr) in m.host.items():
+        name = _NAMES[role].format(l=layer)
+        if t == 0:
+            w.add_tensor(name, arr.astype(np.float32))
+        else:
+            in_dim = {"O": c["n_heads"] * c["head_dim"], "DOWN": c["ffn_dim"]}.get(role, c["embed_dim"])
+            rb = synth.type_size(t, in_dim)
+            w.add_tensor(name, arr.reshape(-1, rb), raw_dtype=gguf.GGMLQuantizationType(t))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("arch,neox", [("llama", 0), ("qwen2", 1)])
+def test_model_from_gguf_equals_model_built_directly(gpu, tmp_path, arch, neox):
+    """qh_load_gguf: a model written to a GGUF file and loaded back gives the logits of the model built
+    tensor by tensor, bit for bit; the configuration (RoPE convention by architecture included) is derived
+    from the metadata."""
+    from saient_quartz_b200.host_model import HostModel, Q4K_M_TYPES
+    cfg = dict(vocab_size=320, embed_dim=2048, n_heads=16, n_kv_heads=4, n_layers=2, ffn_dim=4096, head_dim=128,
+               rope_theta=500000.0, max_seq=64, rope_neox=neox)
+    a = HostModel(repack=True, keep_host=True, types=Q4K_M_TYPES, **cfg)
+    a.fill_synthetic()
+    path = str(tmp_path / "model.gguf")
+    _write_model_gguf(path, a, arch)
+    b = HostModel.from_gguf(path, max_seq=64)
+    for k in ("vocab_size", "embed_dim", "n_heads", "n_kv_heads", "n_layers", "ffn_dim", "head_dim", "max_seq", "rope_neox"):
+        assert b.cfg[k] == cfg[k], k
+    assert b.cfg["rope_theta"] == 500000.0 and b.cfg["n_experts"] == 0
+    for (tok, pos) in ((5, 0), (17, 1), (300, 2)):
+        la = a.step(tok, pos, fused=True)
+        lb = b.step(tok, pos, fused=True)
+        assert np.array_equal(la, lb), (tok, pos)
+    assert np.array_equal(a.step(9, 3, fused=False), b.step(9, 3, fused=False))
+    gpu.check_error()
+    a.close()
+    b.close()
+
+
+@pytest.mark.gpu
+def test_model_from_gguf_reports_what_is_missing(gpu, tmp_path):
+    import gguf
+    from saient_quartz_b200.host_model import HostModel
+    path = str(tmp_path / "broken.gguf")
+    w = gguf.GGUFWriter(path, "llama")
+    w.add_uint32("llama.embedding_length", 256)
+    w.add_uint32("llama.attention.head_count", 4)
+    w.add_uint32("llama.block_count", 1)
+    w.add_uint32("llama.feed_forward_length", 512)
+    w.add_uint32("llama.vocab_size", 32)
+    w.add_tensor("output_norm.weight", np.ones(256, np.float32))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+    with pytest.raises(RuntimeError, match="token_embd.weight"):
+        HostModel.from_gguf(path)
