@@ -208,7 +208,8 @@ void cuda_attn_block(float *out, const float *q, const float *k_new, const float
  * and :760-775) and y_i (+)= W_i * swiglu(gate, up)  (cuda_swiglu / cuda_swiglu_oai + cuda_gemv,
  * src/cuda.rs:777-800).  eps is 1e-5 as in the reference kernel.  Same type/shape/layout conditions as
  * cuda_gemv_q (cuda_gemv_q_supported); in_dim floats of d_x / d_norm_w / d_gate / d_up, 16-byte aligned
- * for the fused form (otherwise the two-launch form runs and uses the caller's scratch slot 3). */
+ * and in_dim <= 8192 for the fused form (otherwise the two-launch form runs and uses the caller's scratch
+ * slot 3: converting a long vector once is cheaper than converting it in every CTA). */
 void cuda_gemv_rmsnorm(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_x,
                        const float *d_norm_w, int in_dim, int out_dim, int accumulate);
 void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_gate,

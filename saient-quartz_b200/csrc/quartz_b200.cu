@@ -1172,7 +1172,9 @@ static void gemv_xsrc(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w,
         slot_of[i] = 7;   // the caller's slot 3: used only if the fused prologue is not taken
     }
     if (!ensure_xq(in_dim)) return;
-    if (use_tma() && ((uintptr_t)src.a & 15) == 0 && ((uintptr_t)src.b & 15) == 0) {
+    // the prologue converts the whole vector in every CTA: worth it for short vectors (one launch less), not for
+    // long ones (14336: +4 us per CTA against a 2 us conversion kernel)
+    if (use_tma() && in_dim <= 8192 && ((uintptr_t)src.a & 15) == 0 && ((uintptr_t)src.b & 15) == 0) {
         g_xsrc = src;
         g_xsrc_pending = true;
         const bool ok = stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
