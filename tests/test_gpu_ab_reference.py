@@ -1,8 +1,9 @@
 """A/B timing on the same GPU: this library's cuda_gemv against the reference's own CUDA kernels
 (oracle/_ref/libkernels_ref.so, compiled unmodified from the reference's src/cuda_kernels.cu for
 sm_100a), shape by shape, same weights, back-to-back launches rotating over enough distinct
-weight copies to exceed the L2.  Prints a markdown table (run with -s) and writes it to
-gpurun_out/ab_reference.md; asserts only that no streaming format is slower than the reference."""
+weight copies to exceed the L2.  Prints a markdown table (run with -s) and writes it to ab_reference.md
+in the report directory ($QUARTZ_REPORT_DIR); asserts only that no streaming format is slower than the
+reference."""
 import os
 
 import numpy as np
@@ -64,6 +65,7 @@ def test_ab_against_reference_kernels(gpu, oracle_mod, tables):
     gpu.check_error()
     table = "\n".join(lines)
     print("\n" + table)
-    os.makedirs("gpurun_out", exist_ok=True)
-    with open(os.path.join("gpurun_out", "ab_reference.md"), "w") as f:
+    out_dir = os.environ.get("QUARTZ_REPORT_DIR", "gpurun_out")
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "ab_reference.md"), "w") as f:
         f.write(table + "\n")
