@@ -355,3 +355,41 @@ def test_rope_kv_matches_separate_calls(gpu):
         assert np.array_equal(kc1.download(), kc2.download())
         assert np.array_equal(vc1.download(), vc2.download())
     gpu.check_error()
+
+
+def test_gemv_batch_of_independent_shapes(gpu, oracle_mod):
+    """cuda_gemv_batch: GEMVs of different types and shapes that do not depend on one another, in one
+    persistent launch, against the oracle and against cuda_gemv (same conversion, same dot products: equal
+    bit for bit)."""
+    from saient_quartz_b200 import synth
+    L = gpu.lib()
+    cases = [(12, 4096, 1024), (14, 14336, 512), (8, 2048, 300), (12, 2048, 4096)]
+    ops, keep = [], []
+    for i, (t, K, N) in enumerate(cases):
+        w = synth.make_weights(t, K, N, tensor_id=650 + i)
+        x = synth.make_x(K, tensor_id=660 + i).reshape(-1)
+        dw = gpu.GpuBuf.upload(w)
+        L.cuda_repack_weights(t, dw.ptr, K, N, 1)
+        dx, dy, dy2 = gpu.GpuBuf.upload(x), gpu.GpuBuf.alloc_f32(N), gpu.GpuBuf.alloc_f32(N)
+        keep.append((t, K, N, w, x, dw, dx, dy, dy2))
+        ops.append(gpu.chain_op(t, [dw.ptr], [dy.ptr], K, N, 0, 3, dx.ptr))
+    arr = (gpu.ChainOp * len(ops))(*ops)
+    assert L.cuda_gemv_chain_supported(len(ops), arr) == 1
+    L.cuda_gemv_batch(len(ops), arr)
+    for (t, K, N, w, x, dw, dx, dy, dy2) in keep:
+        L.cuda_gemv(t, dw.ptr, dx.ptr, dy2.ptr, K, N)
+        y, y2 = dy.download(), dy2.download()
+        assert np.array_equal(y, y2), (t, K, N)
+        ref = oracle_mod.gemv(x, w, t, K, N)
+        assert np.all(np.abs(y - ref) <= oracle_mod.tolerance(w, t, K, N, x)), (t, K, N)
+    gpu.check_error()
+    # an op the persistent kernel does not take (in_dim below 2048) makes the call run launch by launch
+    t, K, N = 12, 1024, 64
+    w = synth.make_weights(t, K, N, tensor_id=670)
+    x = synth.make_x(K, tensor_id=671).reshape(-1)
+    dw, dx, dy = gpu.GpuBuf.upload(w), gpu.GpuBuf.upload(x), gpu.GpuBuf.alloc_f32(N)
+    one = (gpu.ChainOp * 1)(gpu.chain_op(t, [dw.ptr], [dy.ptr], K, N, 0, 3, dx.ptr))
+    assert L.cuda_gemv_chain_supported(1, one) == 0
+    L.cuda_gemv_batch(1, one)
+    assert np.all(np.abs(dy.download() - oracle_mod.gemv(x, w, t, K, N)) <= oracle_mod.tolerance(w, t, K, N, x))
+    gpu.check_error()
