@@ -52,7 +52,10 @@ struct GemmArgs {
     int M, K, N;
     int planes;                // weight layout
     int n_tok_tiles, tok_tile; // tokens per CTA (multiple of 16, <= 256)
-    long long units, units_per_cta;   // (tile, K step) units in all, and per CTA
+    long long units;           // (tile, K step) units in all, tile-major
+    long long dp_units;        // whole-tile part: CTA c owns units [c * dp_units, (c + 1) * dp_units)
+    long long rem_begin;       // first unit of the shared part (= CTAs x dp_units)
+    long long units_per_cta;   // shared part: CTA c owns [rem_begin + c * units_per_cta, + units_per_cta), clipped
     int stages;                // MMA ring depth
     int *status;
 };
@@ -131,6 +134,30 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t *r)
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 32 lanes x 16 / 32 consecutive columns per instruction: one round trip to tensor memory per 16 / 32
+// tokens instead of one per 8 (the round trip, not the data volume, is what an epilogue waits for)
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
@@ -453,26 +480,53 @@ template <int HALVES>
 constexpr int gemm_threads() { return 2 * 128 * HALVES + 32 + 128 * HALVES; }   // producers, MMA warp, epilogue warps
 
 // ---- zero the output tiles that more than one CTA contributes to (their partial sums are added
-//      atomically).  One block per CTA of the GEMM grid: a CTA whose first unit lies strictly inside
-//      a tile's K range marks that tile as shared. ----
+//      atomically).  blockIdx.x = CTA of the GEMM grid: a CTA whose share of the shared part begins
+//      strictly inside a tile's K range marks that tile as shared; blockIdx.y = slice of the tile's tokens. ----
 __global__ void gemm_zero_split_tiles_kernel(float *__restrict__ Y, int M, int N, int ksteps, int n_tok_tiles, int tok_tile,
-                                             int cta_rows, long long units, long long units_per_cta)
+                                             int cta_rows, long long units, long long rem_begin, long long units_per_cta)
 {
-    const long long u0 = (long long)blockIdx.x * units_per_cta;
+    const long long u0 = rem_begin + (long long)blockIdx.x * units_per_cta;
     if (u0 >= units || u0 % ksteps == 0) return;
     const int tile = (int)(u0 / ksteps);
     const int row0 = (tile / n_tok_tiles) * cta_rows, tok0 = (tile % n_tok_tiles) * tok_tile;
     const int rows = min(cta_rows, N - row0), toks = min(tok_tile, M - tok0);
-    for (int i = threadIdx.x; i < rows * toks; i += blockDim.x) {
-        const int tk = i / rows, rr = i - tk * rows;
-        Y[(size_t)(tok0 + tk) * N + row0 + rr] = 0.f;
+    const int per = (toks + gridDim.y - 1) / gridDim.y;
+    const int t0 = blockIdx.y * per, t1 = min(t0 + per, toks);
+    if (((N | rows) & 3) == 0) {   // row0 is a multiple of 128: 16-byte stores
+        const int r4 = rows >> 2;
+        for (int i = threadIdx.x; i < (t1 - t0) * r4; i += blockDim.x) {
+            const int tk = t0 + i / r4, rr = i - (i / r4) * r4;
+            *(float4 *)(Y + (size_t)(tok0 + tk) * N + row0 + 4 * rr) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else {
+        for (int i = threadIdx.x; i < (t1 - t0) * rows; i += blockDim.x) {
+            const int tk = t0 + i / rows, rr = i - (i / rows) * rows;
+            Y[(size_t)(tok0 + tk) * N + row0 + rr] = 0.f;
+        }
     }
 }
 
-// ---- the kernel.  Persistent: the (row tile, token tile, K step) units of the whole problem, tile-major,
-//      are cut into one contiguous, equally long range per CTA, so every SM gets the same amount of
-//      work whatever the tile count; a CTA's range may end inside a tile and the next CTA continues
-//      it.  A tile a single CTA covers completely is stored; a shared one is added atomically onto
+// Unit i of a CTA's work (first its whole tiles, then its share of the shared part) -> (tile, K step).
+struct GemmShare {
+    long long u1, u2;   // first unit of the two ranges
+    int n1, n;          // units in the first range, units in all
+    int ksteps;
+    __device__ void locate(int i, int &tile, int &ks) const
+    {
+        const long long u = i < n1 ? u1 + i : u2 + (i - n1);
+        tile = (int)(u / ksteps);
+        ks = (int)(u - (long long)tile * ksteps);
+    }
+    // units from i to the end of i's tile or of i's range, whichever comes first
+    __device__ int run(int i, int ks) const { return min(ksteps - ks, (i < n1 ? n1 : n) - i); }
+};
+
+// ---- the kernel.  Persistent.  The tiles of the whole problem, in tile-major unit order, are split in
+//      two parts: as many whole tiles per CTA as every CTA can get (stored with plain stores, no other CTA
+//      touches them), and the rest -- less than one tile per CTA -- whose (tile, K step) units are cut
+//      into one contiguous, equally long range per CTA, so every SM gets the same amount of work whatever
+//      the tile count; such a range may end inside a tile and the next CTA continues it.  A tile of the
+//      second part that a single CTA covers completely is stored; a shared one is added atomically onto
 //      zeros.  A CTA owns HALVES x 128 weight rows of a tile (one UMMA M=128 accumulator per half,
 //      side by side in TMEM), so an activation tile fetched from L2 feeds HALVES x 128 rows.
 //      Warps: 8 x HALVES producers | 1 MMA issuer + TMEM owner | 4 x HALVES epilogue. ----
@@ -492,10 +546,16 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
     const size_t row_bytes = (size_t)nb * fi.block_bytes;
     const int ntok = a.tok_tile;                              // UMMA N (multiple of 16)
     const int ksteps = a.K / GEMM_KSTEP;
-    const long long u_begin = (long long)blockIdx.x * a.units_per_cta;
-    const long long u_end = min(u_begin + a.units_per_cta, a.units);
-    const int nunits = u_end > u_begin ? (int)(u_end - u_begin) : 0;
-    const int tile_begin = (int)(u_begin / ksteps), ks_begin = (int)(u_begin - (long long)tile_begin * ksteps);
+    GemmShare sh;
+    sh.ksteps = ksteps;
+    sh.u1 = (long long)blockIdx.x * a.dp_units;
+    sh.n1 = (int)a.dp_units;
+    sh.u2 = a.rem_begin + (long long)blockIdx.x * a.units_per_cta;
+    {
+        const long long e2 = min(sh.u2 + a.units_per_cta, a.units);
+        sh.n = sh.n1 + (e2 > sh.u2 ? (int)(e2 - sh.u2) : 0);
+    }
+    const int nunits = sh.n;
     const int a_bytes = CTA_ROWS * 128, b_bytes = ntok * 128;
     const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -526,21 +586,21 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         //                  i = g, g + 2, ... (one thread per tile row), so two units are always in
         //                  the making and one group's load latency hides behind the other's work ----
         const int r = threadIdx.x % CTA_ROWS, g = threadIdx.x / CTA_ROWS;
-        struct Cursor { int tile, ks; const uint8_t *rowp; };
+        struct Cursor { int i, tile, ks; const uint8_t *rowp; };
         auto rowp_of = [&](int tile) -> const uint8_t * {
             const int row = (tile / a.n_tok_tiles) * CTA_ROWS + r;
             return row < a.N ? a.W + (size_t)row * row_bytes : nullptr;
         };
-        auto advance = [&](Cursor &c, int by) {
-            c.ks += by;
-            while (c.ks >= ksteps) {
-                c.ks -= ksteps;
-                c.tile++;
-                c.rowp = rowp_of(c.tile);
+        auto advance = [&](Cursor &c, int by) {   // to unit c.i + by of this CTA's work
+            c.i += by;
+            int tile;
+            sh.locate(c.i, tile, c.ks);
+            if (tile != c.tile) {
+                c.tile = tile;
+                c.rowp = rowp_of(tile);
             }
         };
-        Cursor ld{tile_begin, ks_begin, nullptr}, st;
-        ld.rowp = rowp_of(ld.tile);
+        Cursor ld{0, -1, 0, nullptr}, st;
         advance(ld, g);
         st = ld;
         int s = g % a.stages;
@@ -599,10 +659,12 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(ntok);
-            int ks = ks_begin, s = 0, seg = 0;
+            int s = 0, seg = 0;
             uint32_t round = 0;
             bool ok = true, first = true;
             for (int i = 0; i < nunits && ok; i++) {
+                int tile_i, ks;
+                sh.locate(i, tile_i, ks);
                 ok = mbar_wait(&full_bar[s], round & 1);
                 if (ok && first && seg > 0) ok = mbar_wait(&acc_free_bar, (seg - 1) & 1);   // accumulator drained
                 if (!ok) break;
@@ -619,9 +681,8 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
                 }
                 tc_commit(&empty_bar[s]);   // arrives once the MMAs above have consumed the stage
                 first = false;
-                if (++ks == ksteps || i + 1 == nunits) {   // the tile's last unit in this CTA's range
+                if (sh.run(i, ks) == 1) {   // the tile's last unit in this CTA's work
                     tc_commit(&done_bar);
-                    ks = 0;
                     seg++;
                     first = true;
                 }
@@ -639,9 +700,11 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         // ---------------- epilogue: four warps per half (a warp reads TMEM lanes 32 * (warp % 4) ..),
         //                  one weight row per thread ----------------
         const int hf = (warp - PWARPS - 1) >> 2, quad = warp & 3;
-        int tile = tile_begin, ks0 = ks_begin, left = nunits, seg = 0;
-        while (left > 0) {
-            const int len = min(ksteps - ks0, left);
+        int i = 0, seg = 0;
+        while (i < nunits) {
+            int tile, ks0;
+            sh.locate(i, tile, ks0);
+            const int len = sh.run(i, ks0);
             if (*(volatile int *)&abort_s || !mbar_wait_sleep(&done_bar, seg & 1, 500)) {
                 atomicExch(a.status, QZ_ERR_TIMEOUT);
                 abort_s = 1;
@@ -651,17 +714,20 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             const bool whole = len == ksteps;
             const int row = (tile / a.n_tok_tiles) * CTA_ROWS + GEMM_ROWS * hf + 32 * quad + lane;
             const int tok0 = (tile % a.n_tok_tiles) * ntok;
-            for (int c0 = 0; c0 < ntok; c0 += 8) {
-                uint32_t v[8];
-                tc_ld8(tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(hf * ntok + c0), v);
+            // ntok is a multiple of 16: 32 columns per round trip, then at most one group of 16
+            for (int c0 = 0; c0 < ntok; c0 += 32) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(hf * ntok + c0);
+                const int nc = min(32, ntok - c0);
+                if (nc == 32) tc_ld32(taddr, v);
+                else tc_ld16(taddr, v);
                 if (row < a.N) {
+                    float *dst = a.Y + (size_t)(tok0 + c0) * a.N + row;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int tok = tok0 + c0 + j;
-                        if (tok < a.M) {
-                            float *dst = a.Y + (size_t)tok * a.N + row;
-                            if (whole) *dst = __uint_as_float(v[j]);
-                            else atomicAdd(dst, __uint_as_float(v[j]));
+                    for (int j = 0; j < 32; j++) {
+                        if (j < nc && tok0 + c0 + j < a.M) {
+                            if (whole) dst[(size_t)j * a.N] = __uint_as_float(v[j]);
+                            else atomicAdd(dst + (size_t)j * a.N, __uint_as_float(v[j]));
                         }
                     }
                 }
@@ -669,9 +735,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_free_bar);
-            left -= len;
-            ks0 = 0;
-            tile++;
+            i += len;
             seg++;
         }
     }

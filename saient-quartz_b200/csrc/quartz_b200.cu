@@ -663,17 +663,27 @@ static void launch_gemm(GemmArgs a)
                                            216 * 1024));
         attr_set = true;
     }
-    // one equal share of the (tile, K step) units per resident CTA; at least 8 units each
+    // work split over the resident CTAs: first as many whole tiles as every CTA can get, then one equal
+    // share of the remaining (tile, K step) units per CTA, at least 8 units each.  Only tiles of that
+    // second part can be shared between CTAs (zeroed here, added atomically by the kernel).
     const int cta_rows = HALVES * GEMM_ROWS, ksteps = a.K / GEMM_KSTEP;
     const long long tiles = (long long)((a.N + cta_rows - 1) / cta_rows) * a.n_tok_tiles;
     a.units = tiles * ksteps;
     long long ctas = (long long)sm_count() * (two ? 2 : 1);
-    if (ctas > (a.units + 7) / 8) ctas = (a.units + 7) / 8;
-    a.units_per_cta = (a.units + ctas - 1) / ctas;
-    ctas = (a.units + a.units_per_cta - 1) / a.units_per_cta;
-    gemm_zero_split_tiles_kernel<<<(unsigned)ctas, 256, 0, g_stream>>>(a.Y, a.M, a.N, ksteps, a.n_tok_tiles, a.tok_tile, cta_rows,
-                                                                    a.units, a.units_per_cta);
-    QZ_LAUNCH_CHECK();
+    const long long whole = tiles / ctas;
+    if (whole == 0 && ctas > (a.units + 7) / 8) ctas = (a.units + 7) / 8;
+    a.dp_units = whole * ksteps;
+    a.rem_begin = ctas * a.dp_units;
+    const long long rem = a.units - a.rem_begin;
+    long long sharers = ctas;
+    if (sharers > (rem + 7) / 8) sharers = (rem + 7) / 8;
+    a.units_per_cta = sharers > 0 ? (rem + sharers - 1) / sharers : 0;
+    if (whole == 0) ctas = (a.units + a.units_per_cta - 1) / a.units_per_cta;
+    if (rem > 0) {
+        gemm_zero_split_tiles_kernel<<<dim3((unsigned)ctas, 8), 256, 0, g_stream>>>(a.Y, a.M, a.N, ksteps, a.n_tok_tiles, a.tok_tile,
+                                                                                 cta_rows, a.units, a.rem_begin, a.units_per_cta);
+        QZ_LAUNCH_CHECK();
+    }
     gemm_tc_kernel<T, PLANES, HALVES><<<(unsigned)ctas, gemm_threads<HALVES>(), smem, g_stream>>>(a);
     QZ_LAUNCH_CHECK();
 }
