@@ -506,19 +506,36 @@ __global__ void gemm_zero_split_tiles_kernel(float *__restrict__ Y, int M, int N
     }
 }
 
-// Unit i of a CTA's work (first its whole tiles, then its share of the shared part) -> (tile, K step).
+// A CTA's work: first its whole tiles (units u1 .. u1 + n1), then its share of the shared part (from u2),
+// n units in all.  A cursor walks it forwards; it divides only when it is placed and when it crosses from
+// the first range into the second.
 struct GemmShare {
-    long long u1, u2;   // first unit of the two ranges
-    int n1, n;          // units in the first range, units in all
+    long long u1, u2;
+    int n1, n;
     int ksteps;
-    __device__ void locate(int i, int &tile, int &ks) const
+    struct Cursor { int i, tile, ks; };
+    __device__ void place(Cursor &c, int i) const
     {
         const long long u = i < n1 ? u1 + i : u2 + (i - n1);
-        tile = (int)(u / ksteps);
-        ks = (int)(u - (long long)tile * ksteps);
+        c.i = i;
+        c.tile = (int)(u / ksteps);
+        c.ks = (int)(u - (long long)c.tile * ksteps);
     }
-    // units from i to the end of i's tile or of i's range, whichever comes first
-    __device__ int run(int i, int ks) const { return min(ksteps - ks, (i < n1 ? n1 : n) - i); }
+    __device__ void advance(Cursor &c, int by) const
+    {
+        if (c.i < n1 && c.i + by >= n1) {
+            place(c, c.i + by);
+            return;
+        }
+        c.i += by;
+        c.ks += by;
+        while (c.ks >= ksteps) {
+            c.ks -= ksteps;
+            c.tile++;
+        }
+    }
+    // units from the cursor to the end of its tile or of its range, whichever comes first
+    __device__ int run(const Cursor &c) const { return min(ksteps - c.ks, (c.i < n1 ? n1 : n) - c.i); }
 };
 
 // ---- the kernel.  Persistent.  The tiles of the whole problem, in tile-major unit order, are split in
@@ -586,22 +603,24 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         //                  i = g, g + 2, ... (one thread per tile row), so two units are always in
         //                  the making and one group's load latency hides behind the other's work ----
         const int r = threadIdx.x % CTA_ROWS, g = threadIdx.x / CTA_ROWS;
-        struct Cursor { int i, tile, ks; const uint8_t *rowp; };
+        struct Cursor { GemmShare::Cursor c; int tile, ks; const uint8_t *rowp; };
         auto rowp_of = [&](int tile) -> const uint8_t * {
             const int row = (tile / a.n_tok_tiles) * CTA_ROWS + r;
             return row < a.N ? a.W + (size_t)row * row_bytes : nullptr;
         };
-        auto advance = [&](Cursor &c, int by) {   // to unit c.i + by of this CTA's work
-            c.i += by;
-            int tile;
-            sh.locate(c.i, tile, c.ks);
-            if (tile != c.tile) {
-                c.tile = tile;
-                c.rowp = rowp_of(tile);
+        auto advance = [&](Cursor &c, int by) {   // `by` units further in this CTA's work
+            sh.advance(c.c, by);
+            c.ks = c.c.ks;
+            if (c.c.tile != c.tile) {
+                c.tile = c.c.tile;
+                c.rowp = rowp_of(c.tile);
             }
         };
-        Cursor ld{0, -1, 0, nullptr}, st;
-        advance(ld, g);
+        Cursor ld, st;
+        sh.place(ld.c, g);
+        ld.tile = ld.c.tile;
+        ld.ks = ld.c.ks;
+        ld.rowp = rowp_of(ld.tile);
         st = ld;
         int s = g % a.stages;
         uint32_t round = g / a.stages;
@@ -662,9 +681,9 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             int s = 0, seg = 0;
             uint32_t round = 0;
             bool ok = true, first = true;
+            GemmShare::Cursor cur;
+            sh.place(cur, 0);
             for (int i = 0; i < nunits && ok; i++) {
-                int tile_i, ks;
-                sh.locate(i, tile_i, ks);
                 ok = mbar_wait(&full_bar[s], round & 1);
                 if (ok && first && seg > 0) ok = mbar_wait(&acc_free_bar, (seg - 1) & 1);   // accumulator drained
                 if (!ok) break;
@@ -681,7 +700,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
                 }
                 tc_commit(&empty_bar[s]);   // arrives once the MMAs above have consumed the stage
                 first = false;
-                if (sh.run(i, ks) == 1) {   // the tile's last unit in this CTA's work
+                if (sh.run(cur) == 1) {   // the tile's last unit in this CTA's work
                     tc_commit(&done_bar);
                     seg++;
                     first = true;
@@ -690,6 +709,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
                     s = 0;
                     round++;
                 }
+                sh.advance(cur, 1);
             }
             if (!ok) {
                 atomicExch(a.status, QZ_ERR_TIMEOUT);
@@ -700,11 +720,12 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         // ---------------- epilogue: four warps per half (a warp reads TMEM lanes 32 * (warp % 4) ..),
         //                  one weight row per thread ----------------
         const int hf = (warp - PWARPS - 1) >> 2, quad = warp & 3;
-        int i = 0, seg = 0;
-        while (i < nunits) {
-            int tile, ks0;
-            sh.locate(i, tile, ks0);
-            const int len = sh.run(i, ks0);
+        int seg = 0;
+        GemmShare::Cursor cur;
+        sh.place(cur, 0);
+        while (cur.i < nunits) {
+            const int tile = cur.tile;
+            const int len = sh.run(cur);
             if (*(volatile int *)&abort_s || !mbar_wait_sleep(&done_bar, seg & 1, 500)) {
                 atomicExch(a.status, QZ_ERR_TIMEOUT);
                 abort_s = 1;
@@ -735,7 +756,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_free_bar);
-            i += len;
+            sh.advance(cur, len);
             seg++;
         }
     }

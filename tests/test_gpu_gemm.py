@@ -58,6 +58,18 @@ def test_gemm_every_format(gpu, oracle_mod, t):
         _check(oracle_mod, y, X, w, t, K, N)
 
 
+@pytest.mark.parametrize("t,repack,M,N", [(12, False, 130, 38400 + 56), (14, True, 16, 300 * 128 + 8), (12, False, 300, 19000)])
+def test_gemm_more_tiles_than_ctas(gpu, oracle_mod, t, repack, M, N):
+    """More tiles than resident CTAs: every CTA first owns whole tiles (plain stores), the remaining tiles
+    are cut into shares of K steps and added atomically.  Both parts and the ragged last row tile are checked."""
+    from saient_quartz_b200 import synth
+    K = 1024
+    w = synth.make_weights(t, K, N, tensor_id=751)
+    X = synth.make_x(K, tensor_id=752, rows=M)
+    y = _gemm(gpu, t, w, X, K, N, repack)
+    _check(oracle_mod, y, X, w, t, K, N)
+
+
 def test_gemm_m1_is_gemv_and_odd_k_falls_back(gpu, oracle_mod):
     from saient_quartz_b200 import synth
     K, N = 4096, 256
