@@ -680,7 +680,9 @@ static void launch_gemm(GemmArgs a)
     a.units_per_cta = sharers > 0 ? (rem + sharers - 1) / sharers : 0;
     if (whole == 0) ctas = (a.units + a.units_per_cta - 1) / a.units_per_cta;
     if (rem > 0) {
-        gemm_zero_split_tiles_kernel<<<dim3((unsigned)ctas, 8), 256, 0, g_stream>>>(a.Y, a.M, a.N, ksteps, a.n_tok_tiles, a.tok_tile,
+        // narrow token tiles are a few KB per tile: one block each; wide ones are split over up to 8
+        const unsigned zero_slices = (unsigned)std::max(1, std::min(8, a.tok_tile / 32));
+        gemm_zero_split_tiles_kernel<<<dim3((unsigned)ctas, zero_slices), 256, 0, g_stream>>>(a.Y, a.M, a.N, ksteps, a.n_tok_tiles, a.tok_tile,
                                                                                  cta_rows, a.units, a.rem_begin, a.units_per_cta);
         QZ_LAUNCH_CHECK();
     }
