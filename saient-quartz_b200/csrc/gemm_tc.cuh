@@ -480,13 +480,15 @@ template <int HALVES>
 constexpr int gemm_threads() { return 2 * 128 * HALVES + 32 + 128 * HALVES; }   // producers, MMA warp, epilogue warps
 
 // ---- zero the output tiles that more than one CTA contributes to (their partial sums are added
-//      atomically).  blockIdx.x = CTA of the GEMM grid: a CTA whose share of the shared part begins
-//      strictly inside a tile's K range marks that tile as shared; blockIdx.y = slice of the tile's tokens. ----
+//      atomically).  blockIdx.x = CTA of the GEMM grid: the first CTA whose share of the shared part begins
+//      strictly inside a tile's K range zeroes that tile; blockIdx.y = slice of the tile's tokens. ----
 __global__ void gemm_zero_split_tiles_kernel(float *__restrict__ Y, int M, int N, int ksteps, int n_tok_tiles, int tok_tile,
                                              int cta_rows, long long units, long long rem_begin, long long units_per_cta)
 {
     const long long u0 = rem_begin + (long long)blockIdx.x * units_per_cta;
-    if (u0 >= units || u0 % ksteps == 0) return;
+    if (u0 >= units) return;
+    const long long off = u0 % ksteps;
+    if (off == 0 || off > units_per_cta) return;   // not inside a tile, or not the first share to begin inside it
     const int tile = (int)(u0 / ksteps);
     const int row0 = (tile / n_tok_tiles) * cta_rows, tok0 = (tile % n_tok_tiles) * tok_tile;
     const int rows = min(cta_rows, N - row0), toks = min(tok_tile, M - tok0);
