@@ -4,8 +4,9 @@
 // The reference has no batched GPU path at all (its GPU prefill is token-by-token GEMV,
 // src/main.rs:1410-1416); its CPU form is dequant::gemm (src/dequant.rs:143-200).
 //
-// Persistent kernel, one CTA per SM (two for narrow token tiles).  The (row tile, token tile, K step)
-// units of the whole problem, tile-major, are cut into one equal contiguous share per CTA; a tile is
+// Persistent kernel, one CTA per SM (two for narrow token tiles).  Every CTA first takes as many whole
+// tiles as all CTAs can get; the (row tile, token tile, K step) units of the remaining tiles, tile-major,
+// are cut into one equal contiguous share per CTA.  A tile is
 // 128 or 256 weight rows (one or two UMMA M=128 accumulators side by side in TMEM) x up to 256 tokens
 // (the UMMA N dimension).  Per 64-wide K step of a tile:
 //   * producer warps -- two groups that take alternate K steps, one thread per weight row --
@@ -20,7 +21,7 @@
 //     f32 in TMEM) and a tcgen05.commit that arrives on the stage's "empty" mbarrier when the tensor
 //     core has finished reading the stage.
 // A 3-4 stage ring lets dequantization run ahead of the MMAs.  Dedicated epilogue warps read a finished
-// tile's accumulator with tcgen05.ld (32 lanes x 8 columns per instruction), one weight row per thread,
+// tile's accumulator with tcgen05.ld (32 lanes x 32 columns per instruction), one weight row per thread,
 // and store it -- or, for a tile that two CTAs share, add it atomically onto zeros -- into the
 // token-major output, then hand the accumulator back to the MMA thread.
 //
