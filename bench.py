@@ -186,6 +186,93 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def gemv_shape_rows(q, L, torch, np, shapes, mats, xs, with_ref, want_parity):
+    """One row per shape of the sweep: cuda_gemv (activation conversion included) over rotating copies of the
+    matrix that together exceed the L2, recorded as one graph and replayed, so the figure is graph-amortised
+    and HBM-fed.  With with_ref the reference's own CUDA kernels (built unmodified for sm_100a, when they were
+    built) run the same shape in the same loop, eagerly, as the same-box GPU baseline; with want_parity every
+    shape's output is checked against the CPU oracle."""
+    from saient_quartz_b200 import synth
+    peak, _ = peaks()
+    R = None
+    if with_ref:
+        import oracle
+        from saient_quartz_b200.iq_tables import load_tables
+        R = oracle.ref_kernels()
+        if R is not None:
+            tb = load_tables()
+            for name in ("iq3s", "iq2s", "iq2xxs", "iq2xs"):
+                getattr(R, f"cuda_set_{name}_grid")(tb[name].ctypes.data)
+            R.cuda_set_ksigns(tb["ksigns"].ctypes.data)
+    rows = []
+    for (label, t, K, N), w, x in zip(shapes, mats["w"], xs):
+        nbytes = synth.type_size(t, K * N)
+        copies = max(2, min(96, int(np.ceil(260e6 / nbytes))))
+        bufs = []
+        for _ in range(copies):
+            b = q.GpuBuf.upload(w)
+            L.cuda_repack_weights(t, b.ptr, K, N, 1)
+            bufs.append(b)
+        dx, dy = q.GpuBuf.upload(x), q.GpuBuf.alloc_f32(N)
+
+        def run():
+            for b in bufs:
+                L.cuda_gemv(t, b.ptr, dx.ptr, dy.ptr, K, N)
+        run()
+        L.cuda_sync()
+        g = None
+        if L.quartz_graph_begin():
+            run()
+            g = L.quartz_graph_end()
+        q.check_error("per-shape graph capture")
+        fn = (lambda: L.quartz_graph_launch(g)) if g else run
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+        by = synth.algorithmic_bytes(t, K, N)
+        row = {"shape": label, "us": us, "gbs": by / us / 1e3, "frac_of_measured_hbm": by / us / 1e3 / peak,
+               "frac_of_8TBs_nominal": by / us / 1e3 / 8000.0, "copies": copies,
+               "launch": "graph replay" if g else "eager"}
+        if g:
+            L.quartz_graph_destroy(g)
+        if want_parity:
+            import oracle
+            ref = oracle.gemv(x, w, t, K, N)
+            tol = oracle.tolerance(w, t, K, N, x)
+            err = np.abs(dy.download().astype(np.float64) - ref)
+            row["max_err_over_tolerance"] = float(np.max(err / tol))
+            assert np.all(err <= tol), f"bench output of {label} failed the parity bound"
+        if R is not None:
+            raw = [q.GpuBuf.upload(w) for _ in range(min(copies, 24))]
+            for i in range(3):
+                R.cuda_gemv(t, raw[i % len(raw)].ptr, dx.ptr, dy.ptr, K, N)
+            torch.cuda.synchronize()
+            n = 2 * len(raw)
+            e0.record()
+            for i in range(n):
+                R.cuda_gemv(t, raw[i % len(raw)].ptr, dx.ptr, dy.ptr, K, N)
+            e1.record()
+            torch.cuda.synchronize()
+            rus = e0.elapsed_time(e1) * 1e3 / n
+            row["ref_cuda_kernels"] = {"us": rus, "gbs": by / rus / 1e3, "launch": "eager",
+                                       "what": "the reference's own kernel for this format, compiled unmodified for sm_100a"}
+            for b in raw:
+                b.drop()
+        for b in bufs + [dx, dy]:
+            b.drop()
+        q.check_error("per-shape rows")
+        rows.append(row)
+    return rows
+
+
 def gemm_section(q, args, torch, np, want_parity, only=None):
     """Batched dequant-GEMM for prefill: Q4_K 4096->14336 and Q6_K 14336->4096 times M = 16, 64, 512, 2048
     f32 activations ~ N(0,1) (bf16 inside the tensor-core tile, f32 accumulation in TMEM)."""
@@ -254,9 +341,10 @@ def gemm_section(q, args, torch, np, want_parity, only=None):
 
 
 def decode_section(q, args, torch, np, want_parity, fused_only=False):
-    """Full batch-1 decode step of a random-init Llama-3-8B-architecture model in the fixed
-    Q4_K_M-style layout (q/k/v/o/gate/up Q4_K, down + output head Q6_K), f32 KV cache pre-filled
-    with N(0,1) at context 1024, decoding position 1024."""
+    """Full batch-1 decode of a random-init Llama-3-8B-architecture model in the fixed Q4_K_M-style layout
+    (q/k/v/o/gate/up Q4_K, down + output head Q6_K), f32 KV cache pre-filled with N(0,1) at context 1024.
+    The headline leg is a GENERATION LOOP: 64 consecutive positions 1024..1087 with 64 different token ids;
+    the step is recorded once (token id and position are device words) and replayed per token."""
     from saient_quartz_b200.host_model import HostModel, LLAMA3_8B
     L = q.lib()
     t0 = time.perf_counter()
@@ -264,56 +352,93 @@ def decode_section(q, args, torch, np, want_parity, fused_only=False):
     m.fill_synthetic()
     kv = m.fill_kv(1024, keep=want_parity)
     build_s = time.perf_counter() - t0
-    token, pos = 4242, 1024
+    pos0, n_gen = 1024, 64
+    rng = np.random.Generator(np.random.PCG64([0x5EED0001, 4242]))
+    tokens = [int(v) for v in rng.integers(0, LLAMA3_8B["vocab_size"], size=n_gen)]
     kv_bytes = 32 * 2 * 1025 * 1024 * 4
     bytes_per_token = m.weight_bytes + kv_bytes
     out = {"model": "llama-3-8b architecture, random init, Q4_K_M-style layout", "context": 1024,
            "bytes_per_token": bytes_per_token, "build_s": round(build_s, 1)}
     peak, _ = peaks()
+
+    def rates(ms):
+        return {"tok_s": 1e3 / ms, "ms_per_token": ms, "gbs": bytes_per_token / (ms * 1e-3) / 1e9,
+                "frac_of_measured_hbm": bytes_per_token / (ms * 1e-3) / 1e9 / peak}
+
     for name, fused in (("chained_graph", 2), ("fused_graph", 1), ("reference_sequence", 0)):
         if fused_only and not fused:
             continue
-        for _ in range(3):
-            m.step_device(token, pos, fused)
+        # device time of a generation loop: every step another token and the next position
+        n = n_gen if fused else 8
+        for i in range(3):
+            m.step_device(tokens[i], pos0 + i, fused)
         torch.cuda.synchronize()
-        n = max(5, min(args.steps, 20))
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(n):
-            m.step_device(token, pos, fused)
+        for i in range(n):
+            m.step_device(tokens[i], pos0 + i, fused)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / n
-        out[name] = {"tok_s": 1e3 / ms, "ms_per_token": ms, "launches_per_token": m.launches(),
-                     "gbs": bytes_per_token / (ms * 1e-3) / 1e9,
-                     "frac_of_measured_hbm": bytes_per_token / (ms * 1e-3) / 1e9 / peak}
+        out[name] = dict(rates(ms), launches_per_token=m.launches(), steps_timed=n,
+                         what="generation loop: consecutive positions from 1024, a different token id per step")
+        if fused:
+            # the same step replayed with a FIXED (token, position): what a replay-only figure would read
+            e0.record()
+            for i in range(20):
+                m.step_device(tokens[0], pos0, fused)
+            e1.record()
+            torch.cuda.synchronize()
+            out[name]["fixed_position_replay_ms"] = e0.elapsed_time(e1) / 20
+            out[name]["graphs_recorded"] = m.graphs_recorded()
         q.check_error("decode " + name)
     if fused_only:
         m.close()
         return out
-    # end to end as the host sees it: token in, 513 KB of logits out, per step
-    n = 5
-    t1 = time.perf_counter()
     best = 2 if out["chained_graph"]["ms_per_token"] <= out["fused_graph"]["ms_per_token"] else 1
-    for _ in range(n):
-        logits = m.step(token, pos, fused=best)
-    out["e2e_tok_s"] = n / (time.perf_counter() - t1)
-    out["e2e_sequence"] = "chained" if best == 2 else "fused"
+    # THE decode figure: generation loop, host to host -- token id in, 513 KB of logits out, every step,
+    # including whatever graph work the host does
+    logits = None
+    m.step(tokens[0], pos0, fused=best)
+    t1 = time.perf_counter()
+    for i in range(n_gen):
+        logits = m.step(tokens[i], pos0 + i, fused=best)
+    wall = time.perf_counter() - t1
+    out["generation_loop"] = dict(rates(wall / n_gen * 1e3), sequence="chained" if best == 2 else "fused", steps=n_gen,
+                                  positions=[pos0, pos0 + n_gen - 1], graphs_recorded=m.graphs_recorded(),
+                                  what="host to host: per step the token id goes in and 513 KB of logits come out; host wall clock")
+    out["e2e_tok_s"] = out["generation_loop"]["tok_s"]
+    out["e2e_sequence"] = out["generation_loop"]["sequence"]
     if want_parity:
         import oracle
         from oracle.forward_ref import RefModel
         from saient_quartz_b200.iq_tables import load_tables
         oracle.set_tables(load_tables())
+        # (1) the first step of the loop against the CPU oracle, from the seeded cache alone
         r = RefModel(m.cfg, m.host)
         for l, (k, v) in enumerate(kv):
             r.set_kv(l, k, v)
+        first = m.step(tokens[0], pos0, fused=best)
         t2 = time.perf_counter()
-        want = r.forward(token, pos)
+        want = r.forward(tokens[0], pos0)
         cpu_s = time.perf_counter() - t2
-        rel = float(np.abs(logits.astype(np.float64) - want).max() / np.abs(want).max())
+        rel = float(np.abs(first.astype(np.float64) - want).max() / np.abs(want).max())
         out["parity_max_rel_err_vs_cpu_oracle"] = rel
         out["cpu_oracle_tok_s"] = 1.0 / cpu_s
         assert rel < 5e-3, f"decode-step logits differ from the CPU oracle: {rel}"
+        # (2) the LAST step of the loop: the oracle takes the cache rows the 63 steps before it appended on
+        # the device (a CPU replay of all 64 steps would take a minute) and must reproduce its logits
+        m.fill_kv(1024)
+        for i in range(n_gen):
+            logits = m.step(tokens[i], pos0 + i, fused=best)
+        r2 = RefModel(m.cfg, m.host)
+        for l, (k, v) in enumerate(kv):
+            k2, v2 = m.read_kv(l, pos0, n_gen - 1)
+            r2.set_kv(l, np.concatenate([k, k2]), np.concatenate([v, v2]))
+        want = r2.forward(tokens[-1], pos0 + n_gen - 1)
+        rel = float(np.abs(logits.astype(np.float64) - want).max() / np.abs(want).max())
+        out["generation_loop"]["last_step_max_rel_err_vs_cpu_oracle"] = rel
+        assert rel < 5e-3, f"last step of the generation loop differs from the CPU oracle: {rel}"
     m.close()
     return out
 
@@ -497,8 +622,6 @@ def main():
     dev = local_rank if world > 1 else 0
     phys_index = ids[dev] if ids and dev < len(ids) else str(dev)
 
-    if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"   # NCCL's version banner goes to stdout, which carries the JSON line
     import numpy as np
     import torch
     import __graft_entry__ as entry
@@ -899,6 +1022,11 @@ def main():
         tol = oracle.tolerance(mats["w"][i], t, K, N, xs[i])
         assert np.all(np.abs(got - ref) <= tol), "bench output failed the parity bound"
 
+    shape_rows = None
+    if rank == 0 and world == 1:
+        shape_rows = gemv_shape_rows(q, L, torch, np, shapes, mats, xs, with_ref=not args.no_cpu_baseline and not args.small,
+                                     want_parity=not args.no_cpu_baseline)
+
     decode = None
     if rank == 0 and world == 1 and not args.small and not args.no_decode:
         decode = decode_section(q, args, torch, np, want_parity=not args.no_cpu_baseline)
@@ -936,6 +1064,7 @@ def main():
                                     "d2h_bytes_per_step": 0, "note": "multi-GPU: operands resident"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
+            "gemv_shapes": shape_rows,
             "decode": decode,
             "gemm": gemm,
             "batched_single_launch": batched,

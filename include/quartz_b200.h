@@ -99,8 +99,10 @@ void quartz_set_stream(void *cuda_stream);
 long long quartz_launch_count(void);
 
 /* Which streaming GEMV serves the formats that have one: 0 = TMA-staged shared-memory ring
- * (default), 1 = register-streaming 128-bit loads.  For A/B measurements; results are
- * bit-identical.  The environment variable QUARTZ_GEMV_IMPL=ldg selects 1 at start-up. */
+ * (default), 1 = register-streaming 128-bit loads.  For A/B measurements; both run the same
+ * per-format integer dot products on the same converted activations and differ only in the
+ * order in which a row's partial sums are added.  The environment variable
+ * QUARTZ_GEMV_IMPL=ldg selects 1 at start-up. */
 void quartz_set_gemv_impl(int impl);
 
 /* The IQ3_XXS codebook (256 x u32); the reference has no IQ3_XXS. */
@@ -129,8 +131,17 @@ void cuda_dequant(uint32_t ggml_type, const uint8_t *d_data, float *d_out, int i
  * on every GPU that loads it) instead of a buffer obtained with cudaMalloc at first use; the
  * call makes no cudaMalloc/cudaFree and uses no allocating library routine.
  *   - limit: in_dim <= 32768; larger sizes set QZ_ERR_TOO_LARGE and leave d_y untouched.
- *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress);
- *     make that first call before starting any stream capture on that device.
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress), and the
+ *     first call with an IQ2_XXS / IQ2_XS / IQ3_XXS matrix uploads the default sign table when the
+ *     host has not called cuda_set_ksigns (a synchronous copy into a library table, no allocation);
+ *     make those first calls before starting any stream capture on that device.
+ *   - it never carries a fused exchange wait: a pending quartz_mgpu_fuse_next_wait() runs as a wait
+ *     kernel of its own if the library's status word exists already (any earlier quartz_mgpu_wait
+ *     or streaming GEMV created it) and is refused with QZ_ERR_BAD_SHAPE otherwise, because
+ *     creating that word takes a cudaMalloc.
+ *   - every block format that has a streaming kernel uses the built-in scratch; shapes and
+ *     pointers the streaming kernel does not take (in_dim not a multiple of 64, unaligned rows)
+ *     run the any-shape kernel, which needs no scratch at all.
  *   - all calls share the one array: two calls whose kernels can overlap on the GPU (different
  *     streams) race on it; calls on one stream are safe.  Nothing in it needs clearing between
  *     calls -- each call rewrites what it reads. */
@@ -163,6 +174,36 @@ void cuda_rope_kv(float *q, float *k, const float *v, float *k_cache, float *v_c
 void cuda_attn_decode(float *out, const float *q, const float *k_cache, const float *v_cache, int n_heads,
                       int n_kv_heads, int seq_len, int head_dim, int kv_dim, float scale, const float *sinks,
                       int out_slot);
+
+/* ---- A decode step whose position and token id live in DEVICE memory, so that ONE recorded graph serves
+ * every step of a generation loop (the reference passes `token` and `pos` to forward_gpu_step per call,
+ * src/cuda.rs:507-851, and bakes them into its launches).  d_step points at two ints on the device:
+ * d_step[0] = token id, d_step[1] = position.
+ *   cuda_step_set          enqueue the update of the two words (a one-thread kernel with the values as
+ *                          arguments: the host may call it again at once, nothing is read from host memory
+ *                          later).  It runs on the stream recorded graphs replay on, so "set, replay, set,
+ *                          replay ..." needs no synchronisation.
+ *   cuda_embed_lookup_dev  cuda_embed_lookup of row d_step[0]
+ *   cuda_attn_step         the whole attention block of the step in ONE launch whose grid does not depend on
+ *                          the position: RoPE on q and k, append of k and v at the position, attention of all
+ *                          heads over cache positions [k_start, pos], merge, and with out_slot >= 0 the
+ *                          activation form of the result (cuda_rope_yarn x2 + cuda_kv_append +
+ *                          cuda_attn_score_all + cuda_softmax_sink_all + cuda_attn_values_all,
+ *                          src/cuda.rs:601-645).  q / k_new / v_new are the projections BEFORE RoPE and are
+ *                          left untouched; caches are [max_seq][n_kv_heads*head_dim].  The position comes from
+ *                          d_step[1] when d_step is not NULL, else from `pos`; positions >= max_seq are
+ *                          clamped to max_seq-1 (src/cuda.rs:517-520).  window > 0: k_start = max(0, pos+1-window)
+ *                          (the sliding-window layers of src/main.rs:231-237), else 0.  sinks may be NULL.
+ *                          One thread-block cluster per kv head; its CTAs split the context and merge their
+ *                          partial results through distributed shared memory.  head_dim a multiple of 32 up to
+ *                          128, at most 16 query heads per kv head (cuda_attn_step_supported tells). */
+void cuda_step_set(int *d_step, int token, int pos);
+void cuda_embed_lookup_dev(float *out, const uint8_t *data, uint32_t ggml_type, const int *d_step, int embed_dim);
+int cuda_attn_step_supported(int n_heads, int n_kv_heads, int head_dim);
+void cuda_attn_step(float *out, const float *q, const float *k_new, const float *v_new, float *k_cache, float *v_cache,
+                    int n_heads, int n_kv_heads, int head_dim, int max_seq, const int *d_step, int pos, int window,
+                    float scale, const float *sinks, float theta, float yarn_scale, int yarn_orig_ctx, int neox,
+                    int out_slot);
 
 /* A chain of dependent GEMVs as ONE persistent kernel (one CTA per SM): op k+1's activation vector is
  * computed from op k's outputs after a grid-wide barrier inside the kernel, while the weight rows of
@@ -256,15 +297,30 @@ void cuda_gemm_bf16(uint32_t ggml_type, const uint8_t *d_data, const uint16_t *d
  * expert GEMV of every token is its own launch, src/cuda.rs:673-800).  d_gate / d_up / d_down point at
  * the stacked expert tensors ([in_dim, out_dim, n_experts]: expert e at byte offset e * size(one
  * matrix), src/main.rs:941-950, src/cuda.rs:250-257); raw or repacked (cuda_repack_weights with
- * n_mats = n_experts).  Routing is decided by the host, as in the reference (src/cuda.rs:673-701):
- * h_expert_ids / h_expert_w are HOST arrays of m * top_k entries (token-major), the weights already
- * normalised.  d_x is [m, embed_dim], d_out [m, embed_dim], both f32 on the device.  The library
- * groups the assignments by expert, gathers the rows, runs three cuda_gemm per expert and scatters the
- * weighted results back; the sum over a token's experts is taken in expert order.  oai = 1 selects
- * the clamped SwiGLU (cuda_swiglu_oai).  Synchronises the stream once (the routing lists are copied). */
+ * n_mats = n_experts).  d_x is [m, embed_dim], d_out [m, embed_dim], both f32 on the device.  The routing
+ * lists hold m * top_k entries, token-major, the weights already normalised.
+ *   cuda_moe_ffn       routing lists in HOST memory (the reference routes on the host, src/cuda.rs:673-701)
+ *   cuda_moe_ffn_dev   routing lists in DEVICE memory (e.g. written by cuda_router_topk): no host involvement
+ * Both group the assignments by expert on the device and run ONE tensor-core launch for gate and up of all
+ * experts and one for down (tiles of every expert in one persistent grid), the SwiGLU between them and the
+ * weighted sum of a token's experts in the order of its list; nothing synchronises with the host.  Shapes the
+ * grouped kernel does not take (in_dim not a multiple of 64, unaligned rows, more than 256 experts) run
+ * expert by expert with the assignments grouped on the host.  oai = 1 selects the clamped SwiGLU
+ * (cuda_swiglu_oai).  Output tiles that two CTAs share are summed atomically (summation order of those
+ * elements is not fixed). */
 void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
                   const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim, int n_experts,
                   int top_k, const int *h_expert_ids, const float *h_expert_w, int oai);
+void cuda_moe_ffn_dev(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
+                      const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim, int n_experts,
+                      int top_k, const int *d_expert_ids, const float *d_expert_w, int oai);
+/* The router's top-k on the device (the reference copies the logits to the host, synchronises and sorts
+ * there, src/cuda.rs:673-701): for each of m rows of d_logits [m, n_experts] (+ d_bias [n_experts] when not
+ * NULL) the top_k largest entries, ties to the lower index, into d_ids [m, top_k], and their weights into
+ * d_w: renorm = 1 softmax over the selected logits, 0 softmax over all experts (src/main.rs:979-986).
+ * n_experts <= 256, top_k <= 8. */
+void cuda_router_topk(const float *d_logits, const float *d_bias, int m, int n_experts, int top_k, int renorm, int *d_ids,
+                      float *d_w);
 
 /* ---- Row-sharded layers over the GPUs of one box (one process per GPU).  No counterpart in the
  * reference, which drives a single device (src/cuda.rs:301-358).  A layer's weight rows are split

@@ -18,7 +18,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libquartz_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libkernels_ref.so")
-REF_CU = os.environ.get("QUARTZ_REFERENCE_ROOT", "/root/reference") + "/src/cuda_kernels.cu"
+
+
+def reference_root():
+    """Where the reference project is mounted: the environment variable QUARTZ_REFERENCE_ROOT, else a
+    directory named `reference` beside this repository; None when neither exists."""
+    cand = os.environ.get("QUARTZ_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src")) else None
+
 
 
 def _newer(target, *sources):
@@ -43,14 +50,16 @@ def build_oracle(force=False):
 
 def build_ref(force=False):
     """Compile the reference's CUDA kernels (GPU A/B baseline and secondary check)."""
-    if not os.path.exists(REF_CU):
+    root = reference_root()
+    ref_cu = os.path.join(root, "src", "cuda_kernels.cu") if root else None
+    if not ref_cu or not os.path.exists(ref_cu):
         return REF_SO if os.path.exists(REF_SO) else None
-    if not force and _newer(REF_SO, REF_CU):
+    if not force and _newer(REF_SO, ref_cu):
         return REF_SO
     os.makedirs(REF_DIR, exist_ok=True)
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
     cmd = [nvcc, "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC",
-           "-o", REF_SO, REF_CU]
+           "-o", REF_SO, ref_cu]
     subprocess.check_call(cmd, stderr=subprocess.DEVNULL)
     return REF_SO
 

@@ -30,9 +30,11 @@ def build_host(force=False):
     if (not force and os.path.exists(HOST_LIB)
             and all(os.path.getmtime(p) <= os.path.getmtime(HOST_LIB) for p in srcs + [LIB] + hdrs)):
         return HOST_LIB
-    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", HOST_LIB] + srcs + ["-L" + HERE, "-lquartz_b200",
+    tmp = HOST_LIB + ".tmp"
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", tmp] + srcs + ["-L" + HERE, "-lquartz_b200",
            "-Wl,-rpath,$ORIGIN"]
     subprocess.check_call(cmd)
+    os.replace(tmp, HOST_LIB)   # a reader never sees a half-written library
     return HOST_LIB
 
 
@@ -43,12 +45,14 @@ def build(force=False, verbose=False):
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
     arch = os.environ.get("QUARTZ_CUDA_ARCH", "sm_100a")   # same variable as the reference's build.rs:33
     cc = arch.replace("sm_", "compute_")
+    tmp = LIB + ".tmp"
     cmd = [nvcc, "-O3", "-std=c++17", "-gencode", f"arch={cc},code={arch}", "-lineinfo", "-shared",
-           "-Xcompiler", "-fPIC", "-o", LIB] + [s for s in sources() if s.endswith(".cu")]
+           "-Xcompiler", "-fPIC", "-o", tmp] + [s for s in sources() if s.endswith(".cu")]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     subprocess.check_call(cmd)
+    os.replace(tmp, LIB)
     build_host(force=True)
     return LIB
 

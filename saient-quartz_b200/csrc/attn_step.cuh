@@ -1,0 +1,287 @@
+// The attention block of one decode step as ONE launch whose shape does not depend on the
+// position: RoPE on q and k, append of k and v at `pos`, attention of every head over cache
+// positions [k_start, pos], merge, and (optionally) the activation form of the result for the
+// output projection (cuda_rope_yarn x2 + cuda_kv_append + cuda_attn_score_all +
+// cuda_softmax_sink_all + cuda_attn_values_all of the reference, src/cuda.rs:601-645).
+//
+// The position is read from a device word, so a recorded graph serves every step of a
+// generation loop.  Grid = n_kv_heads clusters of CL CTAs (thread-block clusters, CL <= 16): the
+// CL CTAs of a kv head split the context into 32-position blocks, each runs an online softmax
+// over its blocks for all query heads of the kv head (K and V rows are staged once per CTA and
+// shared by the head group), and the partial (max, sum, out[head_dim]) triples are merged through
+// distributed shared memory: after a cluster barrier CTA r reads slice r of every peer's
+// partials and finishes G*head_dim/CL outputs.  No global scratch, no second launch, no atomics.
+#pragma once
+
+#include <cooperative_groups.h>
+
+#include "fused_ops.cuh"
+
+namespace qz {
+
+constexpr int AS_THREADS = 256;
+constexpr int AS_WARPS = AS_THREADS / 32;
+constexpr int AS_CHUNK = 64;             // positions staged per round (two 32-position halves)
+constexpr int AS_MAX_G = 16;             // query heads per kv head
+constexpr int AS_KS_STRIDE = ATT_MAX_HD + 4;   // floats; keeps float4 rows conflict-free across a quarter warp
+
+struct AttnStepArgs {
+    float *out;
+    const float *q, *k_new, *v_new;      // projections before RoPE
+    float *k_cache, *v_cache;            // [max_seq][kv_dim]
+    const int *step;                     // device words {token, pos}; NULL: pos_host
+    int pos_host;
+    int n_heads, n_kv_heads, head_dim, kv_dim, max_seq;
+    int window;                          // > 0: attend to the last `window` positions only
+    float scale;
+    const float *sinks;
+    float theta, yarn_scale;
+    int yarn_orig_ctx, neox;
+    XQOut o;
+    int emit_q;
+};
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// dynamic shared memory: ks [AS_CHUNK][AS_KS_STRIDE], vs [AS_CHUNK][ATT_MAX_HD], qs [G][ATT_MAX_HD],
+// ps [AS_WARPS][32], wres [AS_WARPS][2][ATT_MAX_HD + 2] (per-warp partials), res [G][ATT_MAX_HD + 2]
+__host__ __device__ inline size_t attn_step_smem(int G)
+{
+    return sizeof(float) * ((size_t)AS_CHUNK * AS_KS_STRIDE + (size_t)AS_CHUNK * ATT_MAX_HD + (size_t)G * ATT_MAX_HD +
+                            AS_WARPS * 32 + (size_t)AS_WARPS * 2 * (ATT_MAX_HD + 2) + (size_t)G * (ATT_MAX_HD + 2) + ATT_MAX_HD);
+}
+
+__global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArgs a)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CL = (int)cluster.num_blocks();
+    const int rank = (int)cluster.block_rank();
+    extern __shared__ __align__(16) float smem[];
+    const int hd = a.head_dim, half = hd >> 1, hd4 = hd >> 2;
+    const int G = a.n_heads / a.n_kv_heads;
+    float *ks = smem;
+    float *vs = ks + AS_CHUNK * AS_KS_STRIDE;
+    float *qs = vs + AS_CHUNK * ATT_MAX_HD;
+    float *ps = qs + G * ATT_MAX_HD;
+    float *wres = ps + AS_WARPS * 32;
+    float *res = wres + AS_WARPS * 2 * (ATT_MAX_HD + 2);
+    float2 *cs_tab = (float2 *)(res + G * (ATT_MAX_HD + 2));   // (cos, sin) per rotation pair
+    constexpr int RS = ATT_MAX_HD + 2;
+
+    const int kvh = blockIdx.x / CL;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h_lo = kvh * G;
+
+    pdl_wait();
+    pdl_trigger();
+    int pos = a.step ? a.step[1] : a.pos_host;
+    if (pos >= a.max_seq) pos = a.max_seq - 1;   // never write past the caches (src/cuda.rs:517-520)
+    if (pos < 0) pos = 0;
+    const int k_start = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
+    const int seq_len = pos - k_start + 1;
+
+    // this CTA's share of the context, in 32-position blocks
+    const int nblk = (seq_len + 31) >> 5;
+    const int base = nblk / CL, rem = nblk % CL;
+    const int b0 = rank * base + min(rank, rem), bcnt = base + (rank < rem ? 1 : 0);
+    const int p_lo = 32 * b0, p_hi = min(32 * (b0 + bcnt), seq_len);   // relative to k_start
+    const bool owns_new = bcnt > 0 && p_hi == seq_len;
+
+    // rotation table of this position, then the rotated queries of the head group
+    if (threadIdx.x < half) {
+        const RopeArgs r{pos, a.theta, a.yarn_scale, a.yarn_orig_ctx, a.neox};
+        float c, s;
+        rope_cs(r, threadIdx.x, hd, c, s);
+        cs_tab[threadIdx.x] = make_float2(c, s);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * half; idx += AS_THREADS) {
+        const int g = idx / half, i = idx - g * half;
+        const float2 cs = cs_tab[i];
+        const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
+        const float *qh = a.q + (size_t)(h_lo + g) * hd;
+        const float x0 = qh[i0], x1 = qh[i1];
+        qs[g * ATT_MAX_HD + i0] = x0 * cs.x - x1 * cs.y;
+        qs[g * ATT_MAX_HD + i1] = x0 * cs.y + x1 * cs.x;
+    }
+
+    // which (head, half-chunk) this warp serves
+    const int Gw = G < AS_WARPS ? G : AS_WARPS;
+    const int wph = G <= 4 ? 2 : 1;                       // warps per head: a chunk is wph x 32 positions
+    const int n_rounds = (G + AS_WARPS - 1) / AS_WARPS;   // heads per warp (G > 8)
+    const int sub = warp / Gw;
+    const bool warp_active = sub < wph;
+    const int chunk = 32 * wph;
+    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
+    float o_run[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+
+    const float *kc = a.k_cache + (size_t)k_start * a.kv_dim + (size_t)kvh * hd;
+    const float *vc = a.v_cache + (size_t)k_start * a.kv_dim + (size_t)kvh * hd;
+
+    for (int c0 = p_lo; c0 < p_hi; c0 += chunk) {
+        const int n = min(chunk, p_hi - c0);
+        const bool has_new = owns_new && c0 + n == seq_len;   // the new position is this chunk's last row
+        const int n_old = has_new ? n - 1 : n;
+        __syncthreads();   // the previous round's rows are no longer read (also orders qs / cs_tab)
+        for (int idx = threadIdx.x; idx < n_old * hd4; idx += AS_THREADS) {
+            const int t = idx / hd4, c = idx - t * hd4;
+            const size_t g = (size_t)(c0 + t) * a.kv_dim + 4 * c;
+            cp_async16(ks + t * AS_KS_STRIDE + 4 * c, kc + g);
+            cp_async16(vs + t * ATT_MAX_HD + 4 * c, vc + g);
+        }
+        if (has_new) {
+            // the new key (rotated) and value: into the caches and into this chunk's last row
+            const float *kh = a.k_new + (size_t)kvh * hd, *vh = a.v_new + (size_t)kvh * hd;
+            float *kd = a.k_cache + (size_t)pos * a.kv_dim + (size_t)kvh * hd;
+            float *vd = a.v_cache + (size_t)pos * a.kv_dim + (size_t)kvh * hd;
+            for (int i = threadIdx.x; i < half; i += AS_THREADS) {
+                const float2 cs = cs_tab[i];
+                const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
+                const float x0 = kh[i0], x1 = kh[i1];
+                const float r0 = x0 * cs.x - x1 * cs.y, r1 = x0 * cs.y + x1 * cs.x;
+                kd[i0] = r0;
+                kd[i1] = r1;
+                ks[(n - 1) * AS_KS_STRIDE + i0] = r0;
+                ks[(n - 1) * AS_KS_STRIDE + i1] = r1;
+            }
+            for (int j = threadIdx.x; j < hd; j += AS_THREADS) {
+                const float v = vh[j];
+                vd[j] = v;
+                vs[(n - 1) * ATT_MAX_HD + j] = v;
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        if (!warp_active) continue;
+        const int t_lo = 32 * sub;             // this warp's rows inside the chunk
+        const int nt = min(32, n - t_lo);      // may be <= 0
+        if (nt <= 0) continue;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            if (r >= n_rounds) break;
+            const int g = (warp % Gw) + r * AS_WARPS;
+            if (g >= G) break;
+            // one key position per lane
+            const float4 *qv = (const float4 *)(qs + g * ATT_MAX_HD);
+            const float4 *kv = (const float4 *)(ks + (t_lo + lane) * AS_KS_STRIDE);
+            float c0a = 0.f, c1a = 0.f, c2a = 0.f, c3a = 0.f;
+            for (int i = 0; i < hd4; i++) {
+                const float4 qq = qv[i], kk = kv[i];
+                c0a = fmaf(qq.x, kk.x, c0a);
+                c1a = fmaf(qq.y, kk.y, c1a);
+                c2a = fmaf(qq.z, kk.z, c2a);
+                c3a = fmaf(qq.w, kk.w, c3a);
+            }
+            float sc = (c0a + c1a) + (c2a + c3a);
+            sc = lane < nt ? sc * a.scale : -INFINITY;
+            float mx = sc;
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+            const float m_new = fmaxf(m_run[r], mx);
+            const float p = lane < nt ? __expf(sc - m_new) : 0.f;
+            float sum = p;
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o2);
+            const float corr = __expf(m_run[r] - m_new);
+            m_run[r] = m_new;
+            l_run[r] = l_run[r] * corr + sum;
+            __syncwarp();
+            ps[warp * 32 + lane] = p;
+            __syncwarp();
+            // lane owns output dimensions 4*lane .. 4*lane+3 (head_dim <= 128)
+            float4 acc = make_float4(o_run[r][0] * corr, o_run[r][1] * corr, o_run[r][2] * corr, o_run[r][3] * corr);
+            if (4 * lane < hd) {
+                for (int t = 0; t < nt; t++) {
+                    const float pt = ps[warp * 32 + t];
+                    const float4 vv = *(const float4 *)(vs + (t_lo + t) * ATT_MAX_HD + 4 * lane);
+                    acc.x = fmaf(pt, vv.x, acc.x);
+                    acc.y = fmaf(pt, vv.y, acc.y);
+                    acc.z = fmaf(pt, vv.z, acc.z);
+                    acc.w = fmaf(pt, vv.w, acc.w);
+                }
+            }
+            o_run[r][0] = acc.x; o_run[r][1] = acc.y; o_run[r][2] = acc.z; o_run[r][3] = acc.w;
+        }
+    }
+
+    // ---- this CTA's partial per head: combine the warps that shared a head ----
+    __syncthreads();
+    if (warp_active) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            if (r >= n_rounds) break;
+            float *w = wres + (warp * 2 + r) * RS;
+            if (lane == 0) { w[0] = m_run[r]; w[1] = l_run[r]; }
+            if (4 * lane < hd) {
+                *(float2 *)(w + 2 + 4 * lane) = make_float2(o_run[r][0], o_run[r][1]);
+                *(float2 *)(w + 4 + 4 * lane) = make_float2(o_run[r][2], o_run[r][3]);
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * hd; idx += AS_THREADS) {
+        const int g = idx / hd, d = idx - g * hd;
+        const int r = g / AS_WARPS, w0 = g % AS_WARPS;     // G <= 8: r = 0, w0 = g
+        float m = -1e30f;
+        for (int s = 0; s < wph; s++) m = fmaxf(m, wres[((w0 + s * Gw) * 2 + r) * RS]);
+        float l = 0.f, o = 0.f;
+        for (int s = 0; s < wph; s++) {
+            const float *w = wres + ((w0 + s * Gw) * 2 + r) * RS;
+            const float f = __expf(w[0] - m);
+            l = fmaf(w[1], f, l);
+            o = fmaf(w[2 + d], f, o);
+        }
+        res[g * RS + 2 + d] = o;
+        if (d == 0) { res[g * RS] = m; res[g * RS + 1] = l; }
+    }
+
+    // ---- merge across the cluster through distributed shared memory ----
+    cluster.sync();
+    const int S = (G * hd) / CL;          // outputs this CTA finishes: a multiple of 32 (host-checked)
+    for (int j = threadIdx.x; j < S; j += AS_THREADS) {
+        const int idx = rank * S + j;
+        const int g = idx / hd, d = idx - g * hd;
+        const int head = h_lo + g;
+        const float sink = a.sinks ? a.sinks[head] : -INFINITY;
+        const bool has_sink = sink > -1e29f;
+        float mc[16], lc[16], oc[16];
+        float M = has_sink ? sink : -1e30f;
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+            mc[c] = -1e30f; lc[c] = 0.f; oc[c] = 0.f;
+            if (c < CL) {
+                const float *rr = cluster.map_shared_rank(res, c) + g * RS;
+                mc[c] = rr[0];
+                lc[c] = rr[1];
+                oc[c] = rr[2 + d];
+            }
+            M = fmaxf(M, mc[c]);
+        }
+        float tot = has_sink ? __expf(sink - M) : 0.f, acc = 0.f;
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+            const float f = __expf(mc[c] - M);
+            tot = fmaf(lc[c], f, tot);
+            acc = fmaf(oc[c], f, acc);
+        }
+        const float r = acc / tot;
+        a.out[(size_t)head * hd + d] = r;
+        if (a.emit_q) {
+            // lanes 0..7 of each warp own the warp's 32 outputs as 8 groups of 4
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = __shfl_sync(0xFFFFFFFFu, r, (4 * lane + e) & 31);
+            const int first = h_lo * hd + rank * S + (j & ~31);
+            quantize4_store(v, (first >> 2) + (lane & 7), lane < 8, a.o);
+        }
+    }
+    cluster.sync();   // peers may still be reading this CTA's partials
+}
+
+}  // namespace qz

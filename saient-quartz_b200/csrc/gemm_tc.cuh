@@ -46,7 +46,25 @@ constexpr int GEMM_KSTEP = 64;       // one 128-byte swizzle atom of bf16
 constexpr int GEMM_STAGES = 4;
 constexpr int GEMM_MAX_TOKENS = 256; // UMMA N per CTA
 
+// A grouped problem (mixture-of-experts): the rows of the activation matrix are slots grouped by expert,
+// slot ranges and tile counts live in DEVICE memory (built by moe_route_kernel), so the host never needs to
+// know them.  One launch then runs, for every expert e and each of n_mats stacked weight tensors,
+//   Ym[mat][slot, :] = Xtiles(e) * Wm[mat][e]^T     for the slots of expert e.
+constexpr int QZ_MOE_MAX_E = 256;
+struct GemmGroup {
+    int n_experts;
+    int n_tt_total;                      // token tiles of all experts together
+    int counts[QZ_MOE_MAX_E];            // slots of expert e
+    int offsets[QZ_MOE_MAX_E + 1];       // first slot of expert e
+    int tt_prefix[QZ_MOE_MAX_E + 1];     // token tiles before expert e (a token tile = tok_tile slots of one expert)
+};
+
 struct GemmArgs {
+    const GemmGroup *grp;      // NULL: one plain GEMM (W, Y, M below)
+    const uint8_t *Wm[2];      // grouped: stacked expert tensors, expert e at + e * expert_stride
+    float *Ym[2];              // grouped: outputs [slots, N]
+    size_t expert_stride;
+    int n_mats;
     const uint8_t *W;
     const __nv_bfloat16 *Xb;   // bf16 activation tiles, pre-swizzled (see convert_x_bf16_kernel)
     float *Y;                  // [M, N] token-major
@@ -541,6 +559,33 @@ struct GemmShare {
     __device__ int run(const Cursor &c) const { return min(ksteps - c.ks, (c.i < n1 ? n1 : n) - c.i); }
 };
 
+// What a tile index means.  Plain GEMM: tile = row_tile * n_tok_tiles + token tile.  Grouped: tiles are
+// numbered expert by expert, inside an expert matrix by matrix, inside a matrix row tile by row tile.
+struct GemmTile {
+    int row_tile;        // weight rows [row_tile * CTA_ROWS, +CTA_ROWS)
+    int ntok;            // tokens of this tile (multiple of 16): the UMMA N
+    int valid;           // tokens of this tile that exist (the rest is padding)
+    size_t x_tile;       // index of the activation token tile (its K steps follow one another)
+    const uint8_t *W;    // weight matrix of this tile
+    float *Y;            // output row of the tile's first token
+};
+
+struct GemmGroupView {   // the group descriptor as one CTA sees it (shared memory)
+    int n_experts, n_row_tiles, n_mats;
+    int tile_prefix[QZ_MOE_MAX_E + 1];   // GEMM tiles before expert e
+};
+
+__device__ __forceinline__ int group_find(const int *prefix, int n, int v)   // largest e with prefix[e] <= v
+{
+    int lo = 0, hi = n;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= v) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
 // ---- the kernel.  Persistent.  The tiles of the whole problem, in tile-major unit order, are split in
 //      two parts: as many whole tiles per CTA as every CTA can get (stored with plain stores, no other CTA
 //      touches them), and the rest -- less than one tile per CTA -- whose (tile, K step) units are cut
@@ -561,26 +606,20 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
     using P = AProd<T, PLANES>;
     constexpr int PRODUCERS = 256 * HALVES, PWARPS = PRODUCERS / 32, CTA_ROWS = GEMM_ROWS * HALVES;
 
+    __shared__ GemmGroupView gv;
+    __shared__ long long sched[4];   // dp_units, rem_begin, units_per_cta, units
+
     const FormatInfo fi = format_info(T);
     const int nb = a.K / fi.block_elems;
     const size_t row_bytes = (size_t)nb * fi.block_bytes;
-    const int ntok = a.tok_tile;                              // UMMA N (multiple of 16)
+    const int ntok_max = a.tok_tile;                          // widest UMMA N of this launch (multiple of 16)
     const int ksteps = a.K / GEMM_KSTEP;
-    GemmShare sh;
-    sh.ksteps = ksteps;
-    sh.u1 = (long long)blockIdx.x * a.dp_units;
-    sh.n1 = (int)a.dp_units;
-    sh.u2 = a.rem_begin + (long long)blockIdx.x * a.units_per_cta;
-    {
-        const long long e2 = min(sh.u2 + a.units_per_cta, a.units);
-        sh.n = sh.n1 + (e2 > sh.u2 ? (int)(e2 - sh.u2) : 0);
-    }
-    const int nunits = sh.n;
-    const int a_bytes = CTA_ROWS * 128, b_bytes = ntok * 128;
-    const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
+    const int a_bytes = CTA_ROWS * 128, b_stride = ntok_max * 128;
+    const int stage_bytes = a_bytes + ((b_stride + 1023) & ~1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int acc_cols = HALVES * ntok;
+    const int acc_cols = HALVES * ntok_max;
     const uint32_t tmem_cols = acc_cols <= 32 ? 32 : (acc_cols <= 64 ? 64 : (acc_cols <= 128 ? 128 : (acc_cols <= 256 ? 256 : 512)));
+    const GemmGroup *grp = a.grp;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) {
@@ -592,6 +631,34 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (grp) {
+            // Grouped: the tile count comes from the device-side expert counts, so every CTA derives the same
+            // two-part split here that the host computes for a plain GEMM.
+            const int ne = grp->n_experts;
+            gv.n_experts = ne;
+            gv.n_row_tiles = (a.N + CTA_ROWS - 1) / CTA_ROWS;
+            gv.n_mats = a.n_mats;
+            int acc = 0;
+            for (int e = 0; e < ne; e++) {
+                gv.tile_prefix[e] = acc;
+                acc += a.n_mats * gv.n_row_tiles * ((grp->counts[e] + ntok_max - 1) / ntok_max);
+            }
+            gv.tile_prefix[ne] = acc;
+            const long long tiles = acc, units = tiles * ksteps, ctas = gridDim.x;
+            const long long whole = tiles / ctas;
+            const long long dp = whole * ksteps, rem_begin = ctas * dp, rem = units - rem_begin;
+            long long sharers = ctas;
+            if (sharers > (rem + 7) / 8) sharers = (rem + 7) / 8;
+            sched[0] = dp;
+            sched[1] = rem_begin;
+            sched[2] = sharers > 0 ? (rem + sharers - 1) / sharers : 0;
+            sched[3] = units;
+        } else {
+            sched[0] = a.dp_units;
+            sched[1] = a.rem_begin;
+            sched[2] = a.units_per_cta;
+            sched[3] = a.units;
+        }
     }
     if (warp == PWARPS) tmem_alloc(&tmem_base_s, tmem_cols);   // one full warp allocates
     uint8_t *tbl = gsm + (size_t)a.stages * stage_bytes;        // codebook tables of the format, behind the ring
@@ -601,29 +668,74 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
+    GemmShare sh;
+    sh.ksteps = ksteps;
+    sh.u1 = (long long)blockIdx.x * sched[0];
+    sh.n1 = (int)sched[0];
+    sh.u2 = sched[1] + (long long)blockIdx.x * sched[2];
+    {
+        const long long e2 = min(sh.u2 + sched[2], sched[3]);
+        sh.n = sh.n1 + (e2 > sh.u2 ? (int)(e2 - sh.u2) : 0);
+    }
+    const int nunits = sh.n;
+    auto resolve = [&](int tile) -> GemmTile {
+        GemmTile t;
+        if (!grp) {
+            const int tt = tile % a.n_tok_tiles;
+            t.row_tile = tile / a.n_tok_tiles;
+            t.ntok = ntok_max;
+            t.valid = min(ntok_max, a.M - tt * ntok_max);
+            t.x_tile = (size_t)tt;
+            t.W = a.W;
+            t.Y = a.Y + (size_t)tt * ntok_max * a.N;
+        } else {
+            const int e = group_find(gv.tile_prefix, gv.n_experts, tile);
+            int local = tile - gv.tile_prefix[e];
+            const int cnt = grp->counts[e], ntt = (cnt + ntok_max - 1) / ntok_max;
+            const int per_mat = gv.n_row_tiles * ntt;
+            const int mat = local / per_mat;
+            local -= mat * per_mat;
+            const int tt = local % ntt;
+            const int left = cnt - tt * ntok_max;
+            t.row_tile = local / ntt;
+            t.valid = min(ntok_max, left);
+            t.ntok = min(ntok_max, (left + 15) & ~15);
+            t.x_tile = (size_t)(grp->tt_prefix[e] + tt);
+            t.W = a.Wm[mat] + (size_t)e * a.expert_stride;
+            t.Y = a.Ym[mat] + (size_t)(grp->offsets[e] + tt * ntok_max) * a.N;
+        }
+        return t;
+    };
+
     if (warp < PWARPS) {
         // ---------------- producers: two groups of CTA_ROWS threads; group g unpacks the units
         //                  i = g, g + 2, ... (one thread per tile row), so two units are always in
         //                  the making and one group's load latency hides behind the other's work ----
         const int r = threadIdx.x % CTA_ROWS, g = threadIdx.x / CTA_ROWS;
-        struct Cursor { GemmShare::Cursor c; int tile, ks; const uint8_t *rowp; };
-        auto rowp_of = [&](int tile) -> const uint8_t * {
-            const int row = (tile / a.n_tok_tiles) * CTA_ROWS + r;
-            return row < a.N ? a.W + (size_t)row * row_bytes : nullptr;
+        struct Cursor { GemmShare::Cursor c; int tile, ks; const uint8_t *rowp; const uint8_t *xb; uint32_t bb; };
+        auto enter_tile = [&](Cursor &c) {   // the weight row, activation tiles and token count of c.tile
+            const GemmTile t = resolve(c.tile);
+            const int row = t.row_tile * CTA_ROWS + r;
+            c.rowp = row < a.N ? t.W + (size_t)row * row_bytes : nullptr;
+            c.xb = (const uint8_t *)a.Xb + t.x_tile * (size_t)ksteps * (size_t)b_stride;
+            c.bb = (uint32_t)(t.ntok * 128);
         };
         auto advance = [&](Cursor &c, int by) {   // `by` units further in this CTA's work
             sh.advance(c.c, by);
             c.ks = c.c.ks;
             if (c.c.tile != c.tile) {
                 c.tile = c.c.tile;
-                c.rowp = rowp_of(c.tile);
+                enter_tile(c);
             }
         };
         Cursor ld, st;
         sh.place(ld.c, g);
         ld.tile = ld.c.tile;
         ld.ks = ld.c.ks;
-        ld.rowp = rowp_of(ld.tile);
+        ld.rowp = nullptr;
+        ld.xb = nullptr;
+        ld.bb = 0;
+        if (g < nunits) enter_tile(ld);
         st = ld;
         int s = g % a.stages;
         uint32_t round = g / a.stages;
@@ -648,9 +760,9 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             }
             uint8_t *As = gsm + (size_t)s * stage_bytes;
             if (r == 0) {   // the activation tile of this unit: one bulk async copy
-                const uint8_t *src = (const uint8_t *)a.Xb + ((size_t)(st.tile % a.n_tok_tiles) * ksteps + st.ks) * (size_t)b_bytes;
-                mbar_arrive_expect_tx(&full_bar[s], (uint32_t)b_bytes);
-                tma_load_1d(As + a_bytes, src, (uint32_t)b_bytes, &full_bar[s]);
+                const uint8_t *src = st.xb + (size_t)st.ks * (size_t)b_stride;
+                mbar_arrive_expect_tx(&full_bar[s], st.bb);
+                tma_load_1d(As + a_bytes, src, st.bb, &full_bar[s]);
             }
             P::store(As, use, st.rowp, nb, st.ks, r, tbl);   // rows >= 128 land in the second half's tile (r * 128)
             if (!P::TWO_SETS && i + 2 < nunits) {
@@ -680,7 +792,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
     } else if (warp == PWARPS) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(ntok);
+            uint32_t idesc = umma_idesc_bf16(ntok_max);
             int s = 0, seg = 0;
             uint32_t round = 0;
             bool ok = true, first = true;
@@ -690,6 +802,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
                 ok = mbar_wait(&full_bar[s], round & 1);
                 if (ok && first && seg > 0) ok = mbar_wait(&acc_free_bar, (seg - 1) & 1);   // accumulator drained
                 if (!ok) break;
+                if (first && grp) idesc = umma_idesc_bf16(resolve(cur.tile).ntok);   // this tile's token count
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(gsm + (size_t)s * stage_bytes), b_addr = a_addr + a_bytes;
 #pragma unroll
@@ -697,7 +810,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
 #pragma unroll
                     for (int k = 0; k < GEMM_KSTEP / 16; k++) {
                         // advancing K by 16 bf16 inside the swizzle atom = +32 bytes on the start address
-                        tc_mma_bf16(tmem_base + (uint32_t)(hf * ntok), umma_desc_sw128(a_addr + hf * (GEMM_ROWS * 128) + 32 * k),
+                        tc_mma_bf16(tmem_base + (uint32_t)(hf * ntok_max), umma_desc_sw128(a_addr + hf * (GEMM_ROWS * 128) + 32 * k),
                                     umma_desc_sw128(b_addr + 32 * k), idesc, (!first || k > 0) ? 1u : 0u);
                     }
                 }
@@ -736,20 +849,20 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             }
             tc_fence_after();
             const bool whole = len == ksteps;
-            const int row = (tile / a.n_tok_tiles) * CTA_ROWS + GEMM_ROWS * hf + 32 * quad + lane;
-            const int tok0 = (tile % a.n_tok_tiles) * ntok;
-            // ntok is a multiple of 16: 32 columns per round trip, then at most one group of 16
-            for (int c0 = 0; c0 < ntok; c0 += 32) {
+            const GemmTile t = resolve(tile);
+            const int row = t.row_tile * CTA_ROWS + GEMM_ROWS * hf + 32 * quad + lane;
+            // the tile's token count is a multiple of 16: 32 columns per round trip, then at most one group of 16
+            for (int c0 = 0; c0 < t.ntok; c0 += 32) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(hf * ntok + c0);
-                const int nc = min(32, ntok - c0);
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(hf * ntok_max + c0);
+                const int nc = min(32, t.ntok - c0);
                 if (nc == 32) tc_ld32(taddr, v);
                 else tc_ld16(taddr, v);
                 if (row < a.N) {
-                    float *dst = a.Y + (size_t)(tok0 + c0) * a.N + row;
+                    float *dst = t.Y + (size_t)c0 * a.N + row;
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        if (j < nc && tok0 + c0 + j < a.M) {
+                        if (j < nc && c0 + j < t.valid) {
                             if (whole) dst[(size_t)j * a.N] = __uint_as_float(v[j]);
                             else atomicAdd(dst + (size_t)j * a.N, __uint_as_float(v[j]));
                         }

@@ -13,8 +13,10 @@
 // The reference runs each of these GEMVs, and each norm / SwiGLU between them, as a launch of its
 // own (src/cuda.rs:548-823).
 //
-// Every mbarrier wait and the grid barrier's poll are bounded; a timeout sets the status word and an
-// abort word that the other CTAs see at their next barrier, and every thread runs to the kernel's end.
+// Every mbarrier wait and the grid barrier's poll are bounded; a timeout sets the status word, a CTA-wide
+// flag (the CTA's other warps then skip their waits and arithmetic but keep arriving at every barrier of
+// the op, and the whole CTA leaves together at the next op boundary) and an abort word that the other
+// CTAs see at their next grid barrier.  Every thread runs to the kernel's end.
 #pragma once
 
 #include "gemv_tma.cuh"
@@ -88,7 +90,7 @@ __device__ __forceinline__ bool grid_barrier(GridBarrier *gb, int n_ctas, int *s
 template <class F, int MODE>
 __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta, uint8_t *ring, int slot_bytes, int n_slots,
                                               uint64_t *full_bar, uint64_t *empty_bar, float (*part)[4 * (TMA_CONSUMERS / 32)],
-                                              const XQ &xq, RingPos &rp, int *status)
+                                              const XQ &xq, RingPos &rp, int *status, volatile int *cta_dead)
 {
     const FormatInfo fi = format_info(F::TYPE);
     const int nb = op.K / fi.block_elems;
@@ -108,32 +110,38 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
     const int my_tiles = cta < op.n_cta ? (ntiles - cta + op.n_cta - 1) / op.n_cta : 0;
     const uint32_t ring0 = smem_u32(ring), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     const uint32_t row_off = (uint32_t)((worker ? rl : 0) * row_bytes);
-    bool ok = true;
-    for (int t0 = 0; t0 < my_tiles && ok; t0 += 4) {
+    bool ok = true;   // warp-uniform
+    for (int t0 = 0; t0 < my_tiles; t0 += 4) {
         float acc[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             acc[j] = 0.f;
-            if (t0 + j < my_tiles && ok) {
-                if (!mbar_wait_addr(full0 + 8 * rp.s, rp.parity)) {
-                    atomicExch(status, QZ_ERR_TIMEOUT);
-                    ok = false;   // the whole CTA waits on the same barriers: every warp gives up here
-                    continue;
+            if (t0 + j < my_tiles) {
+                if (ok && !mbar_wait_warp(full0 + 8 * rp.s, rp.parity, cta_dead)) {
+                    if (lane == 0) {
+                        atomicExch(status, QZ_ERR_TIMEOUT);
+                        *cta_dead = 1;
+                    }
+                    ok = false;   // the warp keeps walking the stages and the named barriers, computing nothing
                 }
-                if (worker) {
-                    typename F::WRegs w;
-                    F::template load_w<LdSharedAddr>(w, ring0 + (uint32_t)rp.s * (uint32_t)slot_bytes + row_off, off);
-                    acc[j] = F::dot(w, xr, off, nullptr);
+                if (ok) {
+                    if (worker) {
+                        typename F::WRegs w;
+                        F::template load_w<LdSharedAddr>(w, ring0 + (uint32_t)rp.s * (uint32_t)slot_bytes + row_off, off);
+                        acc[j] = F::dot(w, xr, off, nullptr);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_addr(empty0 + 8 * rp.s);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive_addr(empty0 + 8 * rp.s);
                 if (++rp.s == n_slots) { rp.s = 0; rp.parity ^= 1; }
             }
         }
-        if (!ok) break;
         if (!worker) continue;   // (whole warps: n_consumers is a multiple of 32)
         const int row_j0 = (cta + t0 * op.n_cta) * op.RP + rl, row_step = op.n_cta * op.RP;
-        auto store_y = [&](int row, float v) { y[row] = op.accumulate ? __ldcg(y + row) + v : v; };
+        auto store_y = [&](int row, float v) {
+            if (*cta_dead) return;   // a warp of this CTA gave up: its rows are incomplete
+            y[row] = op.accumulate ? __ldcg(y + row) + v : v;
+        };
         const float v = warp_sum4(active ? acc[0] : 0.f, active ? acc[1] : 0.f, active ? acc[2] : 0.f, active ? acc[3] : 0.f,
                                   lane);
         const int j = lane >> 3;
@@ -161,7 +169,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     __shared__ uint64_t full_bar[TMA_MAX_STAGES], empty_bar[TMA_MAX_STAGES];
     __shared__ float part[2][4 * (TMA_CONSUMERS / 32)];
     __shared__ float xred[TMA_CONSUMERS / 32];
-    __shared__ int cta_ok;
+    __shared__ int cta_ok, cta_dead;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.n_slots; s++) {
@@ -169,6 +177,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
             mbar_init(&empty_bar[s], TMA_CONSUMERS / 32);   // every consumer warp releases every stage
         }
         cta_ok = 1;
+        cta_dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -218,18 +227,22 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     RingPos rp{0, 0};
     pdl_wait();   // op 0's inputs come from the preceding kernels
     bool ok = true;
+    volatile int *dead_flag = &cta_dead;
     for (int k = 0; k < a.n_ops; k++) {
         const ChainOp &op = a.op[k];
-        if (k > 0 && a.independent) {
-            named_bar_sync(13, TMA_CONSUMERS);   // every warp has taken its activation registers: the area is free
-        } else if (k > 0) {
-            // ---- grid-wide barrier: op k-1's outputs are complete and visible ----
+        if (k > 0) {
+            // every consumer warp arrives here, whether or not a wait of op k-1 ran out on it; afterwards the
+            // whole CTA takes the same decision.  (Also: every warp has taken its activation registers, the
+            // area is free.)
             named_bar_sync(13, TMA_CONSUMERS);
-            if (threadIdx.x == 0) cta_ok = (ok && grid_barrier(a.gb, gridDim.x, a.status)) ? 1 : 0;
-            named_bar_sync(13, TMA_CONSUMERS);
-            ok = *(volatile int *)&cta_ok != 0;
+            if (!a.independent) {
+                // ---- grid-wide barrier: op k-1's outputs are complete and visible ----
+                if (threadIdx.x == 0) cta_ok = (!*dead_flag && grid_barrier(a.gb, gridDim.x, a.status)) ? 1 : 0;
+                named_bar_sync(13, TMA_CONSUMERS);
+            }
+            ok = *(volatile int *)&cta_ok != 0 && !*dead_flag;
         }
-        if (!ok) break;
+        if (!ok) break;   // uniform over the CTA's consumers
         // ---- op k's activation vector, converted by this CTA into shared memory ----
         int8_t *sxl = (int8_t *)xarea, *sxh = sxl + op.K;
         float *sxs = (float *)(sxh + op.K), *sxsum = sxs + (op.K >> 5);
@@ -290,9 +303,9 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
 #define QZ_CHAIN_CASE(TT, POL)                                                                                              \
     case TT:                                                                                                                \
         ok = op.Upad == 32 ? chain_consume<POL, 1>(op, m, cta, ring, a.slot_bytes, a.n_slots, full_bar, empty_bar, part, xq, rp,  \
-                                                   a.status)                                                                \
+                                                   a.status, dead_flag)                                                     \
                            : chain_consume<POL, 2>(op, m, cta, ring, a.slot_bytes, a.n_slots, full_bar, empty_bar, part, xq, rp,  \
-                                                   a.status);                                                               \
+                                                   a.status, dead_flag);                                                    \
         break;
         switch (op.type) {
             QZ_CHAIN_CASE(T_Q4_K, StreamQ4K)
@@ -301,10 +314,9 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
         default: ok = false; break;
         }
 #undef QZ_CHAIN_CASE
-        if (!ok) {
-            atomicExch(&a.gb->abort, 1);   // the other CTAs leave at their next barrier
-            break;
-        }
+        // a warp whose wait ran out tells the other CTAs (they leave at their next grid barrier) and goes on to
+        // this CTA's next meeting point like every other warp
+        if (!ok) atomicExch(&a.gb->abort, 1);
     }
 }
 

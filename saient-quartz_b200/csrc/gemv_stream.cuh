@@ -46,7 +46,7 @@ constexpr float XQ_RANGE = 32512.0f;   // 127 * 256: h, l both fit int8
 // With `ctrl` set, x is (part of) a row-sharded vector whose slices other ranks push into this
 // rank's window: every CTA first waits for the exchange to complete.  The dependent GEMV has been
 // released by then and streams its weights meanwhile.
-__global__ void quantize_x_kernel(const float *__restrict__ x, int8_t *__restrict__ xl, int8_t *__restrict__ xh,
+__global__ void quantize_x_kernel(const float *x, int8_t *__restrict__ xl, int8_t *__restrict__ xh,
                                   float *__restrict__ xs, float *__restrict__ xsum, int K, const MgpuCtrl *ctrl,
                                   int n_ranks, int *status)
 {
@@ -61,7 +61,9 @@ __global__ void quantize_x_kernel(const float *__restrict__ x, int8_t *__restric
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (k < K) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) v[i] = x[k + i];
+        // L2-coherent loads: with `ctrl` set, x is window memory that peers wrote while this kernel was
+        // already running, so the read-only (non-coherent) path must not serve it
+        for (int i = 0; i < 4; i++) v[i] = __ldcg(x + k + i);
     }
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
     float sum = (v[0] + v[1]) + (v[2] + v[3]);

@@ -11,10 +11,11 @@
 // registers, dp4a on two int8 limbs), reduce each row with shuffles and a
 // row-group named barrier, and hand the stage back through an "empty" mbarrier.
 //
-// Every wait is bounded: a thread that polls an mbarrier for longer than ~1 s of SM
-// clocks records QZ_ERR_TIMEOUT in a device status word and leaves; a timeout on a
-// "full" barrier is seen by all consumers of the CTA at the same stage, so none is
-// left behind at a named barrier, and the producer drains its own outstanding
+// Every wait is bounded: a warp that polls an mbarrier for longer than ~1 s of SM
+// clocks records QZ_ERR_TIMEOUT in a device status word and raises a CTA-wide flag.
+// From then on every consumer warp of the CTA skips its waits and its arithmetic but
+// still walks the remaining stages and arrives at every named barrier, so no warp is
+// left behind at one; nothing more is stored.  The producer drains its own outstanding
 // copies (bounded) before it exits.
 #pragma once
 
@@ -31,8 +32,8 @@ constexpr long long TMA_WAIT_CYCLES = 2000000000LL;   // ~1 s at 1.9 GHz
 
 // Where the activation vector comes from.  mode 0: already converted (xq).  mode 1: RMSNorm of the
 // f32 vector a with weights b (src/cuda_kernels.cu:563-575, eps 1e-5 as there), mode 2: SwiGLU of
-// gate a and up b (src/cuda_kernels.cu:683-698; oai = the clamped variant), mode 3 (gemv_chain_kernel
-// only): the f32 vector a as it is.  For modes 1 to 3 every
+// gate a and up b (src/cuda_kernels.cu:683-698; oai = the clamped variant), mode 3: the f32 vector a
+// as it is (what cuda_gemv gets).  For modes 1 to 3 every
 // CTA converts the vector itself, into shared memory, while its weight pipeline fills: the producer of
 // the activations needs no kernel of its own.
 struct XSrc {
@@ -52,7 +53,6 @@ struct TmaArgs {
     int stage_bytes;         // RP * row_bytes, a multiple of 16
     int n_stages;
     int *status;             // device status word (0 = ok)
-    int probe;               // measurement aid: 1 = consumers release stages without computing (streaming ceiling)
     PushArgs push;           // push.n > 0: rows go to every rank's window instead of y (single matrix)
     XSrc xsrc;
 };
@@ -156,6 +156,24 @@ __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity)
     if (mbar_try_wait_addr(bar, parity)) return true;
     return mbar_wait_slow(bar, parity);
 }
+// The same wait for the consumer warps of the streaming GEMVs: it also ends (false) as soon as another
+// warp of the CTA has raised `*dead_flag`, so that after one timeout nobody spends a second on each stage.
+__device__ __noinline__ bool mbar_wait_slow_flag(uint32_t bar, uint32_t parity, const volatile int *dead_flag)
+{
+    const long long t0 = clock64();
+    while (!mbar_try_wait_addr(bar, parity)) {
+        if (*dead_flag) return false;
+        if (clock64() - t0 > TMA_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+// Warp-uniform result: all 32 lanes call it together; false for the whole warp if any lane gave up.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const volatile int *dead_flag)
+{
+    bool ok = mbar_try_wait_addr(bar, parity);
+    if (!ok) ok = mbar_wait_slow_flag(bar, parity, dead_flag);
+    return __all_sync(0xFFFFFFFFu, ok);
+}
 __device__ __forceinline__ void mbar_arrive_addr(uint32_t bar)
 {
     asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
@@ -171,6 +189,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     __shared__ uint64_t full_bar[TMA_MAX_STAGES], empty_bar[TMA_MAX_STAGES];
     __shared__ float part[2][4 * (TMA_CONSUMERS / 32)];
     __shared__ float xred[TMA_CONSUMERS / 32];
+    __shared__ int cta_dead;   // raised by the first consumer warp whose wait ran out
 
     const int m = blockIdx.x % a.n_mats;
     const int cta = blockIdx.x / a.n_mats, n_cta = gridDim.x / a.n_mats;
@@ -187,6 +206,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], (n_consumers + 31) >> 5);
         }
+        cta_dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -234,6 +254,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     float *__restrict__ y = a.y[m];
     // the row's result: a local store, or (row-sharded layers) a store into every rank's window
     auto store_y = [&](int row, float v) {
+        if (*(const volatile int *)&cta_dead) return;   // a warp of this CTA gave up: its rows are incomplete
         if (a.push.n == 0) {
             y[row] = a.accumulate ? y[row] + v : v;
         } else {
@@ -263,7 +284,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             const int t = it * n_consumers + threadIdx.x;
             if (t < n4) {
                 xa[it] = __ldcg((const float4 *)(pa + 4 * t));
-                xb[it] = __ldcg((const float4 *)(pb + 4 * t));
+                xb[it] = a.xsrc.mode == 3 ? xa[it] : __ldcg((const float4 *)(pb + 4 * t));
             } else {
                 xa[it] = xb[it] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
@@ -292,6 +313,8 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             for (int i = 0; i < 4; i++) {
                 if (a.xsrc.mode == 1) {
                     v[i] = xx[i] * r * yy[i];
+                } else if (a.xsrc.mode == 3) {
+                    v[i] = xx[i];
                 } else if (a.xsrc.oai) {
                     const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
                     v[i] = __fdividef(g, 1.f + __expf(-1.702f * g)) * (up + 1.f);
@@ -314,30 +337,32 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     uint32_t sp = row_base, bar_off = 0, parity = 0;
     int s = 0;
-    for (int t0 = 0; t0 < my_tiles && !dead; t0 += 4) {
+    const volatile int *dead_flag = &cta_dead;
+    for (int t0 = 0; t0 < my_tiles; t0 += 4) {
         float acc[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             acc[j] = 0.f;
             if (t0 + j < my_tiles) {
-                if (dead || !mbar_wait_addr(full0 + bar_off, parity)) {
-                    if (!dead) atomicExch(a.status, QZ_ERR_TIMEOUT);
-                    dead = true;   // the whole CTA waits on the same barriers: every warp gives up here
-                    continue;
+                if (!dead && !mbar_wait_warp(full0 + bar_off, parity, dead_flag)) {
+                    if (lane == 0) {
+                        atomicExch(a.status, QZ_ERR_TIMEOUT);
+                        cta_dead = 1;
+                    }
+                    dead = true;   // warp-uniform; the warp keeps walking the stages and the named barriers
                 }
-                if (!a.probe) {
+                if (!dead) {
                     typename F::WRegs w;
                     F::template load_w<LdSharedAddr>(w, sp, off);
                     acc[j] = F::dot(w, xr, off, tbl);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_addr(empty0 + bar_off);   // this warp no longer reads the stage
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive_addr(empty0 + bar_off);   // this warp no longer reads the stage
                 sp += stage_bytes;
                 bar_off += 8;
                 if (++s == n_stages) { s = 0; sp = row_base; bar_off = 0; parity ^= 1; }
             }
         }
-        if (dead) break;
         // ---- reduce the group's (up to) four rows ----
         // row of group member j: tile (cta + (t0 + j) * n_cta), thread-row rl
         const int row_j0 = (cta + t0 * n_cta) * a.RP + rl, row_step = n_cta * a.RP;
@@ -370,11 +395,11 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             }
         }
     }
-    if (a.push.n > 0 && !dead) {
+    if (a.push.n > 0) {
         // all of this CTA's remote stores are issued: meet, then one thread fences them (the barrier
         // makes the fence cumulative over the other threads' stores) and counts the CTA in
         named_bar_sync(15, n_consumers);
-        if (threadIdx.x == 0) push_publish(a.push, gridDim.x);
+        if (threadIdx.x == 0 && !*(const volatile int *)&cta_dead) push_publish(a.push, gridDim.x);
     }
 }
 

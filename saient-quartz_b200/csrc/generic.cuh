@@ -13,11 +13,14 @@ namespace qz {
 
 // ---- dequant to f32 (bit-exact against src/dequant.rs dequant()) ------------
 template <uint32_t T, bool PLANES>
-__global__ void dequant_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, int K, long long n_sub)
+__global__ void dequant_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, int K, long long n_sub,
+                               const int *__restrict__ row_sel)
 {
     const FormatInfo fi = format_info(T);
     pdl_wait();
     pdl_trigger();
+    // row_sel: the first row to decode is read from device memory (the token id of a recorded decode step)
+    if (row_sel) data += (size_t)row_sel[0] * (size_t)(K / fi.block_elems) * fi.block_bytes;
     long long gs = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gs >= n_sub) return;
     const int subs_per_row = K / 32;
@@ -36,10 +39,13 @@ __global__ void dequant_kernel(const uint8_t *__restrict__ data, float *__restri
 
 // src/dequant.rs:1321-1371 (F32 copy, F16 widen, BF16 shift)
 __global__ void dequant_plain_kernel(const uint8_t *__restrict__ data, float *__restrict__ out, uint32_t type,
-                                     long long n)
+                                     long long n, const int *__restrict__ row_sel, int K)
 {
+    pdl_wait();
+    pdl_trigger();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
+    if (row_sel) data += (size_t)row_sel[0] * (size_t)K * (type == T_F32 ? 4 : 2);
     if (type == T_F32) {
         out[i] = __uint_as_float(ld_u32_bytes(data + 4 * i));
     } else if (type == T_F16) {

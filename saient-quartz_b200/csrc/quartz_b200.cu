@@ -18,6 +18,7 @@
 #include "gemv_tma.cuh"
 #include "decode_ops.cuh"
 #include "fused_ops.cuh"
+#include "attn_step.cuh"
 #include "gemm_tc.cuh"
 #include "moe.cuh"
 #include "gemv_chain.cuh"
@@ -255,7 +256,6 @@ static void poll_status()
     }
 }
 
-static int g_probe = 0;
 static int g_use_tma = -1;
 // set by cuda_gemv_push around its GEMV: the TMA kernel takes it as its epilogue and clears `pending`
 static PushArgs g_push_args;
@@ -263,6 +263,19 @@ static bool g_push_pending = false;
 // set by cuda_gemv_rmsnorm / cuda_gemv_swiglu around their GEMV: the TMA kernel converts the activations itself
 static XSrc g_xsrc = {0, nullptr, nullptr, 0};
 static bool g_xsrc_pending = false;
+// longest activation vector the streaming GEMV converts in its own prologue (every CTA converts the whole
+// vector while its weight ring fills); longer vectors are converted once, by a kernel of their own.
+// QUARTZ_XSRC_MAX_K overrides the default.
+static int xsrc_max_k()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("QUARTZ_XSRC_MAX_K");
+        v = e ? atoi(e) : 8192;
+        if (v < 0) v = 0;
+    }
+    return v;
+}
 static bool use_tma()
 {
     if (g_use_tma < 0) {
@@ -301,7 +314,6 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     a.n_stages = stages;
     a.status = status_word();
     if (!a.status) return false;
-    a.probe = g_probe;
     a.push.n = 0;
     if (g_push_pending && n_mats == 1 && !g.accumulate) {
         a.push = g_push_args;
@@ -409,9 +421,22 @@ static bool try_stream(uint32_t t, int n, const uint8_t *const *W, const float *
         if ((want == 2) != planes[i]) return false;
     }
     if (!ensure_xq(K)) return false;
-    // quantize each distinct activation vector once
     int slot_of[4];
     int n_slots = 0;
+    // one activation vector for all matrices: the TMA kernel converts it in its own prologue (no launch of its
+    // own for the conversion), unless the conversion kernel is needed as the carrier of a fused exchange wait
+    bool same_x = true;
+    for (int i = 1; i < n; i++) same_x = same_x && x[i] == x[0];
+    if (same_x && use_tma() && !g_wait_ctrl && K <= xsrc_max_k() && !((uintptr_t)x[0] & 15)) {
+        for (int i = 0; i < n; i++) slot_of[i] = 0;
+        g_xsrc = XSrc{3, x[0], x[0], 0};
+        g_xsrc_pending = true;
+        const bool ok = stream_core(t, n, W, slot_of, y, K, N, 0);
+        const bool consumed = !g_xsrc_pending;
+        g_xsrc_pending = false;
+        if (ok && consumed) return true;
+    }
+    // otherwise: quantize each distinct activation vector once
     for (int i = 0; i < n; i++) {
         int s = -1;
         for (int j = 0; j < i; j++)
@@ -476,7 +501,7 @@ static void gemv_n(uint32_t t, int n, const uint8_t *const *W, const float *cons
     for (int i = 0; i < n; i++) launch_generic(t, planes[i], W[i], x[i], y[i], K, N);
 }
 
-static void dequant_rows(uint32_t t, const uint8_t *data, float *out, int K, long long rows)
+static void dequant_rows(uint32_t t, const uint8_t *data, float *out, int K, long long rows, const int *row_sel = nullptr)
 {
     const FormatInfo fi = format_info(t);
     if (fi.block_elems == 0) {
@@ -490,8 +515,7 @@ static void dequant_rows(uint32_t t, const uint8_t *data, float *out, int K, lon
     }
     if (is_plain(t)) {
         long long n = rows * K;
-        dequant_plain_kernel<<<(unsigned)((n + 255) / 256), 256, 0, g_stream>>>(data, out, t, n);
-        QZ_LAUNCH_CHECK();
+        launch(dequant_plain_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, data, out, t, n, row_sel, K);
         return;
     }
     const Range *r = find_range(data);
@@ -506,16 +530,15 @@ static void dequant_rows(uint32_t t, const uint8_t *data, float *out, int K, lon
     long long n_sub = rows * (K / 32);
     unsigned grid = (unsigned)((n_sub + 127) / 128);
     switch (t) {
-#define X(TT)                                                                                   \
-    case TT:                                                                                    \
-        if (planes) dequant_kernel<TT, true><<<grid, 128, 0, g_stream>>>(data, out, K, n_sub);  \
-        else dequant_kernel<TT, false><<<grid, 128, 0, g_stream>>>(data, out, K, n_sub);        \
+#define X(TT)                                                                                                \
+    case TT:                                                                                                 \
+        if (planes) launch(dequant_kernel<TT, true>, dim3(grid), dim3(128), 0, data, out, K, n_sub, row_sel);  \
+        else launch(dequant_kernel<TT, false>, dim3(grid), dim3(128), 0, data, out, K, n_sub, row_sel);        \
         break;
         QZ_FOR_BLOCK_TYPES(X)
 #undef X
     default: break;
     }
-    QZ_LAUNCH_CHECK();
 }
 
 // ---- allocation-free GEMV: scratch that lives in the library image -------------------------
@@ -595,9 +618,21 @@ static void gemv_noalloc(uint32_t t, const uint8_t *W, const float *x, float *y,
         }
         planes = true;
     }
+    if (g_wait_ctrl) {
+        // This entry point never carries a fused exchange wait (that path would create the status word with
+        // cudaMalloc): the pending wait runs as a kernel of its own when the status word exists already, and
+        // is refused otherwise.
+        if (g_status) {
+            mgpu_wait_kernel<<<1, 32, 0, g_stream>>>(g_wait_ctrl, g_wait_ranks, g_status);
+            QZ_LAUNCH_CHECK();
+        } else {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_gemv_noalloc: a fused exchange wait is pending but cannot be carried without allocating; call quartz_mgpu_wait instead");
+        }
+        g_wait_ctrl = nullptr;
+    }
     const int want = stream_layout(t);
     const size_t row_bytes = (size_t)(K / fi.block_elems) * fi.block_bytes;
-    const bool streamable = want && K % 64 == 0 && row_bytes % 16 == 0 && !((uintptr_t)W & 15) &&
+    const bool streamable = want && K % 64 == 0 && K / 64 <= 512 && row_bytes % 16 == 0 && !((uintptr_t)W & 15) &&
                             !((uintptr_t)x & 3) && ((want == 2) == planes);
     if (!streamable) {
         launch_generic(t, planes, W, x, y, K, N);   // needs no scratch at all
@@ -633,10 +668,10 @@ static void gemv_noalloc(uint32_t t, const uint8_t *W, const float *x, float *y,
     }
     const int T = a.Upad * a.RP;
     switch (t) {
-    case T_Q4_K: launch_noalloc<StreamQ4K>(a, T); break;
-    case T_Q6_K: launch_noalloc<StreamQ6K>(a, T); break;
-    case T_Q8_0: launch_noalloc<StreamQ8_0>(a, T); break;
-    default: launch_generic(t, planes, W, x, y, K, N); break;
+#define X(TT, POL) case TT: launch_noalloc<POL>(a, T); break;
+        QZ_FOR_STREAM_TYPES(X)
+#undef X
+    default: break;
     }
 }
 
@@ -702,6 +737,42 @@ static void launch_gemm_type(const GemmArgs &a, int halves)
     launch_gemm<T, PLANES, 1>(a);
 }
 
+// Grouped form (a.grp set): the tile count is known on the device only, so the grid is the resident CTA count
+// and the kernel splits the work itself; outputs must be zero beforehand (shared tiles are added atomically).
+template <uint32_t T, bool PLANES>
+static void launch_gemm_grouped(GemmArgs a)
+{
+    const int stage_bytes = GEMM_ROWS * 128 + ((a.tok_tile * 128 + 1023) & ~1023);
+    const bool two = gemm_fast_type<T, PLANES>();
+    constexpr int table_bytes = AProd<T, PLANES>::TABLE_BYTES;
+    const int budget = (two ? 110 : 200) * 1024 - table_bytes;
+    a.stages = budget / stage_bytes;
+    if (a.stages > GEMM_STAGES) a.stages = GEMM_STAGES;
+    const size_t smem = (size_t)a.stages * stage_bytes + table_bytes;
+    static bool attr_set = false;
+    if (!attr_set) {
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<T, PLANES, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
+        attr_set = true;
+    }
+    const unsigned ctas = (unsigned)(sm_count() * (two ? 2 : 1));
+    gemm_tc_kernel<T, PLANES, 1><<<ctas, gemm_threads<1>(), smem, g_stream>>>(a);
+    QZ_LAUNCH_CHECK();
+}
+
+static void gemm_grouped_dispatch(uint32_t t, bool planes, const GemmArgs &a)
+{
+    switch (t) {
+#define X(TT)                                               \
+    case TT:                                                \
+        if (planes) launch_gemm_grouped<TT, true>(a);       \
+        else launch_gemm_grouped<TT, false>(a);             \
+        break;
+        QZ_FOR_BLOCK_TYPES(X)
+#undef X
+    default: break;
+    }
+}
+
 static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y, int M, int K, int N, bool x_bf16 = false)
 {
     const float *x = (const float *)xv;   // (bf16 input: only the tensor-core path below reads it)
@@ -737,7 +808,8 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y
         }
         planes = true;
     }
-    GemmArgs a;
+    GemmArgs a = {};
+    a.grp = nullptr;
     a.W = W; a.Y = y; a.M = M; a.K = K; a.N = N; a.planes = planes;
     a.tok_tile = M >= GEMM_MAX_TOKENS ? GEMM_MAX_TOKENS : ((M + 15) & ~15);
     a.n_tok_tiles = (M + a.tok_tile - 1) / a.tok_tile;
@@ -1035,11 +1107,7 @@ void quartz_clear_error(void)
 }
 void quartz_set_stream(void *s) { g_stream = (cudaStream_t)s; }
 long long quartz_launch_count(void) { return g_launch_count; }
-void quartz_set_gemv_impl(int impl)
-{
-    g_probe = impl == 2 ? 1 : 0;   // 2: streaming-ceiling probe (outputs are meaningless)
-    g_use_tma = impl == 1 ? 0 : 1;
-}
+void quartz_set_gemv_impl(int impl) { g_use_tma = impl == 1 ? 0 : 1; }
 
 int cuda_repack_weights(uint32_t ggml_type, void *d_data, int in_dim, int out_dim, int n_mats)
 {
@@ -1186,7 +1254,7 @@ static void gemv_xsrc(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w,
     if (!ensure_xq(in_dim)) return;
     // the prologue converts the whole vector in every CTA: worth it for short vectors (one launch less), not for
     // long ones (14336: +4 us per CTA against a 2 us conversion kernel)
-    if (use_tma() && in_dim <= 8192 && ((uintptr_t)src.a & 15) == 0 && ((uintptr_t)src.b & 15) == 0) {
+    if (use_tma() && in_dim <= xsrc_max_k() && ((uintptr_t)src.a & 15) == 0 && ((uintptr_t)src.b & 15) == 0) {
         g_xsrc = src;
         g_xsrc_pending = true;
         const bool ok = stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
@@ -1419,8 +1487,138 @@ void cuda_attn_block(float *out, const float *q, const float *k_new, const float
                (const float *)(g_attn_part + 64), n_splits, head_dim, sinks, o, out_slot >= 0 ? 1 : 0);
 }
 
-// ---- CUDA-graph helpers: record a sequence of this library's calls once, replay it per token ----
+// ---- decode step whose position and token live in device memory ----
+__global__ void step_set_kernel(int *step, int token, int pos)
+{
+    pdl_wait();
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        step[0] = token;
+        step[1] = pos;
+    }
+}
+
 static cudaStream_t g_graph_stream = nullptr, g_saved_stream = nullptr;
+
+void cuda_step_set(int *d_step, int token, int pos)
+{
+    if (!d_step) return;
+    // on the stream the recorded graphs replay on (when there is one), so the words are ordered with the replays
+    cudaStream_t s = (g_graph_stream && g_stream == 0) ? g_graph_stream : g_stream;
+    step_set_kernel<<<1, 32, 0, s>>>(d_step, token, pos);
+    QZ_LAUNCH_CHECK();
+}
+
+void cuda_embed_lookup_dev(float *out, const uint8_t *data, uint32_t ggml_type, const int *d_step, int embed_dim)
+{
+    const FormatInfo fi = format_info(ggml_type);
+    if (fi.block_elems == 0 || embed_dim <= 0 || embed_dim % fi.block_elems || !d_step) {
+        set_error(fi.block_elems ? QZ_ERR_BAD_SHAPE : QZ_ERR_UNSUPPORTED_TYPE, "cuda_embed_lookup_dev");
+        return;
+    }
+    dequant_rows(ggml_type, data, out, embed_dim, 1, d_step);
+}
+
+// cluster width of the attention kernel for a head group of G heads: the widest power of two (<= 16, or the
+// value of QUARTZ_ATTN_CLUSTER) that leaves every CTA a whole number of 32-output runs and that the device
+// can schedule; 0 = this head geometry is not served
+static int attn_step_cluster(int G, int head_dim)
+{
+    static int cached_G = -1, cached_hd = -1, cached_cl = 0;
+    if (G == cached_G && head_dim == cached_hd) return cached_cl;
+    int want = 16;
+    if (const char *e = getenv("QUARTZ_ATTN_CLUSTER")) {
+        const int v = atoi(e);
+        if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) want = v;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(attn_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)attn_step_smem(AS_MAX_G)));
+        if (cudaFuncSetAttribute(attn_step_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+            cudaGetLastError();
+        attr_set = true;
+    }
+    int cl = 0;
+    for (int c = want; c >= 1; c >>= 1) {
+        if ((G * head_dim) % (32 * c) != 0) continue;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(c);
+        cfg.blockDim = dim3(AS_THREADS);
+        cfg.dynamicSmemBytes = attn_step_smem(G);
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = c;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, attn_step_kernel, &cfg) == cudaSuccess && n >= 1) {
+            cl = c;
+            break;
+        }
+        cudaGetLastError();
+    }
+    cached_G = G;
+    cached_hd = head_dim;
+    cached_cl = cl;
+    return cl;
+}
+
+int cuda_attn_step_supported(int n_heads, int n_kv_heads, int head_dim)
+{
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return 0;
+    const int G = n_heads / n_kv_heads;
+    if (G > AS_MAX_G || head_dim > ATT_MAX_HD || head_dim % 32 != 0) return 0;
+    return attn_step_cluster(G, head_dim) > 0 ? 1 : 0;
+}
+
+void cuda_attn_step(float *out, const float *q, const float *k_new, const float *v_new, float *k_cache, float *v_cache,
+                    int n_heads, int n_kv_heads, int head_dim, int max_seq, const int *d_step, int pos, int window,
+                    float scale, const float *sinks, float theta, float yarn_scale, int yarn_orig_ctx, int neox,
+                    int out_slot)
+{
+    if (!cuda_attn_step_supported(n_heads, n_kv_heads, head_dim) || max_seq <= 0 || (!d_step && (pos < 0 || pos >= max_seq))) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_attn_step: head_dim must be a multiple of 32 up to 128, at most 16 query heads per kv head, 0 <= pos < max_seq");
+        return;
+    }
+    const int G = n_heads / n_kv_heads;
+    const int cl = attn_step_cluster(G, head_dim);
+    AttnStepArgs a;
+    a.out = out; a.q = q; a.k_new = k_new; a.v_new = v_new; a.k_cache = k_cache; a.v_cache = v_cache;
+    a.step = d_step; a.pos_host = pos;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.kv_dim = n_kv_heads * head_dim;
+    a.max_seq = max_seq; a.window = window; a.scale = scale; a.sinks = sinks;
+    a.theta = theta; a.yarn_scale = yarn_scale; a.yarn_orig_ctx = yarn_orig_ctx; a.neox = neox;
+    a.o = XQOut{nullptr, nullptr, nullptr, nullptr};
+    a.emit_q = 0;
+    if (out_slot >= 0) {
+        if (!user_slot(out_slot, n_heads * head_dim, &a.o)) return;
+        a.emit_q = 1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n_kv_heads * cl));
+    cfg.blockDim = dim3(AS_THREADS);
+    cfg.dynamicSmemBytes = attn_step_smem(G);
+    cfg.stream = g_stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)cl;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.numAttrs = 1;
+    if (g_pdl) {
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = at;
+    g_launch_count++;
+    QZ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, attn_step_kernel, a));
+}
+
+// ---- CUDA-graph helpers: record a sequence of this library's calls once, replay it per token ----
 static bool g_pdl_in_graphs = true;
 static bool g_capturing = false;
 
@@ -1501,36 +1699,52 @@ void cuda_gemm_bf16(uint32_t ggml_type, const uint8_t *d_data, const uint16_t *d
 }
 
 // ======================= batched mixture-of-experts FFN =======================
-static uint8_t *g_moe = nullptr;   // library scratch: index / weight lists, gathered rows, gate, up, down outputs
+static uint8_t *g_moe = nullptr;   // library scratch: routing lists, activation tiles, gate / up / down outputs
 static size_t g_moe_bytes = 0;
 
-void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
-                  const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim, int n_experts,
-                  int top_k, const int *h_expert_ids, const float *h_expert_w, int oai)
+static bool ensure_moe(size_t need)
 {
-    if (m <= 0) return;
+    if (need <= g_moe_bytes) return true;
+    if (g_moe) {
+        cudaStreamSynchronize(g_stream);
+        cudaFree(g_moe);
+    }
+    if (cudaMalloc(&g_moe, need) != cudaSuccess) {
+        cudaGetLastError();
+        g_moe = nullptr;
+        g_moe_bytes = 0;
+        set_error(QZ_ERR_CUDA, "cuda_moe_ffn: cudaMalloc of the scratch failed");
+        return false;
+    }
+    g_moe_bytes = need;
+    return true;
+}
+
+// layout of one matrix type for the grouped kernel: false if the tensor-core kernel does not take it
+static bool moe_mat_ok(uint32_t t, const uint8_t *W, int K, bool *planes)
+{
+    const FormatInfo fi = format_info(t);
+    if (fi.block_elems < 32 || K <= 0 || K % GEMM_KSTEP != 0 || ((uintptr_t)W & 15) ||
+        (((size_t)(K / fi.block_elems) * fi.block_bytes) % 16) != 0 || !tables_ready(t))
+        return false;
+    *planes = false;
+    if (const Range *r = find_range(W)) {
+        if (r->type != t || r->K != K) return false;
+        *planes = true;
+    }
+    return true;
+}
+
+// The per-expert form: assignments grouped on the host, three GEMMs per expert.  Takes every type and shape.
+static void moe_ffn_per_expert(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
+                               const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim,
+                               int n_experts, int top_k, const int *h_expert_ids, const float *h_expert_w, int oai)
+{
     const FormatInfo fg = format_info(type_gate_up), fd = format_info(type_down);
-    if (fg.block_elems == 0 || fd.block_elems == 0) {
-        set_error(QZ_ERR_UNSUPPORTED_TYPE, "cuda_moe_ffn: unsupported ggml_type");
-        return;
-    }
-    if (n_experts <= 0 || top_k <= 0 || top_k > n_experts || embed_dim <= 0 || ffn_dim <= 0 || embed_dim % fg.block_elems ||
-        ffn_dim % fd.block_elems || (embed_dim & 3) || (ffn_dim & 3) || !h_expert_ids || !h_expert_w) {
-        set_error(QZ_ERR_BAD_SHAPE, "cuda_moe_ffn: bad dimensions or routing lists");
-        return;
-    }
-    // group the (token, expert) assignments by expert
     const int A = m * top_k;
     std::vector<int> count(n_experts, 0), start(n_experts + 1, 0), rows(A);
     std::vector<float> wts(A);
-    for (int i = 0; i < A; i++) {
-        const int e = h_expert_ids[i];
-        if (e < 0 || e >= n_experts) {
-            set_error(QZ_ERR_BAD_SHAPE, "cuda_moe_ffn: expert id out of range");
-            return;
-        }
-        count[e]++;
-    }
+    for (int i = 0; i < A; i++) count[h_expert_ids[i]]++;
     for (int e = 0; e < n_experts; e++) start[e + 1] = start[e] + count[e];
     std::vector<int> fill(start.begin(), start.end() - 1);
     for (int i = 0; i < A; i++) {
@@ -1540,21 +1754,7 @@ void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_ga
     }
     const size_t K = (size_t)embed_dim, F = (size_t)ffn_dim;
     const size_t lists = (((size_t)A * 8) + 255) & ~(size_t)255;
-    const size_t need = lists + (size_t)A * (2 * K + 2 * F) * sizeof(float);
-    if (need > g_moe_bytes) {
-        if (g_moe) {
-            cudaStreamSynchronize(g_stream);
-            cudaFree(g_moe);
-        }
-        if (cudaMalloc(&g_moe, need) != cudaSuccess) {
-            cudaGetLastError();
-            g_moe = nullptr;
-            g_moe_bytes = 0;
-            set_error(QZ_ERR_CUDA, "cuda_moe_ffn: cudaMalloc of the scratch failed");
-            return;
-        }
-        g_moe_bytes = need;
-    }
+    if (!ensure_moe(lists + (size_t)A * (2 * K + 2 * F) * sizeof(float))) return;
     int *d_rows = (int *)g_moe;
     float *d_wts = (float *)(g_moe + (size_t)A * 4);
     float *xe = (float *)(g_moe + lists), *g = xe + (size_t)A * K, *u = g + (size_t)A * F, *yd = u + (size_t)A * F;
@@ -1590,6 +1790,164 @@ void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_ga
                                                                              embed_dim);
         QZ_LAUNCH_CHECK();
     }
+}
+
+static bool moe_check(uint32_t type_gate_up, uint32_t type_down, int m, int embed_dim, int ffn_dim, int n_experts, int top_k,
+                      const void *ids, const void *w)
+{
+    const FormatInfo fg = format_info(type_gate_up), fd = format_info(type_down);
+    if (fg.block_elems == 0 || fd.block_elems == 0) {
+        set_error(QZ_ERR_UNSUPPORTED_TYPE, "cuda_moe_ffn: unsupported ggml_type");
+        return false;
+    }
+    if (n_experts <= 0 || top_k <= 0 || top_k > n_experts || embed_dim <= 0 || ffn_dim <= 0 || embed_dim % fg.block_elems ||
+        ffn_dim % fd.block_elems || (embed_dim & 3) || (ffn_dim & 3) || !ids || !w || m <= 0) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_moe_ffn: bad dimensions or routing lists");
+        return false;
+    }
+    return true;
+}
+
+// The grouped form, all on the device.  ids / w are DEVICE arrays of m * top_k entries.  Returns false when the
+// shapes or types are not served (nothing has been launched then).
+static bool moe_ffn_grouped(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
+                            const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim,
+                            int n_experts, int top_k, const int *d_ids, const float *d_w, int oai)
+{
+    bool pg = false, pu = false, pd = false;
+    if (n_experts > QZ_MOE_MAX_E || ((uintptr_t)d_x & 15) || ((uintptr_t)d_out & 15)) return false;
+    if (!moe_mat_ok(type_gate_up, d_gate, embed_dim, &pg) || !moe_mat_ok(type_gate_up, d_up, embed_dim, &pu) || pg != pu ||
+        !moe_mat_ok(type_down, d_down, ffn_dim, &pd))
+        return false;
+    const FormatInfo fg = format_info(type_gate_up), fd = format_info(type_down);
+    const int A = m * top_k;
+    const size_t K = (size_t)embed_dim, F = (size_t)ffn_dim;
+    // token tile: the narrowest of 32 / 64 / 128 slots that holds 1.5 x the mean load of an expert
+    const int mean15 = (3 * A + 2 * n_experts - 1) / (2 * n_experts);
+    const int tok_tile = mean15 <= 32 ? 32 : (mean15 <= 64 ? 64 : 128);
+    const int max_tt = A / tok_tile + n_experts;      // token tiles of all experts together, at most
+    auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t o_grp = up256((size_t)A * 4 * 3), o_xt = o_grp + up256(sizeof(GemmGroup));
+    const size_t xt_bytes = (size_t)max_tt * (K / 64) * tok_tile * 128, ht_bytes = (size_t)max_tt * (F / 64) * tok_tile * 128;
+    const size_t o_g = o_xt + up256(xt_bytes), o_u = o_g + up256((size_t)A * F * 4), o_ht = o_u + up256((size_t)A * F * 4);
+    const size_t o_yd = o_ht + up256(ht_bytes), need = o_yd + up256((size_t)A * K * 4);
+    if (!ensure_moe(need)) return true;   // (error recorded)
+    int *rows = (int *)g_moe, *slot_of = rows + A;
+    float *wts = (float *)(slot_of + A);
+    GemmGroup *grp = (GemmGroup *)(g_moe + o_grp);
+    __nv_bfloat16 *xt = (__nv_bfloat16 *)(g_moe + o_xt), *ht = (__nv_bfloat16 *)(g_moe + o_ht);
+    float *G = (float *)(g_moe + o_g), *U = (float *)(g_moe + o_u), *Yd = (float *)(g_moe + o_yd);
+    int *status = status_word();
+    if (!status) return true;
+
+    moe_route_kernel<<<n_experts, 256, 0, g_stream>>>(d_ids, d_w, A, top_k, n_experts, tok_tile, grp, rows, wts, slot_of);
+    QZ_LAUNCH_CHECK();
+    const int conv_blocks = 4 * sm_count();
+    moe_tiles_kernel<0><<<conv_blocks, 256, 0, g_stream>>>(d_x, nullptr, rows, grp, xt, embed_dim, tok_tile, max_tt,
+                                                           (type_gate_up == T_Q6_K && pg) ? 1 : 0, 0);
+    QZ_LAUNCH_CHECK();
+    QZ_CUDA_CHECK(cudaMemsetAsync(G, 0, (size_t)((uint8_t *)ht - (uint8_t *)G), g_stream));   // G and U: shared tiles are added onto zeros
+    GemmArgs a = {};
+    a.grp = grp;
+    a.Wm[0] = d_gate; a.Wm[1] = d_up;
+    a.Ym[0] = G; a.Ym[1] = U;
+    a.expert_stride = (K * F / fg.block_elems) * fg.block_bytes;
+    a.n_mats = 2;
+    a.Xb = xt;
+    a.K = embed_dim; a.N = ffn_dim; a.M = A; a.planes = pg;
+    a.tok_tile = tok_tile; a.n_tok_tiles = 1;
+    a.status = status;
+    gemm_grouped_dispatch(type_gate_up, pg, a);
+    moe_tiles_kernel<1><<<conv_blocks, 256, 0, g_stream>>>(G, U, rows, grp, ht, ffn_dim, tok_tile, max_tt,
+                                                           (type_down == T_Q6_K && pd) ? 1 : 0, oai);
+    QZ_LAUNCH_CHECK();
+    QZ_CUDA_CHECK(cudaMemsetAsync(Yd, 0, (size_t)A * K * 4, g_stream));
+    a.Wm[0] = d_down; a.Wm[1] = d_down;
+    a.Ym[0] = Yd; a.Ym[1] = Yd;
+    a.expert_stride = (F * K / fd.block_elems) * fd.block_bytes;
+    a.n_mats = 1;
+    a.Xb = ht;
+    a.K = ffn_dim; a.N = embed_dim; a.planes = pd;
+    gemm_grouped_dispatch(type_down, pd, a);
+    const long long n4 = (long long)m * (K / 4);
+    moe_combine_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, g_stream>>>(d_out, Yd, slot_of, d_w, m, top_k, embed_dim);
+    QZ_LAUNCH_CHECK();
+    return true;
+}
+
+void cuda_moe_ffn_dev(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
+                      const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim, int n_experts,
+                      int top_k, const int *d_expert_ids, const float *d_expert_w, int oai)
+{
+    if (!moe_check(type_gate_up, type_down, m, embed_dim, ffn_dim, n_experts, top_k, d_expert_ids, d_expert_w)) return;
+    if (moe_ffn_grouped(type_gate_up, type_down, d_gate, d_up, d_down, d_x, d_out, m, embed_dim, ffn_dim, n_experts, top_k,
+                        d_expert_ids, d_expert_w, oai))
+        return;
+    // not a shape the grouped kernel takes: bring the lists to the host (one synchronisation) and go expert by expert
+    const int A = m * top_k;
+    std::vector<int> ids(A);
+    std::vector<float> w(A);
+    QZ_CUDA_CHECK(cudaMemcpyAsync(ids.data(), d_expert_ids, (size_t)A * 4, cudaMemcpyDeviceToHost, g_stream));
+    QZ_CUDA_CHECK(cudaMemcpyAsync(w.data(), d_expert_w, (size_t)A * 4, cudaMemcpyDeviceToHost, g_stream));
+    QZ_CUDA_CHECK(cudaStreamSynchronize(g_stream));
+    for (int i = 0; i < A; i++)
+        if (ids[i] < 0 || ids[i] >= n_experts) {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_moe_ffn_dev: expert id out of range");
+            return;
+        }
+    moe_ffn_per_expert(type_gate_up, type_down, d_gate, d_up, d_down, d_x, d_out, m, embed_dim, ffn_dim, n_experts, top_k,
+                       ids.data(), w.data(), oai);
+}
+
+void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_gate, const uint8_t *d_up,
+                  const uint8_t *d_down, const float *d_x, float *d_out, int m, int embed_dim, int ffn_dim, int n_experts,
+                  int top_k, const int *h_expert_ids, const float *h_expert_w, int oai)
+{
+    if (!moe_check(type_gate_up, type_down, m, embed_dim, ffn_dim, n_experts, top_k, h_expert_ids, h_expert_w)) return;
+    const int A = m * top_k;
+    for (int i = 0; i < A; i++)
+        if (h_expert_ids[i] < 0 || h_expert_ids[i] >= n_experts) {
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_moe_ffn: expert id out of range");
+            return;
+        }
+    // the routing lists go to a library buffer of their own (copied from pageable memory: staged before the call returns)
+    static int *d_lists = nullptr;
+    static size_t d_lists_cap = 0;
+    if ((size_t)A * 8 > d_lists_cap) {
+        if (d_lists) {
+            cudaStreamSynchronize(g_stream);
+            cudaFree(d_lists);
+        }
+        d_lists_cap = (size_t)A * 8 < 65536 ? 65536 : (size_t)A * 16;
+        if (cudaMalloc(&d_lists, d_lists_cap) != cudaSuccess) {
+            cudaGetLastError();
+            d_lists = nullptr;
+            d_lists_cap = 0;
+            set_error(QZ_ERR_CUDA, "cuda_moe_ffn: cudaMalloc of the routing lists failed");
+            return;
+        }
+    }
+    int *d_ids = d_lists;
+    float *d_w = (float *)(d_lists + A);
+    QZ_CUDA_CHECK(cudaMemcpyAsync(d_ids, h_expert_ids, (size_t)A * 4, cudaMemcpyHostToDevice, g_stream));
+    QZ_CUDA_CHECK(cudaMemcpyAsync(d_w, h_expert_w, (size_t)A * 4, cudaMemcpyHostToDevice, g_stream));
+    if (moe_ffn_grouped(type_gate_up, type_down, d_gate, d_up, d_down, d_x, d_out, m, embed_dim, ffn_dim, n_experts, top_k,
+                        d_ids, d_w, oai))
+        return;
+    moe_ffn_per_expert(type_gate_up, type_down, d_gate, d_up, d_down, d_x, d_out, m, embed_dim, ffn_dim, n_experts, top_k,
+                       h_expert_ids, h_expert_w, oai);
+}
+
+void cuda_router_topk(const float *d_logits, const float *d_bias, int m, int n_experts, int top_k, int renorm, int *d_ids,
+                      float *d_w)
+{
+    if (m <= 0) return;
+    if (n_experts <= 0 || n_experts > QZ_MOE_MAX_E || top_k <= 0 || top_k > 8 || top_k > n_experts || !d_logits || !d_ids || !d_w) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_router_topk: 1 <= top_k <= min(8, n_experts), n_experts <= 256");
+        return;
+    }
+    launch(router_topk_kernel, dim3((unsigned)((m + 7) / 8)), dim3(256), 0, d_logits, d_bias, m, n_experts, top_k, renorm, d_ids,
+           d_w);
 }
 
 // ======================= row-sharded layers: peer windows =======================

@@ -6,7 +6,6 @@
 #include <string.h>
 
 #include <algorithm>
-#include <map>
 #include <utility>
 #include <vector>
 
@@ -107,7 +106,9 @@ struct qh_model {
     std::vector<GpuBuf> kv_k, kv_v;
     bool finalized = false;
     long long last_launches = 0;
-    std::map<std::pair<int, int>, void *> graphs;   // (pos, need_logits) -> recorded step
+    int n_recorded = 0;        // graph recordings made so far
+    GpuBuf d_step;             // two device words {token, pos}: what the recorded step reads instead of arguments
+    void *graphs[3] = {nullptr, nullptr, nullptr};   // one recorded step per sequence kind (1 fused, 2 chained)
     int q_d() const { return c.n_heads * c.head_dim; }
     int kv_d() const { return c.n_kv_heads * c.head_dim; }
 };
@@ -126,7 +127,8 @@ qh_model *qh_create(const qh_config *cfg)
 void qh_destroy(qh_model *m)
 {
     if (!m) return;
-    for (auto &g : m->graphs) quartz_graph_destroy(g.second);
+    for (void *g : m->graphs)
+        if (g) quartz_graph_destroy(g);
     delete m;
 }
 
@@ -195,7 +197,7 @@ int qh_finalize(qh_model *m)
               m->d_expert_out.alloc_f32(fd) && m->d_expert_acc.alloc_f32(d) && m->d_gate_all.alloc_f32(4 * (size_t)fd) &&
               m->d_up_all.alloc_f32(4 * (size_t)fd) && m->d_expert_out_all.alloc_f32(4 * (size_t)fd) &&
               m->d_down_all.alloc_f32(4 * (size_t)d) && m->d_router_logits.alloc_f32(std::max(c.n_experts, 1)) &&
-              m->d_logits.alloc_f32(c.vocab_size);
+              m->d_logits.alloc_f32(c.vocab_size) && m->d_step.alloc_f32(4);
     if (!ok) return -2;
     m->kv_k.resize(c.n_layers);
     m->kv_v.resize(c.n_layers);
@@ -219,6 +221,16 @@ int qh_set_kv(qh_model *m, int layer, const float *k, const float *v, int n_pos)
     if (!m || !m->finalized || layer < 0 || layer >= m->c.n_layers || n_pos > m->c.max_seq) return -1;
     cuda_h2d(m->kv_k[layer].ptr, k, (size_t)n_pos * m->kv_d() * 4);
     cuda_h2d(m->kv_v[layer].ptr, v, (size_t)n_pos * m->kv_d() * 4);
+    return 0;
+}
+
+int qh_get_kv(qh_model *m, int layer, float *k, float *v, int pos0, int n_pos)
+{
+    if (!m || !m->finalized || layer < 0 || layer >= m->c.n_layers || pos0 < 0 || n_pos < 0 || pos0 + n_pos > m->c.max_seq) return -1;
+    const size_t off = (size_t)pos0 * m->kv_d() * 4, bytes = (size_t)n_pos * m->kv_d() * 4;
+    cuda_d2h(k, (const uint8_t *)m->kv_k[layer].ptr + off, bytes);
+    cuda_d2h(v, (const uint8_t *)m->kv_v[layer].ptr + off, bytes);
+    cuda_sync();
     return 0;
 }
 
@@ -389,6 +401,7 @@ static bool fusable(qh_model *m)
     const qh_config &c = m->c;
     if (c.n_experts > 0 || c.head_dim > 128 || c.head_dim % 32 || c.embed_dim % 64 || c.ffn_dim % 64) return false;
     if (m->q_d() % m->kv_d() != 0 || m->q_d() / m->kv_d() + 2 > 8) return false;
+    if (!cuda_attn_step_supported(c.n_heads, c.n_kv_heads, c.head_dim)) return false;
     for (auto &L : m->L) {
         if (!L.q_norm.empty() || !L.k_norm.empty() || L.has_qkv_bias || !L.o_bias.empty()) return false;
         if (L.q.ggml_type != L.k.ggml_type || L.q.ggml_type != L.v.ggml_type || L.gate.ggml_type != L.up.ggml_type) return false;
@@ -401,34 +414,48 @@ static bool fusable(qh_model *m)
     return cuda_gemv_q_supported(m->lm_head.ggml_type, m->lm_head.u8(), c.embed_dim) != 0;
 }
 
-// The fused sequence: seven launches per layer instead of twenty-one (+ seven conversions).
-static void step_fused(qh_model *m, int token, int pos, bool need_logits)
+// Sliding-window layers (src/main.rs:231-237): the window the attention kernel applies on the device.
+static int attn_window(const qh_config &c, int layer) { return (c.swa_window > 0 && layer % 2 == 0) ? c.swa_window : 0; }
+
+// The attention block of layer l as one launch; token position comes from the device step words.
+static void attn_layer(qh_model *m, int l, int out_slot)
 {
     const qh_config &c = m->c;
-    const int d = c.embed_dim, h = c.n_heads, kv = c.n_kv_heads, hd = c.head_dim, q_d = m->q_d(), kv_d = m->kv_d(),
-              fd = c.ffn_dim, seq = pos + 1;
-    const float scale = attn_scale(c);
-    const int q_slices = q_d / kv_d;
-    const size_t q_slice_bytes = ggml_type_size(m->L[0].q.ggml_type, (size_t)d * kv_d);
-    cuda_embed_lookup(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, token, d);
+    Layer &L = m->L[l];
+    cuda_attn_step(m->d_attn_out.f(), m->d_q.f(), m->d_k.f(), m->d_v.f(), m->kv_k[l].f(), m->kv_v[l].f(), c.n_heads,
+                   c.n_kv_heads, c.head_dim, c.max_seq, (const int *)m->d_step.ptr, 0, attn_window(c, l), attn_scale(c),
+                   L.sinks.f(), c.rope_theta, c.yarn_scale, c.yarn_orig_ctx, c.rope_neox, out_slot);
+}
+
+// q (as kv_d-row slices), k and v of layer L as the matrices of one multi-matrix GEMV
+static int qkv_mats(qh_model *m, Layer &L, const uint8_t **W, float **Y)
+{
+    const int d = m->c.embed_dim, kv_d = m->kv_d(), q_slices = m->q_d() / kv_d;
+    const size_t q_slice_bytes = ggml_type_size(L.q.ggml_type, (size_t)d * kv_d);   // per layer: types may differ between layers
+    int n = 0;
+    for (int s = 0; s < q_slices; s++) { W[n] = L.q.u8() + s * q_slice_bytes; Y[n] = m->d_q.f() + (size_t)s * kv_d; n++; }
+    W[n] = L.k.u8(); Y[n] = m->d_k.f(); n++;
+    W[n] = L.v.u8(); Y[n] = m->d_v.f(); n++;
+    return n;
+}
+
+// The fused sequence: five or six launches per layer instead of twenty-one (+ seven conversions).  Token id and
+// position are read from the device step words (cuda_step_set), so the recording serves every step.
+static void step_fused(qh_model *m, bool need_logits)
+{
+    const qh_config &c = m->c;
+    const int d = c.embed_dim, q_d = m->q_d(), kv_d = m->kv_d(), fd = c.ffn_dim;
+    cuda_embed_lookup_dev(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, (const int *)m->d_step.ptr, d);
     for (int l = 0; l < c.n_layers; l++) {
         Layer &L = m->L[l];
-        // q (as kv_d-row slices), k and v in one launch that normalises the hidden state in its prologue
+        // q, k and v in one launch that normalises the hidden state in its prologue
         const uint8_t *W[8];
         float *Y[8];
-        int n = 0;
-        for (int s = 0; s < q_slices; s++) { W[n] = L.q.u8() + s * q_slice_bytes; Y[n] = m->d_q.f() + (size_t)s * kv_d; n++; }
-        W[n] = L.k.u8(); Y[n] = m->d_k.f(); n++;
-        W[n] = L.v.u8(); Y[n] = m->d_v.f(); n++;
+        const int n = qkv_mats(m, L, W, Y);
         cuda_gemv_rmsnorm(L.q.ggml_type, n, W, Y, m->d_hidden.f(), L.attn_norm.f(), d, kv_d, 0);
-        // RoPE + KV append, then split-KV attention and its merge: three launches.  (cuda_attn_block does the
-        // same in one or two launches; inside a replayed graph at a context of 1024 it is the slower choice,
-        // 2.15 against 2.06 ms per token: every attention CTA then rotates its own queries.)
-        cuda_rope_kv(m->d_q.f(), m->d_k.f(), m->d_v.f(), m->kv_k[l].f(), m->kv_v[l].f(), h, kv, hd, pos, c.rope_theta,
-                     c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
-        const int k_start = attn_start(c, l, pos), seq_a = seq - k_start;
-        cuda_attn_decode(m->d_attn_out.f(), m->d_q.f(), m->kv_k[l].f() + (size_t)k_start * kv_d,
-                         m->kv_v[l].f() + (size_t)k_start * kv_d, h, kv, seq_a, hd, kv_d, scale, L.sinks.f(), 1);
+        // RoPE, KV append, attention over the whole context and its merge: one launch, which also leaves the
+        // output projection's activation form in slot 1
+        attn_layer(m, l, 1);
         {   // output projection, residual added in the epilogue
             const uint8_t *w1[1] = {L.o.u8()};
             float *y1[1] = {m->d_hidden.f()};
@@ -452,83 +479,69 @@ static void step_fused(qh_model *m, int token, int pos, bool need_logits)
     cuda_gemv_rmsnorm(m->lm_head.ggml_type, 1, w1, y1, m->d_hidden.f(), m->final_norm.f(), d, c.vocab_size, 0);
 }
 
-// The chained sequence: per layer RoPE + KV append, attention (two kernels) and ONE persistent kernel that
-// runs output projection -> gate/up -> down -> the next layer's q/k/v (or the output head) with grid-wide
-// barriers between the links: four launches per layer.
-static bool chainable(qh_model *m)
+// The chained sequence: per layer the attention launch and ONE persistent kernel that runs output projection ->
+// gate/up -> down -> the next layer's q/k/v (or the output head) with grid-wide barriers between the links: two
+// launches per layer.
+static int chain_ops(qh_model *m, int l, bool need_logits, qz_chain_op *ops, const uint8_t **w1, const uint8_t **w2,
+                     const uint8_t **w3, float **y1, float **y2, const uint8_t **W4, float **Y4)
 {
     const qh_config &c = m->c;
     const int d = c.embed_dim, kv_d = m->kv_d(), q_d = m->q_d(), fd = c.ffn_dim;
-    if (q_d % kv_d != 0 || q_d / kv_d + 2 > 8) return false;
-    Layer &L = m->L[0];
-    const uint8_t *w1[1] = {L.o.u8()};
-    const uint8_t *w2[2] = {L.gate.u8(), L.up.u8()};
-    const uint8_t *w3[1] = {L.down.u8()};
-    const uint8_t *w4[1] = {m->lm_head.u8()};
-    float *y1[1] = {m->d_hidden.f()};
-    float *y2[2] = {m->d_gate.f(), m->d_up.f()};
-    float *y4[1] = {m->d_logits.f()};
-    qz_chain_op ops[4] = {
-        {L.o.ggml_type, 1, w1, y1, q_d, d, 1, 3, m->d_attn_out.f(), nullptr, 0},
-        {L.gate.ggml_type, 2, w2, y2, d, fd, 0, 1, m->d_hidden.f(), L.ffn_norm.f(), 0},
-        {L.down.ggml_type, 1, w3, y1, fd, d, 1, 2, m->d_gate.f(), m->d_up.f(), 0},
-        {m->lm_head.ggml_type, 1, w4, y4, d, c.vocab_size, 0, 1, m->d_hidden.f(), m->final_norm.f(), 0}};
-    return cuda_gemv_chain_supported(4, ops) != 0;
+    Layer &L = m->L[l];
+    w1[0] = L.o.u8();
+    w2[0] = L.gate.u8(); w2[1] = L.up.u8();
+    w3[0] = L.down.u8();
+    y1[0] = m->d_hidden.f();
+    y2[0] = m->d_gate.f(); y2[1] = m->d_up.f();
+    ops[0] = {L.o.ggml_type, 1, w1, y1, q_d, d, 1, 3, m->d_attn_out.f(), nullptr, 0};
+    ops[1] = {L.gate.ggml_type, 2, w2, y2, d, fd, 0, 1, m->d_hidden.f(), L.ffn_norm.f(), 0};
+    ops[2] = {L.down.ggml_type, 1, w3, y1, fd, d, 1, 2, m->d_gate.f(), m->d_up.f(), 0};
+    if (l + 1 < c.n_layers) {
+        Layer &Nx = m->L[l + 1];
+        const int n = qkv_mats(m, Nx, W4, Y4);
+        ops[3] = {Nx.q.ggml_type, n, W4, Y4, d, kv_d, 0, 1, m->d_hidden.f(), Nx.attn_norm.f(), 0};
+        return 4;
+    }
+    if (need_logits) {
+        W4[0] = m->lm_head.u8();
+        Y4[0] = m->d_logits.f();
+        ops[3] = {m->lm_head.ggml_type, 1, W4, Y4, d, c.vocab_size, 0, 1, m->d_hidden.f(), m->final_norm.f(), 0};
+        return 4;
+    }
+    return 3;
 }
 
-static void step_chained(qh_model *m, int token, int pos, bool need_logits)
+static bool chainable(qh_model *m)
 {
     const qh_config &c = m->c;
-    const int d = c.embed_dim, h = c.n_heads, kv = c.n_kv_heads, hd = c.head_dim, q_d = m->q_d(), kv_d = m->kv_d(),
-              fd = c.ffn_dim, seq = pos + 1;
-    const float scale = attn_scale(c);
-    const int q_slices = q_d / kv_d;
-    const size_t q_slice_bytes = ggml_type_size(m->L[0].q.ggml_type, (size_t)d * kv_d);
-    cuda_embed_lookup(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, token, d);
-    auto qkv = [&](Layer &L, const uint8_t **W, float **Y) {
-        int n = 0;
-        for (int s = 0; s < q_slices; s++) { W[n] = L.q.u8() + s * q_slice_bytes; Y[n] = m->d_q.f() + (size_t)s * kv_d; n++; }
-        W[n] = L.k.u8(); Y[n] = m->d_k.f(); n++;
-        W[n] = L.v.u8(); Y[n] = m->d_v.f(); n++;
-        return n;
-    };
+    if (m->q_d() % m->kv_d() != 0 || m->q_d() / m->kv_d() + 2 > 8) return false;
+    for (int l = 0; l < c.n_layers; l++) {   // every layer: quantization types may differ from layer to layer
+        const uint8_t *w1[1], *w2[2], *w3[1], *W4[8];
+        float *y1[1], *y2[2], *Y4[8];
+        qz_chain_op ops[4];
+        const int n_ops = chain_ops(m, l, true, ops, w1, w2, w3, y1, y2, W4, Y4);
+        if (!cuda_gemv_chain_supported(n_ops, ops)) return false;
+    }
+    return true;
+}
+
+static void step_chained(qh_model *m, bool need_logits)
+{
+    const qh_config &c = m->c;
+    const int d = c.embed_dim, kv_d = m->kv_d();
+    cuda_embed_lookup_dev(m->d_hidden.f(), m->embed.u8(), m->embed.ggml_type, (const int *)m->d_step.ptr, d);
     {
         const uint8_t *W[8];
         float *Y[8];
-        const int n = qkv(m->L[0], W, Y);
+        const int n = qkv_mats(m, m->L[0], W, Y);
         cuda_gemv_rmsnorm(m->L[0].q.ggml_type, n, W, Y, m->d_hidden.f(), m->L[0].attn_norm.f(), d, kv_d, 0);
     }
     for (int l = 0; l < c.n_layers; l++) {
-        Layer &L = m->L[l];
-        cuda_rope_kv(m->d_q.f(), m->d_k.f(), m->d_v.f(), m->kv_k[l].f(), m->kv_v[l].f(), h, kv, hd, pos, c.rope_theta,
-                     c.yarn_scale, c.yarn_orig_ctx, c.rope_neox);
-        const int k_start = attn_start(c, l, pos), seq_a = seq - k_start;
-        cuda_attn_decode(m->d_attn_out.f(), m->d_q.f(), m->kv_k[l].f() + (size_t)k_start * kv_d,
-                         m->kv_v[l].f() + (size_t)k_start * kv_d, h, kv, seq_a, hd, kv_d, scale, L.sinks.f(), -1);
-        const uint8_t *w1[1] = {L.o.u8()};
-        const uint8_t *w2[2] = {L.gate.u8(), L.up.u8()};
-        const uint8_t *w3[1] = {L.down.u8()};
-        float *y1[1] = {m->d_hidden.f()};
-        float *y2[2] = {m->d_gate.f(), m->d_up.f()};
-        const uint8_t *W4[8];
-        float *Y4[8];
-        qz_chain_op ops[4] = {
-            {L.o.ggml_type, 1, w1, y1, q_d, d, 1, 3, m->d_attn_out.f(), nullptr, 0},
-            {L.gate.ggml_type, 2, w2, y2, d, fd, 0, 1, m->d_hidden.f(), L.ffn_norm.f(), 0},
-            {L.down.ggml_type, 1, w3, y1, fd, d, 1, 2, m->d_gate.f(), m->d_up.f(), 0},
-            {}};
-        int n_ops = 3;
-        if (l + 1 < c.n_layers) {
-            Layer &Nx = m->L[l + 1];
-            const int n = qkv(Nx, W4, Y4);
-            ops[3] = {Nx.q.ggml_type, n, W4, Y4, d, kv_d, 0, 1, m->d_hidden.f(), Nx.attn_norm.f(), 0};
-            n_ops = 4;
-        } else if (need_logits) {
-            W4[0] = m->lm_head.u8();
-            Y4[0] = m->d_logits.f();
-            ops[3] = {m->lm_head.ggml_type, 1, W4, Y4, d, c.vocab_size, 0, 1, m->d_hidden.f(), m->final_norm.f(), 0};
-            n_ops = 4;
-        }
+        attn_layer(m, l, -1);
+        const uint8_t *w1[1], *w2[2], *w3[1], *W4[8];
+        float *y1[1], *y2[2], *Y4[8];
+        qz_chain_op ops[4];
+        const int n_ops = chain_ops(m, l, need_logits, ops, w1, w2, w3, y1, y2, W4, Y4);
         cuda_gemv_chain(n_ops, ops);
     }
 }
@@ -548,26 +561,23 @@ int qh_step_device(qh_model *m, int token, int pos, int fused)
     }
     // fused == 2 asks for the chained sequence (falls back to the fused one where the chain kernel does not apply)
     const bool chain = fused == 2 && chainable(m);
-    auto step = [&](qh_model *mm, int tk, int ps, bool nl) { chain ? step_chained(mm, tk, ps, nl) : step_fused(mm, tk, ps, nl); };
-    // one recorded graph per (position, token, sequence kind)
-    auto key = std::make_pair(pos, 2 * token + (chain ? 1 : 0));
-    auto it = m->graphs.find(key);
-    if (it == m->graphs.end()) {
-        step(m, token, pos, true);   // eager once: creates every scratch buffer, warms the kernels
+    auto step = [&](qh_model *mm, bool nl) { chain ? step_chained(mm, nl) : step_fused(mm, nl); };
+    // Token id and position go to the device step words; the step itself is recorded once per model and
+    // sequence kind and replayed for every (token, position).
+    cuda_step_set((int *)m->d_step.ptr, token, pos);
+    void *&g = m->graphs[chain ? 2 : 1];
+    if (!g) {
+        step(m, true);   // eager once: creates every scratch buffer, warms the kernels
         cuda_sync();
         const long long b2 = quartz_launch_count();
         if (!quartz_graph_begin()) return -2;
-        step(m, token, pos, true);
-        void *g = quartz_graph_end();
+        step(m, true);
+        g = quartz_graph_end();
         if (!g) return -3;
+        m->n_recorded++;
         m->last_launches = quartz_launch_count() - b2;
-        if (m->graphs.size() > 64) {
-            for (auto &old : m->graphs) quartz_graph_destroy(old.second);
-            m->graphs.clear();
-        }
-        it = m->graphs.emplace(key, g).first;
     }
-    quartz_graph_launch(it->second);
+    quartz_graph_launch(g);
     return 0;
 }
 
@@ -604,5 +614,6 @@ int qh_read_hidden(qh_model *m, float *host)
 }
 
 long long qh_launches_last_step(qh_model *m) { return m ? m->last_launches : 0; }
+int qh_graphs_recorded(qh_model *m) { return m ? m->n_recorded : 0; }
 
 }  // extern "C"

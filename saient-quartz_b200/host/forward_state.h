@@ -7,8 +7,9 @@
  *
  * Two step functions:
  *   qh_forward_step        the reference sequence, call for call (src/cuda.rs:507-851)
- *   qh_forward_step_fused  the same arithmetic through the fused entry points, recorded once
- *                          per position as a CUDA graph and replayed
+ *   qh_forward_step_fused  the same arithmetic through the fused entry points, recorded ONCE per model as
+ *                          a CUDA graph and replayed for every step: token id and position are two
+ *                          device words (cuda_step_set) that the recorded kernels read
  *
  * The C interface below exists so that tests and the benchmark can drive it through ctypes.
  */
@@ -58,6 +59,8 @@ int qh_set_tensor(qh_model *m, int role, int layer, uint32_t ggml_type, const vo
 int qh_finalize(qh_model *m);
 /* write n_pos rows of K and V (f32 [n_pos x kv_dim]) into layer's caches (benchmark pre-fill) */
 int qh_set_kv(qh_model *m, int layer, const float *k, const float *v, int n_pos);
+/* read n_pos rows of K and V of a layer's caches back, starting at row pos0 */
+int qh_get_kv(qh_model *m, int layer, float *k, float *v, int pos0, int n_pos);
 /* returns 0 on success; logits_host (vocab floats) filled when need_logits */
 int qh_forward_step(qh_model *m, int token, int pos, int need_logits, float *logits_host);
 int qh_forward_step_fused(qh_model *m, int token, int pos, int need_logits, float *logits_host);
@@ -68,6 +71,7 @@ int qh_forward_step_chained(qh_model *m, int token, int pos, int need_logits, fl
 int qh_step_device(qh_model *m, int token, int pos, int fused);
 int qh_read_hidden(qh_model *m, float *host);   /* d_hidden, for layer-level tests */
 long long qh_launches_last_step(qh_model *m);    /* kernel launches issued by the last step (graph nodes if fused) */
+int qh_graphs_recorded(qh_model *m);             /* graph recordings made for this model so far (one per sequence kind) */
 
 #ifdef __cplusplus
 }

@@ -47,6 +47,8 @@ def host_lib():
         H.qh_read_hidden.argtypes = [C.c_void_p, C.c_void_p]
         H.qh_launches_last_step.restype = C.c_longlong
         H.qh_launches_last_step.argtypes = [C.c_void_p]
+        H.qh_graphs_recorded.argtypes = [C.c_void_p]
+        H.qh_get_kv.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
         _host = H
     return _host
 
@@ -152,6 +154,14 @@ class HostModel:
                 out.append((k, v))
         return out
 
+    def read_kv(self, layer, pos0, n_pos):
+        """Rows [pos0, pos0 + n_pos) of a layer's K and V caches."""
+        kv_d = self.cfg["n_kv_heads"] * self.cfg["head_dim"]
+        k, v = np.empty((n_pos, kv_d), np.float32), np.empty((n_pos, kv_d), np.float32)
+        if self.H.qh_get_kv(self.m, layer, k.ctypes.data, v.ctypes.data, pos0, n_pos) != 0:
+            raise RuntimeError("qh_get_kv failed")
+        return k, v
+
     def step(self, token, pos, fused=False):
         logits = np.empty(self.cfg["vocab_size"], dtype=np.float32)
         fn = (self.H.qh_forward_step_chained if fused == 2 else self.H.qh_forward_step_fused) if fused else self.H.qh_forward_step
@@ -171,6 +181,10 @@ class HostModel:
 
     def launches(self):
         return int(self.H.qh_launches_last_step(self.m))
+
+    def graphs_recorded(self):
+        """How many times a step sequence has been recorded into a graph for this model."""
+        return int(self.H.qh_graphs_recorded(self.m))
 
     def close(self):
         if self.m:

@@ -65,7 +65,8 @@ def test_ab_against_reference_kernels(gpu, oracle_mod, tables):
     gpu.check_error()
     table = "\n".join(lines)
     print("\n" + table)
-    out_dir = os.environ.get("QUARTZ_REPORT_DIR", "gpurun_out")
-    os.makedirs(out_dir, exist_ok=True)
-    with open(os.path.join(out_dir, "ab_reference.md"), "w") as f:
-        f.write(table + "\n")
+    out_dir = os.environ.get("QUARTZ_REPORT_DIR")   # where to leave the table as a file, if anywhere
+    if out_dir:
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, "ab_reference.md"), "w") as f:
+            f.write(table + "\n")

@@ -84,6 +84,65 @@ def test_decode_several_positions_and_neox(gpu, oracle_mod):
     gpu.check_error()
 
 
+def test_generation_loop_through_one_recorded_graph(gpu, oracle_mod):
+    """Consecutive positions with different tokens through the fused and the chained sequence: token id and
+    position are device words, so the step is recorded once per model and sequence kind and replayed for
+    every step (src/cuda.rs:507-851 takes `token` and `pos` per call)."""
+    for fused in (1, 2):
+        m = _tiny_dense(gpu)
+        kv = m.fill_kv(29, keep=True)
+        ref = _ref_for(m, oracle_mod, kv)
+        # 29 .. 34 crosses a 32-position block boundary of the attention kernel
+        for pos, tok in ((29, 3), (30, 300), (31, 0), (32, 77), (33, 5), (34, 5)):
+            want = ref.forward(tok, pos)
+            got = m.step(tok, pos, fused=fused)
+            assert _rel(got, want) < 5e-3, (fused, pos)
+        assert m.graphs_recorded() == 1, fused
+        m.close()
+    gpu.check_error()
+
+
+def test_layers_with_different_quantization_types(gpu, oracle_mod):
+    """A *_K_M-style mix: q/k/v (and the other projections) use another block format in every layer, so the
+    byte size of a q slice differs from layer to layer."""
+    from saient_quartz_b200 import synth
+    from saient_quartz_b200.host_model import HostModel
+    cfg = dict(vocab_size=320, embed_dim=2048, n_heads=16, n_kv_heads=4, n_layers=3, ffn_dim=4096, head_dim=128,
+               rope_theta=500000.0, max_seq=64)
+    m = HostModel(keep_host=True, **cfg)
+    rng = np.random.Generator(np.random.PCG64([0x717]))
+    d, fd, q_d, kv_d = 2048, 4096, 2048, 512
+    tid = [900]
+
+    def w(role, l, t, K, N):
+        tid[0] += 1
+        m.set(role, l, t, synth.make_weights(t, K, N, tensor_id=tid[0]))
+
+    def norm(role, l, n):
+        m.set(role, l, 0, (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32))
+
+    w("EMBED", 0, 12, d, 320)
+    for l, (tq, to, tg, td) in enumerate(((12, 12, 12, 14), (8, 14, 8, 12), (14, 8, 13, 8))):
+        w("Q", l, tq, d, q_d); w("K", l, tq, d, kv_d); w("V", l, tq, d, kv_d); w("O", l, to, q_d, d)
+        w("GATE", l, tg, d, fd); w("UP", l, tg, d, fd); w("DOWN", l, td, fd, d)
+        norm("ATTN_NORM", l, d); norm("FFN_NORM", l, d)
+    norm("FINAL_NORM", 0, d)
+    w("LM_HEAD", 0, 14, d, 320)
+    m.finalize()
+    kv = m.fill_kv(10, keep=True)
+    ref = _ref_for(m, oracle_mod, kv)
+    for pos, tok in ((10, 1), (11, 319)):
+        want = ref.forward(tok, pos)
+        got_f = m.step(tok, pos, fused=1)
+        assert _rel(got_f, want) < 5e-3, pos
+    assert m.launches() <= 6 * 3 + 2      # the fused sequence ran (not the reference sequence)
+    kv2 = m.fill_kv(10)
+    ref2 = _ref_for(m, oracle_mod, kv)
+    for pos, tok in ((10, 1), (11, 319)):
+        assert _rel(m.step(tok, pos, fused=2), ref2.forward(tok, pos)) < 5e-3, pos
+    gpu.check_error()
+
+
 def test_first_token_empty_cache(gpu, oracle_mod):
     m = _tiny_dense(gpu)
     ref = _ref_for(m, oracle_mod, [])
@@ -330,6 +389,72 @@ def test_attn_block_matches_separate_launches(gpu, neox):
             assert np.abs(got - want).max() <= 2e-5 * max(np.abs(want).max(), 1e-30), (nh, hd, pos, rep)
         assert np.array_equal(dk2.download(), want_k) and np.array_equal(dv2.download(), want_v)
         assert np.array_equal(dq2.download(), q) and np.array_equal(dkn2.download(), k)
+    gpu.check_error()
+
+
+@pytest.mark.parametrize("neox", [0, 1])
+def test_attn_step_matches_separate_launches(gpu, neox):
+    """cuda_attn_step (RoPE + KV append + attention + cluster merge in one launch, position from a device word
+    or from the argument) against cuda_rope_kv + cuda_attn_decode: same output, same cache rows, q / k_new
+    left un-rotated; head groups of 1, 2, 4, 6, 8 and 16 query heads per kv head, sliding windows, sinks,
+    positions inside and across the 32-position blocks the CTAs of a cluster share out."""
+    import ctypes as C
+    L = gpu.lib()
+    r = np.random.Generator(np.random.PCG64([0xA79, neox]))
+    step_words = gpu.GpuBuf.alloc_f32(4)
+    cases = [(32, 8, 128, 1024, 0, 1100, False), (8, 8, 64, 32, 0, 64, True), (12, 2, 96, 69, 65, 128, True),
+             (4, 1, 128, 0, 0, 16, False), (16, 4, 128, 31, 0, 40, False), (64, 8, 128, 600, 0, 640, False),
+             (32, 2, 64, 257, 100, 300, True), (8, 4, 128, 2047, 0, 2048, False), (32, 8, 128, 95, 64, 128, False)]
+    for ci, (nh, nkv, hd, pos, window, max_seq, sink) in enumerate(cases):
+        assert L.cuda_attn_step_supported(nh, nkv, hd) == 1
+        kv_dim = nkv * hd
+        kc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+        vc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+        q = r.standard_normal(nh * hd, dtype=np.float32)
+        k = r.standard_normal(kv_dim, dtype=np.float32)
+        v = r.standard_normal(kv_dim, dtype=np.float32)
+        sinks = r.standard_normal(nh, dtype=np.float32) if sink else np.full(nh, -np.inf, np.float32)
+        scale = np.float32(1.0 / np.sqrt(hd))
+        theta, ys, yc = np.float32(500000.0), np.float32(1.0), 0
+        k_start = max(0, pos + 1 - window) if window > 0 else 0
+        seq = pos - k_start + 1
+        dk1, dv1 = gpu.GpuBuf.upload(kc), gpu.GpuBuf.upload(vc)
+        dq1, dkn1, dvn = gpu.GpuBuf.upload(q), gpu.GpuBuf.upload(k), gpu.GpuBuf.upload(v)
+        ds, o1 = gpu.GpuBuf.upload(sinks), gpu.GpuBuf.alloc_f32(nh * hd)
+        L.cuda_rope_kv(dq1.ptr, dkn1.ptr, dvn.ptr, dk1.ptr, dv1.ptr, nh, nkv, hd, pos, theta, ys, yc, neox)
+        L.cuda_attn_decode(o1.ptr, dq1.ptr, dk1.ptr + 4 * k_start * kv_dim, dv1.ptr + 4 * k_start * kv_dim, nh, nkv, seq, hd,
+                           kv_dim, scale, ds.ptr, -1)
+        want, want_k, want_v = o1.download(), dk1.download(), dv1.download()
+        dk2, dv2 = gpu.GpuBuf.upload(kc), gpu.GpuBuf.upload(vc)
+        dq2, dkn2, o2 = gpu.GpuBuf.upload(q), gpu.GpuBuf.upload(k), gpu.GpuBuf.alloc_f32(nh * hd)
+        for rep in range(2):
+            if (ci + rep) & 1:      # position from the device step words
+                L.cuda_step_set(step_words.ptr, 7, pos)
+                L.cuda_attn_step(o2.ptr, dq2.ptr, dkn2.ptr, dvn.ptr, dk2.ptr, dv2.ptr, nh, nkv, hd, max_seq, step_words.ptr, 0,
+                                 window, scale, ds.ptr, theta, ys, yc, neox, -1)
+            else:
+                L.cuda_attn_step(o2.ptr, dq2.ptr, dkn2.ptr, dvn.ptr, dk2.ptr, dv2.ptr, nh, nkv, hd, max_seq, None, pos,
+                                 window, scale, ds.ptr, theta, ys, yc, neox, -1)
+            got = o2.download()
+            assert np.abs(got - want).max() <= 2e-5 * max(np.abs(want).max(), 1e-30), (nh, nkv, hd, pos, rep)
+        assert np.array_equal(dk2.download(), want_k) and np.array_equal(dv2.download(), want_v)
+        assert np.array_equal(dq2.download(), q) and np.array_equal(dkn2.download(), k)
+    # the activation form it leaves for the output projection equals the conversion of its f32 output
+    nh, nkv, hd, pos, max_seq = 32, 8, 128, 70, 96
+    kv_dim, K, N = nkv * hd, nh * hd, 256
+    from saient_quartz_b200 import synth
+    kc, vc = r.standard_normal((max_seq, kv_dim), dtype=np.float32), r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+    q, k, v = (r.standard_normal(n, dtype=np.float32) for n in (K, kv_dim, kv_dim))
+    dk, dv, dq, dkn, dvn = (gpu.GpuBuf.upload(a) for a in (kc, vc, q, k, v))
+    o = gpu.GpuBuf.alloc_f32(K)
+    w = gpu.GpuBuf.upload(synth.make_weights(12, K, N, tensor_id=690))
+    y1, y2 = gpu.GpuBuf.alloc_f32(N), gpu.GpuBuf.alloc_f32(N)
+    L.cuda_attn_step(o.ptr, dq.ptr, dkn.ptr, dvn.ptr, dk.ptr, dv.ptr, nh, nkv, hd, max_seq, None, pos, 0,
+                     np.float32(0.088), None, np.float32(1e4), np.float32(1.0), 0, neox, 2)
+    W, Y, S = (C.c_void_p * 1)(w.ptr), (C.c_void_p * 1)(y1.ptr), (C.c_int * 1)(2)
+    L.cuda_gemv_q(12, 1, W, S, Y, K, N, 0)
+    L.cuda_gemv(12, w.ptr, o.ptr, y2.ptr, K, N)
+    assert np.array_equal(y1.download(), y2.download())
     gpu.check_error()
 
 

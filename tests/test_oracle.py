@@ -7,7 +7,15 @@ import numpy as np
 import pytest
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "dequant_golden.npz")
-REF = "/root/reference/src"
+
+
+def _ref_src():
+    from oracle import build as ob
+    root = ob.reference_root()
+    return os.path.join(root, "src") if root else None
+
+
+REF = _ref_src()
 
 
 @pytest.fixture(scope="module")
@@ -157,7 +165,7 @@ def test_ksigns_is_parity_table(oracle_mod, tables):
     assert np.array_equal(oracle_mod.ksigns(), tables["ksigns"])
 
 
-@pytest.mark.skipif(not os.path.isdir(REF), reason="reference tree not mounted")
+@pytest.mark.skipif(REF is None, reason="reference tree not mounted")
 def test_codebooks_equal_reference_tables(tables):
     """The gguf-package codebooks are the numbers in src/iq2_tables.rs / src/iq3_tables.rs."""
     def parse(path, name):
