@@ -105,6 +105,14 @@ long long quartz_launch_count(void);
  * QUARTZ_GEMV_IMPL=ldg selects 1 at start-up. */
 void quartz_set_gemv_impl(int impl);
 
+/* Hint for the NEXT streaming GEMV launch of this library (cuda_gemv, cuda_gemv_q, cuda_gemv_rmsnorm, ...): once
+ * that kernel's producer lanes have issued their own weight stream they also pull [d_ptr, d_ptr + bytes) -- the
+ * weights of the operation that will FOLLOW it -- into the L2 cache, so that HBM keeps working while the kernel
+ * drains, exits and its successor starts, and the successor's first tiles come from L2.  Up to four ranges per
+ * launch (call it once per range), each capped at 24 MB (environment variable QUARTZ_PREFETCH_MB; 0 = off).
+ * Purely a performance hint: results are unaffected, a launch that is not the TMA-staged kernel ignores it. */
+void quartz_prefetch_next(const void *d_ptr, size_t bytes);
+
 /* The IQ3_XXS codebook (256 x u32); the reference has no IQ3_XXS. */
 void cuda_set_iq3xxs_grid(const uint32_t *host);
 
@@ -204,6 +212,24 @@ void cuda_attn_step(float *out, const float *q, const float *k_new, const float 
                     int n_heads, int n_kv_heads, int head_dim, int max_seq, const int *d_step, int pos, int window,
                     float scale, const float *sinks, float theta, float yarn_scale, int yarn_orig_ctx, int neox,
                     int out_slot);
+
+/* ---- Batched (prompt) forms of the per-token helpers, for n tokens at consecutive positions pos0 .. pos0+n-1; with
+ * cuda_gemm for the projections they make up a batched GPU prefill (the reference's GPU prefill runs the decode step
+ * token by token, src/main.rs:1410-1416; its batched prefill is CPU-only, src/main.rs:1157-1341).
+ *   cuda_embed_lookup_rows  out[r, :] = dequantized row d_tokens[r] of the embedding table, r < n
+ *   cuda_rms_norm_rows      cuda_rms_norm of every row of x [n_rows, n]; out may alias x
+ *   cuda_rope_kv_rows       cuda_rope_kv for token t at position pos0 + t: q [n, n_heads*head_dim] and k [n, kv_dim]
+ *                           rotated in place, k / v rows appended to the caches
+ *   cuda_attn_prompt        causal attention of the n tokens: token t attends to cache positions [k_start, pos0 + t]
+ *                           (window as in cuda_attn_step); q is already rotated and the caches already hold the n
+ *                           new rows (cuda_rope_kv_rows).  out [n, n_heads*head_dim].  Same head-geometry limits
+ *                           as cuda_attn_step; one CTA per (kv head, token). */
+void cuda_embed_lookup_rows(float *out, const uint8_t *data, uint32_t ggml_type, const int *d_tokens, int n, int embed_dim);
+void cuda_rms_norm_rows(float *out, const float *x, const float *w, int n_rows, int n);
+void cuda_rope_kv_rows(float *q, float *k, const float *v, float *k_cache, float *v_cache, int n_tok, int n_heads,
+                       int n_kv_heads, int head_dim, int pos0, float theta, float yarn_scale, int yarn_orig_ctx, int neox);
+void cuda_attn_prompt(float *out, const float *q, const float *k_cache, const float *v_cache, int n_tok, int n_heads,
+                      int n_kv_heads, int head_dim, int max_seq, int pos0, int window, float scale, const float *sinks);
 
 /* A chain of dependent GEMVs as ONE persistent kernel (one CTA per SM): op k+1's activation vector is
  * computed from op k's outputs after a grid-wide barrier inside the kernel, while the weight rows of
@@ -321,6 +347,24 @@ void cuda_moe_ffn_dev(uint32_t type_gate_up, uint32_t type_down, const uint8_t *
  * n_experts <= 256, top_k <= 8. */
 void cuda_router_topk(const float *d_logits, const float *d_bias, int m, int n_experts, int top_k, int renorm, int *d_ids,
                       float *d_w);
+
+/* Batch-1 (decode) MoE with the experts chosen on the DEVICE, so that a step needs no device-to-host copy and
+ * no synchronisation per layer (the reference reads the router logits back and sorts on the host,
+ * src/cuda.rs:673-701, then passes expert pointers computed on the host, :714-794):
+ *   cuda_gemv_experts        n_act <= 4 GEMVs in one launch; matrix k is the expert slice d_base + d_ids[k] *
+ *                            expert_bytes of a stacked expert tensor (cuda_gemv_moe4 with the pointer arithmetic of
+ *                            gpu_expert_slice, src/cuda.rs:242-258, done by the kernel).  x_stride = 0: every expert
+ *                            reads d_x; otherwise expert k reads d_x + k * x_stride floats.  Output k at d_y + k *
+ *                            out_dim.  Streaming types / shapes only (cuda_gemv_q_supported on d_base).
+ *   cuda_moe_decode_act      h[k] = swiglu(gate[k] + gate_bias[ids[k]], up[k] + up_bias[ids[k]]) (oai = clamped),
+ *                            k < n_act, vectors of ffn_dim; biases [n_experts, ffn_dim] or NULL
+ *   cuda_moe_decode_combine  acc (+)= sum_k d_w[k] * (down[k] + down_bias[ids[k]]), in the order of k */
+void cuda_gemv_experts(uint32_t ggml_type, const uint8_t *d_base, size_t expert_bytes, const int *d_ids, int n_act,
+                       const float *d_x, size_t x_stride, float *d_y, int in_dim, int out_dim);
+void cuda_moe_decode_act(float *d_out, const float *d_gate, const float *d_up, const float *d_gate_bias,
+                         const float *d_up_bias, const int *d_ids, int n_act, int ffn_dim, int oai);
+void cuda_moe_decode_combine(float *d_acc, const float *d_down, const float *d_down_bias, const int *d_ids, const float *d_w,
+                             int n_act, int embed_dim, int accumulate);
 
 /* ---- Row-sharded layers over the GPUs of one box (one process per GPU).  No counterpart in the
  * reference, which drives a single device (src/cuda.rs:301-358).  A layer's weight rows are split

@@ -61,6 +61,7 @@ _SIGS = {
     "quartz_set_stream": (None, [C.c_void_p]),
     "quartz_set_gemv_impl": (None, [C.c_int]),
     "quartz_launch_count": (C.c_longlong, []),
+    "quartz_prefetch_next": (None, [C.c_void_p, C.c_size_t]),
     "cuda_set_iq3xxs_grid": (None, [C.c_void_p]),
     "cuda_repack_weights": (C.c_int, [C.c_uint32, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "cuda_unpack_weights": (C.c_int, [C.c_void_p]),
@@ -101,6 +102,14 @@ _SIGS = {
                               C.c_float, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int]),
     "cuda_moe_ffn_dev": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                 C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
+    "cuda_embed_lookup_rows": (None, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_int, C.c_int]),
+    "cuda_rms_norm_rows": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "cuda_rope_kv_rows": (None, [C.c_void_p] * 5 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int, C.c_int]),
+    "cuda_attn_prompt": (None, [C.c_void_p] * 4 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p]),
+    "cuda_gemv_experts": (None, [C.c_uint32, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p,
+                                 C.c_int, C.c_int]),
+    "cuda_moe_decode_act": (None, [C.c_void_p] * 6 + [C.c_int, C.c_int, C.c_int]),
+    "cuda_moe_decode_combine": (None, [C.c_void_p] * 5 + [C.c_int, C.c_int, C.c_int]),
     "cuda_router_topk": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "cuda_moe_ffn": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                             C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),

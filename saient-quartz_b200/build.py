@@ -1,5 +1,8 @@
-"""Build in-tree: saient-quartz_b200/libquartz_b200.so (the CUDA library, sm_100a only) and
-saient-quartz_b200/libquartz_host.so (the C++ host side of the decode step, a pure client of the C ABI)."""
+"""Build in-tree, from ONE compilation of csrc/quartz_b200.cu for sm_100a:
+  saient-quartz_b200/libquartz_b200.so  the CUDA library (what the tests and the benchmark load)
+  saient-quartz_b200/libkernels.a       the same object as a static archive under the name the reference's
+                                        build.rs links (`static=kernels` + `cudart`, build.rs:52-72)
+and saient-quartz_b200/libquartz_host.so (the C++ host side of the decode step, a pure client of the C ABI)."""
 import os
 import subprocess
 import sys
@@ -7,6 +10,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libquartz_b200.so")
+ARCHIVE = os.path.join(HERE, "libkernels.a")
+OBJ = os.path.join(HERE, "kernels.o")
 HOST_LIB = os.path.join(HERE, "libquartz_host.so")
 HOST_SRC = os.path.join(HERE, "host", "forward_state.cpp")
 
@@ -16,7 +21,7 @@ def sources():
 
 
 def up_to_date():
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(ARCHIVE):
         return False
     t = os.path.getmtime(LIB)
     hdr = os.path.join(HERE, "..", "include", "quartz_b200.h")
@@ -45,14 +50,20 @@ def build(force=False, verbose=False):
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
     arch = os.environ.get("QUARTZ_CUDA_ARCH", "sm_100a")   # same variable as the reference's build.rs:33
     cc = arch.replace("sm_", "compute_")
-    tmp = LIB + ".tmp"
-    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", f"arch={cc},code={arch}", "-lineinfo", "-shared",
-           "-Xcompiler", "-fPIC", "-o", tmp] + [s for s in sources() if s.endswith(".cu")]
+    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", f"arch={cc},code={arch}", "-lineinfo", "-Xcompiler", "-fPIC", "-c",
+           "-o", OBJ] + [s for s in sources() if s.endswith(".cu")]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     subprocess.check_call(cmd)
-    os.replace(tmp, LIB)
+    tmp = LIB + ".tmp"
+    subprocess.check_call([nvcc, "-gencode", f"arch={cc},code={arch}", "-shared", "-o", tmp, OBJ])
+    os.replace(tmp, LIB)   # a reader never sees a half-written library
+    tmp = ARCHIVE + ".tmp"
+    if os.path.exists(tmp):
+        os.remove(tmp)
+    subprocess.check_call(["ar", "rcs", tmp, OBJ])
+    os.replace(tmp, ARCHIVE)
     build_host(force=True)
     return LIB
 

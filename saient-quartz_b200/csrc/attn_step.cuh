@@ -6,11 +6,18 @@
 //
 // The position is read from a device word, so a recorded graph serves every step of a
 // generation loop.  Grid = n_kv_heads clusters of CL CTAs (thread-block clusters, CL <= 16): the
-// CL CTAs of a kv head split the context into 32-position blocks, each runs an online softmax
-// over its blocks for all query heads of the kv head (K and V rows are staged once per CTA and
-// shared by the head group), and the partial (max, sum, out[head_dim]) triples are merged through
-// distributed shared memory: after a cluster barrier CTA r reads slice r of every peer's
-// partials and finishes G*head_dim/CL outputs.  No global scratch, no second launch, no atomics.
+// CL CTAs of a kv head split the context into 32-position blocks.  Order of events in a CTA:
+//   1. BEFORE the programmatic-dependency wait (the kernel that produces q, k, v may still be
+//      running): read the position, start the asynchronous copies of this CTA's cached K and V
+//      rows into shared memory (they were written by earlier steps), build the rotation table;
+//   2. after the wait: rotate the head group's queries, rotate and append the new key / value
+//      (the CTA that owns the last block), finish the copies;
+//   3. every warp runs an online softmax over its 32-row groups for its query head (K and V rows
+//      are staged once per CTA and shared by the whole head group);
+//   4. the CTA's partial (max, sum, out[head_dim]) per head is PUSHED into the shared memory of the
+//      cluster's CTAs (each receives the slice of outputs it will finish), one cluster barrier,
+//      then CTA r merges G*head_dim/CL outputs from what it received.
+// No global scratch, no second launch, no atomics, one cluster barrier.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -21,8 +28,9 @@ namespace qz {
 
 constexpr int AS_THREADS = 256;
 constexpr int AS_WARPS = AS_THREADS / 32;
-constexpr int AS_CHUNK = 64;             // positions staged per round (two 32-position halves)
+constexpr int AS_ROWS = 96;              // most K / V rows staged per round (three 32-position blocks)
 constexpr int AS_MAX_G = 16;             // query heads per kv head
+constexpr int AS_MAX_CL = 16;
 constexpr int AS_KS_STRIDE = ATT_MAX_HD + 4;   // floats; keeps float4 rows conflict-free across a quarter warp
 
 struct AttnStepArgs {
@@ -39,6 +47,11 @@ struct AttnStepArgs {
     int yarn_orig_ctx, neox;
     XQOut o;
     int emit_q;
+    int rows_cap;                        // K / V rows staged per round: 64 or 96 (sizes the shared memory)
+    // prompt mode (grid.y = n tokens): token t = blockIdx.y sits at position pos_host + t; q and out are
+    // [n, n_heads*head_dim]; q is ALREADY rotated and every token's k, v are ALREADY in the caches (appended by
+    // the kernel before this one, so nothing is read ahead of the dependency wait); causal: keys up to pos.
+    int prompt;
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
@@ -47,13 +60,18 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
                  : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// split cluster barrier (every thread of the CTA executes both halves)
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-// dynamic shared memory: ks [AS_CHUNK][AS_KS_STRIDE], vs [AS_CHUNK][ATT_MAX_HD], qs [G][ATT_MAX_HD],
-// ps [AS_WARPS][32], wres [AS_WARPS][2][ATT_MAX_HD + 2] (per-warp partials), res [G][ATT_MAX_HD + 2]
-__host__ __device__ inline size_t attn_step_smem(int G)
+// dynamic shared memory (floats): ks [AS_ROWS][AS_KS_STRIDE], vs [AS_ROWS][ATT_MAX_HD], qs [G][ATT_MAX_HD],
+// ps [AS_WARPS][32], wres [AS_WARPS][2][ATT_MAX_HD + 2] (per-warp partials), recv [CL][2 G + S] (what the cluster's
+// CTAs push here: their (max, sum) of every head and their part of this CTA's S outputs), cs_tab [ATT_MAX_HD / 2] x 2
+__host__ __device__ inline size_t attn_step_smem(int G, int CL, int head_dim, int rows_cap)
 {
-    return sizeof(float) * ((size_t)AS_CHUNK * AS_KS_STRIDE + (size_t)AS_CHUNK * ATT_MAX_HD + (size_t)G * ATT_MAX_HD +
-                            AS_WARPS * 32 + (size_t)AS_WARPS * 2 * (ATT_MAX_HD + 2) + (size_t)G * (ATT_MAX_HD + 2) + ATT_MAX_HD);
+    const int S = (G * head_dim) / CL;
+    return sizeof(float) * ((size_t)rows_cap * AS_KS_STRIDE + (size_t)rows_cap * ATT_MAX_HD + (size_t)G * ATT_MAX_HD +
+                            AS_WARPS * 32 + (size_t)AS_WARPS * 2 * (ATT_MAX_HD + 2) + (size_t)CL * (2 * G + S) + ATT_MAX_HD);
 }
 
 __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArgs a)
@@ -65,85 +83,101 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
     extern __shared__ __align__(16) float smem[];
     const int hd = a.head_dim, half = hd >> 1, hd4 = hd >> 2;
     const int G = a.n_heads / a.n_kv_heads;
+    const int S = (G * hd) / CL;          // outputs this CTA finishes: a multiple of 32 (host-checked)
+    const int RW = 2 * G + S;             // floats one CTA pushes to one peer
+    constexpr int RS = ATT_MAX_HD + 2;
+    const int ROWS = a.rows_cap;
     float *ks = smem;
-    float *vs = ks + AS_CHUNK * AS_KS_STRIDE;
-    float *qs = vs + AS_CHUNK * ATT_MAX_HD;
+    float *vs = ks + ROWS * AS_KS_STRIDE;
+    float *qs = vs + ROWS * ATT_MAX_HD;
     float *ps = qs + G * ATT_MAX_HD;
     float *wres = ps + AS_WARPS * 32;
-    float *res = wres + AS_WARPS * 2 * (ATT_MAX_HD + 2);
-    float2 *cs_tab = (float2 *)(res + G * (ATT_MAX_HD + 2));   // (cos, sin) per rotation pair
-    constexpr int RS = ATT_MAX_HD + 2;
+    float *recv = wres + AS_WARPS * 2 * RS;
+    float2 *cs_tab = (float2 *)(recv + CL * RW);   // (cos, sin) per rotation pair
 
     const int kvh = blockIdx.x / CL;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h_lo = kvh * G;
+    // Shared memory of another CTA may be written only once that CTA runs: arrive now, wait just before the pushes.
+    cluster_arrive();
 
-    pdl_wait();
-    pdl_trigger();
-    int pos = a.step ? a.step[1] : a.pos_host;
+    // ---- 1. everything that does not depend on the kernel before this one ----
+    // (the position words are written by a launch that precedes the whole recorded step)
+    if (a.prompt) pdl_wait();
+    int pos = a.prompt ? a.pos_host + (int)blockIdx.y : (a.step ? a.step[1] : a.pos_host);
     if (pos >= a.max_seq) pos = a.max_seq - 1;   // never write past the caches (src/cuda.rs:517-520)
     if (pos < 0) pos = 0;
     const int k_start = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
     const int seq_len = pos - k_start + 1;
-
     // this CTA's share of the context, in 32-position blocks
     const int nblk = (seq_len + 31) >> 5;
     const int base = nblk / CL, rem = nblk % CL;
     const int b0 = rank * base + min(rank, rem), bcnt = base + (rank < rem ? 1 : 0);
     const int p_lo = 32 * b0, p_hi = min(32 * (b0 + bcnt), seq_len);   // relative to k_start
-    const bool owns_new = bcnt > 0 && p_hi == seq_len;
-
-    // rotation table of this position, then the rotated queries of the head group
-    if (threadIdx.x < half) {
-        const RopeArgs r{pos, a.theta, a.yarn_scale, a.yarn_orig_ctx, a.neox};
-        float c, s;
-        rope_cs(r, threadIdx.x, hd, c, s);
-        cs_tab[threadIdx.x] = make_float2(c, s);
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * half; idx += AS_THREADS) {
-        const int g = idx / half, i = idx - g * half;
-        const float2 cs = cs_tab[i];
-        const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
-        const float *qh = a.q + (size_t)(h_lo + g) * hd;
-        const float x0 = qh[i0], x1 = qh[i1];
-        qs[g * ATT_MAX_HD + i0] = x0 * cs.x - x1 * cs.y;
-        qs[g * ATT_MAX_HD + i1] = x0 * cs.y + x1 * cs.x;
-    }
-
-    // which (head, half-chunk) this warp serves
-    const int Gw = G < AS_WARPS ? G : AS_WARPS;
-    const int wph = G <= 4 ? 2 : 1;                       // warps per head: a chunk is wph x 32 positions
-    const int n_rounds = (G + AS_WARPS - 1) / AS_WARPS;   // heads per warp (G > 8)
-    const int sub = warp / Gw;
-    const bool warp_active = sub < wph;
-    const int chunk = 32 * wph;
-    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
-    float o_run[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-
+    const bool owns_new = !a.prompt && bcnt > 0 && p_hi == seq_len;
     const float *kc = a.k_cache + (size_t)k_start * a.kv_dim + (size_t)kvh * hd;
     const float *vc = a.v_cache + (size_t)k_start * a.kv_dim + (size_t)kvh * hd;
-
-    for (int c0 = p_lo; c0 < p_hi; c0 += chunk) {
-        const int n = min(chunk, p_hi - c0);
-        const bool has_new = owns_new && c0 + n == seq_len;   // the new position is this chunk's last row
-        const int n_old = has_new ? n - 1 : n;
-        __syncthreads();   // the previous round's rows are no longer read (also orders qs / cs_tab)
+    auto stage_rows = [&](int c0, int n_old) {   // cached rows [c0, c0 + n_old) -> shared rows 0 ..
         for (int idx = threadIdx.x; idx < n_old * hd4; idx += AS_THREADS) {
             const int t = idx / hd4, c = idx - t * hd4;
             const size_t g = (size_t)(c0 + t) * a.kv_dim + 4 * c;
             cp_async16(ks + t * AS_KS_STRIDE + 4 * c, kc + g);
             cp_async16(vs + t * ATT_MAX_HD + 4 * c, vc + g);
         }
+    };
+    {
+        const int n = min(ROWS, p_hi - p_lo);
+        const bool has_new = owns_new && p_lo + n == seq_len;
+        stage_rows(p_lo, has_new ? n - 1 : n);
+    }
+    if (threadIdx.x < half) {
+        const RopeArgs r{pos, a.theta, a.yarn_scale, a.yarn_orig_ctx, a.neox};
+        float c, s;
+        rope_cs(r, threadIdx.x, hd, c, s);
+        cs_tab[threadIdx.x] = make_float2(c, s);
+    }
+    pdl_trigger();
+    __syncthreads();
+
+    // ---- 2. the new token's q, k, v ----
+    pdl_wait();
+    const size_t tok_off = a.prompt ? (size_t)blockIdx.y * a.n_heads * hd : 0;
+    for (int idx = threadIdx.x; idx < G * half; idx += AS_THREADS) {
+        const int g = idx / half, i = idx - g * half;
+        const float2 cs = a.prompt ? make_float2(1.f, 0.f) : cs_tab[i];   // prompt mode: q arrives rotated
+        const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
+        const float *qh = a.q + tok_off + (size_t)(h_lo + g) * hd;
+        const float x0 = __ldcg(qh + i0), x1 = __ldcg(qh + i1);
+        qs[g * ATT_MAX_HD + i0] = x0 * cs.x - x1 * cs.y;
+        qs[g * ATT_MAX_HD + i1] = x0 * cs.y + x1 * cs.x;
+    }
+
+    // which (head, 32-row group) this warp serves: head = warp % Gw (+ 8 for the second round when G > 8), groups
+    // sub, sub + wph, ... of every staged round
+    const int Gw = G < AS_WARPS ? G : AS_WARPS;
+    const int wph = AS_WARPS / Gw;                        // warps per head
+    const int n_rounds = (G + AS_WARPS - 1) / AS_WARPS;   // heads per warp (G > 8)
+    const int sub = warp / Gw;
+    const bool warp_active = sub < wph;
+    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
+    float o_run[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+
+    for (int c0 = p_lo; c0 < p_hi; c0 += ROWS) {
+        const int n = min(ROWS, p_hi - c0);
+        const bool has_new = owns_new && c0 + n == seq_len;   // the new position is this round's last row
+        if (c0 > p_lo) {
+            __syncthreads();   // the previous round's rows are no longer read
+            stage_rows(c0, has_new ? n - 1 : n);
+        }
         if (has_new) {
-            // the new key (rotated) and value: into the caches and into this chunk's last row
+            // the new key (rotated) and value: into the caches and into this round's last row
             const float *kh = a.k_new + (size_t)kvh * hd, *vh = a.v_new + (size_t)kvh * hd;
             float *kd = a.k_cache + (size_t)pos * a.kv_dim + (size_t)kvh * hd;
             float *vd = a.v_cache + (size_t)pos * a.kv_dim + (size_t)kvh * hd;
             for (int i = threadIdx.x; i < half; i += AS_THREADS) {
                 const float2 cs = cs_tab[i];
                 const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
-                const float x0 = kh[i0], x1 = kh[i1];
+                const float x0 = __ldcg(kh + i0), x1 = __ldcg(kh + i1);
                 const float r0 = x0 * cs.x - x1 * cs.y, r1 = x0 * cs.y + x1 * cs.x;
                 kd[i0] = r0;
                 kd[i1] = r1;
@@ -151,7 +185,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
                 ks[(n - 1) * AS_KS_STRIDE + i1] = r1;
             }
             for (int j = threadIdx.x; j < hd; j += AS_THREADS) {
-                const float v = vh[j];
+                const float v = __ldcg(vh + j);
                 vd[j] = v;
                 vs[(n - 1) * ATT_MAX_HD + j] = v;
             }
@@ -159,58 +193,59 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
         cp_async_wait_all();
         __syncthreads();
         if (!warp_active) continue;
-        const int t_lo = 32 * sub;             // this warp's rows inside the chunk
-        const int nt = min(32, n - t_lo);      // may be <= 0
-        if (nt <= 0) continue;
+        // ---- 3. online softmax over this warp's 32-row groups ----
+        for (int t_lo = 32 * sub; t_lo < n; t_lo += 32 * wph) {
+            const int nt = min(32, n - t_lo);
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            if (r >= n_rounds) break;
-            const int g = (warp % Gw) + r * AS_WARPS;
-            if (g >= G) break;
-            // one key position per lane
-            const float4 *qv = (const float4 *)(qs + g * ATT_MAX_HD);
-            const float4 *kv = (const float4 *)(ks + (t_lo + lane) * AS_KS_STRIDE);
-            float c0a = 0.f, c1a = 0.f, c2a = 0.f, c3a = 0.f;
-            for (int i = 0; i < hd4; i++) {
-                const float4 qq = qv[i], kk = kv[i];
-                c0a = fmaf(qq.x, kk.x, c0a);
-                c1a = fmaf(qq.y, kk.y, c1a);
-                c2a = fmaf(qq.z, kk.z, c2a);
-                c3a = fmaf(qq.w, kk.w, c3a);
-            }
-            float sc = (c0a + c1a) + (c2a + c3a);
-            sc = lane < nt ? sc * a.scale : -INFINITY;
-            float mx = sc;
-#pragma unroll
-            for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
-            const float m_new = fmaxf(m_run[r], mx);
-            const float p = lane < nt ? __expf(sc - m_new) : 0.f;
-            float sum = p;
-#pragma unroll
-            for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o2);
-            const float corr = __expf(m_run[r] - m_new);
-            m_run[r] = m_new;
-            l_run[r] = l_run[r] * corr + sum;
-            __syncwarp();
-            ps[warp * 32 + lane] = p;
-            __syncwarp();
-            // lane owns output dimensions 4*lane .. 4*lane+3 (head_dim <= 128)
-            float4 acc = make_float4(o_run[r][0] * corr, o_run[r][1] * corr, o_run[r][2] * corr, o_run[r][3] * corr);
-            if (4 * lane < hd) {
-                for (int t = 0; t < nt; t++) {
-                    const float pt = ps[warp * 32 + t];
-                    const float4 vv = *(const float4 *)(vs + (t_lo + t) * ATT_MAX_HD + 4 * lane);
-                    acc.x = fmaf(pt, vv.x, acc.x);
-                    acc.y = fmaf(pt, vv.y, acc.y);
-                    acc.z = fmaf(pt, vv.z, acc.z);
-                    acc.w = fmaf(pt, vv.w, acc.w);
+            for (int r = 0; r < 2; r++) {
+                if (r >= n_rounds) break;
+                const int g = (warp % Gw) + r * AS_WARPS;
+                if (g >= G) break;
+                // one key position per lane
+                const float4 *qv = (const float4 *)(qs + g * ATT_MAX_HD);
+                const float4 *kv = (const float4 *)(ks + (t_lo + lane) * AS_KS_STRIDE);
+                float c0a = 0.f, c1a = 0.f, c2a = 0.f, c3a = 0.f;
+                for (int i = 0; i < hd4; i++) {
+                    const float4 qq = qv[i], kk = kv[i];
+                    c0a = fmaf(qq.x, kk.x, c0a);
+                    c1a = fmaf(qq.y, kk.y, c1a);
+                    c2a = fmaf(qq.z, kk.z, c2a);
+                    c3a = fmaf(qq.w, kk.w, c3a);
                 }
+                float sc = (c0a + c1a) + (c2a + c3a);
+                sc = lane < nt ? sc * a.scale : -INFINITY;
+                float mx = sc;
+#pragma unroll
+                for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+                const float m_new = fmaxf(m_run[r], mx);
+                const float p = lane < nt ? __expf(sc - m_new) : 0.f;
+                float sum = p;
+#pragma unroll
+                for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o2);
+                const float corr = __expf(m_run[r] - m_new);
+                m_run[r] = m_new;
+                l_run[r] = l_run[r] * corr + sum;
+                __syncwarp();
+                ps[warp * 32 + lane] = p;
+                __syncwarp();
+                // lane owns output dimensions 4*lane .. 4*lane+3 (head_dim <= 128)
+                float4 acc = make_float4(o_run[r][0] * corr, o_run[r][1] * corr, o_run[r][2] * corr, o_run[r][3] * corr);
+                if (4 * lane < hd) {
+                    for (int t = 0; t < nt; t++) {
+                        const float pt = ps[warp * 32 + t];
+                        const float4 vv = *(const float4 *)(vs + (t_lo + t) * ATT_MAX_HD + 4 * lane);
+                        acc.x = fmaf(pt, vv.x, acc.x);
+                        acc.y = fmaf(pt, vv.y, acc.y);
+                        acc.z = fmaf(pt, vv.z, acc.z);
+                        acc.w = fmaf(pt, vv.w, acc.w);
+                    }
+                }
+                o_run[r][0] = acc.x; o_run[r][1] = acc.y; o_run[r][2] = acc.z; o_run[r][3] = acc.w;
             }
-            o_run[r][0] = acc.x; o_run[r][1] = acc.y; o_run[r][2] = acc.z; o_run[r][3] = acc.w;
         }
     }
 
-    // ---- this CTA's partial per head: combine the warps that shared a head ----
+    // ---- this CTA's partial per head: the warps that shared a head leave theirs in shared memory ----
     __syncthreads();
     if (warp_active) {
 #pragma unroll
@@ -225,53 +260,64 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * hd; idx += AS_THREADS) {
-        const int g = idx / hd, d = idx - g * hd;
-        const int r = g / AS_WARPS, w0 = g % AS_WARPS;     // G <= 8: r = 0, w0 = g
-        float m = -1e30f;
-        for (int s = 0; s < wph; s++) m = fmaxf(m, wres[((w0 + s * Gw) * 2 + r) * RS]);
-        float l = 0.f, o = 0.f;
-        for (int s = 0; s < wph; s++) {
-            const float *w = wres + ((w0 + s * Gw) * 2 + r) * RS;
-            const float f = __expf(w[0] - m);
-            l = fmaf(w[1], f, l);
-            o = fmaf(w[2 + d], f, o);
-        }
-        res[g * RS + 2 + d] = o;
-        if (d == 0) { res[g * RS] = m; res[g * RS + 1] = l; }
-    }
 
-    // ---- merge across the cluster through distributed shared memory ----
-    cluster.sync();
-    const int S = (G * hd) / CL;          // outputs this CTA finishes: a multiple of 32 (host-checked)
+    // ---- 4. push the partials to the CTAs that finish them: destination d gets, in its recv[rank], this CTA's
+    //         (max, sum) of every head followed by its part of d's S outputs ----
+    cluster_wait();   // (arrived at the top) every CTA of the cluster has started
+    for (int idx = threadIdx.x; idx < G * hd + 2 * G * CL; idx += AS_THREADS) {
+        int dst, off;
+        float val;
+        if (idx < G * hd) {
+            const int g = idx / hd, d = idx - g * hd;
+            const int r = g / AS_WARPS, w0 = g % AS_WARPS;     // G <= 8: r = 0, w0 = g
+            float m = -1e30f;
+            for (int s = 0; s < wph; s++) m = fmaxf(m, wres[((w0 + s * Gw) * 2 + r) * RS]);
+            float o = 0.f;
+            for (int s = 0; s < wph; s++) {
+                const float *w = wres + ((w0 + s * Gw) * 2 + r) * RS;
+                o = fmaf(w[2 + d], __expf(w[0] - m), o);
+            }
+            dst = idx / S;
+            off = 2 * G + (idx - dst * S);
+            val = o;
+        } else {
+            const int j = idx - G * hd;
+            dst = j / (2 * G);
+            const int which = j - dst * (2 * G), g = which >> 1;
+            const int r = g / AS_WARPS, w0 = g % AS_WARPS;
+            float m = -1e30f;
+            for (int s = 0; s < wph; s++) m = fmaxf(m, wres[((w0 + s * Gw) * 2 + r) * RS]);
+            float l = 0.f;
+            for (int s = 0; s < wph; s++) {
+                const float *w = wres + ((w0 + s * Gw) * 2 + r) * RS;
+                l = fmaf(w[1], __expf(w[0] - m), l);
+            }
+            off = which;
+            val = (which & 1) ? l : m;
+        }
+        float *remote = cluster.map_shared_rank(recv, dst);
+        remote[rank * RW + off] = val;
+    }
+    cluster_arrive();
+    cluster_wait();   // every push has landed; nobody touches another CTA's shared memory afterwards
+
+    // ---- merge: this CTA's S outputs from the CL partials it received ----
     for (int j = threadIdx.x; j < S; j += AS_THREADS) {
         const int idx = rank * S + j;
         const int g = idx / hd, d = idx - g * hd;
         const int head = h_lo + g;
         const float sink = a.sinks ? a.sinks[head] : -INFINITY;
         const bool has_sink = sink > -1e29f;
-        float mc[16], lc[16], oc[16];
         float M = has_sink ? sink : -1e30f;
-#pragma unroll
-        for (int c = 0; c < 16; c++) {
-            mc[c] = -1e30f; lc[c] = 0.f; oc[c] = 0.f;
-            if (c < CL) {
-                const float *rr = cluster.map_shared_rank(res, c) + g * RS;
-                mc[c] = rr[0];
-                lc[c] = rr[1];
-                oc[c] = rr[2 + d];
-            }
-            M = fmaxf(M, mc[c]);
-        }
+        for (int c = 0; c < CL; c++) M = fmaxf(M, recv[c * RW + 2 * g]);
         float tot = has_sink ? __expf(sink - M) : 0.f, acc = 0.f;
-#pragma unroll
-        for (int c = 0; c < 16; c++) {
-            const float f = __expf(mc[c] - M);
-            tot = fmaf(lc[c], f, tot);
-            acc = fmaf(oc[c], f, acc);
+        for (int c = 0; c < CL; c++) {
+            const float f = __expf(recv[c * RW + 2 * g] - M);
+            tot = fmaf(recv[c * RW + 2 * g + 1], f, tot);
+            acc = fmaf(recv[c * RW + 2 * G + j], f, acc);
         }
         const float r = acc / tot;
-        a.out[(size_t)head * hd + d] = r;
+        a.out[tok_off + (size_t)head * hd + d] = r;
         if (a.emit_q) {
             // lanes 0..7 of each warp own the warp's 32 outputs as 8 groups of 4
             float v[4];
@@ -281,7 +327,6 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
             quantize4_store(v, (first >> 2) + (lane & 7), lane < 8, a.o);
         }
     }
-    cluster.sync();   // peers may still be reading this CTA's partials
 }
 
 }  // namespace qz

@@ -58,6 +58,26 @@ __global__ void swiglu_q_kernel(const float *__restrict__ gate, const float *__r
     quantize4_store(v, t, valid, o);
 }
 
+// rotation (cos, sin) of pair i at one position, exactly as rope_kv_kernel / src/cuda_kernels.cu:588-620 compute it
+struct RopeArgsLite {
+    int pos;
+    float theta, yarn_scale;
+    int yarn_orig_ctx;
+};
+__device__ __forceinline__ void rope_cs_lite(const RopeArgsLite &r, int i, int head_dim, float &c, float &s)
+{
+    const float PI = 3.14159265358979f;
+    float inv = 1.f / powf(r.theta, 2.f * (float)i / (float)head_dim);
+    float eff = inv;
+    if (r.yarn_scale > 1.f && r.yarn_orig_ctx > 0) {
+        float hi_w = (float)r.yarn_orig_ctx / 32.f, lo_w = (float)r.yarn_orig_ctx / 1.f;
+        float wavelen = 2.f * PI / inv;
+        float ramp = fmaxf(0.f, fminf(1.f, (lo_w - wavelen) / (lo_w - hi_w)));
+        eff = ramp * inv + (1.f - ramp) * (inv / r.yarn_scale);
+    }
+    sincosf((float)r.pos * eff, &s, &c);
+}
+
 // RoPE on q (n_heads) and k (n_kv_heads) in place, then append k, v to the caches at `pos`:
 // cuda_rope_yarn x2 + cuda_kv_append (src/cuda.rs:601-613) as one launch.  grid = n_heads +
 // n_kv_heads, block = head_dim/2 rounded up to a warp.
@@ -96,6 +116,57 @@ __global__ void rope_kv_kernel(float *q, float *k, const float *__restrict__ v, 
     }
     if (is_k) {
         const float *vh = v + (size_t)head * head_dim;
+        float *vc = v_cache + (size_t)pos * kv_dim + (size_t)head * head_dim;
+        for (int j = i; j < head_dim; j += blockDim.x) vc[j] = vh[j];
+    }
+}
+
+// ---- batched (prompt) forms: the same ops for n_tok tokens at consecutive positions ----
+// RMSNorm of every row of x [n_rows, n] (src/cuda_kernels.cu:563-575 per row); one CTA per row.  out may alias x.
+__global__ void rms_norm_rows_kernel(float *out, const float *x, const float *__restrict__ w, int n)
+{
+    __shared__ float sm[32];
+    pdl_wait();
+    pdl_trigger();
+    const float *xr = x + (size_t)blockIdx.x * n;
+    float *orow = out + (size_t)blockIdx.x * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    ss = block_reduce<false>(ss, sm);
+    const float r = rsqrtf(ss / (float)n + 1e-5f);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) orow[i] = xr[i] * r * w[i];
+}
+
+// rope_kv_kernel for token t = blockIdx.y at position pos0 + t: q [n_tok, n_heads*head_dim] and
+// k [n_tok, kv_dim] rotated in place, k and v [n_tok, kv_dim] appended to the caches.
+__global__ void rope_kv_rows_kernel(float *q, float *k, const float *__restrict__ v, float *__restrict__ k_cache,
+                                    float *__restrict__ v_cache, int n_heads, int head_dim, int pos0, float theta,
+                                    float yarn_scale, int yarn_orig_ctx, int neox, int kv_dim)
+{
+    pdl_wait();
+    pdl_trigger();
+    const int i = threadIdx.x, half = head_dim >> 1, t = blockIdx.y, pos = pos0 + t;
+    const bool is_k = (int)blockIdx.x >= n_heads;
+    const int head = is_k ? blockIdx.x - n_heads : blockIdx.x;
+    float *xh = is_k ? k + (size_t)t * kv_dim + (size_t)head * head_dim
+                     : q + (size_t)t * n_heads * head_dim + (size_t)head * head_dim;
+    if (i < half) {
+        const RopeArgsLite r{pos, theta, yarn_scale, yarn_orig_ctx};
+        float s, c;
+        rope_cs_lite(r, i, head_dim, c, s);
+        const int i0 = neox ? i : 2 * i, i1 = neox ? i + half : 2 * i + 1;
+        const float a = xh[i0], b = xh[i1];
+        const float r0 = a * c - b * s, r1 = a * s + b * c;
+        xh[i0] = r0;
+        xh[i1] = r1;
+        if (is_k) {
+            float *kc = k_cache + (size_t)pos * kv_dim + (size_t)head * head_dim;
+            kc[i0] = r0;
+            kc[i1] = r1;
+        }
+    }
+    if (is_k) {
+        const float *vh = v + (size_t)t * kv_dim + (size_t)head * head_dim;
         float *vc = v_cache + (size_t)pos * kv_dim + (size_t)head * head_dim;
         for (int j = i; j < head_dim; j += blockDim.x) vc[j] = vh[j];
     }

@@ -41,6 +41,26 @@ struct XQ {
 };
 
 constexpr float XQ_RANGE = 32512.0f;   // 127 * 256: h, l both fit int8
+// Runs whose largest magnitude is below this (2^-110) are taken as zero: XQ_RANGE / amax would overflow and the
+// scale amax / XQ_RANGE would be subnormal; products of such activations underflow in f32 anyway.
+constexpr float XQ_TINY = 7.703719777548943e-34f;
+
+// Scale handling shared by every conversion site.  amax: largest magnitude of the 32-run; sum32: the run's f32
+// sum, used only to notice a NaN or an infinity anywhere in the run (fmaxf drops NaNs): such a run gets a NaN
+// scale, so every output that touches it becomes NaN, as it would in f32 arithmetic.
+__device__ __forceinline__ void xq_run_scale(float amax, float sum32, float &inv, float &scale)
+{
+    if (!(fabsf(sum32) <= 3.0e38f) || !(amax <= 3.0e38f)) {   // NaN or infinite
+        inv = 0.f;
+        scale = __int_as_float(0x7FC00000);
+    } else if (amax > XQ_TINY) {
+        inv = XQ_RANGE / amax;
+        scale = amax / XQ_RANGE;
+    } else {
+        inv = 0.f;
+        scale = 0.f;
+    }
+}
 
 // one thread per 4 values; 8 threads share a 32-run
 // With `ctrl` set, x is (part of) a row-sharded vector whose slices other ranks push into this
@@ -72,8 +92,10 @@ __global__ void quantize_x_kernel(const float *x, int8_t *__restrict__ xl, int8_
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    const float sum32 = sum + __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
     if (k >= K) return;
-    float inv = amax > 0.f ? XQ_RANGE / amax : 0.f;
+    float inv, scale;
+    xq_run_scale(amax, sum32, inv, scale);
     uint32_t wl = 0, wh = 0;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -85,7 +107,7 @@ __global__ void quantize_x_kernel(const float *x, int8_t *__restrict__ xl, int8_
     }
     ((uint32_t *)xl)[t] = wl;
     ((uint32_t *)xh)[t] = wh;
-    if ((t & 7) == 0) xs[t >> 3] = amax / XQ_RANGE;
+    if ((t & 7) == 0) xs[t >> 3] = scale;
     if ((t & 3) == 0) xsum[t >> 2] = sum;
 }
 
@@ -106,8 +128,10 @@ __device__ __forceinline__ void quantize4_store(const float v[4], int t, bool va
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    const float sum32 = sum + __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
     if (!valid) return;
-    const float inv = amax > 0.f ? XQ_RANGE / amax : 0.f;
+    float inv, scale;
+    xq_run_scale(amax, sum32, inv, scale);
     uint32_t wl = 0, wh = 0;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -119,7 +143,7 @@ __device__ __forceinline__ void quantize4_store(const float v[4], int t, bool va
     }
     ((uint32_t *)o.xl)[t] = wl;
     ((uint32_t *)o.xh)[t] = wh;
-    if ((t & 7) == 0) o.xs[t >> 3] = amax / XQ_RANGE;
+    if ((t & 7) == 0) o.xs[t >> 3] = scale;
     if ((t & 3) == 0) o.xsum[t >> 2] = sum;
 }
 

@@ -42,6 +42,31 @@ struct XSrc {
     int oai;
 };
 
+// Byte ranges (the weights of the operations that FOLLOW this GEMV) that the producer lanes pull into L2 once
+// their own weight stream has been issued: while this kernel drains its ring, reduces, exits and its successor
+// starts up, HBM keeps working for the successor, whose first tiles then come from L2.
+constexpr int QZ_MAX_PREFETCH = 4;
+struct PrefetchHint {
+    const uint8_t *ptr[QZ_MAX_PREFETCH];
+    unsigned bytes[QZ_MAX_PREFETCH];   // per range, a multiple of 16
+    int n;
+};
+
+__device__ __forceinline__ void l2_prefetch_bulk(const void *gmem, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
+}
+
+// 16 KB pieces of every hinted range, piece j issued by CTA j % n_cta: the front of a range (what the successor
+// reads first) is requested first by everybody
+__device__ __forceinline__ void issue_prefetch(const PrefetchHint &h, int cta, int n_cta)
+{
+    for (int i = 0; i < h.n; i++) {
+        for (unsigned o = (unsigned)cta * 16384u; o < h.bytes[i]; o += (unsigned)n_cta * 16384u)
+            l2_prefetch_bulk(h.ptr[i] + o, min(16384u, h.bytes[i] - o));
+    }
+}
+
 struct TmaArgs {
     const uint8_t *W[QZ_MAX_MATS];
     XQ xq[QZ_MAX_MATS];
@@ -55,6 +80,9 @@ struct TmaArgs {
     int *status;             // device status word (0 = ok)
     PushArgs push;           // push.n > 0: rows go to every rank's window instead of y (single matrix)
     XSrc xsrc;
+    PrefetchHint pf;         // weights of the following operations, to be pulled into L2
+    const int *sel;          // not NULL: matrix m really starts at W[m] + sel[m] * sel_stride (expert ids chosen on the device)
+    size_t sel_stride;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -213,12 +241,17 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
     __syncthreads();
     pdl_trigger();
 
-    if (threadIdx.x >= TMA_CONSUMERS) {
+    const int first_producer = (int)blockDim.x - 32;   // the last warp is the producer warp
+    if ((int)threadIdx.x >= first_producer) {
         // ---------------- producer ----------------
         // Weights are written by no kernel, so streaming starts at once, even while the kernel
         // that produces this GEMV's activations is still running.
-        if (threadIdx.x != TMA_CONSUMERS) return;
+        if ((int)threadIdx.x != first_producer) return;
         const uint8_t *W = a.W[m];
+        if (a.sel) {
+            pdl_wait();   // the ids are written by the kernel before this one
+            W += (size_t)a.sel[m] * a.sel_stride;
+        }
         int it = 0, s = 0;
         uint32_t round = 0;
         bool ok = true;
@@ -232,6 +265,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_tma_kernel(const T
             tma_load_1d(ring + (size_t)s * a.stage_bytes, W + (size_t)row0 * row_bytes, bytes, &full_bar[s]);
             if (++s == a.n_stages) { s = 0; round++; }
         }
+        if (ok && a.pf.n > 0) issue_prefetch(a.pf, blockIdx.x, gridDim.x);
         if (!ok) {
             atomicExch(a.status, QZ_ERR_TIMEOUT);
             // drain: copies already issued must land before this CTA's shared memory goes away

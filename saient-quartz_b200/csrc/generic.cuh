@@ -19,8 +19,6 @@ __global__ void dequant_kernel(const uint8_t *__restrict__ data, float *__restri
     const FormatInfo fi = format_info(T);
     pdl_wait();
     pdl_trigger();
-    // row_sel: the first row to decode is read from device memory (the token id of a recorded decode step)
-    if (row_sel) data += (size_t)row_sel[0] * (size_t)(K / fi.block_elems) * fi.block_bytes;
     long long gs = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gs >= n_sub) return;
     const int subs_per_row = K / 32;
@@ -28,7 +26,10 @@ __global__ void dequant_kernel(const uint8_t *__restrict__ data, float *__restri
     long long row = gs / subs_per_row;
     int s = (int)(gs % subs_per_row);
     int nb = K / fi.block_elems;
-    const uint8_t *rowp = data + (size_t)row * nb * fi.block_bytes;
+    // row_sel: output row r decodes source row row_sel[r], read from device memory (token ids of a recorded
+    // decode step or of a prompt)
+    const long long src_row = row_sel ? (long long)row_sel[row] : row;
+    const uint8_t *rowp = data + (size_t)src_row * nb * fi.block_bytes;
     Fields F = block_fields<PLANES>(fi, rowp, nb, s / subs_per_blk);
     float w[32];
     decode32<T>(F, s % subs_per_blk, w);
@@ -45,13 +46,14 @@ __global__ void dequant_plain_kernel(const uint8_t *__restrict__ data, float *__
     pdl_trigger();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    if (row_sel) data += (size_t)row_sel[0] * (size_t)K * (type == T_F32 ? 4 : 2);
+    long long j = i;   // source element
+    if (row_sel) j = (long long)row_sel[i / K] * K + i % K;
     if (type == T_F32) {
-        out[i] = __uint_as_float(ld_u32_bytes(data + 4 * i));
+        out[i] = __uint_as_float(ld_u32_bytes(data + 4 * j));
     } else if (type == T_F16) {
-        out[i] = h2f(ld_u16(data + 2 * i));
+        out[i] = h2f(ld_u16(data + 2 * j));
     } else {
-        out[i] = __uint_as_float((uint32_t)ld_u16(data + 2 * i) << 16);
+        out[i] = __uint_as_float((uint32_t)ld_u16(data + 2 * j) << 16);
     }
 }
 

@@ -244,6 +244,49 @@ __global__ void moe_tiles_kernel(const float *__restrict__ x, const float *__res
     }
 }
 
+// ---- batch-1 (decode) MoE with the experts chosen on the device ----
+// h[k] = swiglu(gate[k] + gate_bias[ids[k]], up[k] + up_bias[ids[k]]) for the n_act active experts
+// (cuda_vec_add x2 + cuda_swiglu / cuda_swiglu_oai per expert, src/cuda.rs:730-745, 765-777); biases may be NULL.
+__global__ void moe_decode_act_kernel(float *__restrict__ out, const float *__restrict__ gate, const float *__restrict__ up,
+                                      const float *__restrict__ gate_bias, const float *__restrict__ up_bias,
+                                      const int *__restrict__ ids, int n_act, int F, int oai)
+{
+    pdl_wait();
+    pdl_trigger();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_act * F) return;
+    const int k = (int)(i / F), j = (int)(i - (long long)k * F);
+    const int e = ids[k];
+    float g = gate[i], u = up[i];
+    if (gate_bias) g += gate_bias[(size_t)e * F + j];
+    if (up_bias) u += up_bias[(size_t)e * F + j];
+    if (oai) {
+        const float x = fminf(g, 7.f), y = fmaxf(-7.f, fminf(7.f, u));
+        out[i] = (x / (1.f + expf(-1.702f * x))) * (y + 1.f);
+    } else {
+        out[i] = (g / (1.f + expf(-g))) * u;
+    }
+}
+
+// acc[j] (+)= sum_k w[k] * (down[k][j] + down_bias[ids[k]][j]), in the order of k (cuda_vec_add +
+// cuda_vec_scale_add per expert, src/cuda.rs:750-760, 788-794)
+__global__ void moe_decode_combine_kernel(float *__restrict__ acc, const float *__restrict__ down,
+                                          const float *__restrict__ down_bias, const int *__restrict__ ids,
+                                          const float *__restrict__ w, int n_act, int D, int accumulate)
+{
+    pdl_wait();
+    pdl_trigger();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= D) return;
+    float s = accumulate ? acc[j] : 0.f;
+    for (int k = 0; k < n_act; k++) {
+        float v = down[(size_t)k * D + j];
+        if (down_bias) v += down_bias[(size_t)ids[k] * D + j];
+        s += w[k] * v;
+    }
+    acc[j] = s;
+}
+
 // out[t, :] = sum_k w[t, k] * y[slot_of[t * top_k + k], :], summed in the order of k (the order in which the
 // reference's per-token loop adds its experts, src/main.rs:979-990).  One thread per float4.
 __global__ void moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const int *__restrict__ slot_of,

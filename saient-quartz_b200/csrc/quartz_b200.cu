@@ -263,6 +263,11 @@ static bool g_push_pending = false;
 // set by cuda_gemv_rmsnorm / cuda_gemv_swiglu around their GEMV: the TMA kernel converts the activations itself
 static XSrc g_xsrc = {0, nullptr, nullptr, 0};
 static bool g_xsrc_pending = false;
+// set by quartz_prefetch_next: ranges the next streaming GEMV pulls into L2 behind its own weight stream
+static PrefetchHint g_pf = {{nullptr, nullptr, nullptr, nullptr}, {0, 0, 0, 0}, 0};
+// set by cuda_gemv_experts around its GEMV: the matrices are expert slices picked by device-side ids
+static const int *g_sel = nullptr;
+static size_t g_sel_stride = 0;
 // longest activation vector the streaming GEMV converts in its own prologue (every CTA converts the whole
 // vector while its weight ring fills); longer vectors are converted once, by a kernel of their own.
 // QUARTZ_XSRC_MAX_K overrides the default.
@@ -294,11 +299,21 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
     for (int i = 0; i < QZ_MAX_MATS; i++) { a.W[i] = g.W[i]; a.xq[i] = g.xq[i]; a.y[i] = g.y[i]; }
     a.accumulate = g.accumulate;
     a.K = g.K; a.N = g.N; a.U = g.U; a.Upad = g.Upad; a.n_mats = n_mats;
-    a.RP = g.Upad >= TMA_CONSUMERS ? 1 : TMA_CONSUMERS / g.Upad;
-    const int sms = sm_count();
+    // consumer threads per CTA: 512 (one CTA per SM), or 256 with two CTAs per SM when the row fits
+    // (QUARTZ_GEMV_CONSUMERS=256): the CTAs of the next kernel of a chain then become resident, and start
+    // streaming, while this kernel's CTAs are still draining
+    static int cons_pref = -1;
+    if (cons_pref < 0) {
+        const char *e = getenv("QUARTZ_GEMV_CONSUMERS");
+        cons_pref = (e && atoi(e) == 256) ? 256 : TMA_CONSUMERS;
+    }
+    const int cons = (cons_pref == 256 && g.Upad <= 256) ? 256 : TMA_CONSUMERS;
+    const int per_sm = cons == 256 ? 2 : 1;
+    a.RP = g.Upad >= cons ? 1 : cons / g.Upad;
+    const int sms = sm_count() * per_sm;
     const int ctas_per_mat = sms / n_mats > 0 ? sms / n_mats : 1;
     a.stage_bytes = (int)((size_t)a.RP * row_bytes);
-    const int smem_budget = 200 * 1024;   // + up to 8 KB of codebook behind it
+    const int smem_budget = (per_sm == 2 ? 100 : 200) * 1024;   // + up to 8 KB of codebook behind it
     // a fused activation source keeps the converted vector (2 K + 3 K / 8 bytes) behind the codebook
     const int x_bytes = g_xsrc_pending ? (int)((2 * (size_t)g.K + g.K / 8 + g.K / 4 + 31) & ~(size_t)15) : 0;
     const int ring_budget = smem_budget - x_bytes;
@@ -324,14 +339,18 @@ static bool launch_tma(const GemvArgs &g, int n_mats)
         a.xsrc = g_xsrc;
         g_xsrc_pending = false;
     }
+    a.pf = g_pf;
+    g_pf.n = 0;
+    a.sel = g_sel;
+    a.sel_stride = g_sel_stride;
     static bool attr_set = false;
     if (!attr_set) {
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_budget + 16 + F::TABLE_BYTES));
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_budget + 16 + F::TABLE_BYTES));
-        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_budget + 16 + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024 + 16 + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024 + 16 + F::TABLE_BYTES));
+        QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_tma_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024 + 16 + F::TABLE_BYTES));
         attr_set = true;
     }
-    const dim3 grid(n_cta * n_mats), block(TMA_CONSUMERS + 32);
+    const dim3 grid(n_cta * n_mats), block(cons + 32);
     const size_t smem = (size_t)stages * a.stage_bytes + ((F::TABLE_BYTES + 15) & ~15) + x_bytes;
     if (g.Upad < 32) launch(gemv_tma_kernel<F, 0>, grid, block, smem, a);
     else if (g.Upad == 32) launch(gemv_tma_kernel<F, 1>, grid, block, smem, a);
@@ -489,7 +508,11 @@ static void gemv_n(uint32_t t, int n, const uint8_t *const *W, const float *cons
             planes[i] = true;
         }
     }
-    if (!is_plain(t) && try_stream(t, n, W, x, y, K, N, planes)) return;
+    if (!is_plain(t) && try_stream(t, n, W, x, y, K, N, planes)) {
+        g_pf.n = 0;
+        return;
+    }
+    g_pf.n = 0;   // a prefetch hint applies to the streaming kernel only
     if (g_wait_ctrl) {   // a fused wait was asked for, but this path converts no activations: wait in a kernel of its own
         int *st = status_word();
         if (st) {
@@ -1109,6 +1132,20 @@ void quartz_set_stream(void *s) { g_stream = (cudaStream_t)s; }
 long long quartz_launch_count(void) { return g_launch_count; }
 void quartz_set_gemv_impl(int impl) { g_use_tma = impl == 1 ? 0 : 1; }
 
+void quartz_prefetch_next(const void *d_ptr, size_t bytes)
+{
+    static long long cap = -1;
+    if (cap < 0) {
+        const char *e = getenv("QUARTZ_PREFETCH_MB");   // per hinted range; 0 switches the hints off
+        cap = (e ? atoll(e) : 24) << 20;
+    }
+    if (!d_ptr || bytes < 16 || cap == 0 || ((uintptr_t)d_ptr & 15) || g_pf.n >= QZ_MAX_PREFETCH) return;
+    if ((long long)bytes > cap) bytes = (size_t)cap;
+    g_pf.ptr[g_pf.n] = (const uint8_t *)d_ptr;
+    g_pf.bytes[g_pf.n] = (unsigned)(bytes & ~(size_t)15);
+    g_pf.n++;
+}
+
 int cuda_repack_weights(uint32_t ggml_type, void *d_data, int in_dim, int out_dim, int n_mats)
 {
     const FormatInfo fi = format_info(ggml_type);
@@ -1231,6 +1268,7 @@ void cuda_gemv_q(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, cons
     }
     if (!ensure_xq(in_dim)) return;
     stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
+    g_pf.n = 0;
 }
 
 // The GEMVs whose activation vector is the RMSNorm of x / the SwiGLU of (gate, up): the streaming kernel
@@ -1260,11 +1298,15 @@ static void gemv_xsrc(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w,
         const bool ok = stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
         const bool consumed = !g_xsrc_pending;
         g_xsrc_pending = false;
-        if (ok && consumed) return;
+        if (ok && consumed) {
+            g_pf.n = 0;
+            return;
+        }
     }
     if (src.mode == 1) cuda_rms_norm_q(src.a, src.b, in_dim, 3, nullptr);
     else cuda_swiglu_q(src.a, src.b, in_dim, 3, src.oai);
     stream_core(ggml_type, n_mats, d_w, slot_of, d_y, in_dim, out_dim, accumulate ? 1 : 0);
+    g_pf.n = 0;
 }
 
 void cuda_gemv_rmsnorm(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w, float *const *d_y, const float *d_x,
@@ -1522,11 +1564,21 @@ void cuda_embed_lookup_dev(float *out, const uint8_t *data, uint32_t ggml_type, 
 // cluster width of the attention kernel for a head group of G heads: the widest power of two (<= 16, or the
 // value of QUARTZ_ATTN_CLUSTER) that leaves every CTA a whole number of 32-output runs and that the device
 // can schedule; 0 = this head geometry is not served
+static int attn_step_rows()
+{
+    static int rows = -1;
+    if (rows < 0) {
+        const char *e = getenv("QUARTZ_ATTN_ROWS");   // 64: less shared memory per CTA (two staging rounds when a CTA owns three blocks)
+        rows = (e && atoi(e) == 64) ? 64 : AS_ROWS;
+    }
+    return rows;
+}
+
 static int attn_step_cluster(int G, int head_dim)
 {
     static int cached_G = -1, cached_hd = -1, cached_cl = 0;
     if (G == cached_G && head_dim == cached_hd) return cached_cl;
-    int want = 16;
+    int want = AS_MAX_CL;
     if (const char *e = getenv("QUARTZ_ATTN_CLUSTER")) {
         const int v = atoi(e);
         if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) want = v;
@@ -1534,7 +1586,7 @@ static int attn_step_cluster(int G, int head_dim)
     static bool attr_set = false;
     if (!attr_set) {
         QZ_CUDA_CHECK(cudaFuncSetAttribute(attn_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)attn_step_smem(AS_MAX_G)));
+                                           (int)attn_step_smem(AS_MAX_G, AS_MAX_CL, ATT_MAX_HD, AS_ROWS)));
         if (cudaFuncSetAttribute(attn_step_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
             cudaGetLastError();
         attr_set = true;
@@ -1545,7 +1597,7 @@ static int attn_step_cluster(int G, int head_dim)
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(c);
         cfg.blockDim = dim3(AS_THREADS);
-        cfg.dynamicSmemBytes = attn_step_smem(G);
+        cfg.dynamicSmemBytes = attn_step_smem(G, c, head_dim, attn_step_rows());
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = c;
@@ -1564,6 +1616,78 @@ static int attn_step_cluster(int G, int head_dim)
     cached_hd = head_dim;
     cached_cl = cl;
     return cl;
+}
+
+void cuda_embed_lookup_rows(float *out, const uint8_t *data, uint32_t ggml_type, const int *d_tokens, int n, int embed_dim)
+{
+    const FormatInfo fi = format_info(ggml_type);
+    if (fi.block_elems == 0 || embed_dim <= 0 || embed_dim % fi.block_elems || !d_tokens || n < 0) {
+        set_error(fi.block_elems ? QZ_ERR_BAD_SHAPE : QZ_ERR_UNSUPPORTED_TYPE, "cuda_embed_lookup_rows");
+        return;
+    }
+    if (n > 0) dequant_rows(ggml_type, data, out, embed_dim, n, d_tokens);
+}
+
+void cuda_rms_norm_rows(float *out, const float *x, const float *w, int n_rows, int n)
+{
+    if (n_rows <= 0 || n <= 0) return;
+    const int bs = n >= 4096 ? 1024 : (n >= 1024 ? 512 : (n >= 256 ? 128 : 32));
+    launch(rms_norm_rows_kernel, dim3((unsigned)n_rows), dim3(bs), 0, out, x, w, n);
+}
+
+void cuda_rope_kv_rows(float *q, float *k, const float *v, float *k_cache, float *v_cache, int n_tok, int n_heads,
+                       int n_kv_heads, int head_dim, int pos0, float theta, float yarn_scale, int yarn_orig_ctx, int neox)
+{
+    if (n_tok <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim < 2 || pos0 < 0) return;
+    const int bs = ((head_dim / 2) + 31) & ~31;
+    launch(rope_kv_rows_kernel, dim3(n_heads + n_kv_heads, n_tok), dim3(bs), 0, q, k, v, k_cache, v_cache, n_heads, head_dim, pos0,
+           theta, yarn_scale, yarn_orig_ctx, neox, n_kv_heads * head_dim);
+}
+
+static int attn_step_rows();
+static int attn_step_cluster(int G, int head_dim);
+
+void cuda_attn_prompt(float *out, const float *q, const float *k_cache, const float *v_cache, int n_tok, int n_heads,
+                      int n_kv_heads, int head_dim, int max_seq, int pos0, int window, float scale, const float *sinks)
+{
+    if (n_tok <= 0) return;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads / n_kv_heads > AS_MAX_G || head_dim > ATT_MAX_HD ||
+        head_dim % 32 != 0 || pos0 < 0 || pos0 + n_tok > max_seq || n_tok > 65535) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_attn_prompt: head_dim must be a multiple of 32 up to 128, at most 16 query heads per kv head, pos0 + n_tok <= max_seq, n_tok <= 65535");
+        return;
+    }
+    const int G = n_heads / n_kv_heads;
+    attn_step_cluster(G, head_dim);   // (sets the kernel's attributes)
+    AttnStepArgs a = {};
+    a.out = out; a.q = q; a.k_new = nullptr; a.v_new = nullptr;
+    a.k_cache = (float *)k_cache; a.v_cache = (float *)v_cache;
+    a.step = nullptr; a.pos_host = pos0;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.kv_dim = n_kv_heads * head_dim;
+    a.max_seq = max_seq; a.window = window; a.scale = scale; a.sinks = sinks;
+    a.theta = 1.f; a.yarn_scale = 1.f; a.yarn_orig_ctx = 0; a.neox = 0;
+    a.o = XQOut{nullptr, nullptr, nullptr, nullptr};
+    a.emit_q = 0;
+    a.rows_cap = attn_step_rows();
+    a.prompt = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)n_kv_heads, (unsigned)n_tok);   // one CTA per (kv head, token): clusters of one
+    cfg.blockDim = dim3(AS_THREADS);
+    cfg.dynamicSmemBytes = attn_step_smem(G, 1, head_dim, a.rows_cap);
+    cfg.stream = g_stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.numAttrs = 1;
+    if (g_pdl) {
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = at;
+    g_launch_count++;
+    QZ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, attn_step_kernel, a));
 }
 
 int cuda_attn_step_supported(int n_heads, int n_kv_heads, int head_dim)
@@ -1593,6 +1717,8 @@ void cuda_attn_step(float *out, const float *q, const float *k_new, const float 
     a.theta = theta; a.yarn_scale = yarn_scale; a.yarn_orig_ctx = yarn_orig_ctx; a.neox = neox;
     a.o = XQOut{nullptr, nullptr, nullptr, nullptr};
     a.emit_q = 0;
+    a.prompt = 0;
+    a.rows_cap = attn_step_rows();
     if (out_slot >= 0) {
         if (!user_slot(out_slot, n_heads * head_dim, &a.o)) return;
         a.emit_q = 1;
@@ -1600,7 +1726,7 @@ void cuda_attn_step(float *out, const float *q, const float *k_new, const float 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(n_kv_heads * cl));
     cfg.blockDim = dim3(AS_THREADS);
-    cfg.dynamicSmemBytes = attn_step_smem(G);
+    cfg.dynamicSmemBytes = attn_step_smem(G, cl, head_dim, a.rows_cap);
     cfg.stream = g_stream;
     cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
@@ -1936,6 +2062,66 @@ void cuda_moe_ffn(uint32_t type_gate_up, uint32_t type_down, const uint8_t *d_ga
         return;
     moe_ffn_per_expert(type_gate_up, type_down, d_gate, d_up, d_down, d_x, d_out, m, embed_dim, ffn_dim, n_experts, top_k,
                        h_expert_ids, h_expert_w, oai);
+}
+
+void cuda_gemv_experts(uint32_t ggml_type, const uint8_t *d_base, size_t expert_bytes, const int *d_ids, int n_act,
+                       const float *d_x, size_t x_stride, float *d_y, int in_dim, int out_dim)
+{
+    if (n_act <= 0 || out_dim <= 0) return;
+    if (n_act > 4 || !d_ids || !cuda_gemv_q_supported(ggml_type, d_base, in_dim) || (expert_bytes & 15) || !use_tma()) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_gemv_experts: at most 4 experts per call, of a type/shape/layout the streaming kernel takes (ask cuda_gemv_q_supported)");
+        return;
+    }
+    if (!tables_ready(ggml_type)) {
+        set_error(QZ_ERR_MISSING_TABLE, "IQ codebook not uploaded (cuda_set_*_grid)");
+        return;
+    }
+    if (!ensure_xq(in_dim)) return;
+    const uint8_t *W[4];
+    float *Y[4];
+    int slot_of[4];
+    for (int i = 0; i < n_act; i++) {
+        W[i] = d_base;
+        Y[i] = d_y + (size_t)i * out_dim;
+        slot_of[i] = x_stride ? i : 0;
+    }
+    g_sel = d_ids;
+    g_sel_stride = expert_bytes;
+    bool done = false;
+    if (!x_stride && in_dim <= xsrc_max_k() && !((uintptr_t)d_x & 15)) {
+        // one activation vector for all experts: converted in the GEMV's own prologue
+        g_xsrc = XSrc{3, d_x, d_x, 0};
+        g_xsrc_pending = true;
+        const bool ok = stream_core(ggml_type, n_act, W, slot_of, Y, in_dim, out_dim, 0);
+        done = ok && !g_xsrc_pending;
+        g_xsrc_pending = false;
+    }
+    if (!done) {
+        const int n_x = x_stride ? n_act : 1;
+        for (int i = 0; i < n_x; i++)
+            launch_quantize(d_x + (size_t)i * x_stride, xq_slot(g_xq.base, g_xq.slot_bytes, i, g_xq.cap_k), in_dim);
+        if (!stream_core(ggml_type, n_act, W, slot_of, Y, in_dim, out_dim, 0))
+            set_error(QZ_ERR_BAD_SHAPE, "cuda_gemv_experts: the streaming kernel did not take this shape");
+    }
+    g_sel = nullptr;
+    g_pf.n = 0;
+}
+
+void cuda_moe_decode_act(float *d_out, const float *d_gate, const float *d_up, const float *d_gate_bias,
+                         const float *d_up_bias, const int *d_ids, int n_act, int ffn_dim, int oai)
+{
+    if (n_act <= 0 || ffn_dim <= 0) return;
+    const long long n = (long long)n_act * ffn_dim;
+    launch(moe_decode_act_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, d_out, d_gate, d_up, d_gate_bias, d_up_bias,
+           d_ids, n_act, ffn_dim, oai);
+}
+
+void cuda_moe_decode_combine(float *d_acc, const float *d_down, const float *d_down_bias, const int *d_ids, const float *d_w,
+                             int n_act, int embed_dim, int accumulate)
+{
+    if (n_act <= 0 || embed_dim <= 0) return;
+    launch(moe_decode_combine_kernel, dim3((unsigned)((embed_dim + 255) / 256)), dim3(256), 0, d_acc, d_down, d_down_bias, d_ids,
+           d_w, n_act, embed_dim, accumulate);
 }
 
 void cuda_router_topk(const float *d_logits, const float *d_bias, int m, int n_experts, int top_k, int renorm, int *d_ids,

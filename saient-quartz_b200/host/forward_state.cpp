@@ -3,6 +3,7 @@
 
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -89,7 +90,7 @@ struct Layer {
     size_t q_norm_len = 0, k_norm_len = 0;
     GpuBuf q_bias, k_bias, v_bias, o_bias, sinks;
     bool has_qkv_bias = false;
-    GpuBuf moe_gate, moe_up, moe_down, router_w;
+    GpuBuf moe_gate, moe_up, moe_down, router_w, router_b_dev;
     std::vector<float> router_b;
     GpuBuf moe_gate_bias, moe_up_bias, moe_down_bias;
 };
@@ -107,6 +108,10 @@ struct qh_model {
     bool finalized = false;
     long long last_launches = 0;
     int n_recorded = 0;        // graph recordings made so far
+    // batched prefill scratch (grown on demand): token ids, hidden rows, normalised rows, q, k, v, attention out, gate, up
+    GpuBuf p_tok, p_x, p_xn, p_q, p_k, p_v, p_att, p_g, p_u, p_ids, p_w;
+    int p_cap = 0;
+    GpuBuf d_moe_ids, d_moe_w; // experts of the current token and their weights, chosen on the device
     GpuBuf d_step;             // two device words {token, pos}: what the recorded step reads instead of arguments
     void *graphs[3] = {nullptr, nullptr, nullptr};   // one recorded step per sequence kind (1 fused, 2 chained)
     int q_d() const { return c.n_heads * c.head_dim; }
@@ -168,7 +173,7 @@ int qh_set_tensor(qh_model *m, int role, int layer, uint32_t t, const void *host
         case QH_ROUTER_W: dst = &l.router_w; break;
         case QH_ROUTER_B:
             l.router_b.assign((const float *)host, (const float *)host + bytes / 4);
-            return 0;
+            return l.router_b_dev.upload(host, bytes) ? 0 : -5;   // the device-side router adds it on the device
         case QH_MOE_GATE_BIAS: dst = &l.moe_gate_bias; break;
         case QH_MOE_UP_BIAS: dst = &l.moe_up_bias; break;
         case QH_MOE_DOWN_BIAS: dst = &l.moe_down_bias; break;
@@ -191,13 +196,15 @@ int qh_finalize(qh_model *m)
     const qh_config &c = m->c;
     const int d = c.embed_dim, q_d = m->q_d(), kv_d = m->kv_d(), fd = c.ffn_dim, nh = c.n_heads;
     const size_t mseq = c.max_seq;
+    const size_t n_slots = (size_t)std::max(4, std::min(c.n_experts_used, 8));   // expert outputs kept side by side
     bool ok = m->d_hidden.alloc_f32(d) && m->d_norm_out.alloc_f32(d) && m->d_q.alloc_f32(q_d) &&
               m->d_k.alloc_f32(kv_d) && m->d_v.alloc_f32(kv_d) && m->d_attn_out.alloc_f32(q_d) &&
               m->d_scores.alloc_f32(nh * mseq) && m->d_gate.alloc_f32(fd) && m->d_up.alloc_f32(fd) &&
-              m->d_expert_out.alloc_f32(fd) && m->d_expert_acc.alloc_f32(d) && m->d_gate_all.alloc_f32(4 * (size_t)fd) &&
-              m->d_up_all.alloc_f32(4 * (size_t)fd) && m->d_expert_out_all.alloc_f32(4 * (size_t)fd) &&
-              m->d_down_all.alloc_f32(4 * (size_t)d) && m->d_router_logits.alloc_f32(std::max(c.n_experts, 1)) &&
-              m->d_logits.alloc_f32(c.vocab_size) && m->d_step.alloc_f32(4);
+              m->d_expert_out.alloc_f32(fd) && m->d_expert_acc.alloc_f32(d) && m->d_gate_all.alloc_f32(n_slots * (size_t)fd) &&
+              m->d_up_all.alloc_f32(n_slots * (size_t)fd) && m->d_expert_out_all.alloc_f32(n_slots * (size_t)fd) &&
+              m->d_down_all.alloc_f32(n_slots * (size_t)d) && m->d_router_logits.alloc_f32(std::max(c.n_experts, 1)) &&
+              m->d_logits.alloc_f32(c.vocab_size) && m->d_step.alloc_f32(4) && m->d_moe_ids.alloc_f32(16) &&
+              m->d_moe_w.alloc_f32(16);
     if (!ok) return -2;
     m->kv_k.resize(c.n_layers);
     m->kv_v.resize(c.n_layers);
@@ -281,9 +288,63 @@ static void route(qh_model *m, int l, std::vector<std::pair<int, float>> &top, s
     for (size_t i = 0; i < top.size(); i++) rw[i] = e[i] / denom;
 }
 
+// Can the experts of this layer be chosen on the device?  Every expert tensor must be served by the streaming
+// GEMV (the kernel that takes device-side expert ids); QUARTZ_HOST_ROUTER=1 keeps the reference's host routing.
+static int g_forced_host_router = -1;
+static bool device_routing(qh_model *m, int l)
+{
+    if (g_forced_host_router < 0) {
+        const char *e = getenv("QUARTZ_HOST_ROUTER");
+        g_forced_host_router = (e && e[0] == '1') ? 1 : 0;
+    }
+    const int forced_host = g_forced_host_router;
+    const qh_config &c = m->c;
+    Layer &L = m->L[l];
+    return !forced_host && c.n_experts <= 256 && c.n_experts_used <= 8 &&
+           cuda_gemv_q_supported(L.moe_gate.ggml_type, L.moe_gate.u8(), c.embed_dim) &&
+           cuda_gemv_q_supported(L.moe_up.ggml_type, L.moe_up.u8(), c.embed_dim) &&
+           cuda_gemv_q_supported(L.moe_down.ggml_type, L.moe_down.u8(), c.ffn_dim);
+}
+
+// MoE FFN of one layer with router, top-k, expert selection and the weighted sum all on the device: the same
+// arithmetic as moe_ffn below without its device-to-host copy and synchronisation per layer
+// (src/cuda.rs:673-701 is what it replaces).
+static void moe_ffn_device(qh_model *m, int l)
+{
+    const qh_config &c = m->c;
+    Layer &L = m->L[l];
+    const int d = c.embed_dim, fd = c.ffn_dim, ne = c.n_experts, n_act = c.n_experts_used;
+    const uint32_t tg = L.moe_gate.ggml_type, tu = L.moe_up.ggml_type, td = L.moe_down.ggml_type;
+    const size_t sg = ggml_type_size(tg, (size_t)d * fd), su = ggml_type_size(tu, (size_t)d * fd),
+                 sd = ggml_type_size(td, (size_t)fd * d);
+    const float *xn = m->d_norm_out.f();
+    const int *ids = (const int *)m->d_moe_ids.ptr;
+    const float *w = m->d_moe_w.f();
+    cuda_gemv(0, L.router_w.u8(), xn, m->d_router_logits.f(), d, ne);
+    cuda_router_topk(m->d_router_logits.f(), L.router_b_dev.empty() ? nullptr : L.router_b_dev.f(), 1, ne, n_act, c.moe_renorm,
+                     (int *)m->d_moe_ids.ptr, m->d_moe_w.f());
+    float *go = m->d_gate_all.f(), *uo = m->d_up_all.f(), *eo = m->d_expert_out_all.f(), *doo = m->d_down_all.f();
+    for (int k0 = 0; k0 < n_act; k0 += 4) {
+        const int n = std::min(4, n_act - k0);
+        cuda_gemv_experts(tg, L.moe_gate.u8(), sg, ids + k0, n, xn, 0, go + (size_t)k0 * fd, d, fd);
+        cuda_gemv_experts(tu, L.moe_up.u8(), su, ids + k0, n, xn, 0, uo + (size_t)k0 * fd, d, fd);
+    }
+    cuda_moe_decode_act(eo, go, uo, L.moe_gate_bias.empty() ? nullptr : L.moe_gate_bias.f(),
+                        L.moe_up_bias.empty() ? nullptr : L.moe_up_bias.f(), ids, n_act, fd, c.clamped_swiglu);
+    for (int k0 = 0; k0 < n_act; k0 += 4) {
+        const int n = std::min(4, n_act - k0);
+        cuda_gemv_experts(td, L.moe_down.u8(), sd, ids + k0, n, eo + (size_t)k0 * fd, (size_t)fd, doo + (size_t)k0 * d, fd, d);
+    }
+    cuda_moe_decode_combine(m->d_expert_acc.f(), doo, L.moe_down_bias.empty() ? nullptr : L.moe_down_bias.f(), ids, w, n_act, d, 0);
+}
+
 // MoE FFN of one layer on d_norm_out -> d_expert_acc (src/cuda.rs:667-798)
 static void moe_ffn(qh_model *m, int l)
 {
+    if (device_routing(m, l)) {
+        moe_ffn_device(m, l);
+        return;
+    }
     const qh_config &c = m->c;
     Layer &L = m->L[l];
     const int d = c.embed_dim, fd = c.ffn_dim;
@@ -439,6 +500,12 @@ static int qkv_mats(qh_model *m, Layer &L, const uint8_t **W, float **Y)
     return n;
 }
 
+// Tell the next streaming GEMV which weights follow it (it pulls their first megabytes into L2 while it drains).
+static void hint_next(const GpuBuf &w, size_t cap = (size_t)16 << 20)
+{
+    if (!w.empty()) quartz_prefetch_next(w.ptr, w.bytes < cap ? w.bytes : cap);
+}
+
 // The fused sequence: five or six launches per layer instead of twenty-one (+ seven conversions).  Token id and
 // position are read from the device step words (cuda_step_set), so the recording serves every step.
 static void step_fused(qh_model *m, bool need_logits)
@@ -452,6 +519,7 @@ static void step_fused(qh_model *m, bool need_logits)
         const uint8_t *W[8];
         float *Y[8];
         const int n = qkv_mats(m, L, W, Y);
+        hint_next(L.o);
         cuda_gemv_rmsnorm(L.q.ggml_type, n, W, Y, m->d_hidden.f(), L.attn_norm.f(), d, kv_d, 0);
         // RoPE, KV append, attention over the whole context and its merge: one launch, which also leaves the
         // output projection's activation form in slot 1
@@ -460,16 +528,26 @@ static void step_fused(qh_model *m, bool need_logits)
             const uint8_t *w1[1] = {L.o.u8()};
             float *y1[1] = {m->d_hidden.f()};
             int s1[1] = {1};
+            hint_next(L.gate, (size_t)12 << 20);
+            hint_next(L.up, (size_t)12 << 20);
             cuda_gemv_q(L.o.ggml_type, 1, w1, s1, y1, q_d, d, 1);
         }
         {
             const uint8_t *w2[2] = {L.gate.u8(), L.up.u8()};
             float *y2[2] = {m->d_gate.f(), m->d_up.f()};
+            hint_next(L.down);
             cuda_gemv_rmsnorm(L.gate.ggml_type, 2, w2, y2, m->d_hidden.f(), L.ffn_norm.f(), d, fd, 0);
         }
         {   // down projection of swiglu(gate, up), computed in its prologue; residual added in the epilogue
             const uint8_t *w1[1] = {L.down.u8()};
             float *y1[1] = {m->d_hidden.f()};
+            if (l + 1 < c.n_layers) {
+                hint_next(m->L[l + 1].q);
+                hint_next(m->L[l + 1].k);
+                hint_next(m->L[l + 1].v);
+            } else if (need_logits) {
+                hint_next(m->lm_head);
+            }
             cuda_gemv_swiglu(L.down.ggml_type, 1, w1, y1, m->d_gate.f(), m->d_up.f(), 0, fd, d, 1);
         }
     }
@@ -581,6 +659,99 @@ int qh_step_device(qh_model *m, int token, int pos, int fused)
     return 0;
 }
 
+// Can a prompt go through the batched path?  Same conditions as the fused decode sequence for the attention
+// block (no QK-norm, no biases); dense FFN, or MoE without expert biases (the grouped MoE kernel has none).
+static bool prefill_batchable(qh_model *m)
+{
+    const qh_config &c = m->c;
+    if (c.head_dim > 128 || c.head_dim % 32 || !cuda_attn_step_supported(c.n_heads, c.n_kv_heads, c.head_dim)) return false;
+    for (auto &L : m->L) {
+        if (!L.q_norm.empty() || !L.k_norm.empty() || L.has_qkv_bias || !L.o_bias.empty()) return false;
+        if (c.n_experts > 0 && (!L.moe_gate_bias.empty() || !L.moe_up_bias.empty() || !L.moe_down_bias.empty() ||
+                                L.moe_gate.ggml_type != L.moe_up.ggml_type))
+            return false;
+    }
+    return c.n_experts == 0 || (c.n_experts <= 256 && c.n_experts_used <= 8);
+}
+
+static bool prefill_scratch(qh_model *m, int n)
+{
+    if (n <= m->p_cap) return true;
+    const qh_config &c = m->c;
+    const size_t N = (size_t)n, d = c.embed_dim, q_d = m->q_d(), kv_d = m->kv_d(), fd = c.ffn_dim;
+    const size_t used = (size_t)std::max(c.n_experts_used, 1);
+    const bool ok = m->p_tok.alloc_f32(N) && m->p_x.alloc_f32(N * d) && m->p_xn.alloc_f32(N * d) && m->p_q.alloc_f32(N * q_d) &&
+                    m->p_k.alloc_f32(N * kv_d) && m->p_v.alloc_f32(N * kv_d) && m->p_att.alloc_f32(N * std::max(q_d, d)) &&
+                    m->p_g.alloc_f32(c.n_experts > 0 ? N * (size_t)std::max(c.n_experts, 1) : N * fd) &&
+                    m->p_u.alloc_f32(c.n_experts > 0 ? 4 : N * fd) && m->p_ids.alloc_f32(N * used) && m->p_w.alloc_f32(N * used);
+    m->p_cap = ok ? n : 0;
+    return ok;
+}
+
+// Batched prefill: the n tokens of a prompt at positions pos0 .. pos0+n-1 in one pass -- every projection a
+// tensor-core GEMM over all tokens (cuda_gemm), RoPE + KV append and causal attention batched over the tokens --
+// instead of n decode steps (what the reference's GPU prefill does, src/main.rs:1410-1416; its batched prefill,
+// src/main.rs:1157-1341, is CPU-only).  Leaves the caches filled and, when logits_host is not NULL, the logits
+// of the LAST token there.  Models the batched path does not take run token by token.
+int qh_prefill(qh_model *m, const int *tokens, int n, int pos0, float *logits_host)
+{
+    if (!m || !m->finalized || !tokens || n <= 0 || pos0 < 0 || pos0 + n > m->c.max_seq) return -1;
+    const qh_config &c = m->c;
+    for (int i = 0; i < n; i++)
+        if (tokens[i] < 0 || tokens[i] >= c.vocab_size) return -1;
+    if (!prefill_batchable(m) || n == 1) {
+        for (int i = 0; i < n; i++) {
+            const int rc = qh_step_device(m, tokens[i], pos0 + i, 1);
+            if (rc) return rc;
+        }
+        if (logits_host) cuda_d2h(logits_host, m->d_logits.ptr, (size_t)c.vocab_size * 4);
+        cuda_sync();
+        return quartz_last_error() == 0 ? 0 : -10;
+    }
+    if (!prefill_scratch(m, n)) return -2;
+    const int d = c.embed_dim, h = c.n_heads, kv = c.n_kv_heads, hd = c.head_dim, q_d = m->q_d(), kv_d = m->kv_d(), fd = c.ffn_dim;
+    const float scale = attn_scale(c);
+    float *X = m->p_x.f(), *Xn = m->p_xn.f(), *Q = m->p_q.f(), *K = m->p_k.f(), *V = m->p_v.f(), *A = m->p_att.f();
+    cuda_h2d(m->p_tok.ptr, tokens, (size_t)n * 4);
+    cuda_embed_lookup_rows(X, m->embed.u8(), m->embed.ggml_type, (const int *)m->p_tok.ptr, n, d);
+    for (int l = 0; l < c.n_layers; l++) {
+        Layer &L = m->L[l];
+        cuda_rms_norm_rows(Xn, X, L.attn_norm.f(), n, d);
+        cuda_gemm(L.q.ggml_type, L.q.u8(), Xn, Q, n, d, q_d);
+        cuda_gemm(L.k.ggml_type, L.k.u8(), Xn, K, n, d, kv_d);
+        cuda_gemm(L.v.ggml_type, L.v.u8(), Xn, V, n, d, kv_d);
+        cuda_rope_kv_rows(Q, K, V, m->kv_k[l].f(), m->kv_v[l].f(), n, h, kv, hd, pos0, c.rope_theta, c.yarn_scale, c.yarn_orig_ctx,
+                          c.rope_neox);
+        cuda_attn_prompt(A, Q, m->kv_k[l].f(), m->kv_v[l].f(), n, h, kv, hd, c.max_seq, pos0, attn_window(c, l), scale, L.sinks.f());
+        cuda_gemm(L.o.ggml_type, L.o.u8(), A, Xn, n, q_d, d);
+        cuda_vec_add(X, Xn, n * d);
+        cuda_rms_norm_rows(Xn, X, L.ffn_norm.f(), n, d);
+        if (c.n_experts > 0) {
+            // router logits of all tokens, top-k and weights on the device, grouped expert FFN
+            float *RL = m->p_g.f();
+            cuda_gemm(L.router_w.ggml_type, L.router_w.u8(), Xn, RL, n, d, c.n_experts);
+            cuda_router_topk(RL, L.router_b_dev.empty() ? nullptr : L.router_b_dev.f(), n, c.n_experts, c.n_experts_used, c.moe_renorm,
+                             (int *)m->p_ids.ptr, m->p_w.f());
+            cuda_moe_ffn_dev(L.moe_gate.ggml_type, L.moe_down.ggml_type, L.moe_gate.u8(), L.moe_up.u8(), L.moe_down.u8(), Xn, A, n, d,
+                             fd, c.n_experts, c.n_experts_used, (const int *)m->p_ids.ptr, m->p_w.f(), c.clamped_swiglu);
+            cuda_vec_add(X, A, n * d);   // (the attention-output rows are free again: they hold the experts' sum)
+        } else {
+            float *Gt = m->p_g.f(), *U = m->p_u.f();
+            cuda_gemm(L.gate.ggml_type, L.gate.u8(), Xn, Gt, n, d, fd);
+            cuda_gemm(L.up.ggml_type, L.up.u8(), Xn, U, n, d, fd);
+            cuda_swiglu(Gt, Gt, U, n * fd);
+            cuda_gemm(L.down.ggml_type, L.down.u8(), Gt, Xn, n, fd, d);
+            cuda_vec_add(X, Xn, n * d);
+        }
+    }
+    // the last token's hidden state -> logits (the only row the caller needs)
+    cuda_rms_norm(m->d_norm_out.f(), X + (size_t)(n - 1) * d, m->final_norm.f(), d);
+    cuda_gemv(m->lm_head.ggml_type, m->lm_head.u8(), m->d_norm_out.f(), m->d_logits.f(), d, c.vocab_size);
+    if (logits_host) cuda_d2h(logits_host, m->d_logits.ptr, (size_t)c.vocab_size * 4);
+    cuda_sync();
+    return quartz_last_error() == 0 ? 0 : -10;
+}
+
 static int step_host(qh_model *m, int token, int pos, int need_logits, float *logits_host, int fused)
 {
     int rc = qh_step_device(m, token, pos, fused);
@@ -615,5 +786,6 @@ int qh_read_hidden(qh_model *m, float *host)
 
 long long qh_launches_last_step(qh_model *m) { return m ? m->last_launches : 0; }
 int qh_graphs_recorded(qh_model *m) { return m ? m->n_recorded : 0; }
+void qh_force_host_router(int on) { g_forced_host_router = on ? 1 : 0; }
 
 }  // extern "C"

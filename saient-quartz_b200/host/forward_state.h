@@ -66,11 +66,21 @@ int qh_forward_step(qh_model *m, int token, int pos, int need_logits, float *log
 int qh_forward_step_fused(qh_model *m, int token, int pos, int need_logits, float *logits_host);
 /* as fused, with output projection -> gate/up -> down -> next q/k/v of every layer as one persistent kernel */
 int qh_forward_step_chained(qh_model *m, int token, int pos, int need_logits, float *logits_host);
+/* Batched prefill: the n tokens of a prompt at positions pos0 .. pos0+n-1 in one pass (tensor-core GEMMs over all
+ * tokens, batched RoPE / KV append / causal attention) instead of n decode steps; the reference's GPU prefill is
+ * token by token (src/main.rs:1410-1416), its batched prefill CPU-only (src/main.rs:1157-1341).  Fills the caches;
+ * logits_host (may be NULL) receives the LAST token's logits.  Models with QK-norm or projection biases run token
+ * by token through the decode step.  0 on success. */
+int qh_prefill(qh_model *m, const int *tokens, int n, int pos0, float *logits_host);
 /* device-only variants for timing: no copies, the result stays in the device logits buffer; fused: 0 reference
  * sequence, 1 fused, 2 chained */
 int qh_step_device(qh_model *m, int token, int pos, int fused);
 int qh_read_hidden(qh_model *m, float *host);   /* d_hidden, for layer-level tests */
 long long qh_launches_last_step(qh_model *m);    /* kernel launches issued by the last step (graph nodes if fused) */
+/* 1: MoE layers route on the host as the reference does (router logits copied back, top-k on the CPU, one
+ * synchronisation per layer, src/cuda.rs:673-701); 0 (default): router top-k and expert selection stay on the
+ * device wherever the expert tensors are served by the streaming GEMV.  Also: QUARTZ_HOST_ROUTER=1. */
+void qh_force_host_router(int on);
 int qh_graphs_recorded(qh_model *m);             /* graph recordings made for this model so far (one per sequence kind) */
 
 #ifdef __cplusplus

@@ -48,6 +48,8 @@ def host_lib():
         H.qh_launches_last_step.restype = C.c_longlong
         H.qh_launches_last_step.argtypes = [C.c_void_p]
         H.qh_graphs_recorded.argtypes = [C.c_void_p]
+        H.qh_force_host_router.argtypes = [C.c_int]
+        H.qh_prefill.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         H.qh_get_kv.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
         _host = H
     return _host
@@ -161,6 +163,16 @@ class HostModel:
         if self.H.qh_get_kv(self.m, layer, k.ctypes.data, v.ctypes.data, pos0, n_pos) != 0:
             raise RuntimeError("qh_get_kv failed")
         return k, v
+
+    def prefill(self, tokens, pos0=0, want_logits=True):
+        """Batched prefill of a prompt (qh_prefill); returns the last token's logits."""
+        tok = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = np.empty(self.cfg["vocab_size"], dtype=np.float32) if want_logits else None
+        rc = self.H.qh_prefill(self.m, tok.ctypes.data, int(tok.size), int(pos0), logits.ctypes.data if want_logits else None)
+        if rc != 0:
+            from . import lib
+            raise RuntimeError(f"prefill failed: {rc} ({lib().quartz_error_string().decode()})")
+        return logits
 
     def step(self, token, pos, fused=False):
         logits = np.empty(self.cfg["vocab_size"], dtype=np.float32)

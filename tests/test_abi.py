@@ -24,6 +24,26 @@ def test_reference_call_surface_is_complete(pkg):
         assert getattr(L, name) is not None
 
 
+def test_static_archive_links_like_the_reference_build(pkg, tmp_path):
+    """build.rs:52-72 of the reference links `static=kernels` and `cudart`: a C program that takes the address of
+    every declared symbol must link against libkernels.a the same way."""
+    import shutil
+    import subprocess
+    from saient_quartz_b200 import build as b
+    assert os.path.exists(b.ARCHIVE), "libkernels.a was not built"
+    names = pkg.declared_symbols()
+    src = tmp_path / "link_test.c"
+    src.write_text("".join(f"extern void {n}(void);\n" for n in names) +
+                   "int main(void) { void (*p[])(void) = {" + ", ".join(names) + "}; return p[0] == 0; }\n")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    exe = tmp_path / "link_test"
+    cc = shutil.which("gcc")
+    assert cc
+    subprocess.check_call([cc, str(src), "-o", str(exe), "-L" + os.path.dirname(b.ARCHIVE), "-lkernels",
+                           "-L" + os.path.join(cuda, "lib64"), "-lcudart", "-lstdc++", "-lm", "-lpthread", "-ldl"])
+    assert exe.exists()
+
+
 def test_error_state_starts_clean(pkg):
     L = pkg.lib()
     L.quartz_clear_error()

@@ -194,6 +194,117 @@ def test_tiny_moe_model(gpu, oracle_mod, n_used):
     gpu.check_error()
 
 
+@pytest.mark.parametrize("n_used", [2, 5])
+def test_moe_model_routed_on_the_device(gpu, oracle_mod, n_used):
+    """MoE layers whose expert tensors the streaming GEMV serves: router top-k, expert selection, bias + SwiGLU and
+    the weighted sum stay on the device (no device-to-host copy per layer, unlike src/cuda.rs:673-701).  Against the
+    CPU oracle, and against the same model routed on the host (same experts, same arithmetic: equal to 1e-5)."""
+    from saient_quartz_b200 import synth
+    from saient_quartz_b200.host_model import HostModel, host_lib
+    cfg = dict(vocab_size=256, embed_dim=512, n_heads=8, n_kv_heads=2, n_layers=2, ffn_dim=1024, head_dim=64,
+               rope_theta=10000.0, max_seq=48, n_experts=6, n_experts_used=n_used, moe_renorm=int(n_used == 2),
+               clamped_swiglu=int(n_used == 5))
+    d, fd, q_d, kv_d, ne = 512, 1024, 512, 128, 6
+    H = host_lib()
+
+    def build():
+        m = HostModel(keep_host=True, **cfg)
+        rng = np.random.Generator(np.random.PCG64([78, n_used]))
+        tid = [700]
+
+        def w(role, l, t, K, N):
+            tid[0] += 1
+            m.set(role, l, t, synth.make_weights(t, K, N, tensor_id=tid[0]))
+
+        def f(role, l, n, scale=1.0, base=0.0):
+            m.set(role, l, 0, (base + scale * rng.standard_normal(n)).astype(np.float32))
+
+        w("EMBED", 0, 12, d, 256)
+        for l in range(2):
+            w("Q", l, 12, d, q_d); w("K", l, 12, d, kv_d); w("V", l, 12, d, kv_d); w("O", l, 12, q_d, d)
+            f("ATTN_NORM", l, d, 0.1, 1.0); f("FFN_NORM", l, d, 0.1, 1.0)
+            w("MOE_GATE", l, 12, d, fd * ne); w("MOE_UP", l, 12 if l else 13, d, fd * ne); w("MOE_DOWN", l, 12, fd, d * ne)
+            f("ROUTER_W", l, ne * d, 0.2); f("ROUTER_B", l, ne, 0.1)
+            f("MOE_GATE_BIAS", l, ne * fd, 0.01); f("MOE_UP_BIAS", l, ne * fd, 0.01); f("MOE_DOWN_BIAS", l, ne * d, 0.01)
+        f("FINAL_NORM", 0, d, 0.1, 1.0)
+        w("LM_HEAD", 0, 12, d, 256)
+        m.finalize()
+        return m
+
+    m = build()
+    kv = m.fill_kv(9, keep=True)
+    ref = _ref_for(m, oracle_mod, kv)
+    got = {}
+    for pos, tok in ((9, 11), (10, 200)):
+        want = ref.forward(tok, pos)
+        got[pos] = m.step(tok, pos, fused=False)
+        assert _rel(got[pos], want) < 5e-3, (n_used, pos)
+    gpu.check_error()
+    try:
+        H.qh_force_host_router(1)
+        m2 = build()
+        m2.fill_kv(9)
+        for pos, tok in ((9, 11), (10, 200)):
+            assert _rel(m2.step(tok, pos, fused=False), got[pos].astype(np.float64)) < 1e-5, (n_used, pos)
+    finally:
+        H.qh_force_host_router(0)
+    gpu.check_error()
+
+
+def test_batched_prefill_matches_token_by_token(gpu, oracle_mod):
+    """qh_prefill (tensor-core GEMMs over the whole prompt, batched RoPE / KV append / causal attention) followed by
+    one decode step gives the logits of n + 1 decode steps (bar 5e-3 of max |logit|; the GEMM carries weights and
+    activations as bf16) and leaves the same cache rows (to the same relative bar); continuing a context (pos0 > 0)
+    and a prompt whose length is not a multiple of any tile; logits of the prompt's last token against the oracle."""
+    for (n, pos0) in ((37, 0), (21, 12)):
+        rng = np.random.Generator(np.random.PCG64([0x9F, n]))
+        tokens = rng.integers(0, 320, size=n + 1)
+        a, b = _tiny_dense(gpu), _tiny_dense(gpu)
+        kv = a.fill_kv(pos0, keep=True) if pos0 else []
+        if pos0:
+            b.fill_kv(pos0)
+        ref = _ref_for(a, oracle_mod, kv)
+        for i in range(n):
+            last_a = a.step(int(tokens[i]), pos0 + i, fused=True)
+            want = ref.forward(int(tokens[i]), pos0 + i)
+        last_b = b.prefill(tokens[:n], pos0)
+        assert _rel(last_b, want) < 5e-3, (n, pos0)
+        assert _rel(last_b, last_a.astype(np.float64)) < 5e-3, (n, pos0)
+        for l in range(3):
+            ka, va = a.read_kv(l, pos0, n)
+            kb, vb = b.read_kv(l, pos0, n)
+            assert np.abs(ka - kb).max() <= 5e-3 * np.abs(ka).max() and np.abs(va - vb).max() <= 5e-3 * np.abs(va).max(), l
+        nxt_a = a.step(int(tokens[n]), pos0 + n, fused=True)
+        nxt_b = b.step(int(tokens[n]), pos0 + n, fused=True)
+        assert _rel(nxt_b, nxt_a.astype(np.float64)) < 5e-3, (n, pos0)
+        a.close(); b.close()
+    gpu.check_error()
+
+
+def test_batched_prefill_llama8b_shape_512_tokens(gpu):
+    """The Llama-3-8B-shaped model: a 512-token prompt through qh_prefill, then one decode step, against 513 decode
+    steps (bar 5e-3 of max |logit|)."""
+    from saient_quartz_b200.host_model import HostModel, LLAMA3_8B
+    n = 512
+    rng = np.random.Generator(np.random.PCG64([0x9E]))
+    tokens = rng.integers(0, LLAMA3_8B["vocab_size"], size=n + 1)
+    m = HostModel(**LLAMA3_8B)
+    m.fill_synthetic()
+    for i in range(n):
+        m.step_device(int(tokens[i]), i, 1)
+    want = m.step(int(tokens[n]), n, fused=True)
+    ka, va = m.read_kv(31, 0, n)
+    m.prefill(tokens[:n], 0, want_logits=False)
+    kb, vb = m.read_kv(31, 0, n)
+    got = m.step(int(tokens[n]), n, fused=True)
+    rk, rv = np.abs(ka - kb).max() / np.abs(ka).max(), np.abs(va - vb).max() / np.abs(va).max()
+    print(f"layer-31 cache rows: rel diff K {rk:.2e} V {rv:.2e}; logits rel diff {_rel(got, want.astype(np.float64)):.2e}")
+    assert rk <= 2e-2 and rv <= 2e-2      # 32 layers of bf16-operand GEMMs against integer-dot GEMVs
+    assert _rel(got, want.astype(np.float64)) < 5e-3
+    m.close()
+    gpu.check_error()
+
+
 def test_fused_entry_points_match_unfused(gpu):
     """cuda_rms_norm_q / cuda_swiglu_q / cuda_quantize_x + cuda_gemv_q reproduce cuda_rms_norm /
     cuda_swiglu + cuda_gemv bit for bit (same conversion, same kernels); accumulate adds."""

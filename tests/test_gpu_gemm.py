@@ -47,6 +47,20 @@ def test_gemm_q4k_q6k_q8_0(gpu, oracle_mod, t, repack, M):
     _check(oracle_mod, y, X, w, t, K, N)
 
 
+@pytest.mark.parametrize("t,repack", [(12, False), (14, False), (8, False), (17, False), (18, False)])
+@pytest.mark.parametrize("K", [256, 512])
+def test_gemm_short_rows(gpu, oracle_mod, t, repack, K):
+    """Short in_dim: with bf16 operands the error does not average out over many products, so the ratio to
+    the bound is at its worst here (a single Q4_K / Q6_K super-block or two per row)."""
+    from saient_quartz_b200 import synth
+    N, M = 300, 70
+    w = synth.make_weights(t, K, N, tensor_id=705)
+    X = synth.make_x(K, tensor_id=706, rows=M)
+    y = _gemm(gpu, t, w, X, K, N, repack)
+    worst = _check(oracle_mod, y, X, w, t, K, N)
+    print(f"type {t} K={K}: max err/tol {worst:.3g}")
+
+
 @pytest.mark.parametrize("t", ALL_BLOCK_TYPES)
 def test_gemm_every_format(gpu, oracle_mod, t):
     from saient_quartz_b200 import synth
