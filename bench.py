@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--no-gemm", action="store_true", help="skip the batched (prefill) dequant-GEMM section")
     ap.add_argument("--decode-only", action="store_true",
                     help="profiling case: run only the fused decode-step section (no CPU parity pass) and print it")
+    ap.add_argument("--moe-only", action="store_true", help="profiling case: run only the batched MoE FFN section and print its rows")
     ap.add_argument("--gemm-only", default=None, metavar="FORMAT:M",
                     help="profiling case: run only this dequant-GEMM case (e.g. Q4_K:2048) and print its row")
     return ap.parse_args()
@@ -633,6 +634,9 @@ def main():
         q.check_error("quartz_set_device")
     if args.decode_only:
         print(json.dumps({"decode": decode_section(q, args, torch, np, False, fused_only=True)}))
+        return
+    if args.moe_only:
+        print(json.dumps({"moe_ffn": moe_section(q, args, torch, np)}))
         return
     if args.gemm_only:
         name, m = args.gemm_only.split(":")

@@ -389,6 +389,20 @@ void cuda_moe_decode_combine(float *d_acc, const float *d_down, const float *d_d
  * Every rank must issue the same sequence of pushes.  A payload region may be overwritten only after a
  * wait that followed an exchange into another region.  The int functions return 0 on success, -1 on
  * failure (see quartz_last_error). */
+/* The NCCL form of the exchange: an all-gather of every rank's f32 slice on a communicator the library creates.
+ * NCCL is bound at run time (libnccl.so.2, or the file QUARTZ_NCCL_LIB names); without it these calls set
+ * QZ_ERR_CUDA and the rest of the library is unaffected.
+ *   quartz_nccl_unique_id   rank 0: write the communicator id (quartz_nccl_id_bytes() bytes) to id_out; the host
+ *                           hands it to the other ranks by whatever means it has
+ *   quartz_nccl_init        every rank, with rank 0's id (collective: returns when all ranks have joined)
+ *   quartz_mgpu_allgather   d_recv[r * count_per_rank ..] = rank r's d_send[0 .. count_per_rank), on the library's
+ *                           stream (ncclAllGather, in place when d_send == d_recv + rank * count_per_rank)
+ *   quartz_nccl_shutdown    destroy the communicator */
+size_t quartz_nccl_id_bytes(void);
+int quartz_nccl_unique_id(void *id_out);
+int quartz_nccl_init(int rank, int world, const void *id);
+void quartz_mgpu_allgather(const float *d_send, float *d_recv, size_t count_per_rank);
+void quartz_nccl_shutdown(void);
 size_t quartz_mgpu_handle_bytes(void);
 int quartz_set_device(int device);
 int quartz_mgpu_init(int rank, int world, size_t data_bytes, void *handle_out);

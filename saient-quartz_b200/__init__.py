@@ -113,6 +113,11 @@ _SIGS = {
     "cuda_router_topk": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "cuda_moe_ffn": (None, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                             C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
+    "quartz_nccl_id_bytes": (C.c_size_t, []),
+    "quartz_nccl_unique_id": (C.c_int, [C.c_void_p]),
+    "quartz_nccl_init": (C.c_int, [C.c_int, C.c_int, C.c_void_p]),
+    "quartz_mgpu_allgather": (None, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "quartz_nccl_shutdown": (None, []),
     "quartz_mgpu_handle_bytes": (C.c_size_t, []),
     "quartz_set_device": (C.c_int, [C.c_int]),
     "quartz_mgpu_init": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.c_void_p]),

@@ -4,7 +4,9 @@
 
 #include "../../include/quartz_b200.h"
 
+#include <dlfcn.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <map>
 #include <mutex>
@@ -2287,6 +2289,101 @@ void quartz_mgpu_fuse_next_wait(void)
     }
     g_wait_ctrl = (const MgpuCtrl *)g_win;
     g_wait_ranks = g_mg_world;
+}
+
+// ---- NCCL all-gather of the f32 output slices (the exchange in library form) ----
+// NCCL is bound at run time (dlopen of libnccl.so.2), so the library itself links against nothing but the CUDA
+// runtime and still loads on machines without NCCL; the declarations below restate the five NCCL entry points
+// used (nccl.h: ncclGetUniqueId, ncclCommInitRank, ncclAllGather, ncclCommDestroy, ncclGetErrorString).
+struct QzNcclId { char internal[128]; };   // ncclUniqueId
+static void *g_nccl_so = nullptr;
+static void *g_nccl_comm = nullptr;
+static int (*p_ncclGetUniqueId)(QzNcclId *) = nullptr;
+static int (*p_ncclCommInitRank)(void **, int, QzNcclId, int) = nullptr;
+static int (*p_ncclAllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
+static int (*p_ncclCommDestroy)(void *) = nullptr;
+static const char *(*p_ncclGetErrorString)(int) = nullptr;
+
+static bool nccl_bind()
+{
+    if (g_nccl_so) return true;
+    const char *names[] = {getenv("QUARTZ_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        if (!n) continue;
+        g_nccl_so = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (g_nccl_so) break;
+    }
+    if (!g_nccl_so) {
+        set_error(QZ_ERR_CUDA, "quartz_nccl: libnccl.so.2 not found (set QUARTZ_NCCL_LIB)");
+        return false;
+    }
+    p_ncclGetUniqueId = (int (*)(QzNcclId *))dlsym(g_nccl_so, "ncclGetUniqueId");
+    p_ncclCommInitRank = (int (*)(void **, int, QzNcclId, int))dlsym(g_nccl_so, "ncclCommInitRank");
+    p_ncclAllGather = (int (*)(const void *, void *, size_t, int, void *, cudaStream_t))dlsym(g_nccl_so, "ncclAllGather");
+    p_ncclCommDestroy = (int (*)(void *))dlsym(g_nccl_so, "ncclCommDestroy");
+    p_ncclGetErrorString = (const char *(*)(int))dlsym(g_nccl_so, "ncclGetErrorString");
+    if (!p_ncclGetUniqueId || !p_ncclCommInitRank || !p_ncclAllGather || !p_ncclCommDestroy) {
+        set_error(QZ_ERR_CUDA, "quartz_nccl: libnccl lacks an entry point");
+        dlclose(g_nccl_so);
+        g_nccl_so = nullptr;
+        return false;
+    }
+    return true;
+}
+
+static bool nccl_ok(int rc, const char *what)
+{
+    if (rc == 0) return true;
+    std::string msg = std::string(what) + ": " + (p_ncclGetErrorString ? p_ncclGetErrorString(rc) : "NCCL error");
+    set_error(QZ_ERR_CUDA, msg.c_str());
+    return false;
+}
+
+size_t quartz_nccl_id_bytes(void) { return sizeof(QzNcclId); }
+
+int quartz_nccl_unique_id(void *id_out)
+{
+    if (!id_out || !nccl_bind()) return -1;
+    QzNcclId id;
+    if (!nccl_ok(p_ncclGetUniqueId(&id), "ncclGetUniqueId")) return -1;
+    memcpy(id_out, &id, sizeof(id));
+    return 0;
+}
+
+int quartz_nccl_init(int rank, int world, const void *id)
+{
+    if (g_nccl_comm || !id || rank < 0 || world < 1 || rank >= world) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_nccl_init: bad rank/world, or already initialised");
+        return -1;
+    }
+    if (!nccl_bind()) return -1;
+    QzNcclId uid;
+    memcpy(&uid, id, sizeof(uid));
+    void *comm = nullptr;
+    if (!nccl_ok(p_ncclCommInitRank(&comm, world, uid, rank), "ncclCommInitRank")) return -1;
+    g_nccl_comm = comm;
+    g_mg_rank = rank;
+    if (!g_mg_world) g_mg_world = world;
+    return 0;
+}
+
+void quartz_mgpu_allgather(const float *d_send, float *d_recv, size_t count_per_rank)
+{
+    if (!g_nccl_comm) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_mgpu_allgather: call quartz_nccl_init first");
+        return;
+    }
+    if (count_per_rank == 0) return;
+    g_launch_count++;
+    nccl_ok(p_ncclAllGather(d_send, d_recv, count_per_rank, 7 /* ncclFloat32 */, g_nccl_comm, g_stream), "ncclAllGather");
+}
+
+void quartz_nccl_shutdown(void)
+{
+    if (!g_nccl_comm) return;
+    cudaDeviceSynchronize();
+    p_ncclCommDestroy(g_nccl_comm);
+    g_nccl_comm = nullptr;
 }
 
 void quartz_mgpu_shutdown(void)

@@ -2,7 +2,8 @@
     python -m torch.distributed.run --nproc-per-node G tests/mgpu_worker.py
 Every rank uploads its row shard of each matrix, runs cuda_gemv_push + quartz_mgpu_wait, and checks the
 COMPLETE vector in its own window against the CPU oracle.  Then a batched block goes through
-cuda_gemm + cuda_push_rows, and last a wait that nobody answers must come back with QZ_ERR_TIMEOUT."""
+cuda_gemm + cuda_push_rows, the NCCL all-gather form of the exchange (quartz_nccl_* / quartz_mgpu_allgather), and
+last a wait that nobody answers must come back with QZ_ERR_TIMEOUT."""
 import os
 import sys
 
@@ -119,6 +120,33 @@ def main():
         ref2 = oracle.gemv(y1, wb, 14, N1, N2)
         tol2 = 1e-3 * oracle.row_norms(wb, 14, N1, N2) * float(np.linalg.norm(y1.astype(np.float64)))
         assert np.all(np.abs(y2 - ref2) <= tol2), f"rank {rank} chain y2"
+    # the NCCL form of the exchange through the C ABI: every rank computes its slice into place, ncclAllGather
+    import ctypes as C
+    idb = C.create_string_buffer(L.quartz_nccl_id_bytes())
+    if rank == 0:
+        assert L.quartz_nccl_unique_id(idb) == 0, L.quartz_error_string()
+    if world > 1:
+        box = [idb.raw]
+        dist.broadcast_object_list(box, src=0)
+        idb = C.create_string_buffer(box[0], len(box[0]))
+    assert L.quartz_nccl_init(rank, world, idb) == 0, L.quartz_error_string()
+    t, K, N = 12, 4096, 1024 * world
+    w = synth.make_weights(t, K, N, tensor_id=980)
+    x = synth.make_x(K, tensor_id=981).reshape(-1)
+    n0, n1, per = shard_rows(N, rank, world)
+    b0, b1 = shard_bytes(t, K, N, rank, world)
+    dw, dxx, dyy = q.GpuBuf.upload(w[b0:b1]), q.GpuBuf.upload(x), q.GpuBuf.alloc_f32(per * world)
+    for rep in range(2):
+        L.cuda_gemv(t, dw.ptr, dxx.ptr, dyy.ptr + 4 * rank * per, K, n1 - n0)
+        L.quartz_mgpu_allgather(dyy.ptr + 4 * rank * per, dyy.ptr, per)
+        L.cuda_sync()
+        q.check_error("nccl all-gather")
+        y = dyy.download()[:N]
+        ref = oracle.gemv(x, w, t, K, N)
+        tol = 1e-3 * oracle.row_norms(w, t, K, N) * float(np.linalg.norm(x.astype(np.float64)))
+        assert np.all(np.abs(y.astype(np.float64) - ref) <= tol), f"rank {rank} nccl all-gather"
+    L.quartz_nccl_shutdown()
+
     if world > 1:
         dist.barrier()
         # rank 0 pushes once more and waits, nobody answers: the bounded wait runs out and reports it
