@@ -609,6 +609,57 @@ def sharded70b_section(q, L, torch, win, rank, world, dist, steps, cpu_baseline=
     return out
 
 
+def sharded_gemm_section(q, L, torch, win, rank, world, dist):
+    """The prefill GEMMs row-sharded over the ranks: Q4_K 4096->14336 and Q6_K 14336->4096 times M = 16, 64, 512,
+    2048 tokens.  Every rank holds the rows [n0, n1) of the matrix, computes its [M, n1-n0] block with cuda_gemm and
+    stores it into every rank's window (cuda_push_rows); after the wait each rank holds the complete [M, N] output.
+    Times are device times, max over ranks; TFLOP/s and GB/s are whole-job figures."""
+    from saient_quartz_b200 import synth
+    from saient_quartz_b200.shard import shard_rows as sr, shard_bytes
+    out = []
+    for (t, K, N) in ((12, 4096, 14336), (14, 14336, 4096)):
+        w = synth.make_weights(t, K, N, tensor_id=400 + t)
+        n0, n1, per = sr(N, rank, world)
+        b0, b1 = shard_bytes(t, K, N, rank, world)
+        dw = q.GpuBuf.upload(w[b0:b1])
+        del w
+        L.cuda_repack_weights(t, dw.ptr, K, n1 - n0, 1)
+        for M in (16, 64, 512, 2048):
+            X = synth.make_x(K, tensor_id=410, rows=M)
+            dx, dy = q.GpuBuf.upload(X), q.GpuBuf.alloc_f32(M * (n1 - n0))
+
+            def step():
+                L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, n1 - n0)
+                win.push_rows(dy.ptr, M, n1 - n0, n0, N)
+                win.wait()
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            reps = 10 if M <= 64 else 5
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            if world > 1:
+                tt = torch.tensor([ms], device="cuda")
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                ms = float(tt.item())
+            q.check_error("sharded gemm")
+            flops = 2.0 * M * K * N
+            nbytes = synth.type_size(t, K * N) + 4.0 * M * K + 4.0 * M * N
+            out.append({"format": synth.FORMATS[t][0], "M": M, "K": K, "N": N, "n_gpus": world, "ms": ms,
+                        "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6,
+                        "exchange": "cuda_push_rows into every rank's window + one wait"})
+            dx.drop(); dy.drop()
+        dw.drop()
+    return out
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -670,6 +721,8 @@ def main():
     # exchange window: the six output vectors (sweep) or the 70B-shaped pair at batch 32, whichever is larger
     half = off
     win_floats = max(2 * half, 32 * (28672 + 8192))
+    if world > 1 and not args.small and not args.no_sharded:
+        win_floats = max(win_floats, 2048 * 14336)   # the complete output of the largest sharded prefill GEMM
     win, win_err = None, None
     if world > 1 or not args.small:
         try:
@@ -1005,6 +1058,10 @@ def main():
     if win is not None and not args.small and not args.no_sharded:
         sharded = sharded70b_section(q, L, torch, win, rank, world, dist, args.steps, cpu_baseline=not args.no_cpu_baseline)
 
+    sharded_gemm = None
+    if win is not None and world > 1 and not args.small and not args.no_sharded:
+        sharded_gemm = sharded_gemm_section(q, L, torch, win, rank, world, dist)
+
     # ---- parity spot check of what was just timed (rank 0, smallest shape) + CPU baseline ----
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -1074,6 +1131,7 @@ def main():
             "batched_single_launch": batched,
             "moe_ffn": moe,
             "sharded70b": sharded,
+            "sharded_gemm": sharded_gemm,
             "nccl_allgather_variant": nccl_variant,
         }
         print(json.dumps(line))
