@@ -963,6 +963,75 @@ def main():
                        "how": "cuda_gemv_batch: the six independent GEMVs in one persistent kernel, graph replay"}
             if gb:
                 L.quartz_graph_destroy(gb)
+    elif win is not None:
+        # sharded: the six GEMVs of this rank's shards AND their exchange as one launch (cuda_gemv_batch_push), one
+        # wait per step; the two window-region parities alternate as in the headline step
+        import ctypes as C
+        dummy = torch.zeros(max(n1 - n0 for (n0, n1, _) in rows) + 64, dtype=torch.float32, device="cuda")
+        ops = [q.chain_op(t, [d_w[i].ptr], [dummy.data_ptr()], K, rows[i][1] - rows[i][0], 0, 3, d_x[i].ptr)
+               for i, (label, t, K, N) in enumerate(shapes)]
+        arr = (q.ChainOp * len(ops))(*ops)
+        offs = [(C.c_size_t * len(ops))(*[par * half + y_off[i] + rows[i][0] for i in range(len(shapes))]) for par in (0, 1)]
+
+        def bstep(par):
+            ok = L.cuda_gemv_batch_push(len(ops), arr, offs[par])
+            win.wait()
+            return ok
+        supported = torch.tensor([1 if bstep(0) else 0], device="cuda")
+        dist.all_reduce(supported, op=dist.ReduceOp.MIN)
+        sync_all()
+        if int(supported.item()) == 1:
+            bstep(1)
+            sync_all()
+            gbs = [None, None]
+            for par in (0, 1):
+                if L.quartz_graph_begin():
+                    bstep(par)
+                    gbs[par] = L.quartz_graph_end()
+            q.check_error("batched sharded graph capture")
+            bno = [0]
+
+            def fnb():
+                par = bno[0] & 1
+                bno[0] += 1
+                if gbs[0] and gbs[1]:
+                    L.quartz_graph_launch(gbs[par])
+                else:
+                    bstep(par)
+            for _ in range(4):
+                fnb()
+            sync_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fnb()
+            e1.record()
+            sync_all()
+            tt = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            bms = float(tt.item())
+            q.check_error("batched sharded sweep")
+            batched = {"ms_per_step": bms, "value": total_bytes / (bms * 1e-3) / 1e9, "unit": UNIT, "launches_per_step": 2,
+                       "how": "cuda_gemv_batch_push: this rank's six shard GEMVs and their peer-store exchange in one "
+                              "persistent kernel, one wait per step, graph replay; device time, max over ranks"}
+            # the complete vectors in this rank's window against the CPU oracle (what was just timed)
+            if rank == 0:
+                import oracle
+                from saient_quartz_b200.iq_tables import load_tables
+                oracle.set_tables(load_tables())
+                par = (bno[0] - 1) & 1
+                for i in (1, 5):
+                    _, t, K, N = shapes[i]
+                    wfull = synth.make_weights(t, K, N, tensor_id=100 + i)
+                    got = np.empty(N, dtype=np.float32)
+                    L.cuda_d2h(got.ctypes.data, win.data_ptr + 4 * (par * half + y_off[i]), 4 * N)
+                    ref = oracle.gemv(xs[i].reshape(-1), wfull, t, K, N)
+                    tol = oracle.tolerance(wfull, t, K, N, xs[i].reshape(-1))
+                    assert np.all(np.abs(got - ref) <= tol), "batched sharded bench output failed the parity bound"
+            sync_all()   # the other ranks must not start the next exchange while rank 0 is still in the oracle
+            for g_ in gbs:
+                if g_:
+                    L.quartz_graph_destroy(g_)
 
     nccl_variant = None
     if world > 1 and win is not None:
@@ -1097,17 +1166,25 @@ def main():
         gemm = gemm_section(q, args, torch, np, want_parity=not args.no_cpu_baseline)
 
     if rank == 0:
-        launches_per_step = 0
-        for (label, t, K, N) in shapes:
-            launches_per_step += 2   # activation conversion + streaming GEMV
+        launches_per_step = len(shapes)   # one streaming GEMV per shape (the activation conversion runs in its prologue)
         if world > 1:
             launches_per_step += 1   # the step's exchange wait
+        six_calls = {"ms_per_step": ms, "value": total_bytes / (ms * 1e-3) / 1e9, "unit": UNIT,
+                     "how": ("CUDA graph replay of the six cuda_gemv calls" if graph else "six cuda_gemv calls, eager") +
+                            ("" if world == 1 else " (cuda_gemv_push per shape, one wait per step)")}
+        headline_how = six_calls["how"]
+        # The six GEMVs of the sweep do not depend on one another: the public call for that is cuda_gemv_batch
+        # (one persistent launch).  The headline is whichever of the two public paths is faster; both are reported.
+        if batched and batched["ms_per_step"] < ms:
+            ms = batched["ms_per_step"]
+            launches_per_step = batched["launches_per_step"]
+            headline_how = batched["how"]
         line = {
             "metric": METRIC, "value": total_bytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "i8 dp4a + f32", "data": "synthetic",
             "config": {"workload": WORKLOAD + (" [small]" if args.small else ""),
-                       "launch": ("CUDA graph replay of the six cuda_gemv calls" if graph else "eager launches"),
+                       "launch": headline_how,
                        "parallelism": "single GPU" if world == 1 else (
                            f"row-sharded x{world}; output slices exchanged by peer stores from the GEMV epilogue (NVLink), one flag wait per step"
                            if win is not None else f"row-sharded x{world}; NCCL all-gather of the f32 slices after every GEMV (peer windows unavailable: {win_err})"),
@@ -1128,6 +1205,7 @@ def main():
             "gemv_shapes": shape_rows,
             "decode": decode,
             "gemm": gemm,
+            "six_separate_calls": six_calls,
             "batched_single_launch": batched,
             "moe_ffn": moe,
             "sharded70b": sharded,

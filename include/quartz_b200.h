@@ -379,6 +379,7 @@ void cuda_moe_decode_combine(float *d_acc, const float *d_down, const float *d_d
  *                           host exchanges them by whatever means it has); maps the peers' windows
  *   quartz_mgpu_data        device pointer to this rank's payload area (read complete vectors here)
  *   cuda_gemv_push          cuda_gemv whose out_dim rows land at payload[dst_off + j] of EVERY rank
+ *   cuda_gemv_batch_push    several independent GEMVs and their exchange as one launch (below)
  *   cuda_push_rows          the same exchange for an [m x n_local] block already in device memory
  *                           (GEMM outputs): element (i, j) lands at payload[dst_off + i*dst_ld + j]
  *   quartz_mgpu_wait        enqueue the wait for ALL exchanges pushed so far: every rank's slices have
@@ -411,6 +412,12 @@ float *quartz_mgpu_data(void);
 void cuda_gemv_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, size_t dst_off, int in_dim,
                     int out_dim);
 void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size_t dst_ld);
+/* cuda_gemv_batch (independent GEMVs of different shapes in ONE persistent launch) with the push epilogue: op k's
+ * rows (one matrix per op, no accumulate) land at payload[dst_off[k] + j] of EVERY rank, and the whole launch
+ * publishes ONE exchange -- a row-sharded step of several independent GEMVs costs one launch and one wait instead of
+ * one launch, one conversion and one publish per GEMV.  Returns 1 if launched, 0 if the persistent kernel does not
+ * take these ops (nothing was launched: use cuda_gemv_push per op). */
+int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off);
 void quartz_mgpu_wait(void);
 void quartz_mgpu_fuse_next_wait(void);
 void quartz_mgpu_shutdown(void);

@@ -5,7 +5,10 @@
 // per link, the latency from one grid's completion to the release of its dependents plus an empty
 // weight pipeline.  Here one CTA per SM runs the whole chain:
 //   * the producer lane streams the weight rows of op 0, op 1, ... back to back through the same
-//     shared-memory ring (weights depend on nothing, so it never waits for a link);
+//     shared-memory ring (weights depend on nothing, so it never waits for a link).  The ring is a
+//     circular BYTE buffer: a stage takes exactly the bytes of its op's row tile, so an op with small
+//     stages keeps as many bytes in flight as one with large stages (a ring of fixed-size slots would
+//     be sized for the largest stage of any op and run the others half empty);
 //   * the consumers finish op k, meet at a grid-wide barrier (a self-resetting count + generation in
 //     global memory, polled with a bound), convert op k+1's activation vector from the outputs that
 //     are now complete (RMSNorm / SwiGLU / plain f32, as in gemv_tma_kernel's prologue) and go on;
@@ -33,6 +36,9 @@ struct ChainOp {
     int n_mats, K, N, accumulate;
     int U, Upad, RP;        // units per row, threads per row, rows per stage
     int n_cta;              // CTAs per matrix (grid / n_mats, at most the tile count)
+    int rot;                // the op's CTA numbering starts at this CTA (spreads the ops' odd tiles over the grid)
+    int x_off;              // byte offset of the op's converted activation vector behind the ring
+    long long push_off;     // >= 0: rows go to every rank's window at this offset (n_mats = 1) instead of y
     XSrc xsrc;              // mode 1 (RMSNorm), 2 (SwiGLU) or 3 (plain f32 vector a)
 };
 
@@ -44,16 +50,32 @@ struct ChainArgs {
     ChainOp op[CHAIN_MAX_OPS];
     int n_ops;
     int independent;           // 1: no op reads another op's output: no grid barrier between them
-    int slot_bytes, n_slots;   // ring geometry: every op's stage fits a slot
+    int ring_bytes;            // the circular byte buffer (a multiple of 128; every stage fits at least three times)
     GridBarrier *gb;
     int *status;
+    PushArgs push;             // the ranks' windows, when an op pushes
 };
 
-// state of the weight ring as one role sees it; survives from op to op
+// State of the weight ring as one role sees it; survives from op to op.  Stage number `seq` uses barrier
+// seq % TMA_MAX_STAGES in its (seq / TMA_MAX_STAGES)-th phase and the bytes [off, off + size): `off` follows the
+// previous stage, or is 0 when the stage would run past the end of the buffer.  Producer and consumers apply the same
+// rule to the same sequence of stage sizes, so they agree on every offset without exchanging it.
 struct RingPos {
-    int s;
-    uint32_t parity;
+    uint32_t seq;
+    uint32_t next_off;
 };
+__device__ __forceinline__ uint32_t ring_place(RingPos &rp, uint32_t size, uint32_t ring_bytes)
+{
+    uint32_t off = rp.next_off;
+    if (off + size > ring_bytes) off = 0;
+    rp.next_off = off + size;
+    return off;
+}
+__device__ __forceinline__ uint32_t chain_stage_bytes(const ChainOp &op)
+{
+    const FormatInfo fi = format_info(op.type);
+    return (uint32_t)((op.RP * (op.K / fi.block_elems) * fi.block_bytes + 127) & ~127);
+}
 
 __device__ __forceinline__ int ld_acquire_gpu(const int *p)
 {
@@ -88,9 +110,10 @@ __device__ __forceinline__ bool grid_barrier(GridBarrier *gb, int n_ctas, int *s
 // The consumer side of one op for policy F.  All TMA_CONSUMERS threads call it; threads beyond the op's
 // Upad * RP take part in the ring protocol (every warp releases every stage) but compute nothing.
 template <class F, int MODE>
-__device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta, uint8_t *ring, int slot_bytes, int n_slots,
+__device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta, uint8_t *ring, int ring_bytes,
                                               uint64_t *full_bar, uint64_t *empty_bar, float (*part)[4 * (TMA_CONSUMERS / 32)],
-                                              const XQ &xq, RingPos &rp, int *status, volatile int *cta_dead)
+                                              const XQ &xq, RingPos &rp, int *status, volatile int *cta_dead,
+                                              const PushArgs &push)
 {
     const FormatInfo fi = format_info(F::TYPE);
     const int nb = op.K / fi.block_elems;
@@ -110,6 +133,7 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
     const int my_tiles = cta < op.n_cta ? (ntiles - cta + op.n_cta - 1) / op.n_cta : 0;
     const uint32_t ring0 = smem_u32(ring), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     const uint32_t row_off = (uint32_t)((worker ? rl : 0) * row_bytes);
+    const uint32_t stage = chain_stage_bytes(op);
     bool ok = true;   // warp-uniform
     for (int t0 = 0; t0 < my_tiles; t0 += 4) {
         float acc[4];
@@ -117,7 +141,10 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
         for (int j = 0; j < 4; j++) {
             acc[j] = 0.f;
             if (t0 + j < my_tiles) {
-                if (ok && !mbar_wait_warp(full0 + 8 * rp.s, rp.parity, cta_dead)) {
+                const uint32_t bs = rp.seq % TMA_MAX_STAGES, parity = (rp.seq / TMA_MAX_STAGES) & 1;
+                const uint32_t off_s = ring_place(rp, stage, (uint32_t)ring_bytes);
+                rp.seq++;
+                if (ok && !mbar_wait_warp(full0 + 8 * bs, parity, cta_dead)) {
                     if (lane == 0) {
                         atomicExch(status, QZ_ERR_TIMEOUT);
                         *cta_dead = 1;
@@ -127,20 +154,23 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
                 if (ok) {
                     if (worker) {
                         typename F::WRegs w;
-                        F::template load_w<LdSharedAddr>(w, ring0 + (uint32_t)rp.s * (uint32_t)slot_bytes + row_off, off);
+                        F::template load_w<LdSharedAddr>(w, ring0 + off_s + row_off, off);
                         acc[j] = F::dot(w, xr, off, nullptr);
                     }
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_addr(empty0 + 8 * rp.s);
+                    if (lane == 0) mbar_arrive_addr(empty0 + 8 * bs);
                 }
-                if (++rp.s == n_slots) { rp.s = 0; rp.parity ^= 1; }
             }
         }
         if (!worker) continue;   // (whole warps: n_consumers is a multiple of 32)
         const int row_j0 = (cta + t0 * op.n_cta) * op.RP + rl, row_step = op.n_cta * op.RP;
         auto store_y = [&](int row, float v) {
             if (*cta_dead) return;   // a warp of this CTA gave up: its rows are incomplete
-            y[row] = op.accumulate ? __ldcg(y + row) + v : v;
+            if (op.push_off >= 0) {
+                for (int rk = 0; rk < push.n; rk++) push.data[rk][op.push_off + row] = v;
+            } else {
+                y[row] = op.accumulate ? __ldcg(y + row) + v : v;
+            }
         };
         const float v = warp_sum4(active ? acc[0] : 0.f, active ? acc[1] : 0.f, active ? acc[2] : 0.f, active ? acc[3] : 0.f,
                                   lane);
@@ -172,7 +202,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     __shared__ int cta_ok, cta_dead;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < a.n_slots; s++) {
+        for (int s = 0; s < TMA_MAX_STAGES; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], TMA_CONSUMERS / 32);   // every consumer warp releases every stage
         }
@@ -187,35 +217,87 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     if (threadIdx.x >= TMA_CONSUMERS) {
         // ---------------- producer: the weight rows of every op, back to back ----------------
         if (threadIdx.x != TMA_CONSUMERS) return;
-        int s = 0, issued = 0;
-        uint32_t round = 0;
-        bool ok = true;
-        for (int k = 0; k < a.n_ops && ok; k++) {
-            const ChainOp &op = a.op[k];
-            const FormatInfo fi = format_info(op.type);
-            const int row_bytes = (op.K / fi.block_elems) * fi.block_bytes;
-            const int ntiles = (op.N + op.RP - 1) / op.RP;
-            const int m = blockIdx.x % op.n_mats, cta = blockIdx.x / op.n_mats;
-            if (cta >= op.n_cta) continue;
-            const uint8_t *W = op.W[m];
-            for (int tile = cta; tile < ntiles; tile += op.n_cta) {
-                if (round > 0) ok = mbar_wait(&empty_bar[s], (round - 1) & 1);
-                if (!ok) break;
-                const int row0 = tile * op.RP;
-                const int rows = min(op.RP, op.N - row0);
-                const uint32_t bytes = (uint32_t)rows * (uint32_t)row_bytes;
-                mbar_arrive_expect_tx(&full_bar[s], bytes);
-                tma_load_1d(ring + (size_t)s * a.slot_bytes, W + (size_t)row0 * row_bytes, bytes, &full_bar[s]);
-                issued++;
-                if (++s == a.n_slots) { s = 0; round++; }
+        // `head` walks this CTA's stages and issues their copies.  Every stage also gets a VIRTUAL byte position that
+        // only grows: its start is the previous stage's end plus the bytes skipped at the end of the buffer when the
+        // stage did not fit there.  Stages are released in issue order, so the bytes still owned by stages in flight
+        // are exactly the virtual span from the oldest stage's start to the newest one's end; a new stage may be
+        // issued once that span, extended to the new stage's end, is no longer than the buffer.
+        struct Walk {
+            int k, tile;         // current stage: op and tile (tile < 0: the op has not been entered yet)
+            RingPos rp;
+            uint32_t off, size;  // the current stage's bytes
+            // constants of op k for this CTA (filled when the op is entered)
+            int n_cta, ntiles, first;
+        };
+        auto enter_op = [&](Walk &w) {   // op w.k: this CTA's first tile (or none), tile stride, stage size
+            const ChainOp &op = a.op[w.k];
+            const int me = ((int)blockIdx.x + (int)gridDim.x - op.rot) % (int)gridDim.x;
+            const int cta = me / op.n_mats;
+            w.n_cta = op.n_cta;
+            w.ntiles = (op.N + op.RP - 1) / op.RP;
+            w.first = cta < op.n_cta ? cta : w.ntiles;   // no tile at all: start past the end
+            w.size = chain_stage_bytes(op);
+        };
+        auto advance = [&](Walk &w) -> bool {   // moves to the CTA's next stage; false when there is none
+            for (;;) {
+                if (w.k >= a.n_ops) return false;
+                if (w.tile < 0) enter_op(w);
+                const int next = w.tile < 0 ? w.first : w.tile + w.n_cta;
+                if (next < w.ntiles) {
+                    w.tile = next;
+                    w.off = ring_place(w.rp, w.size, (uint32_t)a.ring_bytes);
+                    w.rp.seq++;
+                    return true;
+                }
+                w.k++;
+                w.tile = -1;
             }
+        };
+        Walk head{0, -1, {0, 0}, 0, 0, 0, 0, 0};
+        int cur_k = -1, row_bytes = 0, RPk = 0, Nk = 0;
+        const uint8_t *Wk = nullptr;
+        uint32_t vstart[TMA_MAX_STAGES];       // virtual start of stage number n at slot n % TMA_MAX_STAGES
+        uint32_t head_v = 0, prev_end = 0;     // virtual end of the newest stage; buffer offset where it ended
+        uint32_t oldest = 0, in_flight = 0;    // stages [oldest, oldest + in_flight) are in flight
+        bool ok = true;
+        while (ok && advance(head)) {
+            const uint32_t v0 = head_v + (head.off == 0 && prev_end != 0 ? (uint32_t)a.ring_bytes - prev_end : 0u);
+            const uint32_t v1 = v0 + head.size;
+            while (in_flight && (in_flight >= TMA_MAX_STAGES || v1 - vstart[oldest % TMA_MAX_STAGES] > (uint32_t)a.ring_bytes)) {
+                ok = mbar_wait(&empty_bar[oldest % TMA_MAX_STAGES], (oldest / TMA_MAX_STAGES) & 1);
+                if (!ok) break;
+                oldest++;
+                in_flight--;
+            }
+            if (!ok) break;
+            if (head.k != cur_k) {   // first stage of an op: its weight matrix and row geometry
+                cur_k = head.k;
+                const ChainOp &op = a.op[cur_k];
+                const FormatInfo fi = format_info(op.type);
+                row_bytes = (op.K / fi.block_elems) * fi.block_bytes;
+                const int me = ((int)blockIdx.x + (int)gridDim.x - op.rot) % (int)gridDim.x;
+                Wk = op.W[me % op.n_mats];
+                RPk = op.RP;
+                Nk = op.N;
+            }
+            const int row0 = head.tile * RPk;
+            const int rows = min(RPk, Nk - row0);
+            const uint32_t bytes = (uint32_t)rows * (uint32_t)row_bytes;
+            const uint32_t hs = head.rp.seq - 1;
+            mbar_arrive_expect_tx(&full_bar[hs % TMA_MAX_STAGES], bytes);
+            tma_load_1d(ring + head.off, Wk + (size_t)row0 * row_bytes, bytes, &full_bar[hs % TMA_MAX_STAGES]);
+            vstart[hs % TMA_MAX_STAGES] = v0;
+            head_v = v1;
+            prev_end = head.off + head.size;
+            in_flight++;
         }
         if (!ok) {
             atomicExch(a.status, QZ_ERR_TIMEOUT);
             // drain: copies already issued must land before this CTA's shared memory goes away
-            for (int k = 0; k < a.n_slots && k < issued; k++) {
-                const int j = issued - 1 - k;
-                mbar_wait(&full_bar[j % a.n_slots], (j / a.n_slots) & 1);
+            const uint32_t issued = head.rp.seq - 1;   // (the stage whose room was not found has not been issued)
+            for (uint32_t k = 0; k < TMA_MAX_STAGES && k < issued; k++) {
+                const uint32_t j = issued - 1 - k;
+                mbar_wait(&full_bar[j % TMA_MAX_STAGES], (j / TMA_MAX_STAGES) & 1);
             }
         }
         return;
@@ -223,89 +305,102 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
 
     // ---------------- consumers ----------------
     const int lane = threadIdx.x & 31;
-    uint8_t *xarea = ring + (size_t)a.n_slots * a.slot_bytes;
+    uint8_t *xarea = ring + (size_t)a.ring_bytes;
     RingPos rp{0, 0};
     pdl_wait();   // op 0's inputs come from the preceding kernels
     bool ok = true;
     volatile int *dead_flag = &cta_dead;
+    // an op's activation vector, converted by this CTA into its area behind the ring
+    auto convert = [&](const ChainOp &op) {
+        int8_t *sxl = (int8_t *)(xarea + op.x_off), *sxh = sxl + op.K;
+        float *sxs = (float *)(sxh + op.K), *sxsum = sxs + (op.K >> 5);
+        const XQOut o{sxl, sxh, sxs, sxsum};
+        const float *pa = op.xsrc.a, *pb = op.xsrc.b;
+        const int n4 = op.K >> 2;
+        float4 xa[XSRC_MAX_IT], xb[XSRC_MAX_IT];
+#pragma unroll
+        for (int it = 0; it < XSRC_MAX_IT; it++) {
+            const int t = it * TMA_CONSUMERS + threadIdx.x;
+            if (t < n4) {
+                xa[it] = __ldcg((const float4 *)(pa + 4 * t));
+                xb[it] = op.xsrc.mode == 3 ? xa[it] : __ldcg((const float4 *)(pb + 4 * t));
+            } else {
+                xa[it] = xb[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        float r = 1.f;
+        if (op.xsrc.mode == 1) {
+            float ss = 0.f;
+#pragma unroll
+            for (int it = 0; it < XSRC_MAX_IT; it++)
+                ss = fmaf(xa[it].x, xa[it].x, fmaf(xa[it].y, xa[it].y, fmaf(xa[it].z, xa[it].z, fmaf(xa[it].w, xa[it].w, ss))));
+            for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o2);
+            named_bar_sync(14, TMA_CONSUMERS);   // the previous conversion's partial sums have been read
+            if (lane == 0) xred[threadIdx.x >> 5] = ss;
+            named_bar_sync(14, TMA_CONSUMERS);
+            ss = 0.f;
+            for (int w = 0; w < TMA_CONSUMERS / 32; w++) ss += xred[w];
+            r = rsqrtf(ss / (float)op.K + 1e-5f);
+        }
+#pragma unroll
+        for (int it = 0; it < XSRC_MAX_IT; it++) {
+            if (it * TMA_CONSUMERS >= n4) break;   // uniform over the CTA
+            const int t = it * TMA_CONSUMERS + threadIdx.x;
+            const bool valid = t < n4;
+            const float xx[4] = {xa[it].x, xa[it].y, xa[it].z, xa[it].w}, yy[4] = {xb[it].x, xb[it].y, xb[it].z, xb[it].w};
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (op.xsrc.mode == 1) {
+                    v[i] = xx[i] * r * yy[i];
+                } else if (op.xsrc.mode == 3) {
+                    v[i] = xx[i];
+                } else if (op.xsrc.oai) {
+                    const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
+                    v[i] = __fdividef(g, 1.f + __expf(-1.702f * g)) * (up + 1.f);
+                } else {
+                    v[i] = __fdividef(xx[i], 1.f + __expf(-xx[i])) * yy[i];   // fast exp / divide: this runs redundantly in every CTA
+                }
+            }
+            quantize4_store(v, t, valid, o);
+        }
+    };
+    if (a.independent) {
+        // no op reads what another writes: every activation vector is converted up front, each into an area of
+        // its own, while the ring fills; afterwards the ops follow one another without a pause
+        for (int k = 0; k < a.n_ops; k++) convert(a.op[k]);
+        named_bar_sync(14, TMA_CONSUMERS);
+    }
+    bool pushed = false;
     for (int k = 0; k < a.n_ops; k++) {
         const ChainOp &op = a.op[k];
-        if (k > 0) {
+        if (k > 0 && !a.independent) {
             // every consumer warp arrives here, whether or not a wait of op k-1 ran out on it; afterwards the
             // whole CTA takes the same decision.  (Also: every warp has taken its activation registers, the
             // area is free.)
             named_bar_sync(13, TMA_CONSUMERS);
-            if (!a.independent) {
-                // ---- grid-wide barrier: op k-1's outputs are complete and visible ----
-                if (threadIdx.x == 0) cta_ok = (!*dead_flag && grid_barrier(a.gb, gridDim.x, a.status)) ? 1 : 0;
-                named_bar_sync(13, TMA_CONSUMERS);
-            }
+            // ---- grid-wide barrier: op k-1's outputs are complete and visible ----
+            if (threadIdx.x == 0) cta_ok = (!*dead_flag && grid_barrier(a.gb, gridDim.x, a.status)) ? 1 : 0;
+            named_bar_sync(13, TMA_CONSUMERS);
             ok = *(volatile int *)&cta_ok != 0 && !*dead_flag;
         }
-        if (!ok) break;   // uniform over the CTA's consumers
-        // ---- op k's activation vector, converted by this CTA into shared memory ----
-        int8_t *sxl = (int8_t *)xarea, *sxh = sxl + op.K;
-        float *sxs = (float *)(sxh + op.K), *sxsum = sxs + (op.K >> 5);
-        {
-            const XQOut o{sxl, sxh, sxs, sxsum};
-            const float *pa = op.xsrc.a, *pb = op.xsrc.b;
-            const int n4 = op.K >> 2;
-            float4 xa[XSRC_MAX_IT], xb[XSRC_MAX_IT];
-#pragma unroll
-            for (int it = 0; it < XSRC_MAX_IT; it++) {
-                const int t = it * TMA_CONSUMERS + threadIdx.x;
-                if (t < n4) {
-                    xa[it] = __ldcg((const float4 *)(pa + 4 * t));
-                    xb[it] = op.xsrc.mode == 3 ? xa[it] : __ldcg((const float4 *)(pb + 4 * t));
-                } else {
-                    xa[it] = xb[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-            }
-            float r = 1.f;
-            if (op.xsrc.mode == 1) {
-                float ss = 0.f;
-#pragma unroll
-                for (int it = 0; it < XSRC_MAX_IT; it++)
-                    ss = fmaf(xa[it].x, xa[it].x, fmaf(xa[it].y, xa[it].y, fmaf(xa[it].z, xa[it].z, fmaf(xa[it].w, xa[it].w, ss))));
-                for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o2);
-                if (lane == 0) xred[threadIdx.x >> 5] = ss;
-                named_bar_sync(14, TMA_CONSUMERS);
-                ss = 0.f;
-                for (int w = 0; w < TMA_CONSUMERS / 32; w++) ss += xred[w];
-                r = rsqrtf(ss / (float)op.K + 1e-5f);
-            }
-#pragma unroll
-            for (int it = 0; it < XSRC_MAX_IT; it++) {
-                if (it * TMA_CONSUMERS >= n4) break;   // uniform over the CTA
-                const int t = it * TMA_CONSUMERS + threadIdx.x;
-                const bool valid = t < n4;
-                const float xx[4] = {xa[it].x, xa[it].y, xa[it].z, xa[it].w}, yy[4] = {xb[it].x, xb[it].y, xb[it].z, xb[it].w};
-                float v[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    if (op.xsrc.mode == 1) {
-                        v[i] = xx[i] * r * yy[i];
-                    } else if (op.xsrc.mode == 3) {
-                        v[i] = xx[i];
-                    } else if (op.xsrc.oai) {
-                        const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
-                        v[i] = __fdividef(g, 1.f + __expf(-1.702f * g)) * (up + 1.f);
-                    } else {
-                        v[i] = __fdividef(xx[i], 1.f + __expf(-xx[i])) * yy[i];   // fast exp / divide: this runs redundantly in every CTA
-                    }
-                }
-                quantize4_store(v, t, valid, o);
-            }
+        if (!ok) break;   // uniform over the CTA's consumers (independent ops: a dead CTA just walks on, storing nothing)
+        if (!a.independent) {
+            convert(op);
             named_bar_sync(14, TMA_CONSUMERS);
         }
+        int8_t *sxl = (int8_t *)(xarea + op.x_off), *sxh = sxl + op.K;
+        float *sxs = (float *)(sxh + op.K), *sxsum = sxs + (op.K >> 5);
+        pushed = pushed || op.push_off >= 0;
         const XQ xq{sxl, sxh, sxs, sxsum};
-        const int m = blockIdx.x % op.n_mats, cta = blockIdx.x / op.n_mats;
+        const int me = ((int)blockIdx.x + (int)gridDim.x - op.rot) % (int)gridDim.x;
+        const int m = me % op.n_mats, cta = me / op.n_mats;
 #define QZ_CHAIN_CASE(TT, POL)                                                                                              \
     case TT:                                                                                                                \
-        ok = op.Upad == 32 ? chain_consume<POL, 1>(op, m, cta, ring, a.slot_bytes, a.n_slots, full_bar, empty_bar, part, xq, rp,  \
-                                                   a.status, dead_flag)                                                     \
-                           : chain_consume<POL, 2>(op, m, cta, ring, a.slot_bytes, a.n_slots, full_bar, empty_bar, part, xq, rp,  \
-                                                   a.status, dead_flag);                                                    \
+        ok = op.Upad == 32 ? chain_consume<POL, 1>(op, m, cta, ring, a.ring_bytes, full_bar, empty_bar, part, xq, rp,          \
+                                                   a.status, dead_flag, a.push)                                             \
+                           : chain_consume<POL, 2>(op, m, cta, ring, a.ring_bytes, full_bar, empty_bar, part, xq, rp,          \
+                                                   a.status, dead_flag, a.push);                                            \
         break;
         switch (op.type) {
             QZ_CHAIN_CASE(T_Q4_K, StreamQ4K)
@@ -317,6 +412,12 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
         // a warp whose wait ran out tells the other CTAs (they leave at their next grid barrier) and goes on to
         // this CTA's next meeting point like every other warp
         if (!ok) atomicExch(&a.gb->abort, 1);
+        if (a.independent) ok = true;   // (independent ops: walk on; a dead CTA stores nothing and does not publish)
+    }
+    if (pushed) {
+        // all of this CTA's remote stores are issued: meet, then one thread fences them and counts the CTA in
+        named_bar_sync(13, TMA_CONSUMERS);
+        if (threadIdx.x == 0 && !*dead_flag) push_publish(a.push, gridDim.x);
     }
 }
 

@@ -1326,11 +1326,12 @@ void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w,
 }
 
 // ---- a chain of dependent GEMVs as one persistent kernel ----
-static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &smem)
+static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &smem, int independent = 0,
+                       const size_t *push_off = nullptr)
 {
     if (n_ops < 1 || n_ops > CHAIN_MAX_OPS || !use_tma()) return false;
     const int grid = sm_count();
-    int slot = 0, x_bytes = 0;
+    int slot = 0, x_bytes = 0, rot = 0;
     for (int k = 0; k < n_ops; k++) {
         const qz_chain_op &o = ops[k];
         ChainOp &c = a.op[k];
@@ -1339,6 +1340,7 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         if (o.src_mode < 1 || o.src_mode > 3 || !o.d_a || (o.src_mode != 3 && !o.d_b)) return false;
         if (((uintptr_t)o.d_a & 15) || (o.src_mode != 3 && ((uintptr_t)o.d_b & 15))) return false;
         if (o.in_dim < 2048 || o.in_dim % 64 || o.in_dim / 4 > XSRC_MAX_IT * TMA_CONSUMERS) return false;
+        if (push_off && (o.n_mats != 1 || o.accumulate)) return false;
         for (int i = 0; i < o.n_mats; i++)
             if (!cuda_gemv_q_supported(o.ggml_type, o.d_w[i], o.in_dim)) return false;
         const FormatInfo fi = format_info(o.ggml_type);
@@ -1355,6 +1357,11 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         const int ntiles = (o.out_dim + c.RP - 1) / c.RP;
         const int per_mat = grid / o.n_mats;
         c.n_cta = ntiles < per_mat ? ntiles : per_mat;
+        // independent ops: op k's CTA numbering starts where op k-1's odd tiles ended, so that the CTAs that get one
+        // tile more than the others are not the same in every op (dependent ops keep the plain numbering)
+        c.rot = independent ? rot % grid : 0;
+        rot += (ntiles % c.n_cta) * o.n_mats;
+        c.push_off = push_off ? (long long)push_off[k] : -1;
         c.xsrc = XSrc{o.src_mode, o.d_a, o.src_mode == 3 ? o.d_a : o.d_b, o.oai};
         for (int i = 0; i < QZ_MAX_MATS; i++) {
             c.W[i] = o.d_w[i < o.n_mats ? i : 0];
@@ -1363,17 +1370,22 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         const int stage = c.RP * row_bytes;
         if (stage > slot) slot = stage;
         const int xb = (int)((2 * (size_t)o.in_dim + o.in_dim / 8 + o.in_dim / 4 + 31) & ~(size_t)15);
-        if (xb > x_bytes) x_bytes = xb;
+        if (independent) {   // every op's vector has an area of its own (all are converted before the first op runs)
+            c.x_off = x_bytes;
+            x_bytes += xb;
+        } else {
+            c.x_off = 0;
+            if (xb > x_bytes) x_bytes = xb;
+        }
     }
     slot = (slot + 127) & ~127;
-    const int budget = 222 * 1024 - x_bytes;
-    int n_slots = budget / slot;
-    if (n_slots > TMA_MAX_STAGES) n_slots = TMA_MAX_STAGES;
-    if (n_slots < 3) return false;
+    const int budget = (222 * 1024 - x_bytes) & ~127;
+    if (budget < 3 * slot) return false;   // the largest stage must fit the ring at least three times
     a.n_ops = n_ops;
-    a.slot_bytes = slot;
-    a.n_slots = n_slots;
-    smem = (size_t)n_slots * slot + x_bytes;
+    a.ring_bytes = budget;
+    a.independent = independent;
+    a.push.n = 0;
+    smem = (size_t)budget + x_bytes;
     return true;
 }
 
@@ -1384,17 +1396,29 @@ int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops)
     return ops && chain_plan(n_ops, ops, a, smem) ? 1 : 0;
 }
 
-static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent);
+static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent, const size_t *push_off);
 
-void cuda_gemv_chain(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 0); }
-void cuda_gemv_batch(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 1); }
+void cuda_gemv_chain(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 0, nullptr); }
+void cuda_gemv_batch(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 1, nullptr); }
 
-static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent)
+static bool fill_push(PushArgs &p, size_t dst_off, size_t elems);
+
+int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off)
+{
+    if (n_ops <= 0 || !ops || !dst_off) return 0;
+    static ChainArgs probe;   // (large: kept off the stack)
+    size_t smem = 0;
+    if (!chain_plan(n_ops, ops, probe, smem, 1, dst_off)) return 0;
+    gemv_chain_launch(n_ops, ops, 1, dst_off);
+    return 1;
+}
+
+static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent, const size_t *push_off)
 {
     if (n_ops <= 0 || !ops) return;
     static ChainArgs a;   // (large: kept off the stack)
     size_t smem = 0;
-    if (!chain_plan(n_ops, ops, a, smem)) {
+    if (!chain_plan(n_ops, ops, a, smem, independent, push_off)) {
         // not a chain the persistent kernel takes: the same GEMVs one launch at a time
         for (int k = 0; k < n_ops; k++) {
             const qz_chain_op &o = ops[k];
@@ -1408,6 +1432,12 @@ static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent
         }
         return;
     }
+    if (push_off) {
+        // every op's rows go to all ranks' windows; one publish for the whole launch
+        size_t hi = 0;
+        for (int k = 0; k < n_ops; k++) hi = std::max(hi, push_off[k] + (size_t)ops[k].out_dim);
+        if (!fill_push(a.push, 0, hi)) return;
+    }
     if (!g_grid_barrier) {
         if (cudaMalloc(&g_grid_barrier, sizeof(GridBarrier)) != cudaSuccess) {
             cudaGetLastError();
@@ -1418,7 +1448,6 @@ static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent
         cudaMemset(g_grid_barrier, 0, sizeof(GridBarrier));
     }
     a.gb = g_grid_barrier;
-    a.independent = independent;
     a.status = status_word();
     if (!a.status) return;
     static bool attr_set = false;

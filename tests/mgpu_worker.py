@@ -120,8 +120,38 @@ def main():
         ref2 = oracle.gemv(y1, wb, 14, N1, N2)
         tol2 = 1e-3 * oracle.row_norms(wb, 14, N1, N2) * float(np.linalg.norm(y1.astype(np.float64)))
         assert np.all(np.abs(y2 - ref2) <= tol2), f"rank {rank} chain y2"
-    # the NCCL form of the exchange through the C ABI: every rank computes its slice into place, ncclAllGather
+    # several independent sharded GEMVs and their exchange as ONE launch (cuda_gemv_batch_push) + one wait
     import ctypes as C
+    bcases = [(12, 4096, 14336), (14, 14336, 4096), (8, 4096, 4096), (12, 4096, 1024)]
+    ops, keep, offs, base_off = [], [], [], 300000
+    for i, (t, K, N) in enumerate(bcases):
+        w = synth.make_weights(t, K, N, tensor_id=930 + i)
+        x = synth.make_x(K, tensor_id=940 + i).reshape(-1)
+        n0, n1, per = shard_rows(N, rank, world)
+        b0, b1 = shard_bytes(t, K, N, rank, world)
+        dw = q.GpuBuf.upload(w[b0:b1])
+        L.cuda_repack_weights(t, dw.ptr, K, n1 - n0, 1)
+        dxb, dummy = q.GpuBuf.upload(x), q.GpuBuf.alloc_f32(max(n1 - n0, 1))
+        ops.append(q.chain_op(t, [dw.ptr], [dummy.ptr], K, n1 - n0, 0, 3, dxb.ptr))
+        offs.append(base_off + n0)
+        keep.append((t, K, N, w, x, dw, dxb, dummy, base_off))
+        base_off += (N + 63) & ~63
+    arr = (q.ChainOp * len(ops))(*ops)
+    off_arr = (C.c_size_t * len(ops))(*offs)
+    for rep in range(2):
+        assert L.cuda_gemv_batch_push(len(ops), arr, off_arr) == 1
+        win.wait()
+        L.cuda_sync()
+        q.check_error("batch push")
+        for (t, K, N, w, x, dw, dxb, dummy, o) in keep:
+            y = download(o, N)
+            ref = oracle.gemv(x, w, t, K, N)
+            tol = 1e-3 * oracle.row_norms(w, t, K, N) * float(np.linalg.norm(x.astype(np.float64)))
+            assert np.all(np.abs(y.astype(np.float64) - ref) <= tol), f"rank {rank} batch push {t} {K}->{N} rep {rep}"
+        if world > 1:
+            dist.barrier()   # nobody starts the next round while a slower rank still reads this one
+
+    # the NCCL form of the exchange through the C ABI: every rank computes its slice into place, ncclAllGather
     idb = C.create_string_buffer(L.quartz_nccl_id_bytes())
     if rank == 0:
         assert L.quartz_nccl_unique_id(idb) == 0, L.quartz_error_string()
