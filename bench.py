@@ -525,7 +525,7 @@ def sharded70b_section(q, L, torch, win, rank, world, dist, steps, cpu_baseline=
         out["batch1_cpu_oracle"] = {"ms": tc * 1e3, "gbs": (synth.algorithmic_bytes(12, K1, N1) +
                                                              synth.algorithmic_bytes(14, N1, N2)) / tc / 1e9,
                                     "cores": oracle.max_threads()}
-    del w1, w2
+    del w1
     L.cuda_repack_weights(12, d1.ptr, K1, a1 - a0, 1)
     L.cuda_repack_weights(14, d2.ptr, N1, b1 - b0, 1)
     total = synth.algorithmic_bytes(12, K1, N1) + synth.algorithmic_bytes(14, N1, N2)
@@ -578,6 +578,58 @@ def sharded70b_section(q, L, torch, win, rank, world, dist, steps, cpu_baseline=
                           "exchange": "peer stores from the GEMV epilogue; flag wait fused into the consumer's activation conversion"}
     if g:
         L.quartz_graph_destroy(g)
+
+    # the same pair as ONE launch per rank: both GEMVs and the exchange between them inside the persistent kernel
+    # (cuda_gemv_chain_push), one wait for the last exchange
+    import ctypes as C
+    import numpy as np
+    dummy = q.GpuBuf.alloc_f32(max(a1 - a0, b1 - b0, 1))
+    pops = [q.chain_op(12, [d1.ptr], [dummy.ptr], K1, a1 - a0, 0, 3, dx.ptr),
+            q.chain_op(14, [d2.ptr], [dummy.ptr], N1, b1 - b0, 0, 3, base + 4 * A)]
+    parr = (q.ChainOp * 2)(*pops)
+    poff = (C.c_size_t * 2)(A + a0, B + b0)
+
+    def pair_one_launch():
+        ok = L.cuda_gemv_chain_push(2, parr, poff, None)
+        win.wait()
+        return ok
+    sup = torch.tensor([1 if pair_one_launch() else 0], device="cuda")
+    if world > 1:
+        dist.all_reduce(sup, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    q.check_error("sharded pair, one launch")
+    if int(sup.item()) == 1:
+        fn, g = pair_one_launch, None
+        if L.quartz_graph_begin():
+            pair_one_launch()
+            g = L.quartz_graph_end()
+            q.check_error("sharded pair graph capture")
+            if g:
+                fn = lambda: L.quartz_graph_launch(g)   # noqa: E731
+        ms = timed(fn, n)
+        out["batch1_one_launch"] = {"ms": ms, "gbs": total / (ms * 1e-3) / 1e9, "launch": "graph replay" if g else "eager",
+                                    "launches_per_step": 2,
+                                    "exchange": "cuda_gemv_chain_push: both GEMVs in one persistent kernel per rank; the first "
+                                                "exchange is published and polled inside the kernel, the second completed by one wait"}
+        if g:
+            L.quartz_graph_destroy(g)
+        if rank == 0:
+            # what was just timed, against the CPU oracle: the second GEMV of the complete first output
+            import oracle
+            from saient_quartz_b200.iq_tables import load_tables
+            oracle.set_tables(load_tables())
+            h = np.empty(N1, dtype=np.float32)
+            y = np.empty(N2, dtype=np.float32)
+            L.cuda_d2h(h.ctypes.data, base + 4 * A, 4 * N1)
+            L.cuda_d2h(y.ctypes.data, base + 4 * B, 4 * N2)
+            ref = oracle.gemv(h, w2, 14, N1, N2)
+            assert np.all(np.abs(y - ref) <= oracle.tolerance(w2, 14, N1, N2, h)), "sharded one-launch pair failed the parity bound"
+            out["batch1_one_launch"]["parity"] = "second GEMV of the gathered first output within the oracle bound"
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()   # the other ranks must not start the next exchange while rank 0 is still in the oracle
+    del w2
+    dummy.drop()
 
     if world > 1:
         y1 = torch.zeros(per1 * world, dtype=torch.float32, device="cuda")

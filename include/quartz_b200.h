@@ -418,6 +418,17 @@ void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size
  * one launch, one conversion and one publish per GEMV.  Returns 1 if launched, 0 if the persistent kernel does not
  * take these ops (nothing was launched: use cuda_gemv_push per op). */
 int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off);
+/* A chain of DEPENDENT row-sharded GEMVs with the exchanges inside one persistent kernel per rank (a whole sharded
+ * FFN: gate/up shards -> exchange -> SwiGLU -> down shard -> exchange, as one launch).  Op k's rows go to every
+ * rank's window: matrix i of the op at element offset dst_off[k] + i * dst_stride[k] (+ row); dst_stride may be NULL
+ * when every op has one matrix.  Between op k and op k+1 the kernel publishes the exchange and polls, bounded
+ * (~0.5 s, QZ_ERR_TIMEOUT), until every rank has published as many exchanges; op k+1's activation source
+ * (d_a / d_b, normally addresses inside quartz_mgpu_data()) is read after that.  The last op's exchange is published
+ * at the kernel's end and completed by quartz_mgpu_wait() like any other.  Every rank must run the same chain; the
+ * ranks must be on different GPUs (a kernel that waits for another rank's kernel never shares a GPU with it).
+ * No counterpart in the reference (single GPU).  Returns 1 if launched, 0 if the persistent kernel does not take
+ * these ops (nothing was launched: use cuda_gemv_push per op with a wait between them). */
+int cuda_gemv_chain_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off, const size_t *dst_stride);
 void quartz_mgpu_wait(void);
 void quartz_mgpu_fuse_next_wait(void);
 void quartz_mgpu_shutdown(void);

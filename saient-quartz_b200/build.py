@@ -52,6 +52,7 @@ def build(force=False, verbose=False):
     cc = arch.replace("sm_", "compute_")
     cmd = [nvcc, "-O3", "-std=c++17", "-gencode", f"arch={cc},code={arch}", "-lineinfo", "-Xcompiler", "-fPIC", "-c",
            "-o", OBJ] + [s for s in sources() if s.endswith(".cu")]
+    cmd += os.environ.get("QUARTZ_NVCC_FLAGS", "").split()   # extra compiler flags (e.g. -DNAME=value)
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -74,8 +74,23 @@ __host__ __device__ inline size_t attn_step_smem(int G, int CL, int head_dim, in
                             AS_WARPS * 32 + (size_t)AS_WARPS * 2 * (ATT_MAX_HD + 2) + (size_t)CL * (2 * G + S) + ATT_MAX_HD);
 }
 
+#ifdef QZ_CHAIN_TRACE
+__device__ unsigned long long g_attn_trace[160][16];
+__device__ __forceinline__ void attn_mark(int slot)
+{
+    if (threadIdx.x == 0 && blockIdx.x < 160) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_attn_trace[blockIdx.x][slot] = t;
+    }
+}
+#define AT_MARK(s) attn_mark(s)
+#else
+#define AT_MARK(s)
+#endif
 __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArgs a)
 {
+    AT_MARK(0);
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int CL = (int)cluster.num_blocks();
@@ -138,9 +153,11 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
     }
     pdl_trigger();
     __syncthreads();
+    AT_MARK(1);
 
     // ---- 2. the new token's q, k, v ----
     pdl_wait();
+    AT_MARK(2);
     const size_t tok_off = a.prompt ? (size_t)blockIdx.y * a.n_heads * hd : 0;
     for (int idx = threadIdx.x; idx < G * half; idx += AS_THREADS) {
         const int g = idx / half, i = idx - g * half;
@@ -192,6 +209,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
         }
         cp_async_wait_all();
         __syncthreads();
+        AT_MARK(3);
         if (!warp_active) continue;
         // ---- 3. online softmax over this warp's 32-row groups ----
         for (int t_lo = 32 * sub; t_lo < n; t_lo += 32 * wph) {
@@ -247,6 +265,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
 
     // ---- this CTA's partial per head: the warps that shared a head leave theirs in shared memory ----
     __syncthreads();
+    AT_MARK(4);
     if (warp_active) {
 #pragma unroll
         for (int r = 0; r < 2; r++) {
@@ -264,6 +283,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
     // ---- 4. push the partials to the CTAs that finish them: destination d gets, in its recv[rank], this CTA's
     //         (max, sum) of every head followed by its part of d's S outputs ----
     cluster_wait();   // (arrived at the top) every CTA of the cluster has started
+    AT_MARK(5);
     for (int idx = threadIdx.x; idx < G * hd + 2 * G * CL; idx += AS_THREADS) {
         int dst, off;
         float val;
@@ -300,6 +320,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
     }
     cluster_arrive();
     cluster_wait();   // every push has landed; nobody touches another CTA's shared memory afterwards
+    AT_MARK(6);
 
     // ---- merge: this CTA's S outputs from the CL partials it received ----
     for (int j = threadIdx.x; j < S; j += AS_THREADS) {
@@ -327,6 +348,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
             quantize4_store(v, (first >> 2) + (lane & 7), lane < 8, a.o);
         }
     }
+    AT_MARK(7);
 }
 
 }  // namespace qz

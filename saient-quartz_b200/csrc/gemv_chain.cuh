@@ -38,9 +38,25 @@ struct ChainOp {
     int n_cta;              // CTAs per matrix (grid / n_mats, at most the tile count)
     int rot;                // the op's CTA numbering starts at this CTA (spreads the ops' odd tiles over the grid)
     int x_off;              // byte offset of the op's converted activation vector behind the ring
-    long long push_off;     // >= 0: rows go to every rank's window at this offset (n_mats = 1) instead of y
+    long long push_off;     // >= 0: rows go to every rank's window instead of y: matrix m at push_off + m * push_stride
+    long long push_stride;
     XSrc xsrc;              // mode 1 (RMSNorm), 2 (SwiGLU) or 3 (plain f32 vector a)
 };
+
+#ifdef QZ_CHAIN_TRACE
+__device__ unsigned long long g_chain_trace[160][32];
+__device__ __forceinline__ void chain_mark(int slot)
+{
+    if (threadIdx.x == 0 && slot < 32) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_chain_trace[blockIdx.x][slot] = t;
+    }
+}
+#define QZ_MARK(s) chain_mark(s)
+#else
+#define QZ_MARK(s)
+#endif
 
 struct GridBarrier {
     int count, gen, abort;
@@ -50,6 +66,8 @@ struct ChainArgs {
     ChainOp op[CHAIN_MAX_OPS];
     int n_ops;
     int independent;           // 1: no op reads another op's output: no grid barrier between them
+    int exchange;              // 1 (dependent ops that push): between two ops the ranks exchange instead of the grid
+                               // barrier: every CTA counts in, the last one publishes, every CTA polls all ranks' flags
     int ring_bytes;            // the circular byte buffer (a multiple of 128; every stage fits at least three times)
     GridBarrier *gb;
     int *status;
@@ -167,7 +185,7 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
         auto store_y = [&](int row, float v) {
             if (*cta_dead) return;   // a warp of this CTA gave up: its rows are incomplete
             if (op.push_off >= 0) {
-                for (int rk = 0; rk < push.n; rk++) push.data[rk][op.push_off + row] = v;
+                for (int rk = 0; rk < push.n; rk++) push.data[rk][op.push_off + m * op.push_stride + row] = v;
             } else {
                 y[row] = op.accumulate ? __ldcg(y + row) + v : v;
             }
@@ -307,7 +325,9 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     const int lane = threadIdx.x & 31;
     uint8_t *xarea = ring + (size_t)a.ring_bytes;
     RingPos rp{0, 0};
+    QZ_MARK(0);
     pdl_wait();   // op 0's inputs come from the preceding kernels
+    QZ_MARK(1);
     bool ok = true;
     volatile int *dead_flag = &cta_dead;
     // an op's activation vector, converted by this CTA into its area behind the ring
@@ -317,52 +337,57 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
         const XQOut o{sxl, sxh, sxs, sxsum};
         const float *pa = op.xsrc.a, *pb = op.xsrc.b;
         const int n4 = op.K >> 2;
-        float4 xa[XSRC_MAX_IT], xb[XSRC_MAX_IT];
+        // The vector is taken in pieces of XSRC_MAX_IT float4 per thread; all loads of a piece are issued before
+        // anything is computed.  RMSNorm needs the whole vector's sum of squares first: the host only plans it for
+        // vectors of one piece.
+        for (int base = 0; base < n4; base += XSRC_MAX_IT * TMA_CONSUMERS) {
+            float4 xa[XSRC_MAX_IT], xb[XSRC_MAX_IT];
 #pragma unroll
-        for (int it = 0; it < XSRC_MAX_IT; it++) {
-            const int t = it * TMA_CONSUMERS + threadIdx.x;
-            if (t < n4) {
-                xa[it] = __ldcg((const float4 *)(pa + 4 * t));
-                xb[it] = op.xsrc.mode == 3 ? xa[it] : __ldcg((const float4 *)(pb + 4 * t));
-            } else {
-                xa[it] = xb[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-        float r = 1.f;
-        if (op.xsrc.mode == 1) {
-            float ss = 0.f;
-#pragma unroll
-            for (int it = 0; it < XSRC_MAX_IT; it++)
-                ss = fmaf(xa[it].x, xa[it].x, fmaf(xa[it].y, xa[it].y, fmaf(xa[it].z, xa[it].z, fmaf(xa[it].w, xa[it].w, ss))));
-            for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o2);
-            named_bar_sync(14, TMA_CONSUMERS);   // the previous conversion's partial sums have been read
-            if (lane == 0) xred[threadIdx.x >> 5] = ss;
-            named_bar_sync(14, TMA_CONSUMERS);
-            ss = 0.f;
-            for (int w = 0; w < TMA_CONSUMERS / 32; w++) ss += xred[w];
-            r = rsqrtf(ss / (float)op.K + 1e-5f);
-        }
-#pragma unroll
-        for (int it = 0; it < XSRC_MAX_IT; it++) {
-            if (it * TMA_CONSUMERS >= n4) break;   // uniform over the CTA
-            const int t = it * TMA_CONSUMERS + threadIdx.x;
-            const bool valid = t < n4;
-            const float xx[4] = {xa[it].x, xa[it].y, xa[it].z, xa[it].w}, yy[4] = {xb[it].x, xb[it].y, xb[it].z, xb[it].w};
-            float v[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                if (op.xsrc.mode == 1) {
-                    v[i] = xx[i] * r * yy[i];
-                } else if (op.xsrc.mode == 3) {
-                    v[i] = xx[i];
-                } else if (op.xsrc.oai) {
-                    const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
-                    v[i] = __fdividef(g, 1.f + __expf(-1.702f * g)) * (up + 1.f);
+            for (int it = 0; it < XSRC_MAX_IT; it++) {
+                const int t = base + it * TMA_CONSUMERS + threadIdx.x;
+                if (t < n4) {
+                    xa[it] = __ldcg((const float4 *)(pa + 4 * t));
+                    xb[it] = op.xsrc.mode == 3 ? xa[it] : __ldcg((const float4 *)(pb + 4 * t));
                 } else {
-                    v[i] = __fdividef(xx[i], 1.f + __expf(-xx[i])) * yy[i];   // fast exp / divide: this runs redundantly in every CTA
+                    xa[it] = xb[it] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
-            quantize4_store(v, t, valid, o);
+            float r = 1.f;
+            if (op.xsrc.mode == 1) {
+                float ss = 0.f;
+#pragma unroll
+                for (int it = 0; it < XSRC_MAX_IT; it++)
+                    ss = fmaf(xa[it].x, xa[it].x, fmaf(xa[it].y, xa[it].y, fmaf(xa[it].z, xa[it].z, fmaf(xa[it].w, xa[it].w, ss))));
+                for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o2);
+                named_bar_sync(14, TMA_CONSUMERS);   // the previous conversion's partial sums have been read
+                if (lane == 0) xred[threadIdx.x >> 5] = ss;
+                named_bar_sync(14, TMA_CONSUMERS);
+                ss = 0.f;
+                for (int w = 0; w < TMA_CONSUMERS / 32; w++) ss += xred[w];
+                r = rsqrtf(ss / (float)op.K + 1e-5f);
+            }
+#pragma unroll
+            for (int it = 0; it < XSRC_MAX_IT; it++) {
+                if (base + it * TMA_CONSUMERS >= n4) break;   // uniform over the CTA
+                const int t = base + it * TMA_CONSUMERS + threadIdx.x;
+                const bool valid = t < n4;
+                const float xx[4] = {xa[it].x, xa[it].y, xa[it].z, xa[it].w}, yy[4] = {xb[it].x, xb[it].y, xb[it].z, xb[it].w};
+                float v[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (op.xsrc.mode == 1) {
+                        v[i] = xx[i] * r * yy[i];
+                    } else if (op.xsrc.mode == 3) {
+                        v[i] = xx[i];
+                    } else if (op.xsrc.oai) {
+                        const float g = fminf(xx[i], 7.f), up = fmaxf(-7.f, fminf(7.f, yy[i]));
+                        v[i] = __fdividef(g, 1.f + __expf(-1.702f * g)) * (up + 1.f);
+                    } else {
+                        v[i] = __fdividef(xx[i], 1.f + __expf(-xx[i])) * yy[i];   // fast exp / divide: this runs redundantly in every CTA
+                    }
+                }
+                quantize4_store(v, t, valid, o);
+            }
         }
     };
     if (a.independent) {
@@ -371,27 +396,62 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
         for (int k = 0; k < a.n_ops; k++) convert(a.op[k]);
         named_bar_sync(14, TMA_CONSUMERS);
     }
-    bool pushed = false;
+    bool unpublished = false;   // an op has pushed rows that no publish has covered yet
+    // exchanges this rank had published when the kernel started (read after the wait above: the previous kernel's
+    // publish is then complete; this kernel's first publish needs every CTA, this one included, to finish op 0)
+    const int push_base = a.exchange ? *(volatile const int *)&a.push.ctrl[a.push.rank]->pushes : 0;
     for (int k = 0; k < a.n_ops; k++) {
         const ChainOp &op = a.op[k];
+        QZ_MARK(2 + 4 * k);
         if (k > 0 && !a.independent) {
             // every consumer warp arrives here, whether or not a wait of op k-1 ran out on it; afterwards the
             // whole CTA takes the same decision.  (Also: every warp has taken its activation registers, the
             // area is free.)
             named_bar_sync(13, TMA_CONSUMERS);
-            // ---- grid-wide barrier: op k-1's outputs are complete and visible ----
-            if (threadIdx.x == 0) cta_ok = (!*dead_flag && grid_barrier(a.gb, gridDim.x, a.status)) ? 1 : 0;
+            if (!a.exchange) {
+                // ---- grid-wide barrier: op k-1's outputs are complete and visible ----
+                if (threadIdx.x == 0) cta_ok = (!*dead_flag && grid_barrier(a.gb, gridDim.x, a.status)) ? 1 : 0;
+            } else {
+                // ---- exchange: op k-1's rows sit in every rank's window once every rank has published ----
+                // This CTA counts in (the last CTA of the rank publishes); then lanes 0..n-1 poll this rank's flag
+                // words until every rank has published k exchanges more than it had when the kernel started.  The
+                // poll doubles as the grid barrier (this rank's own flag is one of them).  Bounded like every wait.
+                if (threadIdx.x == 0) {
+                    cta_ok = 1;
+                    if (!*dead_flag) push_publish(a.push, gridDim.x);
+                }
+                unpublished = false;
+                if ((int)threadIdx.x < 32) {
+                    bool fine = true;
+                    if ((int)threadIdx.x < a.push.n) {
+                        const MgpuCtrl *mine = a.push.ctrl[a.push.rank];
+                        const int expected = push_base + k;
+                        const long long t0 = clock64();
+                        while (ld_acquire_sys(&mine->flags[threadIdx.x]) - expected < 0) {
+                            if (clock64() - t0 > MGPU_WAIT_CYCLES) {
+                                atomicExch(a.status, QZ_ERR_TIMEOUT);
+                                fine = false;
+                                break;
+                            }
+                            __nanosleep(32);
+                        }
+                    }
+                    if (!__all_sync(0xFFFFFFFFu, fine) && lane == 0) cta_ok = 0;
+                }
+            }
             named_bar_sync(13, TMA_CONSUMERS);
             ok = *(volatile int *)&cta_ok != 0 && !*dead_flag;
         }
         if (!ok) break;   // uniform over the CTA's consumers (independent ops: a dead CTA just walks on, storing nothing)
+        QZ_MARK(3 + 4 * k);
         if (!a.independent) {
             convert(op);
             named_bar_sync(14, TMA_CONSUMERS);
         }
+        QZ_MARK(4 + 4 * k);
         int8_t *sxl = (int8_t *)(xarea + op.x_off), *sxh = sxl + op.K;
         float *sxs = (float *)(sxh + op.K), *sxsum = sxs + (op.K >> 5);
-        pushed = pushed || op.push_off >= 0;
+        unpublished = unpublished || op.push_off >= 0;
         const XQ xq{sxl, sxh, sxs, sxsum};
         const int me = ((int)blockIdx.x + (int)gridDim.x - op.rot) % (int)gridDim.x;
         const int m = me % op.n_mats, cta = me / op.n_mats;
@@ -409,12 +469,13 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
         default: ok = false; break;
         }
 #undef QZ_CHAIN_CASE
+        QZ_MARK(5 + 4 * k);
         // a warp whose wait ran out tells the other CTAs (they leave at their next grid barrier) and goes on to
         // this CTA's next meeting point like every other warp
         if (!ok) atomicExch(&a.gb->abort, 1);
         if (a.independent) ok = true;   // (independent ops: walk on; a dead CTA stores nothing and does not publish)
     }
-    if (pushed) {
+    if (unpublished) {
         // all of this CTA's remote stores are issued: meet, then one thread fences them and counts the CTA in
         named_bar_sync(13, TMA_CONSUMERS);
         if (threadIdx.x == 0 && !*dead_flag) push_publish(a.push, gridDim.x);

@@ -1327,7 +1327,7 @@ void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w,
 
 // ---- a chain of dependent GEMVs as one persistent kernel ----
 static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &smem, int independent = 0,
-                       const size_t *push_off = nullptr)
+                       const size_t *push_off = nullptr, const size_t *push_stride = nullptr)
 {
     if (n_ops < 1 || n_ops > CHAIN_MAX_OPS || !use_tma()) return false;
     const int grid = sm_count();
@@ -1339,8 +1339,10 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         if (o.n_mats < 1 || o.n_mats > QZ_MAX_MATS || o.n_mats > grid || o.out_dim <= 0) return false;
         if (o.src_mode < 1 || o.src_mode > 3 || !o.d_a || (o.src_mode != 3 && !o.d_b)) return false;
         if (((uintptr_t)o.d_a & 15) || (o.src_mode != 3 && ((uintptr_t)o.d_b & 15))) return false;
-        if (o.in_dim < 2048 || o.in_dim % 64 || o.in_dim / 4 > XSRC_MAX_IT * TMA_CONSUMERS) return false;
-        if (push_off && (o.n_mats != 1 || o.accumulate)) return false;
+        if (o.in_dim < 2048 || o.in_dim % 64) return false;
+        if (o.src_mode == 1 && o.in_dim / 4 > XSRC_MAX_IT * TMA_CONSUMERS) return false;   // RMSNorm: one piece only
+        if (push_off && ((o.n_mats != 1 && !push_stride) || o.accumulate)) return false;
+        if (push_off && push_stride && o.n_mats > 1 && push_stride[k] < (size_t)o.out_dim) return false;
         for (int i = 0; i < o.n_mats; i++)
             if (!cuda_gemv_q_supported(o.ggml_type, o.d_w[i], o.in_dim)) return false;
         const FormatInfo fi = format_info(o.ggml_type);
@@ -1362,6 +1364,7 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         c.rot = independent ? rot % grid : 0;
         rot += (ntiles % c.n_cta) * o.n_mats;
         c.push_off = push_off ? (long long)push_off[k] : -1;
+        c.push_stride = push_off && push_stride ? (long long)push_stride[k] : 0;
         c.xsrc = XSrc{o.src_mode, o.d_a, o.src_mode == 3 ? o.d_a : o.d_b, o.oai};
         for (int i = 0; i < QZ_MAX_MATS; i++) {
             c.W[i] = o.d_w[i < o.n_mats ? i : 0];
@@ -1384,6 +1387,7 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
     a.n_ops = n_ops;
     a.ring_bytes = budget;
     a.independent = independent;
+    a.exchange = (!independent && push_off) ? 1 : 0;
     a.push.n = 0;
     smem = (size_t)budget + x_bytes;
     return true;
@@ -1396,12 +1400,18 @@ int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops)
     return ops && chain_plan(n_ops, ops, a, smem) ? 1 : 0;
 }
 
-static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent, const size_t *push_off);
+static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent, const size_t *push_off,
+                              const size_t *push_stride = nullptr);
 
+#ifdef QZ_CHAIN_TRACE
+extern "C" void quartz_chain_trace_read(void *host) { cudaMemcpyFromSymbol(host, g_chain_trace, sizeof(g_chain_trace)); }
+extern "C" void quartz_attn_trace_read(void *host) { cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(g_attn_trace)); }
+#endif
 void cuda_gemv_chain(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 0, nullptr); }
 void cuda_gemv_batch(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 1, nullptr); }
 
 static bool fill_push(PushArgs &p, size_t dst_off, size_t elems);
+static bool mgpu_is_attached();
 
 int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off)
 {
@@ -1413,12 +1423,28 @@ int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_of
     return 1;
 }
 
-static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent, const size_t *push_off)
+int cuda_gemv_chain_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off, const size_t *dst_stride)
+{
+    if (n_ops <= 0 || !ops || !dst_off) return 0;
+    if (!mgpu_is_attached()) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_gemv_chain_push: the windows are not attached (quartz_mgpu_init / quartz_mgpu_attach)");
+        return 0;
+    }
+    static ChainArgs probe;   // (large: kept off the stack)
+    size_t smem = 0;
+    if (!chain_plan(n_ops, ops, probe, smem, 0, dst_off, dst_stride)) return 0;
+    gemv_chain_launch(n_ops, ops, 0, dst_off, dst_stride);
+    return 1;
+}
+
+static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent, const size_t *push_off,
+                              const size_t *push_stride)
 {
     if (n_ops <= 0 || !ops) return;
     static ChainArgs a;   // (large: kept off the stack)
     size_t smem = 0;
-    if (!chain_plan(n_ops, ops, a, smem, independent, push_off)) {
+    if (!chain_plan(n_ops, ops, a, smem, independent, push_off, push_stride)) {
+        if (push_off) return;   // (the push entry points have checked the plan already)
         // not a chain the persistent kernel takes: the same GEMVs one launch at a time
         for (int k = 0; k < n_ops; k++) {
             const qz_chain_op &o = ops[k];
@@ -1435,7 +1461,8 @@ static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent
     if (push_off) {
         // every op's rows go to all ranks' windows; one publish for the whole launch
         size_t hi = 0;
-        for (int k = 0; k < n_ops; k++) hi = std::max(hi, push_off[k] + (size_t)ops[k].out_dim);
+        for (int k = 0; k < n_ops; k++)
+            hi = std::max(hi, push_off[k] + (push_stride ? push_stride[k] * (size_t)(ops[k].n_mats - 1) : 0) + (size_t)ops[k].out_dim);
         if (!fill_push(a.push, 0, hi)) return;
     }
     if (!g_grid_barrier) {
@@ -2243,6 +2270,8 @@ int quartz_mgpu_attach(const void *handles)
 }
 
 float *quartz_mgpu_data(void) { return g_win ? (float *)(g_win + MGPU_CTRL_BYTES) : nullptr; }
+
+static bool mgpu_is_attached() { return g_mg_attached; }
 
 static bool fill_push(PushArgs &p, size_t dst_off, size_t elems)
 {

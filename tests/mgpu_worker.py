@@ -151,6 +151,44 @@ def main():
         if world > 1:
             dist.barrier()   # nobody starts the next round while a slower rank still reads this one
 
+    # a whole row-sharded FFN as ONE launch per rank (cuda_gemv_chain_push): gate/up shards -> exchange inside the
+    # kernel -> SwiGLU of the complete vectors -> down shard -> exchange, one wait at the end
+    Kf, Ff = 4096, 14336
+    OFFG, OFFO = 400000, 440000
+    wg, wu = synth.make_weights(12, Kf, Ff, tensor_id=950), synth.make_weights(12, Kf, Ff, tensor_id=951)
+    wd = synth.make_weights(14, Ff, Kf, tensor_id=952)
+    xf = synth.make_x(Kf, tensor_id=953).reshape(-1)
+    f0, f1, _ = shard_rows(Ff, rank, world)
+    k0, k1, _ = shard_rows(Kf, rank, world)
+    gb0, gb1 = shard_bytes(12, Kf, Ff, rank, world)
+    db0, db1 = shard_bytes(14, Ff, Kf, rank, world)
+    dwg, dwu, dwd = q.GpuBuf.upload(wg[gb0:gb1]), q.GpuBuf.upload(wu[gb0:gb1]), q.GpuBuf.upload(wd[db0:db1])
+    L.cuda_repack_weights(12, dwg.ptr, Kf, f1 - f0, 1)
+    L.cuda_repack_weights(12, dwu.ptr, Kf, f1 - f0, 1)
+    L.cuda_repack_weights(14, dwd.ptr, Ff, k1 - k0, 1)
+    dxf, dumf = q.GpuBuf.upload(xf), q.GpuBuf.alloc_f32(Ff)
+    fops = [q.chain_op(12, [dwg.ptr, dwu.ptr], [dumf.ptr, dumf.ptr], Kf, f1 - f0, 0, 3, dxf.ptr),
+            q.chain_op(14, [dwd.ptr], [dumf.ptr], Ff, k1 - k0, 0, 2, win.data_ptr + 4 * OFFG, win.data_ptr + 4 * (OFFG + Ff))]
+    farr = (q.ChainOp * 2)(*fops)
+    foff = (C.c_size_t * 2)(OFFG + f0, OFFO + k0)
+    fstr = (C.c_size_t * 2)(Ff, 0)
+    for rep in range(2):
+        assert L.cuda_gemv_chain_push(2, farr, foff, fstr) == 1, L.quartz_error_string()
+        win.wait()
+        L.cuda_sync()
+        q.check_error("chain push")
+        g, u, out = download(OFFG, Ff), download(OFFG + Ff, Ff), download(OFFO, Kf)
+        xn = float(np.linalg.norm(xf.astype(np.float64)))
+        for got, w in ((g, wg), (u, wu)):
+            ref = oracle.gemv(xf, w, 12, Kf, Ff)
+            assert np.all(np.abs(got.astype(np.float64) - ref) <= 1e-3 * oracle.row_norms(w, 12, Kf, Ff) * xn), f"rank {rank} chain push gate/up rep {rep}"
+        h = (g.astype(np.float64) / (1.0 + np.exp(-g.astype(np.float64))) * u.astype(np.float64)).astype(np.float32)
+        ref = oracle.gemv(h, wd, 14, Ff, Kf)
+        told = 1e-3 * oracle.row_norms(wd, 14, Ff, Kf) * float(np.linalg.norm(h.astype(np.float64)))
+        assert np.all(np.abs(out.astype(np.float64) - ref) <= told), f"rank {rank} chain push down rep {rep}"
+        if world > 1:
+            dist.barrier()
+
     # the NCCL form of the exchange through the C ABI: every rank computes its slice into place, ncclAllGather
     idb = C.create_string_buffer(L.quartz_nccl_id_bytes())
     if rank == 0:
