@@ -206,6 +206,13 @@ void cuda_attn_decode(float *out, const float *q, const float *k_cache, const fl
  *                          partial results through distributed shared memory.  head_dim a multiple of 32 up to
  *                          128, at most 16 query heads per kv head (cuda_attn_step_supported tells). */
 void cuda_step_set(int *d_step, int token, int pos);
+/* Registers a RoPE parameter set for a pair of step words: from then on cuda_step_set(d_step, ...) also writes the
+ * (cos, sin) of every rotation pair at the new position, in the same launch as the words, and cuda_attn_step calls
+ * with this d_step and these parameters read that table (after checking that it was written for the position in
+ * d_step[1]) instead of computing sin / cos in every CTA of every layer; the values are the same either way.  At
+ * most 4 sets per d_step.  Allocates: call it when the model is built, outside a graph recording.  No counterpart
+ * in the reference (cuda_rope_yarn computes sin / cos per call, src/cuda_kernels.cu:588-620). */
+void cuda_step_rope_table(int *d_step, int head_dim, float theta, float yarn_scale, int yarn_orig_ctx);
 void cuda_embed_lookup_dev(float *out, const uint8_t *data, uint32_t ggml_type, const int *d_step, int embed_dim);
 int cuda_attn_step_supported(int n_heads, int n_kv_heads, int head_dim);
 void cuda_attn_step(float *out, const float *q, const float *k_new, const float *v_new, float *k_cache, float *v_cache,

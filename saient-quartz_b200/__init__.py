@@ -96,6 +96,7 @@ _SIGS = {
     "cuda_attn_block": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int]),
     "cuda_step_set": (None, [C.c_void_p, C.c_int, C.c_int]),
+    "cuda_step_rope_table": (None, [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_int]),
     "cuda_embed_lookup_dev": (None, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_int]),
     "cuda_attn_step_supported": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "cuda_attn_step": (None, [C.c_void_p] * 6 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int,

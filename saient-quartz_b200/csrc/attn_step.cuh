@@ -52,6 +52,9 @@ struct AttnStepArgs {
     // [n, n_heads*head_dim]; q is ALREADY rotated and every token's k, v are ALREADY in the caches (appended by
     // the kernel before this one, so nothing is read ahead of the dependency wait); causal: keys up to pos.
     int prompt;
+    // (cos, sin) per rotation pair of the step's position, written together with the step words (or NULL):
+    // entries [0, head_dim/2), and the position they were computed for, as an int, in entry [ATT_MAX_HD/2].x
+    const float2 *rope_tab;
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
@@ -74,23 +77,8 @@ __host__ __device__ inline size_t attn_step_smem(int G, int CL, int head_dim, in
                             AS_WARPS * 32 + (size_t)AS_WARPS * 2 * (ATT_MAX_HD + 2) + (size_t)CL * (2 * G + S) + ATT_MAX_HD);
 }
 
-#ifdef QZ_CHAIN_TRACE
-__device__ unsigned long long g_attn_trace[160][16];
-__device__ __forceinline__ void attn_mark(int slot)
-{
-    if (threadIdx.x == 0 && blockIdx.x < 160) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_attn_trace[blockIdx.x][slot] = t;
-    }
-}
-#define AT_MARK(s) attn_mark(s)
-#else
-#define AT_MARK(s)
-#endif
 __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArgs a)
 {
-    AT_MARK(0);
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int CL = (int)cluster.num_blocks();
@@ -119,7 +107,11 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
     // ---- 1. everything that does not depend on the kernel before this one ----
     // (the position words are written by a launch that precedes the whole recorded step)
     if (a.prompt) pdl_wait();
-    int pos = a.prompt ? a.pos_host + (int)blockIdx.y : (a.step ? a.step[1] : a.pos_host);
+    // the three small loads go out together, ahead of the burst of row copies (the load/store unit works in order)
+    int pos = a.prompt ? a.pos_host + (int)blockIdx.y : (a.step ? __ldcg(a.step + 1) : a.pos_host);
+    const bool tab_lane = a.rope_tab && (int)threadIdx.x < (a.head_dim >> 1);
+    const int tab_pos = tab_lane ? __float_as_int(__ldcg(&a.rope_tab[ATT_MAX_HD / 2].x)) : -1;
+    const float2 tab_cs = tab_lane ? __ldcg(&a.rope_tab[threadIdx.x]) : make_float2(1.f, 0.f);
     if (pos >= a.max_seq) pos = a.max_seq - 1;   // never write past the caches (src/cuda.rs:517-520)
     if (pos < 0) pos = 0;
     const int k_start = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
@@ -132,12 +124,23 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
     const bool owns_new = !a.prompt && bcnt > 0 && p_hi == seq_len;
     const float *kc = a.k_cache + (size_t)k_start * a.kv_dim + (size_t)kvh * hd;
     const float *vc = a.v_cache + (size_t)k_start * a.kv_dim + (size_t)kvh * hd;
-    auto stage_rows = [&](int c0, int n_old) {   // cached rows [c0, c0 + n_old) -> shared rows 0 ..
-        for (int idx = threadIdx.x; idx < n_old * hd4; idx += AS_THREADS) {
-            const int t = idx / hd4, c = idx - t * hd4;
-            const size_t g = (size_t)(c0 + t) * a.kv_dim + 4 * c;
-            cp_async16(ks + t * AS_KS_STRIDE + 4 * c, kc + g);
-            cp_async16(vs + t * ATT_MAX_HD + 4 * c, vc + g);
+    // cached rows [c0, c0 + n_old) -> shared rows 0 ..: 16-byte asynchronous copies.  A thread keeps its column and
+    // steps through the rows when the row length divides the block (head_dim 32, 64, 128): no division per copy.
+    auto stage_rows = [&](int c0, int n_old) {
+        if (AS_THREADS % hd4 == 0) {
+            const int c = threadIdx.x % hd4, dt = AS_THREADS / hd4;
+            const float *kp = kc + (size_t)c0 * a.kv_dim + 4 * c, *vp = vc + (size_t)c0 * a.kv_dim + 4 * c;
+            for (int t = threadIdx.x / hd4; t < n_old; t += dt) {
+                cp_async16(ks + t * AS_KS_STRIDE + 4 * c, kp + (size_t)t * a.kv_dim);
+                cp_async16(vs + t * ATT_MAX_HD + 4 * c, vp + (size_t)t * a.kv_dim);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < n_old * hd4; idx += AS_THREADS) {
+                const int t = idx / hd4, c = idx - t * hd4;
+                const size_t g = (size_t)(c0 + t) * a.kv_dim + 4 * c;
+                cp_async16(ks + t * AS_KS_STRIDE + 4 * c, kc + g);
+                cp_async16(vs + t * ATT_MAX_HD + 4 * c, vc + g);
+            }
         }
     };
     {
@@ -146,18 +149,21 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
         stage_rows(p_lo, has_new ? n - 1 : n);
     }
     if (threadIdx.x < half) {
-        const RopeArgs r{pos, a.theta, a.yarn_scale, a.yarn_orig_ctx, a.neox};
-        float c, s;
-        rope_cs(r, threadIdx.x, hd, c, s);
-        cs_tab[threadIdx.x] = make_float2(c, s);
+        // the table written with the step words, when it is for this very position; computed here otherwise
+        if (tab_lane && tab_pos == pos) {
+            cs_tab[threadIdx.x] = tab_cs;
+        } else {
+            const RopeArgs r{pos, a.theta, a.yarn_scale, a.yarn_orig_ctx, a.neox};
+            float c, s;
+            rope_cs(r, threadIdx.x, hd, c, s);
+            cs_tab[threadIdx.x] = make_float2(c, s);
+        }
     }
     pdl_trigger();
     __syncthreads();
-    AT_MARK(1);
 
     // ---- 2. the new token's q, k, v ----
     pdl_wait();
-    AT_MARK(2);
     const size_t tok_off = a.prompt ? (size_t)blockIdx.y * a.n_heads * hd : 0;
     for (int idx = threadIdx.x; idx < G * half; idx += AS_THREADS) {
         const int g = idx / half, i = idx - g * half;
@@ -209,7 +215,6 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
         }
         cp_async_wait_all();
         __syncthreads();
-        AT_MARK(3);
         if (!warp_active) continue;
         // ---- 3. online softmax over this warp's 32-row groups ----
         for (int t_lo = 32 * sub; t_lo < n; t_lo += 32 * wph) {
@@ -265,7 +270,6 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
 
     // ---- this CTA's partial per head: the warps that shared a head leave theirs in shared memory ----
     __syncthreads();
-    AT_MARK(4);
     if (warp_active) {
 #pragma unroll
         for (int r = 0; r < 2; r++) {
@@ -283,27 +287,36 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
     // ---- 4. push the partials to the CTAs that finish them: destination d gets, in its recv[rank], this CTA's
     //         (max, sum) of every head followed by its part of d's S outputs ----
     cluster_wait();   // (arrived at the top) every CTA of the cluster has started
-    AT_MARK(5);
-    for (int idx = threadIdx.x; idx < G * hd + 2 * G * CL; idx += AS_THREADS) {
-        int dst, off;
-        float val;
-        if (idx < G * hd) {
-            const int g = idx / hd, d = idx - g * hd;
+    // four outputs (one float4) or one head's (max, sum) pair (one float2) per remote store
+    const int n_out4 = (G * hd) >> 2;
+    for (int it = threadIdx.x; it < n_out4 + G * CL; it += AS_THREADS) {
+        if (it < n_out4) {
+            const int idx = 4 * it;
+            const int g = idx / hd, d = idx - g * hd;          // (hd is a multiple of 32: the four share a head)
             const int r = g / AS_WARPS, w0 = g % AS_WARPS;     // G <= 8: r = 0, w0 = g
             float m = -1e30f;
             for (int s = 0; s < wph; s++) m = fmaxf(m, wres[((w0 + s * Gw) * 2 + r) * RS]);
-            float o = 0.f;
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int s = 0; s < wph; s++) {
                 const float *w = wres + ((w0 + s * Gw) * 2 + r) * RS;
-                o = fmaf(w[2 + d], __expf(w[0] - m), o);
+                const float f = __expf(w[0] - m);
+                const float2 lo = *(const float2 *)(w + 2 + d), hi = *(const float2 *)(w + 4 + d);
+                o.x = fmaf(lo.x, f, o.x);
+                o.y = fmaf(lo.y, f, o.y);
+                o.z = fmaf(hi.x, f, o.z);
+                o.w = fmaf(hi.y, f, o.w);
             }
-            dst = idx / S;
-            off = 2 * G + (idx - dst * S);
-            val = o;
+            const int dst = idx / S;
+            float *remote = cluster.map_shared_rank(recv, dst) + rank * RW + 2 * G + (idx - dst * S);
+            if ((G & 1) == 0) {
+                *(float4 *)remote = o;                          // 16-byte aligned: RW and 2 G are multiples of 4 floats
+            } else {
+                *(float2 *)remote = make_float2(o.x, o.y);
+                *(float2 *)(remote + 2) = make_float2(o.z, o.w);
+            }
         } else {
-            const int j = idx - G * hd;
-            dst = j / (2 * G);
-            const int which = j - dst * (2 * G), g = which >> 1;
+            const int j = it - n_out4;
+            const int dst = j / G, g = j - dst * G;
             const int r = g / AS_WARPS, w0 = g % AS_WARPS;
             float m = -1e30f;
             for (int s = 0; s < wph; s++) m = fmaxf(m, wres[((w0 + s * Gw) * 2 + r) * RS]);
@@ -312,15 +325,12 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
                 const float *w = wres + ((w0 + s * Gw) * 2 + r) * RS;
                 l = fmaf(w[1], __expf(w[0] - m), l);
             }
-            off = which;
-            val = (which & 1) ? l : m;
+            float *remote = cluster.map_shared_rank(recv, dst) + rank * RW + 2 * g;
+            *(float2 *)remote = make_float2(m, l);
         }
-        float *remote = cluster.map_shared_rank(recv, dst);
-        remote[rank * RW + off] = val;
     }
     cluster_arrive();
     cluster_wait();   // every push has landed; nobody touches another CTA's shared memory afterwards
-    AT_MARK(6);
 
     // ---- merge: this CTA's S outputs from the CL partials it received ----
     for (int j = threadIdx.x; j < S; j += AS_THREADS) {
@@ -348,7 +358,6 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
             quantize4_store(v, (first >> 2) + (lane & 7), lane < 8, a.o);
         }
     }
-    AT_MARK(7);
 }
 
 }  // namespace qz

@@ -43,20 +43,6 @@ struct ChainOp {
     XSrc xsrc;              // mode 1 (RMSNorm), 2 (SwiGLU) or 3 (plain f32 vector a)
 };
 
-#ifdef QZ_CHAIN_TRACE
-__device__ unsigned long long g_chain_trace[160][32];
-__device__ __forceinline__ void chain_mark(int slot)
-{
-    if (threadIdx.x == 0 && slot < 32) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_chain_trace[blockIdx.x][slot] = t;
-    }
-}
-#define QZ_MARK(s) chain_mark(s)
-#else
-#define QZ_MARK(s)
-#endif
 
 struct GridBarrier {
     int count, gen, abort;
@@ -325,9 +311,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     const int lane = threadIdx.x & 31;
     uint8_t *xarea = ring + (size_t)a.ring_bytes;
     RingPos rp{0, 0};
-    QZ_MARK(0);
     pdl_wait();   // op 0's inputs come from the preceding kernels
-    QZ_MARK(1);
     bool ok = true;
     volatile int *dead_flag = &cta_dead;
     // an op's activation vector, converted by this CTA into its area behind the ring
@@ -402,7 +386,6 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     const int push_base = a.exchange ? *(volatile const int *)&a.push.ctrl[a.push.rank]->pushes : 0;
     for (int k = 0; k < a.n_ops; k++) {
         const ChainOp &op = a.op[k];
-        QZ_MARK(2 + 4 * k);
         if (k > 0 && !a.independent) {
             // every consumer warp arrives here, whether or not a wait of op k-1 ran out on it; afterwards the
             // whole CTA takes the same decision.  (Also: every warp has taken its activation registers, the
@@ -443,12 +426,10 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
             ok = *(volatile int *)&cta_ok != 0 && !*dead_flag;
         }
         if (!ok) break;   // uniform over the CTA's consumers (independent ops: a dead CTA just walks on, storing nothing)
-        QZ_MARK(3 + 4 * k);
         if (!a.independent) {
             convert(op);
             named_bar_sync(14, TMA_CONSUMERS);
         }
-        QZ_MARK(4 + 4 * k);
         int8_t *sxl = (int8_t *)(xarea + op.x_off), *sxh = sxl + op.K;
         float *sxs = (float *)(sxh + op.K), *sxsum = sxs + (op.K >> 5);
         unpublished = unpublished || op.push_off >= 0;
@@ -469,7 +450,6 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
         default: ok = false; break;
         }
 #undef QZ_CHAIN_CASE
-        QZ_MARK(5 + 4 * k);
         // a warp whose wait ran out tells the other CTAs (they leave at their next grid barrier) and goes on to
         // this CTA's next meeting point like every other warp
         if (!ok) atomicExch(&a.gb->abort, 1);

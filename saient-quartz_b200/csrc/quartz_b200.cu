@@ -1403,10 +1403,6 @@ int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops)
 static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent, const size_t *push_off,
                               const size_t *push_stride = nullptr);
 
-#ifdef QZ_CHAIN_TRACE
-extern "C" void quartz_chain_trace_read(void *host) { cudaMemcpyFromSymbol(host, g_chain_trace, sizeof(g_chain_trace)); }
-extern "C" void quartz_attn_trace_read(void *host) { cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(g_attn_trace)); }
-#endif
 void cuda_gemv_chain(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 0, nullptr); }
 void cuda_gemv_batch(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_ops, ops, 1, nullptr); }
 
@@ -1588,14 +1584,36 @@ void cuda_attn_block(float *out, const float *q, const float *k_new, const float
 }
 
 // ---- decode step whose position and token live in device memory ----
-__global__ void step_set_kernel(int *step, int token, int pos)
+// RoPE parameter sets registered for a pair of step words: cuda_step_set writes their (cos, sin) tables for the new
+// position in the same launch as the words, and cuda_attn_step reads the table instead of computing sin / cos of
+// position * frequency in every CTA of every layer.
+constexpr int QZ_MAX_ROPE_SETS = 4;
+struct RopeSetDev { float2 *tab; int head_dim; float theta, yarn_scale; int yarn_orig_ctx; };
+struct RopeSets { int n; RopeSetDev s[QZ_MAX_ROPE_SETS]; };
+struct RopeReg { const int *step; RopeSetDev d; };
+static RopeReg g_rope_reg[16];
+static int g_rope_regs = 0;
+
+__global__ void step_set_kernel(int *step, int token, int pos, RopeSets sets)
 {
     pdl_wait();
     pdl_trigger();
-    if (threadIdx.x == 0) {
-        step[0] = token;
-        step[1] = pos;
+    if (blockIdx.x == 0) {
+        if (threadIdx.x == 0) {
+            step[0] = token;
+            step[1] = pos;
+        }
+        return;
     }
+    const RopeSetDev &e = sets.s[blockIdx.x - 1];
+    const int i = threadIdx.x;
+    if (i < e.head_dim / 2) {
+        const RopeArgs r{pos, e.theta, e.yarn_scale, e.yarn_orig_ctx, 0};
+        float c, s;
+        rope_cs(r, i, e.head_dim, c, s);
+        e.tab[i] = make_float2(c, s);
+    }
+    if (i == 0) e.tab[ATT_MAX_HD / 2] = make_float2(__int_as_float(pos), 0.f);
 }
 
 static cudaStream_t g_graph_stream = nullptr, g_saved_stream = nullptr;
@@ -1605,8 +1623,48 @@ void cuda_step_set(int *d_step, int token, int pos)
     if (!d_step) return;
     // on the stream the recorded graphs replay on (when there is one), so the words are ordered with the replays
     cudaStream_t s = (g_graph_stream && g_stream == 0) ? g_graph_stream : g_stream;
-    step_set_kernel<<<1, 32, 0, s>>>(d_step, token, pos);
+    RopeSets sets;
+    sets.n = 0;
+    for (int i = 0; i < g_rope_regs && sets.n < QZ_MAX_ROPE_SETS; i++)
+        if (g_rope_reg[i].step == d_step) sets.s[sets.n++] = g_rope_reg[i].d;
+    step_set_kernel<<<1 + sets.n, ATT_MAX_HD / 2, 0, s>>>(d_step, token, pos, sets);
     QZ_LAUNCH_CHECK();
+}
+
+void cuda_step_rope_table(int *d_step, int head_dim, float theta, float yarn_scale, int yarn_orig_ctx)
+{
+    if (!d_step || head_dim < 2 || head_dim > ATT_MAX_HD || head_dim % 2) {
+        set_error(QZ_ERR_BAD_SHAPE, "cuda_step_rope_table: head_dim must be even and at most 128");
+        return;
+    }
+    int same_step = 0;
+    for (int i = 0; i < g_rope_regs; i++) {
+        const RopeReg &e = g_rope_reg[i];
+        if (e.step != d_step) continue;
+        if (e.d.head_dim == head_dim && e.d.theta == theta && e.d.yarn_scale == yarn_scale && e.d.yarn_orig_ctx == yarn_orig_ctx) return;
+        same_step++;
+    }
+    if (g_rope_regs >= 16 || same_step >= QZ_MAX_ROPE_SETS) return;   // no room: such calls keep computing in the kernel
+    float2 *tab = nullptr;
+    if (cudaMalloc(&tab, (ATT_MAX_HD / 2 + 1) * sizeof(float2)) != cudaSuccess) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "cuda_step_rope_table: cudaMalloc failed");
+        return;
+    }
+    cudaMemset(tab, 0xFF, (ATT_MAX_HD / 2 + 1) * sizeof(float2));   // position -1: matches no step until cuda_step_set ran
+    g_rope_reg[g_rope_regs++] = RopeReg{d_step, RopeSetDev{tab, head_dim, theta, yarn_scale, yarn_orig_ctx}};
+}
+
+// the registered table of (step words, parameters), or NULL
+static const float2 *rope_table_of(const int *d_step, int head_dim, float theta, float yarn_scale, int yarn_orig_ctx)
+{
+    for (int i = 0; i < g_rope_regs; i++) {
+        const RopeReg &e = g_rope_reg[i];
+        if (e.step == d_step && e.d.head_dim == head_dim && e.d.theta == theta && e.d.yarn_scale == yarn_scale &&
+            e.d.yarn_orig_ctx == yarn_orig_ctx)
+            return e.d.tab;
+    }
+    return nullptr;
 }
 
 void cuda_embed_lookup_dev(float *out, const uint8_t *data, uint32_t ggml_type, const int *d_step, int embed_dim)
@@ -1776,6 +1834,7 @@ void cuda_attn_step(float *out, const float *q, const float *k_new, const float 
     a.o = XQOut{nullptr, nullptr, nullptr, nullptr};
     a.emit_q = 0;
     a.prompt = 0;
+    a.rope_tab = d_step ? rope_table_of(d_step, head_dim, theta, yarn_scale, yarn_orig_ctx) : nullptr;
     a.rows_cap = attn_step_rows();
     if (out_slot >= 0) {
         if (!user_slot(out_slot, n_heads * head_dim, &a.o)) return;

@@ -206,6 +206,8 @@ int qh_finalize(qh_model *m)
               m->d_logits.alloc_f32(c.vocab_size) && m->d_step.alloc_f32(4) && m->d_moe_ids.alloc_f32(16) &&
               m->d_moe_w.alloc_f32(16);
     if (!ok) return -2;
+    // the (cos, sin) table of a step's position is written together with the step words
+    cuda_step_rope_table((int *)m->d_step.ptr, c.head_dim, c.rope_theta, c.yarn_scale, c.yarn_orig_ctx);
     m->kv_k.resize(c.n_layers);
     m->kv_v.resize(c.n_layers);
     std::vector<float> zeros(std::max(q_d, kv_d), 0.f), no_sink(nh, -INFINITY);

@@ -513,6 +513,9 @@ def test_attn_step_matches_separate_launches(gpu, neox):
     L = gpu.lib()
     r = np.random.Generator(np.random.PCG64([0xA79, neox]))
     step_words = gpu.GpuBuf.alloc_f32(4)
+    # head_dim 128 and 64 read the (cos, sin) table that cuda_step_set writes with the words; 96 computes it in the kernel
+    L.cuda_step_rope_table(step_words.ptr, 128, np.float32(500000.0), np.float32(1.0), 0)
+    L.cuda_step_rope_table(step_words.ptr, 64, np.float32(500000.0), np.float32(1.0), 0)
     cases = [(32, 8, 128, 1024, 0, 1100, False), (8, 8, 64, 32, 0, 64, True), (12, 2, 96, 69, 65, 128, True),
              (4, 1, 128, 0, 0, 16, False), (16, 4, 128, 31, 0, 40, False), (64, 8, 128, 600, 0, 640, False),
              (32, 2, 64, 257, 100, 300, True), (8, 4, 128, 2047, 0, 2048, False), (32, 8, 128, 95, 64, 128, False)]
