@@ -37,7 +37,9 @@ struct ChainOp {
     int U, Upad, RP;        // units per row, threads per row, rows per stage
     int n_cta;              // CTAs per matrix (grid / n_mats, at most the tile count)
     int rot;                // the op's CTA numbering starts at this CTA (spreads the ops' odd tiles over the grid)
-    int x_off;              // byte offset of the op's converted activation vector behind the ring
+    int x_off;              // byte offset of the op's converted activation vector behind the ring; < 0: the vector
+                            // was converted by a kernel before this one and is read from `xg` (global memory)
+    XQ xg;
     long long push_off;     // >= 0: rows go to every rank's window instead of y: matrix m at push_off + m * push_stride
     long long push_stride;
     XSrc xsrc;              // mode 1 (RMSNorm), 2 (SwiGLU) or 3 (plain f32 vector a)
@@ -377,8 +379,13 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     if (a.independent) {
         // no op reads what another writes: every activation vector is converted up front, each into an area of
         // its own, while the ring fills; afterwards the ops follow one another without a pause
-        for (int k = 0; k < a.n_ops; k++) convert(a.op[k]);
-        named_bar_sync(14, TMA_CONSUMERS);
+        bool any = false;
+        for (int k = 0; k < a.n_ops; k++)
+            if (a.op[k].x_off >= 0) {
+                convert(a.op[k]);
+                any = true;
+            }
+        if (any) named_bar_sync(14, TMA_CONSUMERS);
     }
     bool unpublished = false;   // an op has pushed rows that no publish has covered yet
     // exchanges this rank had published when the kernel started (read after the wait above: the previous kernel's
@@ -425,15 +432,20 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
             named_bar_sync(13, TMA_CONSUMERS);
             ok = *(volatile int *)&cta_ok != 0 && !*dead_flag;
         }
+        // Independent ops need no grid barrier, but the CTA's consumer warps still meet between two ops: the named
+        // barriers (ids 1 + row group, counted per op's row geometry) and the partial-sum buffer of the row
+        // reduction are laid out per op, and a warp that ran ahead into op k would use them with op k's thread
+        // counts while a slower warp is still inside op k-1.
+        if (k > 0 && a.independent) named_bar_sync(13, TMA_CONSUMERS);
         if (!ok) break;   // uniform over the CTA's consumers (independent ops: a dead CTA just walks on, storing nothing)
         if (!a.independent) {
             convert(op);
             named_bar_sync(14, TMA_CONSUMERS);
         }
-        int8_t *sxl = (int8_t *)(xarea + op.x_off), *sxh = sxl + op.K;
+        int8_t *sxl = (int8_t *)(xarea + (op.x_off >= 0 ? op.x_off : 0)), *sxh = sxl + op.K;
         float *sxs = (float *)(sxh + op.K), *sxsum = sxs + (op.K >> 5);
         unpublished = unpublished || op.push_off >= 0;
-        const XQ xq{sxl, sxh, sxs, sxsum};
+        const XQ xq = op.x_off >= 0 ? XQ{sxl, sxh, sxs, sxsum} : op.xg;
         const int me = ((int)blockIdx.x + (int)gridDim.x - op.rot) % (int)gridDim.x;
         const int m = me % op.n_mats, cta = me / op.n_mats;
 #define QZ_CHAIN_CASE(TT, POL)                                                                                              \

@@ -147,6 +147,29 @@ __device__ __forceinline__ void quantize4_store(const float v[4], int t, bool va
     if ((t & 3) == 0) o.xsum[t >> 2] = sum;
 }
 
+// Several vectors in one launch (grid.y = vector): what quantize_x_kernel does for one.
+constexpr int QZ_QUANT_MULTI = 8;
+struct QuantMulti {
+    const float *x[QZ_QUANT_MULTI];
+    XQOut o[QZ_QUANT_MULTI];
+    int K[QZ_QUANT_MULTI];
+};
+__global__ void quantize_x_multi_kernel(const QuantMulti q)
+{
+    pdl_wait();
+    pdl_trigger();
+    const int i = blockIdx.y, K = q.K[i];
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (4 * (int)(blockIdx.x * blockDim.x) >= K) return;   // whole block past the end of this vector
+    const bool valid = 4 * t < K;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (valid) {
+        const float4 f = __ldcg((const float4 *)(q.x[i] + 4 * t));
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    }
+    quantize4_store(v, t, valid, q.o[i]);
+}
+
 // d = sum over 4 bytes a_i (unsigned) * b_i (signed) + c
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
 {

@@ -8,6 +8,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <string>
@@ -1326,6 +1327,31 @@ void cuda_gemv_swiglu(uint32_t ggml_type, int n_mats, const uint8_t *const *d_w,
 }
 
 // ---- a chain of dependent GEMVs as one persistent kernel ----
+// Activation scratch of the batched form: the plain-f32 vectors of independent ops are converted by ONE small
+// kernel ahead of the persistent one (every CTA then reads its slices from L2), so the persistent kernel keeps its
+// whole shared memory for the weight ring.
+static XQScratch g_bxq;
+static bool ensure_bxq(int K)
+{
+    if ((size_t)K <= g_bxq.cap_k) return true;
+    if (g_bxq.base) {
+        cudaStreamSynchronize(g_stream);
+        cudaFree(g_bxq.base);
+        g_bxq.base = nullptr;
+        g_bxq.cap_k = 0;
+    }
+    const size_t cap = (size_t)K < 32768 ? 32768 : (size_t)K;
+    const size_t sb = xq_slot_bytes(cap);
+    if (cudaMalloc(&g_bxq.base, CHAIN_MAX_OPS * sb) != cudaSuccess) {
+        cudaGetLastError();
+        set_error(QZ_ERR_CUDA, "cudaMalloc of the batch activation scratch failed");
+        return false;
+    }
+    g_bxq.cap_k = cap;
+    g_bxq.slot_bytes = sb;
+    return true;
+}
+
 static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &smem, int independent = 0,
                        const size_t *push_off = nullptr, const size_t *push_stride = nullptr)
 {
@@ -1333,7 +1359,8 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
     const int grid = sm_count();
     int slot = 0, x_bytes = 0, rot = 0;
     for (int k = 0; k < n_ops; k++) {
-        const qz_chain_op &o = ops[k];
+        const int src = k;
+        const qz_chain_op &o = ops[src];
         ChainOp &c = a.op[k];
         if (o.ggml_type != T_Q4_K && o.ggml_type != T_Q6_K && o.ggml_type != T_Q8_0) return false;
         if (o.n_mats < 1 || o.n_mats > QZ_MAX_MATS || o.n_mats > grid || o.out_dim <= 0) return false;
@@ -1342,7 +1369,7 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         if (o.in_dim < 2048 || o.in_dim % 64) return false;
         if (o.src_mode == 1 && o.in_dim / 4 > XSRC_MAX_IT * TMA_CONSUMERS) return false;   // RMSNorm: one piece only
         if (push_off && ((o.n_mats != 1 && !push_stride) || o.accumulate)) return false;
-        if (push_off && push_stride && o.n_mats > 1 && push_stride[k] < (size_t)o.out_dim) return false;
+        if (push_off && push_stride && o.n_mats > 1 && push_stride[src] < (size_t)o.out_dim) return false;
         for (int i = 0; i < o.n_mats; i++)
             if (!cuda_gemv_q_supported(o.ggml_type, o.d_w[i], o.in_dim)) return false;
         const FormatInfo fi = format_info(o.ggml_type);
@@ -1363,8 +1390,8 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         // tile more than the others are not the same in every op (dependent ops keep the plain numbering)
         c.rot = independent ? rot % grid : 0;
         rot += (ntiles % c.n_cta) * o.n_mats;
-        c.push_off = push_off ? (long long)push_off[k] : -1;
-        c.push_stride = push_off && push_stride ? (long long)push_stride[k] : 0;
+        c.push_off = push_off ? (long long)push_off[src] : -1;
+        c.push_stride = push_off && push_stride ? (long long)push_stride[src] : 0;
         c.xsrc = XSrc{o.src_mode, o.d_a, o.src_mode == 3 ? o.d_a : o.d_b, o.oai};
         for (int i = 0; i < QZ_MAX_MATS; i++) {
             c.W[i] = o.d_w[i < o.n_mats ? i : 0];
@@ -1373,7 +1400,13 @@ static bool chain_plan(int n_ops, const qz_chain_op *ops, ChainArgs &a, size_t &
         const int stage = c.RP * row_bytes;
         if (stage > slot) slot = stage;
         const int xb = (int)((2 * (size_t)o.in_dim + o.in_dim / 8 + o.in_dim / 4 + 31) & ~(size_t)15);
-        if (independent) {   // every op's vector has an area of its own (all are converted before the first op runs)
+        if (independent && o.src_mode == 3) {
+            // a plain vector of an independent op: converted ahead of the persistent kernel, read from global memory
+            if (!ensure_bxq(o.in_dim)) return false;
+            const XQMut q = xq_slot(g_bxq.base, g_bxq.slot_bytes, k, g_bxq.cap_k);
+            c.x_off = -1;
+            c.xg = XQ{q.xl, q.xh, q.xs, q.xsum};
+        } else if (independent) {   // an area of its own (all are converted before the first op runs)
             c.x_off = x_bytes;
             x_bytes += xb;
         } else {
@@ -1473,6 +1506,22 @@ static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent
     a.gb = g_grid_barrier;
     a.status = status_word();
     if (!a.status) return;
+    {
+        // the vectors that are converted ahead of the persistent kernel: one launch for all of them
+        QuantMulti qm;
+        int nq = 0, max_k = 0;
+        for (int k = 0; k < n_ops; k++) {
+            if (a.op[k].x_off >= 0) continue;
+            const XQMut q = xq_slot(g_bxq.base, g_bxq.slot_bytes, k, g_bxq.cap_k);
+            qm.x[nq] = a.op[k].xsrc.a;
+            qm.o[nq] = XQOut{q.xl, q.xh, q.xs, q.xsum};
+            qm.K[nq] = a.op[k].K;
+            max_k = std::max(max_k, a.op[k].K);
+            nq++;
+        }
+        for (int i = nq; i < QZ_QUANT_MULTI; i++) { qm.x[i] = nullptr; qm.K[i] = 0; qm.o[i] = XQOut{nullptr, nullptr, nullptr, nullptr}; }
+        if (nq > 0) launch(quantize_x_multi_kernel, dim3((max_k / 4 + 255) / 256, nq), dim3(256), 0, qm);
+    }
     static bool attr_set = false;
     if (!attr_set) {
         QZ_CUDA_CHECK(cudaFuncSetAttribute(gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));

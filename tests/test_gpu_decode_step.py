@@ -622,6 +622,27 @@ def test_gemv_batch_of_independent_shapes(gpu, oracle_mod):
         ref = oracle_mod.gemv(x, w, t, K, N)
         assert np.all(np.abs(y - ref) <= oracle_mod.tolerance(w, t, K, N, x)), (t, K, N)
     gpu.check_error()
+    # long ops whose rows are shared out differently (2 warps per row, then 7, then 2): the consumer warps of a CTA
+    # meet between two ops, so a warp that runs ahead never uses the next op's barrier counts beside a slower one
+    cases2 = [(14, 4096, 32064), (14, 14336, 4096), (12, 4096, 14336), (8, 4096, 4096), (14, 14336, 1000)]
+    ops2, keep2 = [], []
+    for i, (t, K, N) in enumerate(cases2):
+        w = synth.make_weights(t, K, N, tensor_id=680 + i)
+        x = synth.make_x(K, tensor_id=690 + i).reshape(-1)
+        dw = gpu.GpuBuf.upload(w)
+        L.cuda_repack_weights(t, dw.ptr, K, N, 1)
+        dx, dy, dy2 = gpu.GpuBuf.upload(x), gpu.GpuBuf.alloc_f32(N), gpu.GpuBuf.alloc_f32(N)
+        keep2.append((t, K, N, dw, dx, dy, dy2))
+        ops2.append(gpu.chain_op(t, [dw.ptr], [dy.ptr], K, N, 0, 3, dx.ptr))
+    arr2 = (gpu.ChainOp * len(ops2))(*ops2)
+    assert L.cuda_gemv_chain_supported(len(ops2), arr2) == 1
+    for rep in range(3):
+        L.cuda_gemv_batch(len(ops2), arr2)
+    L.cuda_sync()
+    gpu.check_error("batch of long ops")
+    for (t, K, N, dw, dx, dy, dy2) in keep2:
+        L.cuda_gemv(t, dw.ptr, dx.ptr, dy2.ptr, K, N)
+        assert np.array_equal(dy.download(), dy2.download()), (t, K, N)
     # an op the persistent kernel does not take (in_dim below 2048) makes the call run launch by launch
     t, K, N = 12, 1024, 64
     w = synth.make_weights(t, K, N, tensor_id=670)
