@@ -1010,9 +1010,9 @@ def main():
             torch.cuda.synchronize()
             bms = e0.elapsed_time(e1) / args.steps
             q.check_error("batched sweep")
-            batched = {"ms_per_step": bms, "value": total_bytes / (bms * 1e-3) / 1e9, "unit": UNIT, "launches_per_step": 1,
+            batched = {"ms_per_step": bms, "value": total_bytes / (bms * 1e-3) / 1e9, "unit": UNIT, "launches_per_step": 2,
                        "outputs_identical_to_separate_calls": bool(same),
-                       "how": "cuda_gemv_batch: the six independent GEMVs in one persistent kernel, graph replay"}
+                       "how": "cuda_gemv_batch: one kernel converts the six activation vectors, one persistent kernel runs the six independent GEMVs; graph replay"}
             if gb:
                 L.quartz_graph_destroy(gb)
     elif win is not None:
@@ -1063,9 +1063,10 @@ def main():
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             bms = float(tt.item())
             q.check_error("batched sharded sweep")
-            batched = {"ms_per_step": bms, "value": total_bytes / (bms * 1e-3) / 1e9, "unit": UNIT, "launches_per_step": 2,
-                       "how": "cuda_gemv_batch_push: this rank's six shard GEMVs and their peer-store exchange in one "
-                              "persistent kernel, one wait per step, graph replay; device time, max over ranks"}
+            batched = {"ms_per_step": bms, "value": total_bytes / (bms * 1e-3) / 1e9, "unit": UNIT, "launches_per_step": 3,
+                       "how": "cuda_gemv_batch_push: one kernel converts the six activation vectors, one persistent kernel runs "
+                              "this rank's six shard GEMVs and their peer-store exchange, one wait per step; graph replay; "
+                              "device time, max over ranks"}
             # the complete vectors in this rank's window against the CPU oracle (what was just timed)
             if rank == 0:
                 import oracle
