@@ -1254,8 +1254,11 @@ def main():
                        "l2": "inputs larger than L2: each step streams 543 MB of distinct weights (> 126 MB L2); the roofline loop alternates two 431 MB copies of the matrix",
                        "pct_of_8TBs_nominal": 100.0 * total_bytes / (ms * 1e-3) / 8e12},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": dom_bytes * 1.0003 if world == 1 else None,
-                         "traffic_note": "ncu dram__bytes_read+write of a 134 MB launch of the same kernel = 1.0003 x algorithmic, scaled by rows (profiles/)",
+                         "traffic": dom_bytes * 1.0006 if world == 1 else None,
+                         "traffic_note": "ncu dram__bytes_read.sum of the 134 MB launch (4096->40080) of this kernel = 134.75 MB = 1.0006 x its weight bytes "
+                                         "(its write counter also shows 4 MB of write-backs of earlier buffers; the kernel stores 160 KB); "
+                                         "scaled by rows to the full launch; captured with gemv_tma.cuh as of commit fe36a7e "
+                                         "(profiles/gemv_tma_q6k_q4k_ncu.md)",
                          "kernel": f"gemv_tma_kernel<{synth.FORMATS[dt_][0]}> {dK}->{n1 - n0}",
                          "bytes_per_launch": dom_bytes, "avg_us": dom_avg * 1e3, "min_us": dom_ms[0] * 1e3,
                          "launches_timed": 3 * reps, "frac_of_8TBs_nominal": achieved / 8000.0,
