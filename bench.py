@@ -663,8 +663,9 @@ def sharded70b_section(q, L, torch, win, rank, world, dist, steps, cpu_baseline=
 
 def sharded_gemm_section(q, L, torch, win, rank, world, dist):
     """The prefill GEMMs row-sharded over the ranks: Q4_K 4096->14336 and Q6_K 14336->4096 times M = 16, 64, 512,
-    2048 tokens.  Every rank holds the rows [n0, n1) of the matrix, computes its [M, n1-n0] block with cuda_gemm and
-    stores it into every rank's window (cuda_push_rows); after the wait each rank holds the complete [M, N] output.
+    2048 tokens.  Every rank holds the rows [n0, n1) of the matrix and computes its [M, n1-n0] block; the block goes
+    into every rank's window from the GEMM's own epilogue (cuda_gemm_push) or, timed beside it, by a copy kernel after
+    the GEMM (cuda_gemm + cuda_push_rows); after the wait each rank holds the complete [M, N] output.
     Times are device times, max over ranks; TFLOP/s and GB/s are whole-job figures."""
     from saient_quartz_b200 import synth
     from saient_quartz_b200.shard import shard_rows as sr, shard_bytes
@@ -680,33 +681,53 @@ def sharded_gemm_section(q, L, torch, win, rank, world, dist):
             X = synth.make_x(K, tensor_id=410, rows=M)
             dx, dy = q.GpuBuf.upload(X), q.GpuBuf.alloc_f32(M * (n1 - n0))
 
-            def step():
+            def step_copy():
                 L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, n1 - n0)
                 win.push_rows(dy.ptr, M, n1 - n0, n0, N)
                 win.wait()
-            for _ in range(3):
-                step()
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
+
+            def step():   # the exchange in the GEMM's epilogue
+                if not L.cuda_gemm_push(t, dw.ptr, dx.ptr, M, K, n1 - n0, n0, N):
+                    L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, n1 - n0)
+                    win.push_rows(dy.ptr, M, n1 - n0, n0, N)
+                win.wait()
             reps = 10 if M <= 64 else 5
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                step()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / reps
-            if world > 1:
-                tt = torch.tensor([ms], device="cuda")
-                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-                ms = float(tt.item())
+
+            def timed_ms(fn):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                v = e0.elapsed_time(e1) / reps
+                if world > 1:
+                    tt = torch.tensor([v], device="cuda")
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                    v = float(tt.item())
+                return v
+            ms_copy = timed_ms(step_copy)
+            ms = timed_ms(step)
             q.check_error("sharded gemm")
             flops = 2.0 * M * K * N
             nbytes = synth.type_size(t, K * N) + 4.0 * M * K + 4.0 * M * N
-            out.append({"format": synth.FORMATS[t][0], "M": M, "K": K, "N": N, "n_gpus": world, "ms": ms,
-                        "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6,
-                        "exchange": "cuda_push_rows into every rank's window + one wait"})
+            # what must cross NVLink INTO every rank: the other ranks' blocks of the f32 output
+            link_bytes = 4.0 * M * N * (world - 1) / world
+            row = {"format": synth.FORMATS[t][0], "M": M, "K": K, "N": N, "n_gpus": world, "ms": ms,
+                   "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6,
+                   "exchange": "cuda_gemm_push: peer stores from the GEMM's epilogue + one wait",
+                   "ms_gemm_then_copy_kernel": ms_copy}
+            if world > 1:
+                # roofline of the fused kernel: the slower of flops / measured bf16 peak and link bytes / 770 GB/s
+                t_link, t_flop = link_bytes / 770e9 * 1e3, flops / world / 1.6156e15 * 1e3
+                row["nvlink_bytes_in_per_rank"] = link_bytes
+                row["frac_of_fused_roofline"] = max(t_link, t_flop) / ms
+            out.append(row)
             dx.drop(); dy.drop()
         dw.drop()
     return out

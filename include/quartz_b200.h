@@ -424,6 +424,16 @@ void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size
  * publishes ONE exchange -- a row-sharded step of several independent GEMVs costs one launch and one wait instead of
  * one launch, one conversion and one publish per GEMV.  Returns 1 if launched, 0 if the persistent kernel does not
  * take these ops (nothing was launched: use cuda_gemv_push per op). */
+/* The batched (tensor-core) GEMM of a row shard with the exchange in its epilogue: this rank's [m x out_dim] block
+ * (out_dim = the rows this rank owns) of Y = X W^T goes straight from the accumulators into EVERY rank's window,
+ * token t / local row n at element dst_off + t * dst_ld + n, and the last CTA publishes the exchange; complete it
+ * with quartz_mgpu_wait() like any other.  One kernel does the tensor-core tiles and the peer stores, so the
+ * transfer of finished tiles overlaps the computation of the others.  d_x is [m, in_dim] f32, replicated on every
+ * rank.  Returns 1 if launched, 0 if the tensor-core kernel does not take the shape (m = 1, in_dim not a multiple
+ * of 64, misaligned pointers; nothing was launched: use cuda_gemm + cuda_push_rows).  No counterpart in the
+ * reference (single GPU, no batched GPU path). */
+int cuda_gemm_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, int m, int in_dim, int out_dim,
+                   size_t dst_off, size_t dst_ld);
 int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off);
 /* A chain of DEPENDENT row-sharded GEMVs with the exchanges inside one persistent kernel per rank (a whole sharded
  * FFN: gate/up shards -> exchange -> SwiGLU -> down shard -> exchange, as one launch).  Op k's rows go to every

@@ -77,6 +77,11 @@ struct GemmArgs {
     long long units_per_cta;   // shared part: CTA c owns [rem_begin + c * units_per_cta, + units_per_cta), clipped
     int stages;                // MMA ring depth
     int *status;
+    // row-sharded GEMM (push.n > 0): the epilogue stores every output element into ALL ranks' windows, token m /
+    // local row n at push_off + m * push_ld + n, straight from the accumulator, and the last CTA publishes the
+    // exchange.  The host uses this form only with a schedule of whole tiles (no tile shared between CTAs).
+    PushArgs push;
+    long long push_off, push_ld;
 };
 
 // ---- f32 or bf16 [M,K] -> bf16 tiles in exactly the shared-memory image the MMA reads: for every
@@ -568,6 +573,7 @@ struct GemmTile {
     size_t x_tile;       // index of the activation token tile (its K steps follow one another)
     const uint8_t *W;    // weight matrix of this tile
     float *Y;            // output row of the tile's first token
+    int tok0;            // index of the tile's first token (plain GEMM)
 };
 
 struct GemmGroupView {   // the group descriptor as one CTA sees it (shared memory)
@@ -688,6 +694,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             t.x_tile = (size_t)tt;
             t.W = a.W;
             t.Y = a.Y + (size_t)tt * ntok_max * a.N;
+            t.tok0 = tt * ntok_max;
         } else {
             const int e = group_find(gv.tile_prefix, gv.n_experts, tile);
             int local = tile - gv.tile_prefix[e];
@@ -703,6 +710,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             t.x_tile = (size_t)(grp->tt_prefix[e] + tt);
             t.W = a.Wm[mat] + (size_t)e * a.expert_stride;
             t.Y = a.Ym[mat] + (size_t)(grp->offsets[e] + tt * ntok_max) * a.N;
+            t.tok0 = 0;
         }
         return t;
     };
@@ -858,7 +866,18 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
                 const int nc = min(32, t.ntok - c0);
                 if (nc == 32) tc_ld32(taddr, v);
                 else tc_ld16(taddr, v);
-                if (row < a.N) {
+                if (row < a.N && a.push.n > 0 && whole) {
+                    // row-sharded: straight into every rank's window (a warp writes 32 consecutive floats per token and
+                    // rank: coalesced 128-byte stores, local or over NVLink)
+                    const long long base = a.push_off + (long long)(t.tok0 + c0) * a.push_ld + row;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (j < nc && c0 + j < t.valid) {
+                            const float f = __uint_as_float(v[j]);
+                            for (int rk = 0; rk < a.push.n; rk++) a.push.data[rk][base + (long long)j * a.push_ld] = f;
+                        }
+                    }
+                } else if (row < a.N) {
                     float *dst = t.Y + (size_t)c0 * a.N + row;
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
@@ -884,6 +903,9 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
     tc_fence_before();
     __syncthreads();
     if (warp == PWARPS) tmem_dealloc(tmem_base, tmem_cols);
+    // row-sharded: all of this CTA's remote stores are issued and the CTA has met: one thread counts the CTA in, the
+    // last CTA of the grid fences and publishes (a CTA that gave up does not count: the peers' bounded waits report it)
+    if (a.push.n > 0 && threadIdx.x == 0 && !*(volatile int *)&abort_s) push_publish(a.push, gridDim.x);
 }
 
 }  // namespace qz

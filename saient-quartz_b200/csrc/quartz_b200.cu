@@ -704,6 +704,26 @@ static void gemv_noalloc(uint32_t t, const uint8_t *W, const float *x, float *y,
 // ---- batched GEMM on tcgen05 ------------------------------------------------------------------
 static __nv_bfloat16 *g_xb = nullptr;   // bf16 copy of the activation tile (library scratch, grows)
 static size_t g_xb_elems = 0;
+// row-sharded GEMM (cuda_gemm_push) when tiles are scarce: the block is computed into this scratch and copied out
+static float *g_gemm_ys = nullptr;
+static size_t g_gemm_ys_elems = 0;
+static bool ensure_gemm_push_scratch(size_t y_elems)
+{
+    if (y_elems <= g_gemm_ys_elems) return true;
+    if (g_gemm_ys) {
+        cudaStreamSynchronize(g_stream);
+        cudaFree(g_gemm_ys);
+    }
+    if (cudaMalloc(&g_gemm_ys, y_elems * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        g_gemm_ys = nullptr;
+        g_gemm_ys_elems = 0;
+        set_error(QZ_ERR_CUDA, "cuda_gemm_push: cudaMalloc of the local output scratch failed");
+        return false;
+    }
+    g_gemm_ys_elems = y_elems;
+    return true;
+}
 
 template <uint32_t T, bool PLANES, int HALVES>
 static void launch_gemm(GemmArgs a)
@@ -739,8 +759,28 @@ static void launch_gemm(GemmArgs a)
     long long sharers = ctas;
     if (sharers > (rem + 7) / 8) sharers = (rem + 7) / 8;
     a.units_per_cta = sharers > 0 ? (rem + sharers - 1) / sharers : 0;
-    if (whole == 0) ctas = (a.units + a.units_per_cta - 1) / a.units_per_cta;
-    if (rem > 0) {
+    bool zero_shared = rem > 0;
+    PushArgs copy_out;
+    copy_out.n = 0;
+    if (a.push.n > 0 && (whole >= 1 || (tiles * 2 >= ctas && ksteps <= 64))) {
+        // row-sharded with about one tile per CTA or more: whole tiles only (the tiles left over after the equal part
+        // go one each to the first CTAs), so every tile goes to the peers straight from its accumulator
+        if (whole == 0) {
+            ctas = tiles;
+            a.dp_units = 0;
+            a.rem_begin = 0;
+        }
+        a.units_per_cta = ksteps;
+        zero_shared = false;
+    } else if (a.push.n > 0) {
+        // tiles are scarce: sharing them between CTAs (K-wise) matters more than the fused epilogue.  The block is
+        // summed in local scratch as usual and a copy kernel stores it into the windows (measured faster than
+        // having the completing warp of every shared tile read its sums back and push them)
+        copy_out = a.push;
+        a.push.n = 0;
+    }
+    if (whole == 0 && a.push.n == 0) ctas = (a.units + a.units_per_cta - 1) / a.units_per_cta;
+    if (zero_shared) {
         // narrow token tiles are a few KB per tile: one block each; wide ones are split over up to 8
         const unsigned zero_slices = (unsigned)std::max(1, std::min(8, a.tok_tile / 32));
         gemm_zero_split_tiles_kernel<<<dim3((unsigned)ctas, zero_slices), 256, 0, g_stream>>>(a.Y, a.M, a.N, ksteps, a.n_tok_tiles, a.tok_tile,
@@ -749,6 +789,13 @@ static void launch_gemm(GemmArgs a)
     }
     gemm_tc_kernel<T, PLANES, HALVES><<<(unsigned)ctas, gemm_threads<HALVES>(), smem, g_stream>>>(a);
     QZ_LAUNCH_CHECK();
+    if (copy_out.n > 0) {
+        const long long total = (long long)a.M * a.N;
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > sm_count()) blocks = sm_count();
+        mgpu_push_rows_kernel<<<blocks, 256, 0, g_stream>>>(a.Y, a.M, a.N, a.push_ld, copy_out);
+        QZ_LAUNCH_CHECK();
+    }
 }
 
 template <uint32_t T, bool PLANES>
@@ -799,10 +846,13 @@ static void gemm_grouped_dispatch(uint32_t t, bool planes, const GemmArgs &a)
     }
 }
 
-static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y, int M, int K, int N, bool x_bf16 = false)
+// push != nullptr: row-sharded form (cuda_gemm_push): returns false, having launched nothing, when the tensor-core
+// kernel does not take the shape
+static bool gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y, int M, int K, int N, bool x_bf16 = false,
+                          const PushArgs *push = nullptr, long long push_off = 0, long long push_ld = 0)
 {
     const float *x = (const float *)xv;   // (bf16 input: only the tensor-core path below reads it)
-    if (M <= 0 || N <= 0) return;
+    if (M <= 0 || N <= 0) return false;
     const FormatInfo fi = format_info(t);
     // n == 1 is the GEMV (src/dequant.rs:151-153); shapes/types the tensor-core kernel does not take
     // run token by token (what the reference's GPU prefill does, src/main.rs:1410-1416)
@@ -810,8 +860,9 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y
                        !((uintptr_t)x & 15) && (((size_t)(K / fi.block_elems) * fi.block_bytes) % 16 == 0);
     if (x_bf16 && !tc_ok) {
         set_error(QZ_ERR_BAD_SHAPE, "cuda_gemm_bf16: in_dim must be a multiple of 64 and the pointers 16-byte aligned");
-        return;
+        return false;
     }
+    if (push && (M == 1 || !tc_ok)) return false;
     if (!x_bf16 && (M == 1 || !tc_ok)) {
         for (int tkn = 0; tkn < M; tkn++) {
             const uint8_t *Wp[1] = {W};
@@ -819,18 +870,18 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y
             float *yp[1] = {y + (size_t)tkn * N};
             gemv_n(t, 1, Wp, xp, yp, K, N);
         }
-        return;
+        return true;
     }
     if (!tables_ready(t)) {
-        QZ_CUDA_CHECK(cudaMemsetAsync(y, 0, (size_t)M * N * sizeof(float), g_stream));
+        if (!push) QZ_CUDA_CHECK(cudaMemsetAsync(y, 0, (size_t)M * N * sizeof(float), g_stream));
         set_error(QZ_ERR_MISSING_TABLE, "IQ codebook not uploaded (cuda_set_*_grid)");
-        return;
+        return false;
     }
     bool planes = false;
     if (const Range *r = find_range(W)) {
         if (r->type != t || r->K != K) {
             set_error(QZ_ERR_BAD_SHAPE, "cuda_gemm: pointer lies in a repacked range of another type/in_dim");
-            return;
+            return false;
         }
         planes = true;
     }
@@ -851,7 +902,7 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y
             g_xb = nullptr;
             g_xb_elems = 0;
             set_error(QZ_ERR_CUDA, "cudaMalloc of the bf16 activation scratch failed");
-            return;
+            return false;
         }
         g_xb_elems = need;
     }
@@ -871,7 +922,15 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y
     const bool fast = (t == T_Q4_K && !planes) || (planes && (t == T_Q6_K || t == T_IQ2_XS || t == T_IQ3_XXS));
     const int halves = (fast && a.tok_tile >= 128) ? 2 : 1;
     a.status = status_word();
-    if (!a.status) return;
+    if (!a.status) return false;
+    a.push.n = 0;
+    if (push) {
+        if (!ensure_gemm_push_scratch((size_t)m_pad * N)) return false;
+        a.push = *push;
+        a.push_off = push_off;
+        a.push_ld = push_ld;
+        a.Y = g_gemm_ys;
+    }
     switch (t) {
 #define X(TT)                                              \
     case TT:                                               \
@@ -882,6 +941,7 @@ static void gemm_dispatch(uint32_t t, const uint8_t *W, const void *xv, float *y
 #undef X
     default: break;
     }
+    return true;
 }
 
 }  // namespace qz
@@ -2415,6 +2475,15 @@ void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size
     if (blocks < 1) blocks = 1;
     mgpu_push_rows_kernel<<<blocks, 256, 0, g_stream>>>(d_src, m, n_local, (long long)dst_ld, p);
     QZ_LAUNCH_CHECK();
+}
+
+int cuda_gemm_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, int m, int in_dim, int out_dim,
+                   size_t dst_off, size_t dst_ld)
+{
+    if (m <= 0 || out_dim <= 0 || dst_ld < (size_t)out_dim) return 0;
+    PushArgs p;
+    if (!fill_push(p, dst_off, (size_t)(m - 1) * dst_ld + (size_t)out_dim)) return 0;
+    return gemm_dispatch(ggml_type, d_data, d_x, nullptr, m, in_dim, out_dim, false, &p, (long long)dst_off, (long long)dst_ld) ? 1 : 0;
 }
 
 void cuda_gemv_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, size_t dst_off, int in_dim, int out_dim)

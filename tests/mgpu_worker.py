@@ -92,6 +92,40 @@ def main():
         tol = 1e-3 * norms * float(np.linalg.norm(X[m].astype(np.float64)))
         assert np.all(np.abs(Y[m].astype(np.float64) - ref[m]) <= tol), f"rank {rank} gemm token {m}"
 
+    # the same block, and larger ones, with the exchange in the GEMM's own epilogue (cuda_gemm_push): the tensor-core
+    # tiles go from the accumulators straight into every rank's window; ragged row counts, several token tiles,
+    # Q4_K (raw layout), Q6_K (plane layout, 256-row tiles at 128+ tokens)
+    for ci, (t, K, N, M) in enumerate([(12, 2048, 768, 24), (14, 2048, 1000, 300), (12, 4096, 1536, 130)]):
+        w = synth.make_weights(t, K, N, tensor_id=992 + ci)
+        X = synth.make_x(K, tensor_id=996 + ci, rows=M)
+        n0, n1, per = shard_rows(N, rank, world)
+        b0, b1 = shard_bytes(t, K, N, rank, world)
+        dwp, dxp = q.GpuBuf.upload(w[b0:b1]), q.GpuBuf.upload(X)
+        if t == 14:
+            L.cuda_repack_weights(t, dwp.ptr, K, n1 - n0, 1)
+        off = 500000 if ci & 1 else 65536
+        for rep in range(2):
+            L.cuda_vec_zero(win.data_ptr + 4 * off, M * N)
+            L.cuda_sync()
+            if world > 1:
+                dist.barrier()   # nobody pushes into a region another rank is still clearing
+            assert L.cuda_gemm_push(t, dwp.ptr, dxp.ptr, M, K, n1 - n0, off + n0, N) == 1, L.quartz_error_string()
+            win.wait()
+            L.cuda_sync()
+            q.check_error("gemm push (epilogue)")
+            Y = download(off, M * N).reshape(M, N)
+            ref = oracle.gemm(X, w, t, K, N, M)
+            norms = oracle.row_norms(w, t, K, N)
+            for m in range(M):
+                tol = 1e-3 * norms * float(np.linalg.norm(X[m].astype(np.float64)))
+                assert np.all(np.abs(Y[m].astype(np.float64) - ref[m]) <= tol), f"rank {rank} gemm_push case {ci} token {m}"
+            if world > 1:
+                dist.barrier()
+        dwp.drop()
+        dxp.drop()
+    # a single token is not taken by the tensor-core kernel: nothing is launched, the caller uses the GEMV form
+    assert L.cuda_gemm_push(12, dw.ptr, dx.ptr, 1, 2048, 8, 65536, 768) == 0
+
     # a chain whose second GEMV reads the first one's gathered output, the wait fused into its conversion
     K, N1, N2 = 2048, 4096, 1024
     wa, wb = synth.make_weights(12, K, N1, tensor_id=970), synth.make_weights(14, N1, N2, tensor_id=971)
