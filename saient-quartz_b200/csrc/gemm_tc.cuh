@@ -14,7 +14,7 @@
 //     layout tcgen05.mma reads (raw bytes of the thread's next step are loaded into registers while the
 //     current one is unpacked; Q4_K / Q6_K use packed bf16x2 arithmetic: nibble|0x4300 is the bf16
 //     128+q, an exact HSUB2 removes the 128, one HFMA2 applies scale and min; IQ2_XS / IQ3_XXS read
-//     bf16 grids and sign masks from shared-memory tables), and one thread starts the bulk async copy
+//     bf16 grids and sign bytes from shared-memory tables), and one thread starts the bulk async copy
 //     of the step's pre-swizzled bf16 activation tile;
 //   * they fence the generic->async proxy and arrive on the stage's "full" mbarrier;
 //   * one elected thread issues four tcgen05.mma per accumulator (K=16 each, kind::f16, bf16 x bf16 ->
@@ -375,21 +375,25 @@ struct AProd<T_Q6_K, true> {
 };
 
 // ---- codebook formats: the grids are kept in shared memory already converted to bf16 and already in
-//      tile order ((w0,w2),(w1,w3) per four weights), next to a table of sign-bit masks per 7-bit sign
-//      index in the same order.  Eight weights then cost two table reads, four XORs and four HMUL2s. ----
+//      tile order ((w0,w2),(w1,w3) per four weights), next to the 128 sign bytes.  Eight weights then cost
+//      one or two grid reads, one byte read, the mask arithmetic, four XORs and four HMUL2s. ----
 __device__ __forceinline__ uint32_t bf16x2_of(float a, float b)
 {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *(uint32_t *)&v;
 }
-// entry i of the sign table: XOR masks for eight weights, words (s0,s2) (s1,s3) (s4,s6) (s5,s7)
-__device__ __forceinline__ void build_sign_table(uint4 *dst, int tid, int n)
+// The sign bytes (one bit per weight of a group of eight) are kept in shared memory as they are: 128 bytes, one
+// row of banks, so a warp's 32 random reads never conflict.  sign_masks() spreads a byte into the XOR masks of the
+// eight bf16 weights in tile order, words (s0,s2) (s1,s3) (s4,s6) (s5,s7): a dozen integer instructions instead
+// of a 16-byte table entry per group (random 16-byte reads conflict two- to three-fold).
+__device__ __forceinline__ void build_sign_table(uint8_t *dst, int tid, int n)
 {
-    for (int i = tid; i < 128; i += n) {
-        const uint32_t s = g_ksigns[i];
-        auto m = [&](int a, int b) { return (((s >> a) & 1u) << 15) | (((s >> b) & 1u) << 31); };
-        dst[i] = make_uint4(m(0, 2), m(1, 3), m(4, 6), m(5, 7));
-    }
+    for (int i = tid; i < 128; i += n) dst[i] = g_ksigns[i];
+}
+__device__ __forceinline__ uint4 sign_masks(uint32_t s)
+{
+    return make_uint4(((s & 1u) << 15) | ((s & 4u) << 29), ((s & 2u) << 14) | ((s & 8u) << 28),
+                      ((s & 16u) << 11) | ((s & 64u) << 25), ((s & 32u) << 10) | ((s & 128u) << 24));
 }
 __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, __nv_bfloat162 s)
 {
@@ -403,7 +407,7 @@ template <>
 struct AProd<T_IQ2_XS, true> {
     struct Raw { uint4 q; uint32_t sc, d; };
     static constexpr bool TWO_SETS = true;
-    static constexpr int TABLE_BYTES = 512 * 16 + 128 * 16;
+    static constexpr int TABLE_BYTES = 512 * 16 + 128;
     __device__ static void build_table(uint8_t *tbl, int tid, int n)
     {
         uint4 *g = (uint4 *)tbl;
@@ -412,7 +416,7 @@ struct AProd<T_IQ2_XS, true> {
             auto b = [&](int j) { return (float)(int)(int8_t)(v >> (8 * j)); };
             g[i] = make_uint4(bf16x2_of(b(0), b(2)), bf16x2_of(b(1), b(3)), bf16x2_of(b(4), b(6)), bf16x2_of(b(5), b(7)));
         }
-        build_sign_table(g + 512, tid, n);
+        build_sign_table((uint8_t *)(g + 512), tid, n);
     }
     __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
     {
@@ -428,7 +432,8 @@ struct AProd<T_IQ2_XS, true> {
     }
     __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int, int r, const uint8_t *tbl)
     {
-        const uint4 *grid = (const uint4 *)tbl, *sign = grid + 512;
+        const uint4 *grid = (const uint4 *)tbl;
+        const uint8_t *sign = (const uint8_t *)(grid + 512);
         const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
         const float d = 0.25f * h2f((uint16_t)w.d);
 #pragma unroll
@@ -437,7 +442,7 @@ struct AProd<T_IQ2_XS, true> {
             const uint32_t nib = (w.sc >> (8 * (l >> 2) + 4 * ((l >> 1) & 1))) & 0xF;
             const float db = d * (0.5f + (float)nib);
             const __nv_bfloat162 s2 = __floats2bfloat162_rn(db, db);
-            const uint4 g = grid[q & 511], m = sign[q >> 9];
+            const uint4 g = grid[q & 511], m = sign_masks(sign[q >> 9]);
             *(uint4 *)(As + sw128(r, l)) = make_uint4(hmul2_bits(g.x ^ m.x, s2), hmul2_bits(g.y ^ m.y, s2),
                                                       hmul2_bits(g.z ^ m.z, s2), hmul2_bits(g.w ^ m.w, s2));
         }
@@ -450,7 +455,7 @@ template <>
 struct AProd<T_IQ3_XXS, true> {
     struct Raw { uint4 q; uint2 sas; uint32_t d; };
     static constexpr bool TWO_SETS = true;
-    static constexpr int TABLE_BYTES = 256 * 8 + 128 * 16;
+    static constexpr int TABLE_BYTES = 256 * 8 + 128;
     __device__ static void build_table(uint8_t *tbl, int tid, int n)
     {
         uint2 *g = (uint2 *)tbl;
@@ -459,7 +464,7 @@ struct AProd<T_IQ3_XXS, true> {
             auto b = [&](int j) { return (float)((v >> (8 * j)) & 0xFF); };
             g[i] = make_uint2(bf16x2_of(b(0), b(2)), bf16x2_of(b(1), b(3)));
         }
-        build_sign_table((uint4 *)(tbl + 256 * 8), tid, n);
+        build_sign_table(tbl + 256 * 8, tid, n);
     }
     __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
     {
@@ -477,7 +482,7 @@ struct AProd<T_IQ3_XXS, true> {
     __device__ static void store(uint8_t *As, const Raw &w, const uint8_t *, int, int, int r, const uint8_t *tbl)
     {
         const uint2 *grid = (const uint2 *)tbl;
-        const uint4 *sign = (const uint4 *)(tbl + 256 * 8);
+        const uint8_t *sign = tbl + 256 * 8;
         const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
         const float d = 0.5f * h2f((uint16_t)w.d);
 #pragma unroll
@@ -489,7 +494,7 @@ struct AProd<T_IQ3_XXS, true> {
             for (int l = 0; l < 4; l++) {
                 const uint32_t two = (qw[2 * h + (l >> 1)] >> (16 * (l & 1))) & 0xFFFF;   // index bytes 2l, 2l+1
                 const uint2 g1 = grid[two & 0xFF], g2 = grid[two >> 8];
-                const uint4 m = sign[(a1 >> (7 * l)) & 127];
+                const uint4 m = sign_masks(sign[(a1 >> (7 * l)) & 127]);
                 *(uint4 *)(As + sw128(r, 4 * h + l)) = make_uint4(hmul2_bits(g1.x ^ m.x, s2), hmul2_bits(g1.y ^ m.y, s2),
                                                                   hmul2_bits(g2.x ^ m.z, s2), hmul2_bits(g2.y ^ m.w, s2));
             }

@@ -553,6 +553,25 @@ def test_attn_step_matches_separate_launches(gpu, neox):
             assert np.abs(got - want).max() <= 2e-5 * max(np.abs(want).max(), 1e-30), (nh, nkv, hd, pos, rep)
         assert np.array_equal(dk2.download(), want_k) and np.array_equal(dv2.download(), want_v)
         assert np.array_equal(dq2.download(), q) and np.array_equal(dkn2.download(), k)
+    # the (cos, sin) table belongs to the position cuda_step_set wrote: when the position word is changed behind its
+    # back (a plain copy), the kernel notices that the table is for another position and computes the rotation itself
+    nh, nkv, hd, max_seq = 32, 8, 128, 256
+    kv_dim = nkv * hd
+    kc, vc = r.standard_normal((max_seq, kv_dim), dtype=np.float32), r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+    q, k, v = (r.standard_normal(n, dtype=np.float32) for n in (nh * hd, kv_dim, kv_dim))
+    theta, scale = np.float32(500000.0), np.float32(1.0 / np.sqrt(hd))
+    outs = []
+    for stale in (False, True):
+        dk, dv, dq, dkn, dvn = (gpu.GpuBuf.upload(a) for a in (kc, vc, q, k, v))
+        o = gpu.GpuBuf.alloc_f32(nh * hd)
+        L.cuda_step_set(step_words.ptr, 3, 17 if stale else 200)
+        if stale:
+            words = np.array([3, 200], dtype=np.int32)
+            L.cuda_h2d(step_words.ptr, words.ctypes.data, 8)
+        L.cuda_attn_step(o.ptr, dq.ptr, dkn.ptr, dvn.ptr, dk.ptr, dv.ptr, nh, nkv, hd, max_seq, step_words.ptr, 0, 0, scale,
+                         None, theta, np.float32(1.0), 0, neox, -1)
+        outs.append((o.download(), dk.download()[200].copy()))
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
     # the activation form it leaves for the output projection equals the conversion of its f32 output
     nh, nkv, hd, pos, max_seq = 32, 8, 128, 70, 96
     kv_dim, K, N = nkv * hd, nh * hd, 256
