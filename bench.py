@@ -276,7 +276,8 @@ def gemv_shape_rows(q, L, torch, np, shapes, mats, xs, with_ref, want_parity):
 
 def gemm_section(q, args, torch, np, want_parity, only=None):
     """Batched dequant-GEMM for prefill: Q4_K 4096->14336 and Q6_K 14336->4096 times M = 16, 64, 512, 2048
-    f32 activations ~ N(0,1) (bf16 inside the tensor-core tile, f32 accumulation in TMEM)."""
+    f32 activations ~ N(0,1) (bf16 inside the tensor-core tile, f32 accumulation in TMEM); the bf16-activation
+    entry point is timed beside it."""
     from saient_quartz_b200 import synth
     L = q.lib()
     peaks_file = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -318,6 +319,19 @@ def gemm_section(q, args, torch, np, want_parity, only=None):
                    "gbs": nbytes / ms / 1e6, "frac_of_measured_bf16_burst": flops / ms / 1e9 / tf_burst,
                    "frac_of_measured_bf16_sustained": flops / ms / 1e9 / tf_sust,
                    "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm, "bound": "hbm" if M <= 64 else "tensor"}
+            # the same GEMM fed bf16 activations (cuda_gemm_bf16: what a host that keeps bf16 activations calls)
+            xb16 = torch.from_numpy(X).to(torch.bfloat16).cuda().contiguous()
+            for _ in range(2):
+                L.cuda_gemm_bf16(t, dw.ptr, xb16.data_ptr(), dy.ptr, M, K, N)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(reps):
+                L.cuda_gemm_bf16(t, dw.ptr, xb16.data_ptr(), dy.ptr, M, K, N)
+            e1.record()
+            torch.cuda.synchronize()
+            row["ms_bf16_activations"] = e0.elapsed_time(e1) / reps
+            q.check_error("gemm bf16")
+            L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, N)   # (the parity check below reads the f32 form's output)
             if want_parity and M in (16, 512):
                 import oracle
                 y = dy.download().reshape(M, N)
