@@ -448,6 +448,11 @@ int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_of
 int cuda_gemv_chain_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off, const size_t *dst_stride);
 void quartz_mgpu_wait(void);
 void quartz_mgpu_fuse_next_wait(void);
+/* The next cuda_gemv_batch_push / cuda_gemv_chain_push / cuda_gemm_push completes its own exchange: the thread that
+ * publishes then waits (bounded, ~0.5 s, QZ_ERR_TIMEOUT) until every rank has published as many exchanges, so the
+ * kernel's end is the exchange's end and no quartz_mgpu_wait() launch is needed after it.  Every rank must have
+ * launched the same call (the ranks run on different GPUs). */
+void quartz_mgpu_wait_in_next_push(void);
 void quartz_mgpu_shutdown(void);
 
 #ifdef __cplusplus

@@ -126,6 +126,7 @@ _SIGS = {
     "quartz_mgpu_data": (C.c_void_p, []),
     "cuda_gemv_push": (None, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int]),
     "cuda_gemv_batch_push": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p]),
+    "quartz_mgpu_wait_in_next_push": (None, []),
     "cuda_gemm_push": (C.c_int, [C.c_uint32, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_size_t]),
     "cuda_gemv_chain_push": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cuda_push_rows": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_size_t]),

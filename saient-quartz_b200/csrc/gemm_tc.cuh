@@ -910,7 +910,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
     if (warp == PWARPS) tmem_dealloc(tmem_base, tmem_cols);
     // row-sharded: all of this CTA's remote stores are issued and the CTA has met: one thread counts the CTA in, the
     // last CTA of the grid fences and publishes (a CTA that gave up does not count: the peers' bounded waits report it)
-    if (a.push.n > 0 && threadIdx.x == 0 && !*(volatile int *)&abort_s) push_publish(a.push, gridDim.x);
+    if (a.push.n > 0 && threadIdx.x == 0 && !*(volatile int *)&abort_s) push_publish(a.push, gridDim.x, a.status, true);
 }
 
 }  // namespace qz

@@ -470,7 +470,7 @@ __global__ void __launch_bounds__(TMA_CONSUMERS + 32, 1) gemv_chain_kernel(const
     if (unpublished) {
         // all of this CTA's remote stores are issued: meet, then one thread fences them and counts the CTA in
         named_bar_sync(13, TMA_CONSUMERS);
-        if (threadIdx.x == 0 && !*dead_flag) push_publish(a.push, gridDim.x);
+        if (threadIdx.x == 0 && !*dead_flag) push_publish(a.push, gridDim.x, a.status, true);
     }
 }
 

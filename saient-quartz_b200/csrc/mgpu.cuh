@@ -42,6 +42,8 @@ struct PushArgs {
     int n;                            // ranks (0 = no push: plain local store)
     int rank;
     long long dst_off;                // element offset of row 0 of this slice inside the data area
+    int wait_after;                   // 1: the thread that publishes then waits (bounded) until every rank has published
+                                      //    as many exchanges, so the kernel's end is the exchange's end (no wait launch)
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int *p)
@@ -60,7 +62,7 @@ __device__ __forceinline__ void st_relaxed_sys(int *p, int v)
 // cumulative over the other threads' stores, and the last CTA to count in has thereby acquired every
 // CTA's stores.  That CTA publishes the exchange: one system-scope fence, then the new counter
 // stored into every rank's flag array.
-__device__ __forceinline__ void push_publish(const PushArgs &p, int total_ctas)
+__device__ __forceinline__ void push_publish(const PushArgs &p, int total_ctas, int *status = nullptr, bool may_wait = false)
 {
     MgpuCtrl *mine = p.ctrl[p.rank];
     int prev;
@@ -73,6 +75,19 @@ __device__ __forceinline__ void push_publish(const PushArgs &p, int total_ctas)
         // (a few microseconds each) once per rank
         __threadfence_system();
         for (int r = 0; r < p.n; r++) st_relaxed_sys(&p.ctrl[r]->flags[p.rank], e);
+        if (may_wait && p.wait_after) {
+            // the exchange is complete once every rank's flag has reached this rank's own count; bounded like every wait
+            const long long t0 = clock64();
+            for (int r = 0; r < p.n; r++) {
+                while (ld_acquire_sys(&mine->flags[r]) - e < 0) {
+                    if (clock64() - t0 > MGPU_WAIT_CYCLES) {
+                        if (status) atomicExch(status, QZ_ERR_TIMEOUT);
+                        return;
+                    }
+                    __nanosleep(64);
+                }
+            }
+        }
     }
 }
 

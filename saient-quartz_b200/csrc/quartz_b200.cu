@@ -793,8 +793,14 @@ static void launch_gemm(GemmArgs a)
         const long long total = (long long)a.M * a.N;
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count()) blocks = sm_count();
+        const bool wait_after = copy_out.wait_after != 0;
+        copy_out.wait_after = 0;
         mgpu_push_rows_kernel<<<blocks, 256, 0, g_stream>>>(a.Y, a.M, a.N, a.push_ld, copy_out);
         QZ_LAUNCH_CHECK();
+        if (wait_after) {   // (this form has no kernel that could carry the wait)
+            mgpu_wait_kernel<<<1, 32, 0, g_stream>>>((const MgpuCtrl *)copy_out.ctrl[copy_out.rank], copy_out.n, a.status);
+            QZ_LAUNCH_CHECK();
+        }
     }
 }
 
@@ -1501,13 +1507,17 @@ void cuda_gemv_batch(int n_ops, const qz_chain_op *ops) { gemv_chain_launch(n_op
 
 static bool fill_push(PushArgs &p, size_t dst_off, size_t elems);
 static bool mgpu_is_attached();
+static bool push_wait_after_take();   // the pending quartz_mgpu_wait_in_next_push request, cleared
 
 int cuda_gemv_batch_push(int n_ops, const qz_chain_op *ops, const size_t *dst_off)
 {
     if (n_ops <= 0 || !ops || !dst_off) return 0;
     static ChainArgs probe;   // (large: kept off the stack)
     size_t smem = 0;
-    if (!chain_plan(n_ops, ops, probe, smem, 1, dst_off)) return 0;
+    if (!chain_plan(n_ops, ops, probe, smem, 1, dst_off)) {
+        push_wait_after_take();   // (a pending request belongs to this call, launched or not)
+        return 0;
+    }
     gemv_chain_launch(n_ops, ops, 1, dst_off);
     return 1;
 }
@@ -1521,7 +1531,10 @@ int cuda_gemv_chain_push(int n_ops, const qz_chain_op *ops, const size_t *dst_of
     }
     static ChainArgs probe;   // (large: kept off the stack)
     size_t smem = 0;
-    if (!chain_plan(n_ops, ops, probe, smem, 0, dst_off, dst_stride)) return 0;
+    if (!chain_plan(n_ops, ops, probe, smem, 0, dst_off, dst_stride)) {
+        push_wait_after_take();
+        return 0;
+    }
     gemv_chain_launch(n_ops, ops, 0, dst_off, dst_stride);
     return 1;
 }
@@ -1553,6 +1566,7 @@ static void gemv_chain_launch(int n_ops, const qz_chain_op *ops, int independent
         for (int k = 0; k < n_ops; k++)
             hi = std::max(hi, push_off[k] + (push_stride ? push_stride[k] * (size_t)(ops[k].n_mats - 1) : 0) + (size_t)ops[k].out_dim);
         if (!fill_push(a.push, 0, hi)) return;
+        a.push.wait_after = push_wait_after_take() ? 1 : 0;
     }
     if (!g_grid_barrier) {
         if (cudaMalloc(&g_grid_barrier, sizeof(GridBarrier)) != cudaSuccess) {
@@ -2459,7 +2473,26 @@ static bool fill_push(PushArgs &p, size_t dst_off, size_t elems)
     p.n = g_mg_world;
     p.rank = g_mg_rank;
     p.dst_off = (long long)dst_off;
+    p.wait_after = 0;
     return true;
+}
+
+// set by quartz_mgpu_wait_in_next_push: the next cuda_gemv_batch_push / cuda_gemv_chain_push / cuda_gemm_push kernel
+// completes its own exchange before it ends
+static bool g_push_wait_after = false;
+static bool push_wait_after_take()
+{
+    const bool v = g_push_wait_after;
+    g_push_wait_after = false;
+    return v;
+}
+void quartz_mgpu_wait_in_next_push(void)
+{
+    if (!g_mg_attached) {
+        set_error(QZ_ERR_BAD_SHAPE, "quartz_mgpu_wait_in_next_push: the windows are not attached");
+        return;
+    }
+    g_push_wait_after = true;
 }
 
 void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size_t dst_ld)
@@ -2483,6 +2516,7 @@ int cuda_gemm_push(uint32_t ggml_type, const uint8_t *d_data, const float *d_x, 
     if (m <= 0 || out_dim <= 0 || dst_ld < (size_t)out_dim) return 0;
     PushArgs p;
     if (!fill_push(p, dst_off, (size_t)(m - 1) * dst_ld + (size_t)out_dim)) return 0;
+    p.wait_after = push_wait_after_take() ? 1 : 0;
     return gemm_dispatch(ggml_type, d_data, d_x, nullptr, m, in_dim, out_dim, false, &p, (long long)dst_off, (long long)dst_ld) ? 1 : 0;
 }
 

@@ -172,9 +172,12 @@ def main():
         base_off += (N + 63) & ~63
     arr = (q.ChainOp * len(ops))(*ops)
     off_arr = (C.c_size_t * len(ops))(*offs)
-    for rep in range(2):
+    for rep in range(3):
+        if rep == 2:    # the exchange completed inside the kernel itself: no wait launch
+            L.quartz_mgpu_wait_in_next_push()
         assert L.cuda_gemv_batch_push(len(ops), arr, off_arr) == 1
-        win.wait()
+        if rep < 2:
+            win.wait()
         L.cuda_sync()
         q.check_error("batch push")
         for (t, K, N, w, x, dw, dxb, dummy, o) in keep:
