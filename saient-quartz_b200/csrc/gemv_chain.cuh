@@ -121,11 +121,15 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
                                               const XQ &xq, RingPos &rp, int *status, volatile int *cta_dead,
                                               const PushArgs &push)
 {
+    // the fields of the op that the loops below use, in registers (the op sits in the kernel's parameter space and
+    // is picked with a run-time index)
+    const int op_n_cta = op.n_cta, op_RP = op.RP, op_N = op.N, op_acc = op.accumulate;
+    const long long op_push_off = op.push_off, op_push_stride = op.push_stride;
     const FormatInfo fi = format_info(F::TYPE);
     const int nb = op.K / fi.block_elems;
     const int row_bytes = nb * fi.block_bytes;
-    const int ntiles = (op.N + op.RP - 1) / op.RP;
-    const int n_consumers = op.Upad * op.RP;
+    const int ntiles = (op_N + op_RP - 1) / op_RP;
+    const int n_consumers = op.Upad * op_RP;
     const bool worker = (int)threadIdx.x < n_consumers;
     const int u = threadIdx.x % op.Upad, rl = threadIdx.x / op.Upad;
     const bool active = worker && u < op.U;
@@ -136,7 +140,7 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
     typename F::XRegs xr;
     F::load_x(xr, xq, active ? u : 0);
     const typename F::Off off = F::make_off(nb, active ? u : 0);
-    const int my_tiles = cta < op.n_cta ? (ntiles - cta + op.n_cta - 1) / op.n_cta : 0;
+    const int my_tiles = cta < op_n_cta ? (ntiles - cta + op_n_cta - 1) / op_n_cta : 0;
     const uint32_t ring0 = smem_u32(ring), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     const uint32_t row_off = (uint32_t)((worker ? rl : 0) * row_bytes);
     const uint32_t stage = chain_stage_bytes(op);
@@ -169,13 +173,13 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
             }
         }
         if (!worker) continue;   // (whole warps: n_consumers is a multiple of 32)
-        const int row_j0 = (cta + t0 * op.n_cta) * op.RP + rl, row_step = op.n_cta * op.RP;
+        const int row_j0 = (cta + t0 * op_n_cta) * op_RP + rl, row_step = op_n_cta * op_RP;
         auto store_y = [&](int row, float v) {
             if (*cta_dead) return;   // a warp of this CTA gave up: its rows are incomplete
-            if (op.push_off >= 0) {
-                for (int rk = 0; rk < push.n; rk++) push.data[rk][op.push_off + m * op.push_stride + row] = v;
+            if (op_push_off >= 0) {
+                for (int rk = 0; rk < push.n; rk++) push.data[rk][op_push_off + m * op_push_stride + row] = v;
             } else {
-                y[row] = op.accumulate ? __ldcg(y + row) + v : v;
+                y[row] = op_acc ? __ldcg(y + row) + v : v;
             }
         };
         const float v = warp_sum4(active ? acc[0] : 0.f, active ? acc[1] : 0.f, active ? acc[2] : 0.f, active ? acc[3] : 0.f,
@@ -183,7 +187,7 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
         const int j = lane >> 3;
         if (MODE == 1) {
             const int row = row_j0 + j * row_step;
-            if ((lane & 7) == 0 && t0 + j < my_tiles && row < op.N) store_y(row, v);
+            if ((lane & 7) == 0 && t0 + j < my_tiles && row < op_N) store_y(row, v);
         } else {
             float *p = part[(t0 >> 2) & 1] + rl * wpr * 4;
             if ((lane & 7) == 0) p[j * wpr + wir] = v;
@@ -192,7 +196,7 @@ __device__ __forceinline__ bool chain_consume(const ChainOp &op, int m, int cta,
                 float t = 0.f;
                 for (int k = 0; k < wpr; k++) t += p[lane * wpr + k];
                 const int row = row_j0 + lane * row_step;
-                if (t0 + lane < my_tiles && row < op.N) store_y(row, t);
+                if (t0 + lane < my_tiles && row < op_N) store_y(row, t);
             }
         }
     }
