@@ -262,7 +262,11 @@ int cuda_gemv_chain_supported(int n_ops, const qz_chain_op *ops);
 void cuda_gemv_chain(int n_ops, const qz_chain_op *ops);
 /* The same kernel for GEMVs that do NOT depend on one another (no op reads what another writes): no
  * barrier between them, the weight stream runs through all of them without a break.  The
- * generalisation of cuda_gemv_moe4 (src/cuda.rs:39-45) to matrices of different shapes and types. */
+ * generalisation of cuda_gemv_moe4 (src/cuda.rs:39-45) to matrices of different shapes and types.
+ * Plain-f32 activation vectors (src_mode 3) are converted by ONE small kernel ahead of the persistent one, into a
+ * library scratch that is allocated at the first call (make that call outside a graph recording); the ops may
+ * be run in any order inside the kernel.  Ops the persistent kernel does not take (cuda_gemv_chain_supported
+ * tells) make the call run GEMV by GEMV with the same results. */
 void cuda_gemv_batch(int n_ops, const qz_chain_op *ops);
 
 /* The whole attention block of one decode step as ONE launch (two when the context spans more than 8
