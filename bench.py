@@ -296,6 +296,15 @@ def gemm_section(q, args, torch, np, want_parity, only=None):
         w = synth.make_weights(t, K, N, tensor_id=400 + t)
         dw = q.GpuBuf.upload(w)
         L.cuda_repack_weights(t, dw.ptr, K, N, 1)
+        # The small-M rows are HBM-bound by definition, so they must stream from HBM: the timed loop rotates over
+        # copies of the matrix that together exceed the 126 MB L2 (one 33 / 48 MB matrix would simply stay in L2).
+        n_copies = int(np.ceil(150e6 / w.nbytes)) + 1
+        extra = []
+        for _ in range(n_copies - 1):
+            b = q.GpuBuf.upload(w)
+            L.cuda_repack_weights(t, b.ptr, K, N, 1)
+            extra.append(b)
+        ring = [dw] + extra
         for M in (16, 64, 512, 2048):
             if only and M != only[1]:
                 continue
@@ -304,11 +313,11 @@ def gemm_section(q, args, torch, np, want_parity, only=None):
             for _ in range(2):
                 L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, N)
             torch.cuda.synchronize()
-            reps = 10 if M <= 64 else 5
+            reps = 2 * len(ring) if M <= 64 else 5
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for _ in range(reps):
-                L.cuda_gemm(t, dw.ptr, dx.ptr, dy.ptr, M, K, N)
+            for i in range(reps):
+                L.cuda_gemm(t, (ring[i % len(ring)] if M <= 64 else dw).ptr, dx.ptr, dy.ptr, M, K, N)
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / reps
@@ -349,9 +358,12 @@ def gemm_section(q, args, torch, np, want_parity, only=None):
                     oracle.gemm(X, w, t, K, N, M)
                     row["cpu_oracle_ms"] = (time.perf_counter() - tc0) * 1e3
                     row["cpu_cores"] = oracle.max_threads()
+            if M <= 64:
+                row["weights"] = f"rotating over {len(ring)} copies of the matrix (> L2): every launch streams from HBM"
             out.append(row)
             dx.drop(); dy.drop()
-        dw.drop()
+        for b in ring:
+            b.drop()
     return out
 
 

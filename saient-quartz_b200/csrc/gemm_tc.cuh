@@ -231,6 +231,17 @@ __device__ __forceinline__ void bytes4_to_bf16(uint32_t v, __nv_bfloat162 bias, 
     o13 = *(uint32_t *)&b;
 }
 
+// L2 prefetch of a row's bytes a few blocks ahead of the loads: one thread walks one weight row, 16 to 48 bytes per
+// K step, so without it every load is a full HBM round trip and only a few KB per SM are ever in flight (the
+// kernel then runs at a few percent of the DRAM bandwidth, bound by that latency).  `pf` 256-weight blocks ahead
+// (GEMM_PF_BLOCKS, or 0 = off), issued once per block by the thread that handles the block's first K step; never
+// past the row's end.
+#ifndef QZ_GEMM_PF_BLOCKS
+#define QZ_GEMM_PF_BLOCKS 2
+#endif
+constexpr int GEMM_PF_BLOCKS = QZ_GEMM_PF_BLOCKS;
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // ---- A-tile producers: one thread per weight row and K step (64 weights = the tile row's eight
 //      16-byte chunks).  load() only issues the global loads of a K step into registers, so they
 //      are in flight while the thread's previous step is unpacked; store() unpacks to bf16 and
@@ -241,7 +252,7 @@ struct AProd {   // generic: any format, either layout, through the bit-exact de
     static constexpr bool TWO_SETS = false;
     static constexpr int TABLE_BYTES = 0;
     __device__ static void build_table(uint8_t *, int, int) {}
-    __device__ static void load(Raw &, const uint8_t *, int, int) {}
+    __device__ static void load(Raw &, const uint8_t *, int, int, int) {}
     __device__ static void store(uint8_t *As, const Raw &, const uint8_t *rowp, int nb, int kstep, int r, const uint8_t *)
     {
         const FormatInfo fi = format_info(T);
@@ -279,11 +290,13 @@ struct AProd<T_Q4_K, false> {
     static constexpr bool TWO_SETS = true;
     static constexpr int TABLE_BYTES = 0;
     __device__ static void build_table(uint8_t *, int, int) {}
-    __device__ static void load(Raw &w, const uint8_t *rowp, int, int kstep)
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep, int pf)
     {
         if (rowp) {
             const uint8_t *blk = rowp + (size_t)(kstep >> 2) * 144;
             const int p = kstep & 3;
+            // (144-byte blocks: the line that holds a block's last byte is the one no earlier block has asked for)
+            if (pf > 0 && p == 0 && (kstep >> 2) + pf < nb) prefetch_l2(blk + pf * 144 + 143);
             w.hdr = __ldg((const uint4 *)blk);
             w.q0 = __ldg((const uint4 *)(blk + 16 + 32 * p));
             w.q1 = __ldg((const uint4 *)(blk + 32 + 32 * p));
@@ -332,10 +345,15 @@ struct AProd<T_Q6_K, true> {
     static constexpr bool TWO_SETS = true;
     static constexpr int TABLE_BYTES = 0;
     __device__ static void build_table(uint8_t *, int, int) {}
-    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep, int pf)
     {
         if (rowp) {
             const int b = kstep >> 2, n = (kstep >> 1) & 1, lh = kstep & 1;
+            if (pf > 0 && (kstep & 3) == 0 && b + pf < nb) {   // ql: one line per block; qh: one line per two blocks
+                prefetch_l2(rowp + (size_t)(b + pf) * 128);
+                if ((b & 1) == 0) prefetch_l2(rowp + (size_t)nb * 128 + (size_t)(b + pf) * 64);
+                if ((b & 7) == 0) prefetch_l2(rowp + (size_t)nb * 192 + (size_t)(b + pf) * 16);
+            }
             const uint8_t *pl = rowp + (size_t)b * 128 + 64 * n + 16 * lh;
             w.a0 = __ldg((const uint4 *)pl);            // runs 0 (low nibbles) and 2 (high nibbles)
             w.a1 = __ldg((const uint4 *)(pl + 32));     // runs 1 and 3
@@ -418,10 +436,12 @@ struct AProd<T_IQ2_XS, true> {
         }
         build_sign_table((uint8_t *)(g + 512), tid, n);
     }
-    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep, int pf)
     {
         if (rowp) {
             const int b = kstep >> 2, p = kstep & 3;
+            if (pf > 0 && p == 0 && (b & 1) == 0 && b + pf < nb)   // qs: one 128-byte line per two blocks
+                prefetch_l2(rowp + (size_t)nb * 2 + (size_t)(b + pf) * 64);
             w.q = __ldg((const uint4 *)(rowp + (size_t)nb * 2 + (size_t)b * 64 + 16 * p));
             w.sc = __ldg((const uint16_t *)(rowp + (size_t)nb * 66 + (size_t)b * 8 + 2 * p));
             w.d = __ldg((const uint16_t *)(rowp + (size_t)b * 2));
@@ -466,10 +486,14 @@ struct AProd<T_IQ3_XXS, true> {
         }
         build_sign_table(tbl + 256 * 8, tid, n);
     }
-    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep)
+    __device__ static void load(Raw &w, const uint8_t *rowp, int nb, int kstep, int pf)
     {
         if (rowp) {
             const int b = kstep >> 2, p = kstep & 3;
+            if (pf > 0 && p == 0 && (b & 1) == 0 && b + pf < nb) {   // qs: a line per two blocks; signs/scales: per four
+                prefetch_l2(rowp + (size_t)nb * 2 + (size_t)(b + pf) * 64);
+                if ((b & 3) == 0) prefetch_l2(rowp + (size_t)nb * 66 + (size_t)(b + pf) * 32);
+            }
             w.q = __ldg((const uint4 *)(rowp + (size_t)nb * 2 + (size_t)b * 64 + 16 * p));
             w.sas = __ldg((const uint2 *)(rowp + (size_t)nb * 66 + (size_t)b * 32 + 8 * p));
             w.d = __ldg((const uint16_t *)(rowp + (size_t)b * 2));
@@ -725,6 +749,9 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         //                  i = g, g + 2, ... (one thread per tile row), so two units are always in
         //                  the making and one group's load latency hides behind the other's work ----
         const int r = threadIdx.x % CTA_ROWS, g = threadIdx.x / CTA_ROWS;
+        // prefetch distance in blocks; off when every weight tile is unpacked for several token tiles (all but the
+        // first of them find the bytes in L2 anyway, and the extra instructions then only cost issue slots)
+        const int pf = (grp || a.n_tok_tiles == 1) ? GEMM_PF_BLOCKS : 0;
         struct Cursor { GemmShare::Cursor c; int tile, ks; const uint8_t *rowp; const uint8_t *xb; uint32_t bb; };
         auto enter_tile = [&](Cursor &c) {   // the weight row, activation tiles and token count of c.tile
             const GemmTile t = resolve(c.tile);
@@ -759,7 +786,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
         auto produce = [&](typename P::Raw &use, typename P::Raw &pre, int i) {
             if (P::TWO_SETS && i + 2 < nunits) {
                 advance(ld, 2);
-                P::load(pre, ld.rowp, nb, ld.ks);
+                P::load(pre, ld.rowp, nb, ld.ks, pf);
             }
             if (round > 0 && !mbar_wait_sleep(&empty_bar[s], (round - 1) & 1, 32)) {
                 atomicExch(a.status, QZ_ERR_TIMEOUT);
@@ -780,7 +807,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             P::store(As, use, st.rowp, nb, st.ks, r, tbl);   // rows >= 128 land in the second half's tile (r * 128)
             if (!P::TWO_SETS && i + 2 < nunits) {
                 advance(ld, 2);
-                P::load(use, ld.rowp, nb, ld.ks);
+                P::load(use, ld.rowp, nb, ld.ks, pf);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core
             __syncwarp();
@@ -793,7 +820,7 @@ __global__ void __launch_bounds__(gemm_threads<HALVES>(), (gemm_fast_type<T, PLA
             }
         };
         typename P::Raw r0, r1;
-        if (g < nunits) P::load(r0, ld.rowp, nb, ld.ks);
+        if (g < nunits) P::load(r0, ld.rowp, nb, ld.ks, pf);
         if (P::TWO_SETS) {
             for (int i = g; i < nunits && live; i += 4) {
                 produce(r0, r1, i);
