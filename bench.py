@@ -466,6 +466,23 @@ def decode_section(q, args, torch, np, want_parity, fused_only=False):
         rel = float(np.abs(logits.astype(np.float64) - want).max() / np.abs(want).max())
         out["generation_loop"]["last_step_max_rel_err_vs_cpu_oracle"] = rel
         assert rel < 5e-3, f"last step of the generation loop differs from the CPU oracle: {rel}"
+    # batched prefill of a 512-token prompt (tensor-core GEMMs over the whole prompt, batched RoPE / KV append, causal
+    # prompt attention): host wall clock from the token ids to the last token's logits; against it, the same 512
+    # tokens through the replayed decode step would take 512 x ms_per_token
+    n_prompt = 512
+    prompt = [int(v) for v in rng.integers(0, LLAMA3_8B["vocab_size"], size=n_prompt)]
+    try:
+        m.prefill(prompt, pos0=0)
+        t3 = time.perf_counter()
+        for _ in range(3):
+            m.prefill(prompt, pos0=0)
+        pw = (time.perf_counter() - t3) / 3
+        q.check_error("prefill")
+        out["prefill"] = {"tokens": n_prompt, "ms": pw * 1e3, "tok_s": n_prompt / pw,
+                          "vs_token_by_token_decode": (n_prompt * out["fused_graph"]["ms_per_token"] * 1e-3) / pw,
+                          "what": "qh_prefill: 512-token prompt from position 0, host to host (token ids in, last token's logits out)"}
+    except RuntimeError as e:   # (a model the batched path does not take would fall here; this one is taken)
+        out["prefill"] = {"error": str(e)}
     m.close()
     return out
 
