@@ -230,7 +230,8 @@ void cuda_attn_step(float *out, const float *q, const float *k_new, const float 
  *   cuda_attn_prompt        causal attention of the n tokens: token t attends to cache positions [k_start, pos0 + t]
  *                           (window as in cuda_attn_step); q is already rotated and the caches already hold the n
  *                           new rows (cuda_rope_kv_rows).  out [n, n_heads*head_dim].  Same head-geometry limits
- *                           as cuda_attn_step; one CTA per (kv head, token). */
+ *                           as cuda_attn_step.  One CTA per (kv head, tile of up to 16 tokens): the tile's query
+ *                           rows share every staged K / V row. */
 void cuda_embed_lookup_rows(float *out, const uint8_t *data, uint32_t ggml_type, const int *d_tokens, int n, int embed_dim);
 void cuda_rms_norm_rows(float *out, const float *x, const float *w, int n_rows, int n);
 void cuda_rope_kv_rows(float *q, float *k, const float *v, float *k_cache, float *v_cache, int n_tok, int n_heads,

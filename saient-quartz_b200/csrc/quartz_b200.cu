@@ -22,6 +22,7 @@
 #include "decode_ops.cuh"
 #include "fused_ops.cuh"
 #include "attn_step.cuh"
+#include "attn_prompt.cuh"
 #include "gemm_tc.cuh"
 #include "moe.cuh"
 #include "gemv_chain.cuh"
@@ -1896,6 +1897,28 @@ void cuda_attn_prompt(float *out, const float *q, const float *k_cache, const fl
         return;
     }
     const int G = n_heads / n_kv_heads;
+    static int simple = -1;   // QUARTZ_ATTN_PROMPT=simple: one CTA per (kv head, token), the decode kernel's prompt mode
+    if (simple < 0) {
+        const char *e = getenv("QUARTZ_ATTN_PROMPT");
+        simple = (e && std::string(e) == "simple") ? 1 : 0;
+    }
+    if (!simple) {
+        // tiles of TQ tokens: TQ * G query rows per CTA share every staged K / V row
+        AttnPromptArgs p;
+        p.out = out; p.q = q; p.k_cache = k_cache; p.v_cache = v_cache;
+        p.n_tok = n_tok; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.kv_dim = n_kv_heads * head_dim;
+        p.pos0 = pos0; p.window = window; p.scale = scale; p.sinks = sinks;
+        p.tq = std::max(1, std::min(16, AP_MAX_ROWS / G));
+        const size_t smem = attn_prompt_smem(p.tq * G, head_dim);
+        static bool attr_set = false;
+        if (!attr_set) {
+            QZ_CUDA_CHECK(cudaFuncSetAttribute(attn_prompt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)attn_prompt_smem(AP_MAX_ROWS, ATT_MAX_HD)));
+            attr_set = true;
+        }
+        launch(attn_prompt_kernel, dim3((unsigned)n_kv_heads, (unsigned)((n_tok + p.tq - 1) / p.tq)), dim3(AP_THREADS), smem, p);
+        return;
+    }
     attn_step_cluster(G, head_dim);   // (sets the kernel's attributes)
     AttnStepArgs a = {};
     a.out = out; a.q = q; a.k_new = nullptr; a.v_new = nullptr;

@@ -672,3 +672,46 @@ def test_gemv_batch_of_independent_shapes(gpu, oracle_mod):
     L.cuda_gemv_batch(1, one)
     assert np.all(np.abs(dy.download() - oracle_mod.gemv(x, w, t, K, N)) <= oracle_mod.tolerance(w, t, K, N, x))
     gpu.check_error()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,n_tok,pos0,window,sink", [
+    (32, 8, 128, 70, 0, 0, False),        # Llama-3 heads, several token tiles, ragged last tile
+    (32, 8, 128, 33, 100, 0, True),       # a prompt continuing an existing context, sinks
+    (12, 2, 96, 45, 7, 16, True),         # six heads per kv head, head_dim 96, sliding window
+    (8, 8, 64, 17, 0, 0, False),          # one head per kv head
+    (64, 4, 128, 9, 3, 5, False),         # sixteen heads per kv head, window shorter than the prompt
+])
+def test_attn_prompt_against_numpy(gpu, nh, nkv, hd, n_tok, pos0, window, sink):
+    """cuda_attn_prompt (causal attention of a whole prompt over the caches, token tiles sharing the staged K / V
+    rows) against a float64 numpy softmax(q K^T) V per token and head: token t at position pos0 + t sees positions
+    [max(0, p + 1 - window), p] (all of [0, p] without a window); sinks add exp(sink) to the denominator
+    (src/cuda_kernels.cu:640-672).  Bar: 2e-5 of the largest output."""
+    L = gpu.lib()
+    r = np.random.Generator(np.random.PCG64([0xA77, nh, nkv, hd, n_tok]))
+    max_seq = pos0 + n_tok + 5
+    kv_dim, G = nkv * hd, nh // nkv
+    kc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+    vc = r.standard_normal((max_seq, kv_dim), dtype=np.float32)
+    q = r.standard_normal((n_tok, nh * hd), dtype=np.float32)
+    sinks = r.standard_normal(nh).astype(np.float32) if sink else None
+    scale = np.float32(1.0 / np.sqrt(hd))
+    dk, dv, dq = gpu.GpuBuf.upload(kc), gpu.GpuBuf.upload(vc), gpu.GpuBuf.upload(q)
+    ds = gpu.GpuBuf.upload(sinks) if sink else None
+    out = gpu.GpuBuf.alloc_f32(n_tok * nh * hd)
+    L.cuda_attn_prompt(out.ptr, dq.ptr, dk.ptr, dv.ptr, n_tok, nh, nkv, hd, max_seq, pos0, window, scale, ds.ptr if sink else None)
+    got = out.download().reshape(n_tok, nh, hd).astype(np.float64)
+    gpu.check_error("cuda_attn_prompt")
+    want = np.zeros_like(got)
+    for t in range(n_tok):
+        p = pos0 + t
+        lo = max(0, p + 1 - window) if window > 0 else 0
+        for h in range(nh):
+            kvh = h // G
+            K = kc[lo:p + 1, kvh * hd:(kvh + 1) * hd].astype(np.float64)
+            V = vc[lo:p + 1, kvh * hd:(kvh + 1) * hd].astype(np.float64)
+            s = K @ q[t, h * hd:(h + 1) * hd].astype(np.float64) * float(scale)
+            mx = max(s.max(), float(sinks[h])) if sink else s.max()
+            e = np.exp(s - mx)
+            den = e.sum() + (np.exp(float(sinks[h]) - mx) if sink else 0.0)
+            want[t, h] = (e[:, None] * V).sum(axis=0) / den
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max(), np.abs(got - want).max()
