@@ -26,8 +26,11 @@
 namespace qz {
 
 constexpr int TMA_MAX_STAGES = 16;
-constexpr int TMA_CONSUMERS = 512;
-constexpr int XSRC_MAX_IT = 8;             // float4 loads per consumer thread in the fused activation prologue
+#ifndef QZ_TMA_CONSUMERS
+#define QZ_TMA_CONSUMERS 512
+#endif
+constexpr int TMA_CONSUMERS = QZ_TMA_CONSUMERS;
+constexpr int XSRC_MAX_IT = 4;             // float4 loads per consumer thread in the fused activation prologue
 constexpr long long TMA_WAIT_CYCLES = 2000000000LL;   // ~1 s at 1.9 GHz
 
 // Where the activation vector comes from.  mode 0: already converted (xq).  mode 1: RMSNorm of the
