@@ -228,6 +228,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
                 const float4 *qv = (const float4 *)(qs + g * ATT_MAX_HD);
                 const float4 *kv = (const float4 *)(ks + (t_lo + lane) * AS_KS_STRIDE);
                 float c0a = 0.f, c1a = 0.f, c2a = 0.f, c3a = 0.f;
+#pragma unroll 8
                 for (int i = 0; i < hd4; i++) {
                     const float4 qq = qv[i], kk = kv[i];
                     c0a = fmaf(qq.x, kk.x, c0a);
@@ -254,6 +255,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_step_kernel(const AttnStepArg
                 // lane owns output dimensions 4*lane .. 4*lane+3 (head_dim <= 128)
                 float4 acc = make_float4(o_run[r][0] * corr, o_run[r][1] * corr, o_run[r][2] * corr, o_run[r][3] * corr);
                 if (4 * lane < hd) {
+#pragma unroll 8
                     for (int t = 0; t < nt; t++) {
                         const float pt = ps[warp * 32 + t];
                         const float4 vv = *(const float4 *)(vs + (t_lo + t) * ATT_MAX_HD + 4 * lane);
