@@ -97,10 +97,23 @@ __device__ __forceinline__ void push_publish(const PushArgs &p, int total_ctas, 
 __global__ void mgpu_push_rows_kernel(const float *__restrict__ src, int M, int n_local, long long dst_ld, PushArgs p)
 {
     const long long total = (long long)M * n_local;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long m = i / n_local, j = i - m * n_local;
-        const float v = src[i];
-        for (int r = 0; r < p.n; r++) p.data[r][p.dst_off + m * dst_ld + j] = v;
+    // 16 bytes per thread and store when rows, leading dimension, offset and pointers allow it (the usual case:
+    // row counts and offsets that are multiples of four); a warp then writes 512 contiguous bytes per rank
+    const bool vec = (n_local & 3) == 0 && (dst_ld & 3) == 0 && (p.dst_off & 3) == 0 && (((uintptr_t)src) & 15) == 0;
+    if (vec) {
+        const long long total4 = total >> 2;
+        const int n4 = n_local >> 2;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+            const long long m = i / n4, j = (i - m * n4) << 2;
+            const float4 v = __ldcs((const float4 *)src + i);
+            for (int r = 0; r < p.n; r++) *(float4 *)(p.data[r] + p.dst_off + m * dst_ld + j) = v;
+        }
+    } else {
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+            const long long m = i / n_local, j = i - m * n_local;
+            const float v = src[i];
+            for (int r = 0; r < p.n; r++) p.data[r][p.dst_off + m * dst_ld + j] = v;
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) push_publish(p, gridDim.x);

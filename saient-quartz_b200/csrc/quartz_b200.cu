@@ -792,8 +792,9 @@ static void launch_gemm(GemmArgs a)
     QZ_LAUNCH_CHECK();
     if (copy_out.n > 0) {
         const long long total = (long long)a.M * a.N;
-        int blocks = (int)((total + 255) / 256);
-        if (blocks > sm_count()) blocks = sm_count();
+        int blocks = (int)((total / 4 + 255) / 256);
+        if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+        if (blocks < 1) blocks = 1;
         const bool wait_after = copy_out.wait_after != 0;
         copy_out.wait_after = 0;
         mgpu_push_rows_kernel<<<blocks, 256, 0, g_stream>>>(a.Y, a.M, a.N, a.push_ld, copy_out);
@@ -2526,8 +2527,8 @@ void cuda_push_rows(const float *d_src, int m, int n_local, size_t dst_off, size
     PushArgs p;
     const long long total = (long long)m * n_local;
     if (!fill_push(p, dst_off, total ? (size_t)(m - 1) * dst_ld + n_local : 0)) return;
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > sm_count()) blocks = sm_count();
+    int blocks = (int)((total / 4 + 255) / 256);   // (a thread moves up to four values per pass)
+    if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
     if (blocks < 1) blocks = 1;
     mgpu_push_rows_kernel<<<blocks, 256, 0, g_stream>>>(d_src, m, n_local, (long long)dst_ld, p);
     QZ_LAUNCH_CHECK();
