@@ -7,17 +7,25 @@ Q6_K 4096->128256, Q8_0 4096->4096 -- on seeded synthetic GGUF-layout weights
 (543 MB of distinct weight bytes per step, > the 126 MB L2, so every step streams from
 HBM) and f32 activations ~ N(0,1).  One step = one pass over the six GEMVs.
 
-  value      algorithmic GB/s of the whole step, operands resident in HBM
-  e2e        the same through the reference-facing host path (GpuScratch.gemv: H2D x from
-             pinned host memory, cuda_gemv, D2H y, sync -- src/cuda.rs:107-127)
+  value      algorithmic GB/s of the whole step, operands resident in HBM: the faster of six
+             cuda_gemv calls (graph replay) and cuda_gemv_batch (one conversion kernel + one
+             persistent kernel); both are reported (six_separate_calls, batched_single_launch)
+  e2e        host to host: page-locked arenas, cuda_h2d_async, the six GEMVs, cuda_d2h_async,
+             replayed as one graph, cuda_sync per step; beside it the reference's own call
+             sequence (GpuScratch.gemv: cuda_h2d, cuda_gemv, cuda_d2h, cuda_sync per GEMV,
+             src/cuda.rs:107-127)
   roofline   the dominant kernel (Q6_K streaming GEMV at the lm_head shape) against the
              measured HBM copy bandwidth in MEASURED_PEAKS.json
   cpu_baseline  the CPU oracle (C port of the reference's src/dequant.rs gemv, rows over
              all host cores) on the same six shapes
+  gemv_shapes, decode (generation loop, prefill), gemm, moe_ffn, sharded70b, sharded_gemm:
+             the other configurations of the baseline, each checked against the oracle
 
-N>1 (torchrun, one rank per GPU): every matrix is row-sharded over the output
-dimension, each rank computes its slice and an NCCL all-gather assembles the f32
-outputs; total work is fixed ("strong" scaling).
+N>1 (torchrun, one rank per GPU): every matrix is row-sharded over the output dimension;
+each rank computes its slices and stores them into every rank's window from the kernel's
+epilogue (peer stores over NVLink): cuda_gemv_batch_push runs a rank's six shard GEMVs, their
+exchange and its wait as one persistent launch (the headline), six cuda_gemv_push calls and
+the NCCL all-gather form are timed beside it; total work is fixed ("strong" scaling).
 
 --impl reference times the CPU oracle alone (the reference has no buildable CPU
 binary here: its host is Rust and there is no Rust toolchain).
